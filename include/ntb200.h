@@ -1,0 +1,154 @@
+/*
+ * ntb200 — C ABI of the B200 (sm_100a) kernels behind nestedtensor's ragged<->dense,
+ * mask and varlen multi-head-attention path.
+ *
+ * Conventions for every entry point
+ *   - plain pointers and sizes only; all data pointers are DEVICE pointers unless the
+ *     parameter name starts with `h_` (host);
+ *   - returns NTB200_OK (0) or a negative ntb200_status; never throws, never
+ *     synchronises, never allocates (scratch memory, where a kernel needs it, is passed
+ *     in by the caller and sized by the matching *_workspace_bytes function);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = default stream);
+ *   - re-entrant and thread-safe; arguments are validated on the host before any launch,
+ *     so an invalid call launches nothing;
+ *   - "ragged buffer" = the constituents of a nested tensor concatenated row-major in
+ *     one 1-D buffer; `offsets[b]` = element offset of constituent b in that buffer
+ *     (B+1 entries, int64, offsets[0] = 0); `sizes[b*size_stride + j]` = extent of
+ *     constituent b along its j-th irregular dimension (int64).
+ *
+ * The reference (pytorch/nestedtensor) has no C ABI: it exposes C++ template launchers
+ * that return void and never check launch errors.  Each function below cites the
+ * reference interface it replaces as  path:line  inside that project.
+ */
+#ifndef NTB200_H_
+#define NTB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ntb200_status {
+  NTB200_OK = 0,
+  NTB200_INVALID_ARG = -1,
+  NTB200_UNSUPPORTED_DTYPE = -2,
+  NTB200_MISALIGNED = -3,
+  NTB200_LAUNCH_FAILED = -4,
+  NTB200_DEVICE_TIMEOUT = -5,
+  NTB200_WORKSPACE_TOO_SMALL = -6,
+  NTB200_UNSUPPORTED_SHAPE = -7
+} ntb200_status;
+
+/* element types of the MHA entry points (copies take an element size instead) */
+typedef enum ntb200_dtype {
+  NTB200_F32 = 0,
+  NTB200_F16 = 1,
+  NTB200_BF16 = 2
+} ntb200_dtype;
+
+/* Human-readable name of a status code (static storage). */
+const char* ntb200_status_string(int status);
+
+/* ABI version of the loaded library: major*1000 + minor. */
+int ntb200_version(void);
+
+/* ------------------------------------------------------------------ ragged -> dense
+ * out[b, i_0..i_{nd-1}] = (i_j < sizes[b][j] for all j) ? ragged[offsets[b] + lin_b(i)] : pad
+ * with lin_b the row-major index inside constituent b and the dense output shaped
+ * (B, h_max_sizes[0..nd-2], h_max_sizes[nd-1]*inner).  `inner` (>= 1) is the number of
+ * contiguous elements per innermost index, i.e. the product of the trailing regular
+ * dimensions: a (L_i, D) constituent is nd = 1, sizes[b] = L_i, inner = D.
+ *   elem_size  1, 2, 4 or 8 bytes; the copy is bit-exact for any dtype of that width
+ *   pad_bits   the padding value's bit pattern in the low elem_size bytes
+ *   padded     must be 16-byte aligned; ragged must be elem_size aligned
+ * Replaces add_padding_kernelLauncher<T> + add_padding_{1,2,3}
+ * (nestedtensor/csrc/cuda/padding.cu:10-215, declared nestedtensor/csrc/cuda/padding.h:12-22),
+ * called from to_padded_tensor (nestedtensor/csrc/masking.cpp:591-616).
+ */
+int ntb200_pad_nd(const void* ragged, void* padded, const int64_t* offsets, const int64_t* sizes,
+                  int64_t size_stride, int nd, int64_t inner, int64_t batch,
+                  const int64_t* h_max_sizes, int elem_size, uint64_t pad_bits, void* stream);
+
+/* ------------------------------------------------------------------ dense -> ragged
+ * ragged[offsets[b] + lin_b(i)] = padded[b, i] for every i inside sizes[b].
+ *   total_elems = offsets[batch] (the caller knows it on the host)
+ *   ragged must be 16-byte aligned; padded must be elem_size aligned
+ * Replaces remove_padding_kernelLauncher<T> + remove_padding_2 / remove_padding
+ * (nestedtensor/csrc/cuda/padding.cu:286-414, padding.h:36-45), called from
+ * from_padded_tensor (nestedtensor/csrc/masking.cpp:459-509).
+ */
+int ntb200_unpad_nd(const void* padded, void* ragged, const int64_t* offsets, const int64_t* sizes,
+                    int64_t size_stride, int nd, int64_t inner, int64_t batch,
+                    const int64_t* h_max_sizes, int64_t total_elems, int elem_size, void* stream);
+
+/* ------------------------------------------------------------------ validity mask
+ * mask[b, i_0..i_{nd-1}] = (i_j < sizes[b][j] for all j) ? 1 : 0, one byte per entry,
+ * shape (B, h_max_sizes[0..nd-1]); `mask` must be 16-byte aligned.
+ * Replaces the host double loop of to_mask (nestedtensor/csrc/masking.cpp:436-451), the
+ * per-constituent pad of a ones tensor in pad_nt/_create_nt_mask (masking.cpp:138-179,353-406)
+ * and the mask half of add_padding_mask (nestedtensor/csrc/cuda/padding.cu:217-236).
+ */
+int ntb200_mask_from_sizes(uint8_t* mask, const int64_t* sizes, int64_t size_stride, int nd,
+                           int64_t batch, const int64_t* h_max_sizes, void* stream);
+
+/* ------------------------------------------------------------------ data + mask in one call
+ * ntb200_pad_nd with padding 0 followed by ntb200_mask_from_sizes over the first
+ * mask_nd (<= nd) dimensions (mask_h_max_sizes), enqueued back to back on `stream`.
+ * Replaces add_padding_mask_kernelLauncher<T> (nestedtensor/csrc/cuda/padding.cu:217-284,
+ * padding.h:24-34) called from to_tensor_mask (nestedtensor/csrc/masking.cpp:254-296),
+ * without its pre-zeroing passes and int32 -> bool cast.
+ */
+int ntb200_pad_with_mask(const void* ragged, void* padded, uint8_t* mask, const int64_t* offsets,
+                         const int64_t* sizes, int64_t size_stride, int nd, int64_t inner,
+                         int64_t batch, const int64_t* h_max_sizes, int elem_size,
+                         const int64_t* mask_sizes, int64_t mask_size_stride, int mask_nd,
+                         const int64_t* mask_h_max_sizes, void* stream);
+
+/* ------------------------------------------------------------------ sizes from a padded tensor
+ * For a dense (B, h_dims[0..nd-1]) tensor: out_sizes[b][j] = 1 + the largest index along
+ * dimension j of an element of entry b that differs from the padding value (0 if none),
+ * out_counts[b] = number of such elements.  An entry is a well-formed padded constituent
+ * iff out_counts[b] == prod_j out_sizes[b][j].  Comparison follows the dtype's `!=`
+ * (IEEE for floating point: -0.0 == 0.0, NaN != anything).
+ *   cmp_kind  0 = compare bit patterns (integers, bool), 1 = IEEE float of that width
+ *             (elem_size 2: f16), 2 = bfloat16 (elem_size 2)
+ * out_sizes (B*nd int64) and out_counts (B int64) are cleared by this call.
+ * Replaces `tensor != padding` (nestedtensor/nested/masking.py:12-14) plus the per-element
+ * host recursion of nt_from_tensor_mask (nestedtensor/csrc/masking.cpp:181-249).
+ */
+int ntb200_sizes_from_padded(const void* padded, int64_t* out_sizes, int64_t* out_counts, int nd,
+                             int64_t batch, const int64_t* h_dims, int elem_size, int cmp_kind,
+                             uint64_t pad_bits, void* stream);
+
+/* Same, for an explicit byte mask (non-zero = valid) of shape (B, h_dims[0..nd-1]):
+ * the sizes a prefix mask describes.  Replaces the mask walk of nt_from_tensor_mask
+ * (nestedtensor/csrc/masking.cpp:181-249). */
+int ntb200_sizes_from_mask(const uint8_t* mask, int64_t* out_sizes, int64_t* out_counts, int nd,
+                           int64_t batch, const int64_t* h_dims, void* stream);
+
+/* ------------------------------------------------------------------ offsets (exclusive scan)
+ * offsets[0] = 0, offsets[b+1] = offsets[b] + inner * prod_j sizes[b*size_stride + j], j < nd.
+ * Device-side replacement of the host loop batch_offsets_from_efficient_size
+ * (nestedtensor/csrc/masking.cpp:110-125) and of exclusiveScan_kernelLauncher
+ * (nestedtensor/csrc/cuda/cuda_kernels.cu:282-517).
+ * `workspace` must hold ntb200_offsets_workspace_bytes(batch) bytes (8-byte aligned).
+ */
+size_t ntb200_offsets_workspace_bytes(int64_t batch);
+int ntb200_offsets_from_sizes(const int64_t* sizes, int64_t size_stride, int nd, int64_t inner,
+                              int64_t batch, int64_t* offsets, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ token index
+ * For token t in [0, total_tokens): batch_idx[t] = b and word_idx[t] = t - token_offsets[b]
+ * with token_offsets[b] <= t < token_offsets[b+1] (int32 outputs).
+ * Replaces compress_bert_input (nestedtensor/csrc/cuda/cuda_kernels.cu:171-223).
+ */
+int ntb200_token_index(const int64_t* token_offsets, int64_t batch, int64_t total_tokens,
+                       int32_t* batch_idx, int32_t* word_idx, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NTB200_H_ */

@@ -1,0 +1,74 @@
+"""``nested_tensor`` / ``as_nested_tensor`` (nestedtensor/nested/creation.py:9-26 and the
+constructor nestedtensor/csrc/creation.cpp:191-222)."""
+from __future__ import annotations
+
+import torch
+
+from .nested import NestedTensor, _sizes_from_list, build_meta
+
+_ADVICE = ("To form a valid NestedTensor all Tensor / NestedTensor constiuents of the given list must be of the same "
+           "dimension, layout, device, scalar type and either all or none require gradients.")
+
+
+def _verify(tensors):
+    """nestedtensor/csrc/creation.cpp:28-171"""
+    first = tensors[0]
+    for t in tensors:
+        if t.dim() != first.dim():
+            raise RuntimeError("Given Tensor / NestedTensor constiuent of dimension {} doesn't match another constiuent "
+                               "of dimension {}. {}".format(t.dim(), first.dim(), _ADVICE))
+        if t.layout != first.layout:
+            raise RuntimeError("Given Tensor / NestedTensor constiuent of layout {} doesn't match another constiuent "
+                               "of layout {}. {}".format(t.layout, first.layout, _ADVICE))
+        if t.device != first.device:
+            raise RuntimeError("Given Tensor / NestedTensor constiuent of device {} doesn't match another constiuent "
+                               "of device {}. ".format(t.device, first.device))
+        if t.dtype != first.dtype:
+            raise RuntimeError("Given Tensor / NestedTensor constiuent of scalar type {} doesn't match another "
+                               "constiuent of scalar type {}. ".format(t.dtype, first.dtype))
+        if t.requires_grad != first.requires_grad:
+            raise RuntimeError("Given Tensor / NestedTensor constiuent requires gradient in contrast to another "
+                               "constiuent. " + _ADVICE)
+
+
+def nested_tensor(data, dtype=None, device=None, requires_grad=False, pin_memory=False, channels_last=False):
+    """Arguments match ``torch.tensor``.  The constituents are copied into one buffer
+    (storage/Packed.h:75-98) with a single concatenation, then moved/cast once."""
+    if requires_grad:
+        raise RuntimeError(
+            "This version of nestedtensor currently does not support autograd. Please open an issue on "
+            "https://github.com/pytorch/nestedtensor if you need this.")
+    if channels_last:
+        raise NotImplementedError("nestedtensor_b200: channels_last nested tensors are outside the implemented path")
+    if dtype is None:
+        dtype = torch.get_default_dtype()
+    if device is None:
+        device = torch.device("cpu")
+    device = torch.device(device)
+    if not isinstance(data, (list, tuple)):
+        raise RuntimeError("Currently only supporting a flat sequence of Tensors.")
+    tensors = list(data)
+    for t in tensors:
+        if isinstance(t, NestedTensor):
+            raise RuntimeError("Currently do not support NestedTensor entries.")
+        if not torch.is_tensor(t):
+            raise RuntimeError("Currently only supporting a sequence of Tensors.")
+    if len(tensors) > 0:
+        _verify(tensors)
+    sizes = _sizes_from_list(tensors)
+    if len(tensors) == 0:
+        buffer = torch.empty(0, dtype=dtype, device=device)
+    else:
+        buffer = torch.cat([t.detach().reshape(-1) for t in tensors]).to(device=device, dtype=dtype)
+        if buffer.data_ptr() == tensors[0].data_ptr():  # single contiguous constituent already in place
+            buffer = buffer.clone()
+    if pin_memory:
+        buffer = buffer.pin_memory()
+    meta = build_meta(sizes, device) if device.type == "cuda" else None
+    return NestedTensor(buffer, sizes, meta)
+
+
+def as_nested_tensor(data, dtype=None, device=None, requires_grad=False, pin_memory=False):
+    if not isinstance(data, NestedTensor):
+        return nested_tensor(data, dtype, device, requires_grad, pin_memory)
+    return data

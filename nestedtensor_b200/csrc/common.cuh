@@ -1,0 +1,96 @@
+// Shared device/host helpers for the ntb200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ntb200.h"
+
+namespace ntb200 {
+
+// Number of SMs on a B200; grids of persistent kernels are sized in multiples of it.
+constexpr int kNumSMs = 148;
+
+// ---------------------------------------------------------------------------------
+// Division of a 31-bit dividend by a launch-constant 30-bit divisor with one
+// multiply-high, one add and one shift (Granlund & Montgomery, "Division by invariant
+// integers using multiplication", PLDI 1994, round-up variant).
+// Valid for 1 <= d <= 2^30 and n < 2^31.
+struct FastDiv {
+  uint32_t d;
+  uint32_t mul;
+  uint32_t shift;
+};
+
+inline FastDiv make_fastdiv(uint64_t d64) {
+  FastDiv f;
+  uint32_t d = (uint32_t)d64;
+  if (d == 0) d = 1;
+  uint32_t shift = 0;
+  while (shift < 32 && (1ull << shift) < d) ++shift;
+  uint64_t magic = ((1ull << 32) * ((1ull << shift) - d)) / d + 1;
+  f.d = d;
+  f.mul = (uint32_t)magic;
+  f.shift = shift;
+  return f;
+}
+
+__host__ __device__ __forceinline__ uint32_t fastdiv(uint32_t n, const FastDiv& f) {
+#ifdef __CUDA_ARCH__
+  return (__umulhi(n, f.mul) + n) >> f.shift;
+#else
+  return (uint32_t)((((uint64_t)n * f.mul) >> 32) + n) >> f.shift;
+#endif
+}
+
+// Index arithmetic policy: 32-bit + FastDiv when one padded entry has < 2^30 elements,
+// true 64-bit division otherwise.
+template <bool BIG>
+struct IdxPolicy;
+template <>
+struct IdxPolicy<false> {
+  using T = uint32_t;
+  static __device__ __forceinline__ T div(T n, const FastDiv& f, uint64_t) { return fastdiv(n, f); }
+};
+template <>
+struct IdxPolicy<true> {
+  using T = uint64_t;
+  static __device__ __forceinline__ T div(T n, const FastDiv&, uint64_t d) { return n / d; }
+};
+
+// quotient/remainder of two non-negative 64-bit values, 32-bit fast path when both fit
+__device__ __forceinline__ void divmod_u64(uint64_t n, uint64_t d, uint64_t& q, uint64_t& r) {
+  if (((n | d) >> 32) == 0) {
+    uint32_t qq = (uint32_t)n / (uint32_t)d;
+    q = qq;
+    r = (uint32_t)n - qq * (uint32_t)d;
+  } else {
+    q = n / d;
+    r = n - q * d;
+  }
+}
+
+template <int ES>
+struct ElemBits;
+template <>
+struct ElemBits<1> { using T = uint8_t; };
+template <>
+struct ElemBits<2> { using T = uint16_t; };
+template <>
+struct ElemBits<4> { using T = uint32_t; };
+template <>
+struct ElemBits<8> { using T = uint64_t; };
+
+// 16-byte global accesses.  Copies touch every byte once, so loads bypass L1
+// allocation where the whole vector is consumed by one thread and stores are marked
+// streaming (evict-first) to keep the 126 MB L2 for the metadata and ragged source.
+__device__ __forceinline__ uint4 ld_global_16_stream(const void* p) {
+  return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void st_global_16_stream(void* p, const uint4& v) {
+  __stcs(reinterpret_cast<uint4*>(p), v);
+}
+
+inline int status_from_cuda(cudaError_t e) { return e == cudaSuccess ? NTB200_OK : NTB200_LAUNCH_FAILED; }
+
+}  // namespace ntb200

@@ -1,0 +1,422 @@
+// Torch operator layer of nestedtensor_b200: the `nestedtensor::*` operators of the reference
+// (nestedtensor/csrc/masking.cpp:652-675, nestedtensor/csrc/cuda/mha.cpp:109-113) re-implemented
+// over a plain record instead of a TensorImpl subclass:
+//
+//     buffer  1-D CUDA tensor, the constituents concatenated row-major
+//     sizes   CPU int64 [B, tensor_dim], one row of extents per constituent
+//     meta    CUDA int64 [(B+1) + B*tensor_dim] = element offsets followed by a copy of `sizes`
+//
+// Every operator validates on the host, allocates its outputs through torch's caching
+// allocator and enqueues the sm_100a kernels of libntb200 (C ABI, include/ntb200.h) on the
+// CURRENT stream.  There is no CPU implementation: a non-CUDA buffer is an error.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <cstring>
+#include <tuple>
+#include <vector>
+
+#include "ntb200.h"
+
+namespace {
+
+using at::Tensor;
+
+void check_rc(int rc, const char* fn) {
+  TORCH_CHECK(rc == NTB200_OK, "nestedtensor_b200: ", fn, " failed: ", ntb200_status_string(rc), " (", rc, ")");
+}
+
+void* cur_stream() { return static_cast<void*>(at::cuda::getCurrentCUDAStream().stream()); }
+
+struct Record {
+  int64_t B;
+  int64_t tdim;
+  const int64_t* sz;  // host sizes, row stride tdim
+  const int64_t* d_offsets;
+  const int64_t* d_sizes;
+  std::vector<int64_t> max_sizes;  // per tensor dim
+  std::vector<bool> regular;       // per tensor dim: same extent in every constituent
+  bool any_empty;
+  int64_t numel;
+};
+
+Record make_record(const Tensor& sizes, const Tensor& meta) {
+  TORCH_CHECK(sizes.device().is_cpu() && sizes.scalar_type() == at::kLong && sizes.dim() == 2 && sizes.is_contiguous(),
+              "nestedtensor_b200: sizes must be a contiguous CPU int64 [B, tensor_dim] tensor");
+  Record r;
+  r.B = sizes.size(0);
+  r.tdim = sizes.size(1);
+  r.sz = sizes.data_ptr<int64_t>();
+  TORCH_CHECK(meta.is_cuda(),
+              "nestedtensor_b200: this operator needs a CUDA nested tensor (this build has no CPU implementation)");
+  TORCH_CHECK(meta.scalar_type() == at::kLong && meta.is_contiguous() && meta.numel() == (r.B + 1) + r.B * r.tdim,
+              "nestedtensor_b200: meta must be a CUDA int64 tensor of (B+1) + B*tensor_dim entries");
+  r.d_offsets = meta.data_ptr<int64_t>();
+  r.d_sizes = r.d_offsets + (r.B + 1);
+  r.max_sizes.assign(r.tdim, 0);
+  r.regular.assign(r.tdim, true);
+  r.any_empty = false;
+  r.numel = 0;
+  for (int64_t b = 0; b < r.B; ++b) {
+    int64_t n = 1;
+    for (int64_t j = 0; j < r.tdim; ++j) {
+      const int64_t v = r.sz[b * r.tdim + j];
+      TORCH_CHECK(v >= 0, "nestedtensor_b200: negative size");
+      n *= v;
+      if (v > r.max_sizes[j]) r.max_sizes[j] = v;
+      if (v != r.sz[j]) r.regular[j] = false;
+    }
+    if (n == 0) r.any_empty = true;
+    r.numel += n;
+  }
+  return r;
+}
+
+// Fold trailing regular dims: the kernels see `nd` leading dims and `inner` contiguous elements per
+// innermost index.  `dense_dims` (optional) are the dense tensor's trailing extents; a regular
+// dim can only be folded when the dense extent equals the common size.
+void fold_dims(const Record& r, const int64_t* dense_dims, int* nd, int64_t* inner) {
+  int64_t k = r.tdim;
+  int64_t in = 1;
+  while (k > 1) {
+    const int64_t j = k - 1;
+    const bool foldable = r.regular[j] && (dense_dims == nullptr || dense_dims[j] == r.max_sizes[j]) && r.max_sizes[j] > 0;
+    if (!foldable) break;
+    in *= r.max_sizes[j];
+    --k;
+  }
+  TORCH_CHECK(k >= 1 && k <= 3, "nestedtensor_b200: at most 3 leading ragged dimensions are supported, got ", k);
+  *nd = (int)k;
+  *inner = in;
+}
+
+uint64_t scalar_bits(const at::Scalar& value, at::ScalarType dtype, int64_t elem_size) {
+  Tensor t = at::full({1}, value, at::TensorOptions().dtype(dtype).device(at::kCPU));
+  uint64_t bits = 0;
+  std::memcpy(&bits, t.data_ptr(), (size_t)elem_size);
+  return bits;
+}
+
+void check_buffer(const Tensor& buffer, const Record& r, const char* op) {
+  TORCH_CHECK(buffer.is_cuda(), "nestedtensor_b200: ", op,
+              " needs a CUDA nested tensor (this build has no CPU implementation)");
+  TORCH_CHECK(buffer.dim() == 1 && buffer.is_contiguous() && buffer.numel() == r.numel,
+              "nestedtensor_b200: buffer must be 1-D contiguous with sum(numel) elements");
+  const int64_t es = buffer.element_size();
+  TORCH_CHECK(es == 1 || es == 2 || es == 4 || es == 8, "Input datatype ", buffer.dtype(), " is not supported.");
+}
+
+std::vector<int64_t> dense_shape(const Record& r) {
+  std::vector<int64_t> shape;
+  shape.push_back(r.B);
+  for (auto m : r.max_sizes) shape.push_back(m);
+  return shape;
+}
+
+// ------------------------------------------------------------------ to_padded_tensor
+// nestedtensor/csrc/masking.cpp:558-650
+Tensor to_padded_tensor(const Tensor& buffer, const Tensor& sizes, const Tensor& meta, double padding) {
+  Record r = make_record(sizes, meta);
+  if (r.B == 0) return at::scalar_tensor(padding, at::TensorOptions().dtype(at::kDouble)).reshape({1});
+  check_buffer(buffer, r, "to_padded_tensor");
+  c10::cuda::CUDAGuard guard(buffer.device());
+  if (r.tdim == 0) return buffer.clone();  // constituents are scalars: already dense
+  Tensor out = at::empty(dense_shape(r), buffer.options());
+  if (out.numel() == 0) return out;
+  int nd;
+  int64_t inner;
+  fold_dims(r, nullptr, &nd, &inner);
+  const int64_t es = buffer.element_size();
+  const uint64_t bits = scalar_bits(at::Scalar(padding), buffer.scalar_type(), es);
+  check_rc(ntb200_pad_nd(buffer.data_ptr(), out.data_ptr(), r.d_offsets, r.d_sizes, r.tdim, nd, inner, r.B,
+                         r.max_sizes.data(), (int)es, bits, cur_stream()),
+           "ntb200_pad_nd");
+  return out;
+}
+
+// Number of mask dims left after the reference's collapse rule (merge_tensor_mask,
+// nestedtensor/csrc/masking.cpp:12-43), derived from the sizes alone: a trailing mask dim can be
+// dropped iff that tensor dim is regular (every slice is then all-1 or all-0); the batch dim can
+// be dropped because no constituent is empty.  Sets *collapsed when at least one dim was dropped.
+int64_t resolve_mask_dim(const Record& r, c10::optional<int64_t> mask_dim, bool* collapsed) {
+  int64_t md = r.tdim + 1;
+  *collapsed = false;
+  while (true) {
+    if (mask_dim && md == *mask_dim) break;
+    if (md == 0) break;
+    const bool can = (md == 1) ? true : r.regular[md - 2];
+    if (can) {
+      --md;
+      *collapsed = true;
+      continue;
+    }
+    if (mask_dim && *mask_dim != md) {
+      TORCH_CHECK(false, "Mask dimension is too small to represent data tensor.");
+    }
+    break;
+  }
+  return md;
+}
+
+Tensor alloc_mask(const Record& r, int64_t md, bool as_bool, const at::Device& dev) {
+  std::vector<int64_t> shape;
+  if (md >= 1) shape.push_back(r.B);
+  for (int64_t j = 0; j + 1 < md; ++j) shape.push_back(r.max_sizes[j]);
+  return at::empty(shape, at::TensorOptions().dtype(as_bool ? at::kBool : at::kByte).device(dev));
+}
+
+void check_mask_dim_arg(c10::optional<int64_t> mask_dim, int64_t dim) {
+  TORCH_CHECK(!mask_dim || *mask_dim <= dim, "Requested mask dimension ", *mask_dim, " is bigger than dimension ", dim,
+              " of given NestedTensor.");
+}
+
+// ------------------------------------------------------------------ to_tensor_mask
+// nestedtensor/csrc/masking.cpp:251-320
+std::tuple<Tensor, Tensor> to_tensor_mask(const Tensor& buffer, const Tensor& sizes, const Tensor& meta,
+                                          c10::optional<int64_t> mask_dim) {
+  Record r = make_record(sizes, meta);
+  check_mask_dim_arg(mask_dim, r.tdim + 1);
+  if (r.B == 0) {
+    // masking.cpp:152-155 then the collapse of a one-element all-false mask
+    Tensor t = at::zeros({1}, at::TensorOptions().dtype(at::kLong));
+    if (mask_dim && *mask_dim == 1) return std::make_tuple(t, at::zeros({1}, at::TensorOptions().dtype(at::kByte)));
+    return std::make_tuple(t, at::zeros({}, at::TensorOptions().dtype(at::kBool)));
+  }
+  check_buffer(buffer, r, "to_tensor_mask");
+  c10::cuda::CUDAGuard guard(buffer.device());
+  if (r.tdim == 0 && r.B == 1) {
+    // masking.cpp:305-313
+    Tensor m = (!mask_dim || *mask_dim == 0) ? at::ones({}, at::TensorOptions().dtype(at::kBool))
+                                             : at::ones({1}, at::TensorOptions().dtype(at::kBool));
+    return std::make_tuple(buffer.reshape({-1}), m);
+  }
+  TORCH_CHECK(!r.any_empty, "Empty tensors are not yet supported.");
+  bool collapsed;
+  const int64_t md = resolve_mask_dim(r, mask_dim, &collapsed);
+  const bool as_bool = collapsed || r.tdim == 0;
+  Tensor mask = alloc_mask(r, md, as_bool, buffer.device());
+  if (r.tdim == 0) {
+    mask.fill_(true);
+    return std::make_tuple(buffer.clone(), mask);
+  }
+  Tensor out = at::empty(dense_shape(r), buffer.options());
+  int nd;
+  int64_t inner;
+  fold_dims(r, nullptr, &nd, &inner);
+  const int64_t es = buffer.element_size();
+  if (md >= 2) {
+    const int mask_nd = (int)(md - 1);
+    TORCH_CHECK(mask_nd <= 3, "nestedtensor_b200: masks over more than 3 ragged dimensions are not supported");
+    check_rc(ntb200_pad_with_mask(buffer.data_ptr(), out.data_ptr(), static_cast<uint8_t*>(mask.data_ptr()),
+                                  r.d_offsets, r.d_sizes, r.tdim, nd, inner, r.B, r.max_sizes.data(), (int)es,
+                                  r.d_sizes, r.tdim, mask_nd, r.max_sizes.data(), cur_stream()),
+             "ntb200_pad_with_mask");
+  } else {
+    check_rc(ntb200_pad_nd(buffer.data_ptr(), out.data_ptr(), r.d_offsets, r.d_sizes, r.tdim, nd, inner, r.B,
+                           r.max_sizes.data(), (int)es, 0, cur_stream()),
+             "ntb200_pad_nd");
+    mask.fill_(true);  // (B,) or scalar: every constituent is non-empty
+  }
+  return std::make_tuple(out, mask);
+}
+
+// ------------------------------------------------------------------ to_mask
+// nestedtensor/csrc/masking.cpp:408-457.  The reference builds this mask on the host; here it is
+// written on the device that holds the nested tensor.
+Tensor to_mask(const Tensor& sizes, const Tensor& meta, c10::optional<int64_t> mask_dim) {
+  Record r = make_record(sizes, meta);
+  const int64_t dim = r.tdim + 1;
+  check_mask_dim_arg(mask_dim, dim);
+  c10::cuda::CUDAGuard guard(meta.device());
+  if (r.tdim == 0 && r.B == 1) {
+    return (!mask_dim || *mask_dim == 0) ? at::ones({}, at::TensorOptions().dtype(at::kBool))
+                                         : at::ones({1}, at::TensorOptions().dtype(at::kBool));
+  }
+  if (dim > 1 && mask_dim && *mask_dim > 1) {
+    // leading (mask_dim-1) tensor dims, no collapse (masking.cpp:426-453)
+    const int mask_nd = (int)(*mask_dim - 1);
+    if (!(*mask_dim == 2 && dim == 3)) {
+      for (int64_t b = 0; b < r.B; ++b) {
+        int64_t n = 1;
+        for (int j = 0; j < mask_nd; ++j) n *= r.sz[b * r.tdim + j];
+        TORCH_CHECK(n > 0, "Empty tensors are not yet supported.");
+      }
+    }
+    TORCH_CHECK(mask_nd <= 3, "nestedtensor_b200: masks over more than 3 ragged dimensions are not supported");
+    Tensor mask = alloc_mask(r, *mask_dim, false, meta.device());
+    if (mask.numel() > 0)
+      check_rc(ntb200_mask_from_sizes(static_cast<uint8_t*>(mask.data_ptr()), r.d_sizes, r.tdim, mask_nd, r.B,
+                                      r.max_sizes.data(), cur_stream()),
+               "ntb200_mask_from_sizes");
+    return mask;
+  }
+  if (r.B == 0) {
+    if (mask_dim && *mask_dim == 1) return at::zeros({1}, at::TensorOptions().dtype(at::kByte));
+    return at::zeros({}, at::TensorOptions().dtype(at::kBool));
+  }
+  TORCH_CHECK(!r.any_empty, "Empty tensors are not yet supported.");
+  bool collapsed;
+  const int64_t md = resolve_mask_dim(r, mask_dim, &collapsed);
+  Tensor mask = alloc_mask(r, md, collapsed || r.tdim == 0, meta.device());
+  if (md >= 2) {
+    TORCH_CHECK(md - 1 <= 3, "nestedtensor_b200: masks over more than 3 ragged dimensions are not supported");
+    check_rc(ntb200_mask_from_sizes(static_cast<uint8_t*>(mask.data_ptr()), r.d_sizes, r.tdim, (int)(md - 1), r.B,
+                                    r.max_sizes.data(), cur_stream()),
+             "ntb200_mask_from_sizes");
+  } else {
+    mask.fill_(true);
+  }
+  return mask;
+}
+
+// ------------------------------------------------------------------ from_padded_tensor
+// nestedtensor/csrc/masking.cpp:459-533 — returns the ragged buffer for the given target sizes.
+Tensor from_padded_tensor(const Tensor& padded_, const Tensor& sizes, const Tensor& meta) {
+  Record r = make_record(sizes, meta);
+  TORCH_CHECK(padded_.dim() == r.tdim + 1, "Target size has different dimension as input padded Tensor.");
+  TORCH_CHECK(padded_.is_cuda(), "nestedtensor_b200: from_padded_tensor needs a CUDA tensor (this build has no CPU implementation)");
+  TORCH_CHECK(padded_.size(0) == r.B, "nestedtensor_b200: padded.size(0) differs from the number of target sizes");
+  c10::cuda::CUDAGuard guard(padded_.device());
+  Tensor padded = padded_.contiguous();
+  const int64_t es = padded.element_size();
+  TORCH_CHECK(es == 1 || es == 2 || es == 4 || es == 8, "Input datatype ", padded.dtype(), " is not supported.");
+  Tensor out = at::empty({r.numel}, padded.options());
+  if (r.numel == 0) return out;
+  if (r.tdim == 0) {
+    out.copy_(padded.reshape({-1}));
+    return out;
+  }
+  std::vector<int64_t> dims(padded.sizes().begin() + 1, padded.sizes().end());
+  for (int64_t j = 0; j < r.tdim; ++j)
+    TORCH_CHECK(r.max_sizes[j] <= dims[j], "nestedtensor_b200: target size exceeds the padded tensor along dim ", j + 1);
+  int nd;
+  int64_t inner;
+  fold_dims(r, dims.data(), &nd, &inner);
+  check_rc(ntb200_unpad_nd(padded.data_ptr(), out.data_ptr(), r.d_offsets, r.d_sizes, r.tdim, nd, inner, r.B,
+                           dims.data(), r.numel, (int)es, cur_stream()),
+           "ntb200_unpad_nd");
+  return out;
+}
+
+// ------------------------------------------------------------------ sizes from dense data
+int cmp_kind_of(at::ScalarType t) {
+  switch (t) {
+    case at::kHalf: return 1;
+    case at::kFloat: return 1;
+    case at::kDouble: return 1;
+    case at::kBFloat16: return 2;
+    default: return 0;
+  }
+}
+
+// (sizes [B, nd], counts [B]) on the device for `tensor != padding`
+// (nestedtensor/nested/masking.py:12-14 without materialising the mask).
+std::tuple<Tensor, Tensor> sizes_from_padded(const Tensor& tensor_, const at::Scalar& padding) {
+  TORCH_CHECK(tensor_.is_cuda(), "nestedtensor_b200: sizes_from_padded needs a CUDA tensor (this build has no CPU implementation)");
+  TORCH_CHECK(tensor_.dim() >= 2 && tensor_.dim() <= 4, "nestedtensor_b200: sizes_from_padded supports 2 to 4 dimensional tensors");
+  c10::cuda::CUDAGuard guard(tensor_.device());
+  Tensor tensor = tensor_.contiguous();
+  const int64_t B = tensor.size(0);
+  const int nd = (int)tensor.dim() - 1;
+  const int64_t es = tensor.element_size();
+  TORCH_CHECK(es == 1 || es == 2 || es == 4 || es == 8, "Input datatype ", tensor.dtype(), " is not supported.");
+  std::vector<int64_t> dims(tensor.sizes().begin() + 1, tensor.sizes().end());
+  auto opt = at::TensorOptions().dtype(at::kLong).device(tensor.device());
+  Tensor out_sizes = at::empty({B, nd}, opt);
+  Tensor out_counts = at::empty({B}, opt);
+  // A padding value the dtype cannot hold exactly equals no element: everything is valid.
+  const int kind = cmp_kind_of(tensor.scalar_type());
+  bool representable = true;
+  if (kind == 0) {
+    if (padding.isFloatingPoint()) {
+      const double v = padding.toDouble();
+      representable = (v == (double)(int64_t)v);
+    }
+    if (representable) {
+      Tensor probe = at::full({1}, padding, at::TensorOptions().dtype(tensor.scalar_type()));
+      representable = probe.to(at::kDouble).item<double>() == padding.toDouble();
+    }
+  }
+  if (!representable) {
+    Tensor full = at::tensor(dims, at::TensorOptions().dtype(at::kLong)).to(tensor.device());
+    out_sizes.copy_(full.unsqueeze(0).expand({B, nd}));
+    int64_t P = 1;
+    for (auto d : dims) P *= d;
+    out_counts.fill_(P);
+    return std::make_tuple(out_sizes, out_counts);
+  }
+  const uint64_t bits = scalar_bits(padding, tensor.scalar_type(), es);
+  check_rc(ntb200_sizes_from_padded(tensor.data_ptr(), out_sizes.data_ptr<int64_t>(), out_counts.data_ptr<int64_t>(),
+                                    nd, B, dims.data(), (int)es, kind, bits, cur_stream()),
+           "ntb200_sizes_from_padded");
+  return std::make_tuple(out_sizes, out_counts);
+}
+
+std::tuple<Tensor, Tensor> sizes_from_mask(const Tensor& mask_) {
+  TORCH_CHECK(mask_.is_cuda(), "nestedtensor_b200: sizes_from_mask needs a CUDA tensor (this build has no CPU implementation)");
+  TORCH_CHECK(mask_.dim() >= 2 && mask_.dim() <= 4, "nestedtensor_b200: sizes_from_mask supports 2 to 4 dimensional masks");
+  TORCH_CHECK(mask_.scalar_type() == at::kBool || mask_.scalar_type() == at::kByte,
+              "nestedtensor_b200: mask must be bool or uint8");
+  c10::cuda::CUDAGuard guard(mask_.device());
+  Tensor mask = mask_.contiguous();
+  const int64_t B = mask.size(0);
+  const int nd = (int)mask.dim() - 1;
+  std::vector<int64_t> dims(mask.sizes().begin() + 1, mask.sizes().end());
+  auto opt = at::TensorOptions().dtype(at::kLong).device(mask.device());
+  Tensor out_sizes = at::empty({B, nd}, opt);
+  Tensor out_counts = at::empty({B}, opt);
+  check_rc(ntb200_sizes_from_mask(static_cast<const uint8_t*>(mask.data_ptr()), out_sizes.data_ptr<int64_t>(),
+                                  out_counts.data_ptr<int64_t>(), nd, B, dims.data(), cur_stream()),
+           "ntb200_sizes_from_mask");
+  return std::make_tuple(out_sizes, out_counts);
+}
+
+// ------------------------------------------------------------------ metadata on the device
+// meta = [offsets (B+1) | sizes (B*tdim)] from device-resident sizes
+// (device-side batch_offsets_from_efficient_size, nestedtensor/csrc/masking.cpp:110-125).
+Tensor meta_from_device_sizes(const Tensor& d_sizes) {
+  TORCH_CHECK(d_sizes.is_cuda() && d_sizes.scalar_type() == at::kLong && d_sizes.dim() == 2 && d_sizes.is_contiguous(),
+              "nestedtensor_b200: device sizes must be a contiguous CUDA int64 [B, tensor_dim] tensor");
+  c10::cuda::CUDAGuard guard(d_sizes.device());
+  const int64_t B = d_sizes.size(0), tdim = d_sizes.size(1);
+  Tensor meta = at::empty({(B + 1) + B * tdim}, d_sizes.options());
+  const size_t ws_bytes = ntb200_offsets_workspace_bytes(B);
+  Tensor ws = at::empty({(int64_t)((ws_bytes + 7) / 8)}, d_sizes.options());
+  check_rc(ntb200_offsets_from_sizes(d_sizes.data_ptr<int64_t>(), tdim, (int)tdim, 1, B, meta.data_ptr<int64_t>(),
+                                     ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, cur_stream()),
+           "ntb200_offsets_from_sizes");
+  if (B * tdim > 0) meta.narrow(0, B + 1, B * tdim).copy_(d_sizes.reshape({-1}));
+  return meta;
+}
+
+// batch_idx / word_idx of every token (compress_bert_input, nestedtensor/csrc/cuda/cuda_kernels.cu:171-223)
+std::tuple<Tensor, Tensor> token_index(const Tensor& token_offsets, int64_t total_tokens) {
+  TORCH_CHECK(token_offsets.is_cuda() && token_offsets.scalar_type() == at::kLong && token_offsets.is_contiguous() &&
+                  token_offsets.dim() == 1 && token_offsets.numel() >= 1,
+              "nestedtensor_b200: token_offsets must be a contiguous CUDA int64 [B+1] tensor");
+  c10::cuda::CUDAGuard guard(token_offsets.device());
+  auto opt = at::TensorOptions().dtype(at::kInt).device(token_offsets.device());
+  Tensor bi = at::empty({total_tokens}, opt), wi = at::empty({total_tokens}, opt);
+  check_rc(ntb200_token_index(token_offsets.data_ptr<int64_t>(), token_offsets.numel() - 1, total_tokens,
+                              bi.data_ptr<int32_t>(), wi.data_ptr<int32_t>(), cur_stream()),
+           "ntb200_token_index");
+  return std::make_tuple(bi, wi);
+}
+
+}  // namespace
+
+// The operator names follow the reference's `nestedtensor` namespace
+// (nestedtensor/csrc/masking.cpp:652-675); the nested tensor argument is spelled out as its
+// record (buffer, sizes, meta) and the Python wrapper's __torch_function__ does the spelling.
+TORCH_LIBRARY(nestedtensor, m) {
+  m.def("to_padded_tensor(Tensor buffer, Tensor sizes, Tensor meta, float padding) -> Tensor", &to_padded_tensor);
+  m.def("to_tensor_mask(Tensor buffer, Tensor sizes, Tensor meta, int? mask_dim) -> (Tensor, Tensor)", &to_tensor_mask);
+  m.def("to_mask(Tensor sizes, Tensor meta, int? mask_dim) -> Tensor", &to_mask);
+  m.def("from_padded_tensor(Tensor padded, Tensor sizes, Tensor meta) -> Tensor", &from_padded_tensor);
+  m.def("sizes_from_padded(Tensor tensor, Scalar padding) -> (Tensor, Tensor)", &sizes_from_padded);
+  m.def("sizes_from_mask(Tensor mask) -> (Tensor, Tensor)", &sizes_from_mask);
+  m.def("meta_from_device_sizes(Tensor sizes) -> Tensor", &meta_from_device_sizes);
+  m.def("token_index(Tensor token_offsets, int total_tokens) -> (Tensor, Tensor)", &token_index);
+}

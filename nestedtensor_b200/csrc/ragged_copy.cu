@@ -1,0 +1,926 @@
+// Ragged <-> dense copy kernels, validity masks and size recovery for nested tensors.
+//
+// Design (B200, HBM-bound byte movers):
+//   * every kernel walks its OUTPUT as a flat array of 16-byte vectors, so stores are
+//     always full-width and aligned whatever the row pitch; the matching input address is
+//     derived per vector with launch-constant multiply-shift division (no per-element / or %);
+//   * 64-bit element indices everywhere (a (4096,1024,1024) bf16 output has 2^32 elements);
+//   * loads fall back to element-wise only where source and destination differ in
+//     16-byte phase (ragged rows of odd length) or at row / entry edges.
+// The reference's counterparts are add_padding_{1,2,3}, remove_padding_2 / remove_padding and
+// add_padding_mask in nestedtensor/csrc/cuda/padding.cu:10-414 (scalar strided copies with int
+// indices, one thread per sequence for the mask variant).
+
+#include "common.cuh"
+
+namespace ntb200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVecPerThread = 4;  // 16-byte vectors per thread per tile
+
+// ------------------------------------------------------------------------------ pad
+struct PadParams {
+  const void* src;
+  void* dst;
+  const int64_t* offsets;
+  const int64_t* sizes;
+  int64_t size_stride;
+  int64_t batch;
+  int64_t total;    // batch * P output elements
+  uint64_t P;       // padded elements per entry
+  uint64_t m[3];    // padded extents, outer -> inner (first ND used)
+  FastDiv divP;     // by P
+  FastDiv div1;     // ND==2: by m[1];  ND==3: by m[1]*m[2]
+  FastDiv div2;     // ND==3: by m[2]
+  uint64_t pad_bits;
+  int64_t inner;    // contiguous elements per innermost index (folded regular trailing dims);
+                    // m[ND-1] is already multiplied by it, sizes[.][ND-1] is not
+};
+
+// Value of output element r of entry b (general path, used at row and entry edges).
+template <int ES, int ND, bool MASK, bool BIG>
+__device__ __forceinline__ typename ElemBits<ES>::T pad_elem(const PadParams& p, int64_t b, uint64_t r) {
+  using E = typename ElemBits<ES>::T;
+  using IP = IdxPolicy<BIG>;
+  using I = typename IP::T;
+  const int64_t* s = p.sizes + b * p.size_stride;
+  bool valid;
+  int64_t lin;
+  if (ND == 1) {
+    valid = (int64_t)r < s[0] * p.inner;
+    lin = (int64_t)r;
+  } else if (ND == 2) {
+    I i0 = IP::div((I)r, p.div1, p.m[1]);
+    I c = (I)r - i0 * (I)p.m[1];
+    int64_t s1 = s[1] * p.inner;
+    valid = (int64_t)i0 < s[0] && (int64_t)c < s1;
+    lin = (int64_t)i0 * s1 + (int64_t)c;
+  } else {
+    const uint64_t m12 = p.m[1] * p.m[2];
+    I i0 = IP::div((I)r, p.div1, m12);
+    I rem = (I)r - i0 * (I)m12;
+    I i1 = IP::div(rem, p.div2, p.m[2]);
+    I c = rem - i1 * (I)p.m[2];
+    int64_t s1 = s[1], s2 = s[2] * p.inner;
+    valid = (int64_t)i0 < s[0] && (int64_t)i1 < s1 && (int64_t)c < s2;
+    lin = ((int64_t)i0 * s1 + (int64_t)i1) * s2 + (int64_t)c;
+  }
+  if (MASK) return (E)(valid ? 1 : 0);
+  if (!valid) return (E)p.pad_bits;
+  return reinterpret_cast<const E*>(p.src)[p.offsets[b] + lin];
+}
+
+template <int ES, int ND, bool MASK, bool BIG>
+__global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
+  using E = typename ElemBits<ES>::T;
+  using IP = IdxPolicy<BIG>;
+  using I = typename IP::T;
+  constexpr int VE = 16 / ES;
+  constexpr uint32_t kTileElems = kThreads * kVecPerThread * VE;
+
+  const int64_t tile_e0 = (int64_t)blockIdx.x * kTileElems;
+  const uint64_t b0 = (uint64_t)tile_e0 / p.P;
+  const I r0 = (I)((uint64_t)tile_e0 - b0 * p.P);
+  const E padv = (E)p.pad_bits;
+  E* __restrict__ dst = reinterpret_cast<E*>(p.dst);
+  const E* __restrict__ src = reinterpret_cast<const E*>(p.src);
+
+#pragma unroll
+  for (int u = 0; u < kVecPerThread; ++u) {
+    const uint32_t rel = (uint32_t)(u * kThreads + threadIdx.x) * VE;
+    const int64_t e = tile_e0 + rel;
+    if (e >= p.total) break;
+    const I t = r0 + (I)rel;
+    const I qb = IP::div(t, p.divP, p.P);
+    const I r = t - qb * (I)p.P;
+    const int64_t b = (int64_t)b0 + (int64_t)qb;
+
+    union {
+      uint4 v;
+      E e[VE];
+    } out;
+
+    // locate the innermost row holding element r
+    const int64_t* s = p.sizes + b * p.size_stride;
+    I c;
+    uint64_t row_len;
+    bool outer_valid;
+    int64_t s_last, src_row;
+    if (ND == 1) {
+      c = r;
+      row_len = p.P;
+      outer_valid = true;
+      s_last = s[0] * p.inner;
+      src_row = MASK ? 0 : p.offsets[b];
+    } else if (ND == 2) {
+      I i0 = IP::div(r, p.div1, p.m[1]);
+      c = r - i0 * (I)p.m[1];
+      row_len = p.m[1];
+      outer_valid = (int64_t)i0 < s[0];
+      s_last = s[1] * p.inner;
+      src_row = MASK ? 0 : p.offsets[b] + (int64_t)i0 * s_last;
+    } else {
+      const uint64_t m12 = p.m[1] * p.m[2];
+      I i0 = IP::div(r, p.div1, m12);
+      I rem = r - i0 * (I)m12;
+      I i1 = IP::div(rem, p.div2, p.m[2]);
+      c = rem - i1 * (I)p.m[2];
+      row_len = p.m[2];
+      int64_t s1 = s[1];
+      outer_valid = (int64_t)i0 < s[0] && (int64_t)i1 < s1;
+      s_last = s[2] * p.inner;
+      src_row = MASK ? 0 : p.offsets[b] + ((int64_t)i0 * s1 + (int64_t)i1) * s_last;
+    }
+
+    if ((uint64_t)c + VE <= row_len) {
+      // the whole vector lies in one innermost row
+      int64_t nvalid = outer_valid ? (s_last - (int64_t)c) : 0;
+      nvalid = nvalid < 0 ? 0 : (nvalid > VE ? VE : nvalid);
+      if (nvalid == VE) {
+        if (MASK) {
+#pragma unroll
+          for (int k = 0; k < VE; ++k) out.e[k] = (E)1;
+        } else {
+          const E* sp = src + src_row + (int64_t)c;
+          if ((reinterpret_cast<uintptr_t>(sp) & 15) == 0) {
+            out.v = ld_global_16_stream(sp);
+          } else {
+#pragma unroll
+            for (int k = 0; k < VE; ++k) out.e[k] = sp[k];
+          }
+        }
+      } else if (nvalid == 0) {
+#pragma unroll
+        for (int k = 0; k < VE; ++k) out.e[k] = MASK ? (E)0 : padv;
+      } else {
+        const E* sp = src + src_row + (int64_t)c;
+#pragma unroll
+        for (int k = 0; k < VE; ++k) {
+          if (k < nvalid) out.e[k] = MASK ? (E)1 : sp[k];
+          else out.e[k] = MASK ? (E)0 : padv;
+        }
+      }
+    } else {
+      // the vector crosses a row (possibly an entry) boundary: one element at a time
+#pragma unroll
+      for (int k = 0; k < VE; ++k) {
+        uint64_t rk = (uint64_t)r + k;
+        int64_t bk = b;
+        while (rk >= p.P) {
+          rk -= p.P;
+          ++bk;
+        }
+        out.e[k] = (e + k < p.total) ? pad_elem<ES, ND, MASK, BIG>(p, bk, rk) : (E)0;
+      }
+    }
+
+    if (e + VE <= p.total) {
+      st_global_16_stream(dst + e, out.v);
+    } else {
+#pragma unroll
+      for (int k = 0; k < VE; ++k)
+        if (e + k < p.total) dst[e + k] = out.e[k];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------- unpad
+struct UnpadParams {
+  const void* src;
+  void* dst;
+  const int64_t* offsets;
+  const int64_t* sizes;
+  int64_t size_stride;
+  int64_t batch;
+  int64_t total;  // offsets[batch]
+  uint64_t P;
+  uint64_t m[3];  // m[ND-1] already multiplied by inner
+  int64_t inner;
+};
+
+// largest b in [lo, hi] with offsets[b] <= e (requires offsets[lo] <= e)
+__device__ __forceinline__ int64_t find_entry(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
+  while (lo < hi) {
+    const int64_t mid = (lo + hi + 1) >> 1;
+    if (offsets[mid] <= e) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+// source index (in the padded tensor) of element r of entry b, and the number of
+// elements left in that innermost row starting at r
+template <int ND>
+__device__ __forceinline__ void unpad_locate(const UnpadParams& p, int64_t b, uint64_t r, int64_t& src_idx,
+                                             int64_t& run) {
+  const int64_t* s = p.sizes + b * p.size_stride;
+  const int64_t base = b * (int64_t)p.P;
+  if (ND == 1) {
+    src_idx = base + (int64_t)r;
+    run = s[0] * p.inner - (int64_t)r;
+  } else if (ND == 2) {
+    uint64_t i0, c;
+    const uint64_t s1 = (uint64_t)(s[1] * p.inner);
+    divmod_u64(r, s1, i0, c);
+    src_idx = base + (int64_t)(i0 * p.m[1] + c);
+    run = (int64_t)(s1 - c);
+  } else {
+    uint64_t i0, rem, i1, c;
+    const uint64_t s1 = (uint64_t)s[1], s2 = (uint64_t)(s[2] * p.inner);
+    divmod_u64(r, s1 * s2, i0, rem);
+    divmod_u64(rem, s2, i1, c);
+    src_idx = base + (int64_t)((i0 * p.m[1] + i1) * p.m[2] + c);
+    run = (int64_t)(s2 - c);
+  }
+}
+
+template <int ES, int ND>
+__global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
+  using E = typename ElemBits<ES>::T;
+  constexpr int VE = 16 / ES;
+  constexpr uint32_t kTileElems = kThreads * kVecPerThread * VE;
+  __shared__ int64_t s_range[2];
+
+  const int64_t tile_e0 = (int64_t)blockIdx.x * kTileElems;
+  if (threadIdx.x == 0) {
+    int64_t tile_last = tile_e0 + kTileElems - 1;
+    if (tile_last > p.total - 1) tile_last = p.total - 1;
+    const int64_t lo = find_entry(p.offsets, 0, p.batch - 1, tile_e0);
+    s_range[0] = lo;
+    s_range[1] = find_entry(p.offsets, lo, p.batch - 1, tile_last);
+  }
+  __syncthreads();
+  const int64_t blo = s_range[0], bhi = s_range[1];
+  E* __restrict__ dst = reinterpret_cast<E*>(p.dst);
+  const E* __restrict__ src = reinterpret_cast<const E*>(p.src);
+
+#pragma unroll
+  for (int u = 0; u < kVecPerThread; ++u) {
+    const int64_t e = tile_e0 + (int64_t)(u * kThreads + threadIdx.x) * VE;
+    if (e >= p.total) break;
+    int64_t b = find_entry(p.offsets, blo, bhi, e);
+    const int64_t off = p.offsets[b];
+    int64_t src_idx, run;
+    unpad_locate<ND>(p, b, (uint64_t)(e - off), src_idx, run);
+
+    union {
+      uint4 v;
+      E e[VE];
+    } out;
+    if (run >= VE) {
+      const E* sp = src + src_idx;
+      if ((reinterpret_cast<uintptr_t>(sp) & 15) == 0) {
+        out.v = ld_global_16_stream(sp);
+      } else {
+#pragma unroll
+        for (int k = 0; k < VE; ++k) out.e[k] = sp[k];
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < VE; ++k) {
+        const int64_t ek = e + k;
+        if (ek < p.total) {
+          while (ek >= p.offsets[b + 1]) ++b;  // skips empty entries too
+          int64_t si, rr;
+          unpad_locate<ND>(p, b, (uint64_t)(ek - p.offsets[b]), si, rr);
+          out.e[k] = src[si];
+        } else {
+          out.e[k] = (E)0;
+        }
+      }
+    }
+    if (e + VE <= p.total) {
+      st_global_16_stream(dst + e, out.v);
+    } else {
+#pragma unroll
+      for (int k = 0; k < VE; ++k)
+        if (e + k < p.total) dst[e + k] = out.e[k];
+    }
+  }
+}
+
+// ------------------------------------------------------------- sizes from padded / mask
+struct ScanParams {
+  const void* src;
+  unsigned long long* out_sizes;   // [batch, ND]
+  unsigned long long* out_counts;  // [batch]
+  int64_t batch;
+  int64_t total;
+  uint64_t P;
+  uint64_t m[3];
+  FastDiv divP, div1, div2;
+  uint64_t pad_bits;
+};
+
+// CMP: 0 bit pattern, 1 IEEE float of the element width, 2 bfloat16
+template <int ES, int CMP>
+struct NotPad {
+  using E = typename ElemBits<ES>::T;
+  E pad;
+  __device__ explicit NotPad(uint64_t bits) : pad((E)bits) {}
+  __device__ __forceinline__ bool operator()(E x) const { return x != pad; }
+};
+__device__ __forceinline__ float half_bits_to_float(uint16_t h) {
+  // exact widening of IEEE binary16
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  const uint32_t ex = (h >> 10) & 0x1fu;
+  const uint32_t man = h & 0x3ffu;
+  if (ex == 0x1f) return __uint_as_float(sign | 0x7f800000u | (man << 13));
+  if (ex == 0) {
+    const float f = (float)man * 5.9604644775390625e-8f;  // man * 2^-24
+    return sign ? -f : f;
+  }
+  return __uint_as_float(sign | ((ex + 112u) << 23) | (man << 13));
+}
+template <>
+struct NotPad<2, 1> {
+  float pad;
+  __device__ explicit NotPad(uint64_t bits) { pad = half_bits_to_float((uint16_t)bits); }
+  __device__ __forceinline__ bool operator()(uint16_t x) const { return half_bits_to_float(x) != pad; }
+};
+template <>
+struct NotPad<2, 2> {
+  float pad;
+  __device__ explicit NotPad(uint64_t bits) { pad = __uint_as_float((uint32_t)(bits & 0xffffu) << 16); }
+  __device__ __forceinline__ bool operator()(uint16_t x) const { return __uint_as_float((uint32_t)x << 16) != pad; }
+};
+template <>
+struct NotPad<4, 1> {
+  float pad;
+  __device__ explicit NotPad(uint64_t bits) { pad = __uint_as_float((uint32_t)bits); }
+  __device__ __forceinline__ bool operator()(uint32_t x) const { return __uint_as_float(x) != pad; }
+};
+template <>
+struct NotPad<8, 1> {
+  double pad;
+  __device__ explicit NotPad(uint64_t bits) { pad = __longlong_as_double((long long)bits); }
+  __device__ __forceinline__ bool operator()(uint64_t x) const { return __longlong_as_double((long long)x) != pad; }
+};
+
+template <int ND, bool BIG>
+__device__ __forceinline__ void decompose(const ScanParams& p, uint64_t r, uint64_t idx[3]) {
+  using IP = IdxPolicy<BIG>;
+  using I = typename IP::T;
+  if (ND == 1) {
+    idx[0] = r;
+  } else if (ND == 2) {
+    I i0 = IP::div((I)r, p.div1, p.m[1]);
+    idx[0] = i0;
+    idx[1] = (I)r - i0 * (I)p.m[1];
+  } else {
+    const uint64_t m12 = p.m[1] * p.m[2];
+    I i0 = IP::div((I)r, p.div1, m12);
+    I rem = (I)r - i0 * (I)m12;
+    I i1 = IP::div(rem, p.div2, p.m[2]);
+    idx[0] = i0;
+    idx[1] = i1;
+    idx[2] = rem - i1 * (I)p.m[2];
+  }
+}
+
+template <int ND>
+__device__ __forceinline__ void scan_flush(const ScanParams& p, int64_t b, unsigned long long cnt,
+                                           const unsigned long long mx[3]) {
+  if (cnt == 0) return;
+  atomicAdd(p.out_counts + b, cnt);
+#pragma unroll
+  for (int j = 0; j < ND; ++j) atomicMax(p.out_sizes + b * ND + j, mx[j]);
+}
+
+template <int ES, int ND, int CMP, bool BIG>
+__global__ void __launch_bounds__(kThreads) sizes_scan_kernel(const ScanParams p) {
+  using E = typename ElemBits<ES>::T;
+  using IP = IdxPolicy<BIG>;
+  using I = typename IP::T;
+  constexpr int VE = 16 / ES;
+  constexpr uint32_t kTileElems = kThreads * kVecPerThread * VE;
+  const NotPad<ES, CMP> notpad(p.pad_bits);
+
+  const int64_t tile_e0 = (int64_t)blockIdx.x * kTileElems;
+  const uint64_t b0 = (uint64_t)tile_e0 / p.P;
+  const I r0 = (I)((uint64_t)tile_e0 - b0 * p.P);
+  const E* __restrict__ src = reinterpret_cast<const E*>(p.src);
+
+  // accumulators for the tile's first entry (reduced over the block at the end);
+  // elements of later entries inside the tile go to global atomics directly
+  unsigned long long cnt0 = 0, mx0[3] = {0, 0, 0};
+
+#pragma unroll
+  for (int u = 0; u < kVecPerThread; ++u) {
+    const uint32_t rel = (uint32_t)(u * kThreads + threadIdx.x) * VE;
+    const int64_t e = tile_e0 + rel;
+    if (e >= p.total) break;
+    const I t = r0 + (I)rel;
+    const I qb = IP::div(t, p.divP, p.P);
+    const I r = t - qb * (I)p.P;
+    const int64_t b = (int64_t)b0 + (int64_t)qb;
+
+    union {
+      uint4 v;
+      E e[VE];
+    } in;
+    if (e + VE <= p.total) {
+      in.v = ld_global_16_stream(src + e);
+    } else {
+#pragma unroll
+      for (int k = 0; k < VE; ++k) in.e[k] = (e + k < p.total) ? src[e + k] : (E)p.pad_bits;
+    }
+    uint32_t bits = 0;
+#pragma unroll
+    for (int k = 0; k < VE; ++k)
+      if (e + k < p.total && notpad(in.e[k])) bits |= 1u << k;
+    if (bits == 0) continue;
+
+    uint64_t idx[3];
+    decompose<ND, BIG>(p, (uint64_t)r, idx);
+    const uint64_t row_len = (ND == 1) ? p.P : p.m[ND - 1];
+    if (idx[ND - 1] + VE <= row_len) {
+      unsigned long long mx[3];
+#pragma unroll
+      for (int j = 0; j < ND - 1; ++j) mx[j] = idx[j] + 1;
+      mx[ND - 1] = idx[ND - 1] + (32 - __clz(bits));
+      const unsigned long long c = __popc(bits);
+      if (qb == 0) {
+        cnt0 += c;
+#pragma unroll
+        for (int j = 0; j < ND; ++j) mx0[j] = mx0[j] > mx[j] ? mx0[j] : mx[j];
+      } else {
+        scan_flush<ND>(p, b, c, mx);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < VE; ++k) {
+        if (!(bits & (1u << k))) continue;
+        uint64_t rk = (uint64_t)r + k;
+        int64_t bk = b;
+        while (rk >= p.P) {
+          rk -= p.P;
+          ++bk;
+        }
+        uint64_t ik[3];
+        decompose<ND, BIG>(p, rk, ik);
+        unsigned long long mx[3];
+#pragma unroll
+        for (int j = 0; j < ND; ++j) mx[j] = ik[j] + 1;
+        scan_flush<ND>(p, bk, 1ull, mx);
+      }
+    }
+  }
+
+  // block reduction of the first-entry accumulators
+  __shared__ unsigned long long s_red[kThreads / 32][4];
+  const unsigned full = 0xffffffffu;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    cnt0 += __shfl_xor_sync(full, cnt0, o);
+#pragma unroll
+    for (int j = 0; j < ND; ++j) {
+      const unsigned long long other = __shfl_xor_sync(full, mx0[j], o);
+      mx0[j] = mx0[j] > other ? mx0[j] : other;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    s_red[warp][0] = cnt0;
+#pragma unroll
+    for (int j = 0; j < ND; ++j) s_red[warp][1 + j] = mx0[j];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long c = 0, mx[3] = {0, 0, 0};
+    for (int w = 0; w < kThreads / 32; ++w) {
+      c += s_red[w][0];
+      for (int j = 0; j < ND; ++j) mx[j] = mx[j] > s_red[w][1 + j] ? mx[j] : s_red[w][1 + j];
+    }
+    if ((int64_t)b0 < p.batch) scan_flush<ND>(p, (int64_t)b0, c, mx);
+  }
+}
+
+// ------------------------------------------------------------------- offsets (scan)
+constexpr int kScanThreads = 1024;
+
+__device__ __forceinline__ int64_t entry_numel(const int64_t* sizes, int64_t stride, int nd, int64_t inner, int64_t b) {
+  int64_t n = inner;
+  for (int j = 0; j < nd; ++j) n *= sizes[b * stride + j];
+  return n;
+}
+
+// block-wide exclusive scan of one value per thread; returns the exclusive prefix and
+// leaves the block total in *total (valid for all threads after the call)
+__device__ __forceinline__ int64_t block_exclusive_scan(int64_t v, int64_t* total) {
+  __shared__ int64_t s_warp[kScanThreads / 32];
+  __shared__ int64_t s_total;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int64_t incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int64_t n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int64_t w = (lane < kScanThreads / 32) ? s_warp[lane] : 0;
+    int64_t wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int64_t n = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += n;
+    }
+    if (lane < kScanThreads / 32) s_warp[lane] = wi - w;  // exclusive prefix of warp sums
+    if (lane == 31) s_total = wi;
+  }
+  __syncthreads();
+  const int64_t r = incl - v + s_warp[warp];
+  *total = s_total;
+  __syncthreads();  // the shared arrays may be reused by the caller's next scan
+  return r;
+}
+
+// phase 1: per-block exclusive scan of entry sizes; block totals to block_sums (or, for a
+// single block, the grand total straight to offsets[batch])
+__global__ void __launch_bounds__(kScanThreads) offsets_phase1(const int64_t* sizes, int64_t stride, int nd,
+                                                                int64_t inner, int64_t batch, int64_t* offsets,
+                                                                int64_t* block_sums) {
+  const int64_t b = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  const int64_t v = b < batch ? entry_numel(sizes, stride, nd, inner, b) : 0;
+  int64_t total;
+  const int64_t ex = block_exclusive_scan(v, &total);
+  if (b < batch) offsets[b] = ex;
+  if (threadIdx.x == 0) {
+    if (gridDim.x == 1) offsets[batch] = total;
+    else block_sums[blockIdx.x] = total;
+  }
+}
+
+// phase 2: one block turns block_sums[0..n) into its exclusive scan and writes the grand total
+__global__ void __launch_bounds__(kScanThreads) offsets_phase2(int64_t* block_sums, int64_t n, int64_t* grand_total) {
+  int64_t carry = 0;
+  for (int64_t base = 0; base < n; base += kScanThreads) {
+    const int64_t i = base + threadIdx.x;
+    const int64_t v = i < n ? block_sums[i] : 0;
+    int64_t total;
+    const int64_t ex = block_exclusive_scan(v, &total);
+    if (i < n) block_sums[i] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0) *grand_total = carry;
+}
+
+// phase 3: add each block's base
+__global__ void __launch_bounds__(kScanThreads) offsets_phase3(int64_t* offsets, const int64_t* block_sums, int64_t batch) {
+  const int64_t b = (int64_t)blockIdx.x * kScanThreads + threadIdx.x;
+  if (b < batch) offsets[b] += block_sums[blockIdx.x];
+}
+
+// ---------------------------------------------------------------------- token index
+__global__ void __launch_bounds__(kThreads) token_index_kernel(const int64_t* __restrict__ offsets, int64_t batch,
+                                                                int64_t total, int32_t* __restrict__ batch_idx,
+                                                                int32_t* __restrict__ word_idx) {
+  const int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (t >= total) return;
+  const int64_t b = find_entry(offsets, 0, batch - 1, t);
+  batch_idx[t] = (int32_t)b;
+  word_idx[t] = (int32_t)(t - offsets[b]);
+}
+
+// ------------------------------------------------------------------------ host side
+struct Geometry {
+  uint64_t P;
+  uint64_t m[3];
+  bool big;
+};
+
+int make_geometry(int nd, const int64_t* h_max_sizes, int64_t inner, Geometry* g) {
+  if (nd < 1 || nd > 3 || h_max_sizes == nullptr || inner < 1) return NTB200_INVALID_ARG;
+  g->P = 1;
+  g->m[0] = g->m[1] = g->m[2] = 1;
+  for (int j = 0; j < nd; ++j) {
+    if (h_max_sizes[j] < 0) return NTB200_INVALID_ARG;
+    g->m[j] = (uint64_t)h_max_sizes[j];
+    if (j == nd - 1) {
+      if (g->m[j] != 0 && (uint64_t)inner > (uint64_t)INT64_MAX / g->m[j]) return NTB200_INVALID_ARG;
+      g->m[j] *= (uint64_t)inner;
+    }
+    // overflow-safe product
+    if (g->m[j] != 0 && g->P > (uint64_t)INT64_MAX / g->m[j]) return NTB200_INVALID_ARG;
+    g->P *= g->m[j];
+  }
+  g->big = g->P > (1ull << 30);
+  return NTB200_OK;
+}
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+template <int ES, int ND, bool MASK>
+int launch_pad_es_nd(const PadParams& p, bool big, cudaStream_t st) {
+  constexpr int VE = 16 / ES;
+  const int64_t tile = (int64_t)kThreads * kVecPerThread * VE;
+  const int64_t blocks = ceil_div(p.total, tile);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  if (big) pad_kernel<ES, ND, MASK, true><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+  else pad_kernel<ES, ND, MASK, false><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+  return status_from_cuda(cudaGetLastError());
+}
+
+template <int ES, bool MASK>
+int launch_pad_es(const PadParams& p, int nd, bool big, cudaStream_t st) {
+  switch (nd) {
+    case 1: return launch_pad_es_nd<ES, 1, MASK>(p, big, st);
+    case 2: return launch_pad_es_nd<ES, 2, MASK>(p, big, st);
+    case 3: return launch_pad_es_nd<ES, 3, MASK>(p, big, st);
+  }
+  return NTB200_INVALID_ARG;
+}
+
+void fill_divs(int nd, const Geometry& g, FastDiv* divP, FastDiv* div1, FastDiv* div2) {
+  *divP = make_fastdiv(g.big ? 1 : g.P);
+  *div1 = make_fastdiv(1);
+  *div2 = make_fastdiv(1);
+  if (!g.big) {
+    if (nd == 2) *div1 = make_fastdiv(g.m[1]);
+    if (nd == 3) {
+      *div1 = make_fastdiv(g.m[1] * g.m[2]);
+      *div2 = make_fastdiv(g.m[2]);
+    }
+  }
+}
+
+template <int ES, int ND>
+int launch_unpad_es_nd(const UnpadParams& p, cudaStream_t st) {
+  constexpr int VE = 16 / ES;
+  const int64_t tile = (int64_t)kThreads * kVecPerThread * VE;
+  const int64_t blocks = ceil_div(p.total, tile);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  unpad_kernel<ES, ND><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+  return status_from_cuda(cudaGetLastError());
+}
+
+template <int ES>
+int launch_unpad_es(const UnpadParams& p, int nd, cudaStream_t st) {
+  switch (nd) {
+    case 1: return launch_unpad_es_nd<ES, 1>(p, st);
+    case 2: return launch_unpad_es_nd<ES, 2>(p, st);
+    case 3: return launch_unpad_es_nd<ES, 3>(p, st);
+  }
+  return NTB200_INVALID_ARG;
+}
+
+template <int ES, int ND, int CMP>
+int launch_scan_es_nd(const ScanParams& p, bool big, cudaStream_t st) {
+  constexpr int VE = 16 / ES;
+  const int64_t tile = (int64_t)kThreads * kVecPerThread * VE;
+  const int64_t blocks = ceil_div(p.total, tile);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  if (big) sizes_scan_kernel<ES, ND, CMP, true><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+  else sizes_scan_kernel<ES, ND, CMP, false><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+  return status_from_cuda(cudaGetLastError());
+}
+
+template <int ES, int CMP>
+int launch_scan_es(const ScanParams& p, int nd, bool big, cudaStream_t st) {
+  switch (nd) {
+    case 1: return launch_scan_es_nd<ES, 1, CMP>(p, big, st);
+    case 2: return launch_scan_es_nd<ES, 2, CMP>(p, big, st);
+    case 3: return launch_scan_es_nd<ES, 3, CMP>(p, big, st);
+  }
+  return NTB200_INVALID_ARG;
+}
+
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+}  // namespace
+}  // namespace ntb200
+
+using namespace ntb200;
+
+extern "C" {
+
+const char* ntb200_status_string(int status) {
+  switch (status) {
+    case NTB200_OK: return "ok";
+    case NTB200_INVALID_ARG: return "invalid argument";
+    case NTB200_UNSUPPORTED_DTYPE: return "unsupported dtype";
+    case NTB200_MISALIGNED: return "misaligned pointer";
+    case NTB200_LAUNCH_FAILED: return "kernel launch failed";
+    case NTB200_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case NTB200_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case NTB200_UNSUPPORTED_SHAPE: return "unsupported shape";
+  }
+  return "unknown status";
+}
+
+int ntb200_version(void) { return 1000; }
+
+int ntb200_pad_nd(const void* ragged, void* padded, const int64_t* offsets, const int64_t* sizes,
+                  int64_t size_stride, int nd, int64_t inner, int64_t batch, const int64_t* h_max_sizes,
+                  int elem_size, uint64_t pad_bits, void* stream) {
+  Geometry g;
+  int rc = make_geometry(nd, h_max_sizes, inner, &g);
+  if (rc != NTB200_OK) return rc;
+  if (batch < 0 || size_stride < nd) return NTB200_INVALID_ARG;
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return NTB200_UNSUPPORTED_DTYPE;
+  if (batch == 0 || g.P == 0) return NTB200_OK;
+  if (g.P > (uint64_t)INT64_MAX / (uint64_t)batch) return NTB200_INVALID_ARG;
+  if (padded == nullptr || offsets == nullptr || sizes == nullptr) return NTB200_INVALID_ARG;
+  if (!aligned_to(padded, 16)) return NTB200_MISALIGNED;
+  if (ragged != nullptr && !aligned_to(ragged, (size_t)elem_size)) return NTB200_MISALIGNED;
+
+  PadParams p;
+  p.src = ragged;
+  p.dst = padded;
+  p.offsets = offsets;
+  p.sizes = sizes;
+  p.size_stride = size_stride;
+  p.batch = batch;
+  p.P = g.P;
+  p.total = batch * (int64_t)g.P;
+  for (int j = 0; j < 3; ++j) p.m[j] = g.m[j];
+  fill_divs(nd, g, &p.divP, &p.div1, &p.div2);
+  p.pad_bits = pad_bits;
+  p.inner = inner;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (elem_size) {
+    case 1: return launch_pad_es<1, false>(p, nd, g.big, st);
+    case 2: return launch_pad_es<2, false>(p, nd, g.big, st);
+    case 4: return launch_pad_es<4, false>(p, nd, g.big, st);
+    case 8: return launch_pad_es<8, false>(p, nd, g.big, st);
+  }
+  return NTB200_UNSUPPORTED_DTYPE;
+}
+
+int ntb200_mask_from_sizes(uint8_t* mask, const int64_t* sizes, int64_t size_stride, int nd, int64_t batch,
+                           const int64_t* h_max_sizes, void* stream) {
+  Geometry g;
+  int rc = make_geometry(nd, h_max_sizes, 1, &g);
+  if (rc != NTB200_OK) return rc;
+  if (batch < 0 || size_stride < nd) return NTB200_INVALID_ARG;
+  if (batch == 0 || g.P == 0) return NTB200_OK;
+  if (g.P > (uint64_t)INT64_MAX / (uint64_t)batch) return NTB200_INVALID_ARG;
+  if (mask == nullptr || sizes == nullptr) return NTB200_INVALID_ARG;
+  if (!aligned_to(mask, 16)) return NTB200_MISALIGNED;
+  PadParams p;
+  p.src = nullptr;
+  p.dst = mask;
+  p.offsets = nullptr;
+  p.sizes = sizes;
+  p.size_stride = size_stride;
+  p.batch = batch;
+  p.P = g.P;
+  p.total = batch * (int64_t)g.P;
+  for (int j = 0; j < 3; ++j) p.m[j] = g.m[j];
+  fill_divs(nd, g, &p.divP, &p.div1, &p.div2);
+  p.pad_bits = 0;
+  p.inner = 1;
+  return launch_pad_es<1, true>(p, nd, g.big, static_cast<cudaStream_t>(stream));
+}
+
+int ntb200_pad_with_mask(const void* ragged, void* padded, uint8_t* mask, const int64_t* offsets,
+                         const int64_t* sizes, int64_t size_stride, int nd, int64_t inner, int64_t batch,
+                         const int64_t* h_max_sizes, int elem_size, const int64_t* mask_sizes,
+                         int64_t mask_size_stride, int mask_nd, const int64_t* mask_h_max_sizes, void* stream) {
+  int rc = ntb200_pad_nd(ragged, padded, offsets, sizes, size_stride, nd, inner, batch, h_max_sizes, elem_size, 0,
+                         stream);
+  if (rc != NTB200_OK) return rc;
+  return ntb200_mask_from_sizes(mask, mask_sizes, mask_size_stride, mask_nd, batch, mask_h_max_sizes, stream);
+}
+
+int ntb200_unpad_nd(const void* padded, void* ragged, const int64_t* offsets, const int64_t* sizes,
+                    int64_t size_stride, int nd, int64_t inner, int64_t batch, const int64_t* h_max_sizes,
+                    int64_t total_elems, int elem_size, void* stream) {
+  Geometry g;
+  int rc = make_geometry(nd, h_max_sizes, inner, &g);
+  if (rc != NTB200_OK) return rc;
+  if (batch < 0 || size_stride < nd || total_elems < 0) return NTB200_INVALID_ARG;
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return NTB200_UNSUPPORTED_DTYPE;
+  if (batch == 0 || total_elems == 0) return NTB200_OK;
+  if (g.P > (uint64_t)INT64_MAX / (uint64_t)batch) return NTB200_INVALID_ARG;
+  if ((uint64_t)total_elems > g.P * (uint64_t)batch) return NTB200_INVALID_ARG;
+  if (padded == nullptr || ragged == nullptr || offsets == nullptr || sizes == nullptr) return NTB200_INVALID_ARG;
+  if (!aligned_to(ragged, 16)) return NTB200_MISALIGNED;
+  if (!aligned_to(padded, (size_t)elem_size)) return NTB200_MISALIGNED;
+  UnpadParams p;
+  p.src = padded;
+  p.dst = ragged;
+  p.offsets = offsets;
+  p.sizes = sizes;
+  p.size_stride = size_stride;
+  p.batch = batch;
+  p.total = total_elems;
+  p.P = g.P;
+  for (int j = 0; j < 3; ++j) p.m[j] = g.m[j];
+  p.inner = inner;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (elem_size) {
+    case 1: return launch_unpad_es<1>(p, nd, st);
+    case 2: return launch_unpad_es<2>(p, nd, st);
+    case 4: return launch_unpad_es<4>(p, nd, st);
+    case 8: return launch_unpad_es<8>(p, nd, st);
+  }
+  return NTB200_UNSUPPORTED_DTYPE;
+}
+
+static int sizes_scan_common(const void* src, int64_t* out_sizes, int64_t* out_counts, int nd, int64_t batch,
+                             const int64_t* h_dims, int elem_size, int cmp_kind, uint64_t pad_bits, void* stream) {
+  Geometry g;
+  int rc = make_geometry(nd, h_dims, 1, &g);
+  if (rc != NTB200_OK) return rc;
+  if (batch < 0) return NTB200_INVALID_ARG;
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return NTB200_UNSUPPORTED_DTYPE;
+  if (cmp_kind < 0 || cmp_kind > 2) return NTB200_UNSUPPORTED_DTYPE;
+  if (cmp_kind == 2 && elem_size != 2) return NTB200_UNSUPPORTED_DTYPE;
+  if (cmp_kind == 1 && elem_size == 1) return NTB200_UNSUPPORTED_DTYPE;
+  if (batch == 0) return NTB200_OK;
+  if (out_sizes == nullptr || out_counts == nullptr) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t ce = cudaMemsetAsync(out_sizes, 0, sizeof(int64_t) * (size_t)batch * nd, st);
+  if (ce != cudaSuccess) return NTB200_LAUNCH_FAILED;
+  ce = cudaMemsetAsync(out_counts, 0, sizeof(int64_t) * (size_t)batch, st);
+  if (ce != cudaSuccess) return NTB200_LAUNCH_FAILED;
+  if (g.P == 0) return NTB200_OK;
+  if (g.P > (uint64_t)INT64_MAX / (uint64_t)batch) return NTB200_INVALID_ARG;
+  if (src == nullptr) return NTB200_INVALID_ARG;
+  if (!aligned_to(src, 16)) return NTB200_MISALIGNED;
+  ScanParams p;
+  p.src = src;
+  p.out_sizes = reinterpret_cast<unsigned long long*>(out_sizes);
+  p.out_counts = reinterpret_cast<unsigned long long*>(out_counts);
+  p.batch = batch;
+  p.P = g.P;
+  p.total = batch * (int64_t)g.P;
+  for (int j = 0; j < 3; ++j) p.m[j] = g.m[j];
+  fill_divs(nd, g, &p.divP, &p.div1, &p.div2);
+  p.pad_bits = pad_bits;
+  if (cmp_kind == 0) {
+    switch (elem_size) {
+      case 1: return launch_scan_es<1, 0>(p, nd, g.big, st);
+      case 2: return launch_scan_es<2, 0>(p, nd, g.big, st);
+      case 4: return launch_scan_es<4, 0>(p, nd, g.big, st);
+      case 8: return launch_scan_es<8, 0>(p, nd, g.big, st);
+    }
+  } else if (cmp_kind == 1) {
+    switch (elem_size) {
+      case 2: return launch_scan_es<2, 1>(p, nd, g.big, st);
+      case 4: return launch_scan_es<4, 1>(p, nd, g.big, st);
+      case 8: return launch_scan_es<8, 1>(p, nd, g.big, st);
+    }
+  } else {
+    return launch_scan_es<2, 2>(p, nd, g.big, st);
+  }
+  return NTB200_UNSUPPORTED_DTYPE;
+}
+
+int ntb200_sizes_from_padded(const void* padded, int64_t* out_sizes, int64_t* out_counts, int nd, int64_t batch,
+                             const int64_t* h_dims, int elem_size, int cmp_kind, uint64_t pad_bits, void* stream) {
+  return sizes_scan_common(padded, out_sizes, out_counts, nd, batch, h_dims, elem_size, cmp_kind, pad_bits, stream);
+}
+
+int ntb200_sizes_from_mask(const uint8_t* mask, int64_t* out_sizes, int64_t* out_counts, int nd, int64_t batch,
+                           const int64_t* h_dims, void* stream) {
+  return sizes_scan_common(mask, out_sizes, out_counts, nd, batch, h_dims, 1, 0, 0, stream);
+}
+
+size_t ntb200_offsets_workspace_bytes(int64_t batch) {
+  if (batch <= kScanThreads) return 0;
+  return sizeof(int64_t) * (size_t)ceil_div(batch, kScanThreads);
+}
+
+int ntb200_offsets_from_sizes(const int64_t* sizes, int64_t size_stride, int nd, int64_t inner, int64_t batch,
+                              int64_t* offsets, void* workspace, size_t workspace_bytes, void* stream) {
+  if (batch < 0 || nd < 0 || nd > 8 || size_stride < nd || inner < 0) return NTB200_INVALID_ARG;
+  if (offsets == nullptr) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (batch == 0) {
+    return status_from_cuda(cudaMemsetAsync(offsets, 0, sizeof(int64_t), st));
+  }
+  if (sizes == nullptr && nd > 0) return NTB200_INVALID_ARG;
+  const int64_t nblk = ceil_div(batch, kScanThreads);
+  if (nblk > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  const size_t need = ntb200_offsets_workspace_bytes(batch);
+  if (need > 0) {
+    if (workspace == nullptr || workspace_bytes < need) return NTB200_WORKSPACE_TOO_SMALL;
+    if (!aligned_to(workspace, 8)) return NTB200_MISALIGNED;
+  }
+  int64_t* block_sums = static_cast<int64_t*>(workspace);
+  offsets_phase1<<<(unsigned)nblk, kScanThreads, 0, st>>>(sizes, size_stride, nd, inner, batch, offsets, block_sums);
+  if (nblk > 1) {
+    offsets_phase2<<<1, kScanThreads, 0, st>>>(block_sums, nblk, offsets + batch);
+    offsets_phase3<<<(unsigned)nblk, kScanThreads, 0, st>>>(offsets, block_sums, batch);
+  }
+  return status_from_cuda(cudaGetLastError());
+}
+
+int ntb200_token_index(const int64_t* token_offsets, int64_t batch, int64_t total_tokens, int32_t* batch_idx,
+                       int32_t* word_idx, void* stream) {
+  if (batch < 0 || total_tokens < 0) return NTB200_INVALID_ARG;
+  if (total_tokens == 0) return NTB200_OK;
+  if (batch == 0 || token_offsets == nullptr || batch_idx == nullptr || word_idx == nullptr) return NTB200_INVALID_ARG;
+  const int64_t blocks = ceil_div(total_tokens, kThreads);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  token_index_kernel<<<(unsigned)blocks, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      token_offsets, batch, total_tokens, batch_idx, word_idx);
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // extern "C"
