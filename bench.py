@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Benchmark of the nestedtensor hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload pad|unpad|mha] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded
+synthetic input:
+
+  pad    (default) configuration 2: `to_padded_tensor(padding=0)` of 4096 bf16 sequences (L_i, 1024)
+         -> (4096, 1024, 1024); metric = HBM GB/s = algorithmic bytes (ragged read once + dense
+         written once) / time
+  unpad  the inverse with known sizes (2 * valid bytes)
+  mha    configuration 5: BERT-large varlen self-attention forward, bf16; metric = valid tokens/s
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): the global job is N batches of the
+configuration drawn as one sequence list and cut into N contiguous token-balanced shards; no
+collective on the data path (weak scaling).  `value` is whole-job throughput over the slowest rank.
+
+`--impl reference` times the CPU restatement of the reference's own implementation
+(oracle/ntref.py; the reference extension cannot be built against this torch) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+# ----------------------------------------------------------------------------- helpers
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS,
+                "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {}
+        for n in dir(nv):
+            if n.startswith("nvmlClocksThrottleReason") or n.startswith("nvmlClocksEventReason"):
+                v = getattr(nv, n)
+                if isinstance(v, int) and v not in (0,):
+                    names[v] = n.replace("nvmlClocksThrottleReason", "").replace("nvmlClocksEventReason", "")
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if bit & (bit - 1) == 0 and mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        ignore = {"GpuIdle", "None", "ApplicationsClocksSetting"}
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "samples": len(s),
+                "reasons": sorted(r for r in self.reasons if r not in ignore)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def timed_region(fn, steps, world, device):
+    """barrier + synchronize, K steps between two CUDA events on the current stream, synchronize +
+    barrier; returns the max over ranks of the elapsed milliseconds."""
+    import torch.distributed as dist
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def all_sum(x, world, device):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([float(x)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+# --------------------------------------------------------------------------- workloads
+def shard_lengths(kind, world, rank):
+    """Lengths of this rank's shard: N batches of the configuration drawn as ONE list (generator of the
+    configuration, batch = N * config batch) and cut token-balanced into N contiguous slices."""
+    from nestedtensor_b200 import workloads, sharding
+    if kind in ("pad", "unpad"):
+        L = workloads.lengths_c2(workloads._gen(2), 4096 * world)
+    else:
+        L = workloads.lengths_c5(workloads._gen(5), 1024 * world)
+    parts = sharding.token_balanced_partition(L.tolist(), world)
+    a, b = parts[rank]
+    return L[a:b].contiguous(), sharding.imbalance(L.tolist(), parts)
+
+
+def host_values(n, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    out = torch.empty(n, dtype=dtype)
+    chunk = 1 << 26
+    for a in range(0, n, chunk):
+        b = min(n, a + chunk)
+        out[a:b] = torch.randn(b - a, generator=g).to(dtype)
+    return out
+
+
+def cpu_pad_sample(L, hidden, dtype, seqs):
+    """The reference's CPU to_padded_tensor (oracle port) on the first `seqs` sequences."""
+    from oracle import ntref
+    Ls = L[:seqs].tolist()
+    g = torch.Generator().manual_seed(11)
+    tensors = [torch.randn(l, hidden, generator=g).to(dtype) for l in Ls]
+    es = tensors[0].element_size()
+    nbytes = es * (sum(Ls) * hidden + len(Ls) * max(Ls) * hidden)
+    return tensors, nbytes, (lambda: ntref.to_padded_tensor(tensors, 0))
+
+
+def cpu_unpad_sample(L, hidden, dtype, seqs):
+    from oracle import ntref
+    Ls = L[:seqs].tolist()
+    g = torch.Generator().manual_seed(11)
+    padded = torch.randn(len(Ls), max(Ls), hidden, generator=g).to(dtype)
+    sizes = [[l, hidden] for l in Ls]
+    nbytes = 2 * padded.element_size() * sum(Ls) * hidden
+    return padded, nbytes, (lambda: ntref.from_padded_tensor(padded, sizes))
+
+
+def time_cpu(fn, warmup, iters):
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+# ------------------------------------------------------------------------- pad / unpad
+def run_copy(args, kind, rank, world, local):
+    import nestedtensor_b200 as nt
+    from nestedtensor_b200 import _ops
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    hidden, dtype = 1024, torch.bfloat16
+    es = 2
+    L, imb = shard_lengths(kind, world, rank)
+    B, T, maxL = int(L.numel()), int(L.sum()), int(L.max())
+    sizes = torch.stack([L, torch.full_like(L, hidden)], 1).contiguous()
+    n_valid, n_pad = T * hidden, B * maxL * hidden
+    alg_bytes = es * (n_valid + n_pad) if kind == "pad" else 2 * es * n_valid
+
+    # resident inputs (generated on the host, copied once, outside the timed region)
+    host = host_values(n_valid, dtype, 20242 + rank)
+    ragged = host.to(device)
+    a = nt.NestedTensor(ragged, sizes)
+    ops = _ops.ops()
+    buf, sz, meta = a._record()
+    if kind == "pad":
+        step = lambda: ops.to_padded_tensor(buf, sz, meta, 0.0)
+    else:
+        padded = ops.to_padded_tensor(buf, sz, meta, 0.0)
+        step = lambda: ops.from_padded_tensor(padded, sz, meta)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    with ClockSampler(local) as clocks:
+        ms = timed_region(step, args.steps, world, device)
+        ms2 = timed_region(step, args.steps, world, device)  # second pass keeps the sampler busy longer
+    ms = min(ms, ms2)
+    total_bytes = all_sum(alg_bytes, world, device)
+    value = total_bytes / (ms / args.steps * 1e-3) / 1e9
+    kernel_ms = ms / args.steps
+
+    # parity spot check in the same run (size-independent property): round trip is the identity
+    chk = ops.from_padded_tensor(ops.to_padded_tensor(buf, sz, meta, 0.0), sz, meta)
+    parity_ok = bool(torch.equal(chk.view(torch.int16), ragged.view(torch.int16)))
+    del chk
+
+    # end to end: pinned host input -> device -> kernel -> pinned host output, every step
+    e2e = None
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = 0
+    out_elems = n_pad if kind == "pad" else n_valid
+    in_elems = n_valid if kind == "pad" else n_pad
+    need = es * (out_elems + in_elems)
+    if avail > 3 * need * max(world, 1):
+        if kind == "unpad":
+            del padded
+        torch.cuda.empty_cache()
+        h_in = torch.empty(in_elems, dtype=dtype).pin_memory()
+        if kind == "pad":
+            h_in.copy_(host)
+        else:
+            h_in.normal_()
+        h_out = torch.empty(out_elems, dtype=dtype).pin_memory()
+        d_in = torch.empty(in_elems, dtype=dtype, device=device)
+
+        def e2e_step():
+            d_in.copy_(h_in, non_blocking=True)
+            if kind == "pad":
+                r = ops.to_padded_tensor(d_in, sz, meta, 0.0)
+            else:
+                r = ops.from_padded_tensor(d_in.view(B, maxL, hidden), sz, meta)
+            h_out.copy_(r.reshape(-1), non_blocking=True)
+
+        e2e_steps = max(2, min(args.steps, 5))
+        e2e_step()
+        with ClockSampler(local) as clocks2:
+            ems = timed_region(e2e_step, e2e_steps, world, device)
+        e2e = {"value": total_bytes / (ems / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": es * in_elems, "d2h_bytes_per_step": es * out_elems,
+               "ms_per_step": ems / e2e_steps, "steps": e2e_steps, "sample": "full shard"}
+        clocks.samples += clocks2.samples
+        clocks.reasons |= clocks2.reasons
+    else:
+        e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+               "sample": "skipped: host has %.1f GB available, needs %.1f GB pinned per rank" % (avail / 1e9, need / 1e9)}
+
+    peaks = measured_peaks()
+    line = None
+    if rank == 0:
+        cpu = None
+        if world == 1 or True:
+            seqs = 256
+            if kind == "pad":
+                _, nbytes, fn = cpu_pad_sample(L, hidden, dtype, seqs)
+            else:
+                _, nbytes, fn = cpu_unpad_sample(L, hidden, dtype, seqs)
+            torch.set_num_threads(os.cpu_count() or 1)
+            t = time_cpu(fn, 1, 3)
+            cpu = {"value": nbytes / t / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                   "sample": "first %d sequences of the shard, median of 3, torch CPU ops of the reference's "
+                             "CPU branch (constant_pad_nd + stack)" % seqs if kind == "pad" else
+                             "first %d sequences of the shard, median of 3, reference CPU branch (mask + masked_select)" % seqs}
+        line = {
+            "metric": "to_padded_tensor HBM GB/s" if kind == "pad" else "from_padded_tensor HBM GB/s",
+            "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 (bit copy, u16)", "data": "synthetic",
+            "config": {"workload": "config2: %d bf16 sequences (L_i,1024), L_i=clip(round(lognormal(ln200,0.6)),1,1024) "
+                                   "per GPU; %s" % (4096, "to_padded_tensor(padding=0)" if kind == "pad" else
+                                                    "from_padded_tensor with known sizes"),
+                       "batch_per_gpu": B, "tokens_per_gpu": T, "max_len": maxL, "hidden": hidden,
+                       "algorithmic_bytes_per_gpu": alg_bytes, "token_imbalance": imb,
+                       "l2": "inputs+outputs (%.1f GB) far larger than the 126 MB L2" % (alg_bytes / 1e9)},
+            "roofline": {"bound": "hbm", "achieved": alg_bytes / (kernel_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": alg_bytes / (kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                         "frac_of_nominal_8000": alg_bytes / (kernel_ms * 1e-3) / 1e9 / 8000.0,
+                         "peak_source": peaks["source"], "traffic": NCU_TRAFFIC.get(kind)},
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": args.steps,
+            "clocks": clocks.summary(),
+            "parity_roundtrip_bit_exact": parity_ok,
+        }
+    return line
+
+
+# Per-launch DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from the
+# ncu capture summarised under profiles/; None until a capture exists for that workload.
+NCU_TRAFFIC = {"pad": None, "unpad": None, "mha": None}
+
+
+# ---------------------------------------------------------------------- reference arm
+def run_reference(args, kind, rank, world):
+    """The reference's own CPU implementation of the path (oracle port) on the host cores; rank 0 only."""
+    if rank != 0:
+        return None
+    torch.set_num_threads(os.cpu_count() or 1)
+    L, _ = shard_lengths("pad" if kind in ("pad", "unpad") else kind, 1, 0)
+    hidden, dtype = 1024, torch.bfloat16
+    seqs = 256
+    if kind == "pad":
+        _, nbytes, fn = cpu_pad_sample(L, hidden, dtype, seqs)
+        metric = "to_padded_tensor HBM GB/s"
+    elif kind == "unpad":
+        _, nbytes, fn = cpu_unpad_sample(L, hidden, dtype, seqs)
+        metric = "from_padded_tensor HBM GB/s"
+    else:
+        return run_reference_mha(args)
+    for _ in range(max(1, min(args.warmup, 2))):
+        fn()
+    steps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    v = nbytes / dt / 1e9
+    cores = torch.get_num_threads()
+    sample = "each step = the first %d sequences of configuration 2 (%.2f GB algorithmic)" % (seqs, nbytes / 1e9)
+    return {"impl": "reference", "metric": metric, "value": v, "unit": "GB/s", "n_gpus": world, "steps": steps,
+            "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 (bit copy, u16)", "data": "synthetic",
+            "config": {"workload": "config2 (CPU sample): " + sample},
+            "cpu_baseline": {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def run_reference_mha(args):
+    return {"impl": "reference", "unavailable": "mha reference arm not wired yet"}
+
+
+def run_mha(args, rank, world, local):
+    raise SystemExit("mha workload not built yet")
+
+
+# ------------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="pad", choices=["pad", "unpad", "mha"])
+    args = ap.parse_args()
+
+    rank, world, local = dist_env()
+    if world == 1 and args.gpus > 1 and args.impl == "ours":
+        # plain invocation with N > 1: re-launch one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
+               "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.abspath(__file__)] + sys.argv[1:]
+        os.execv(sys.executable, cmd)
+
+    if args.impl == "reference":
+        line = run_reference(args, args.workload, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in nestedtensor_b200)")
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    try:
+        if args.workload in ("pad", "unpad"):
+            line = run_copy(args, args.workload, rank, world, local)
+        else:
+            line = run_mha(args, rank, world, local)
+        if rank == 0 and line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,194 @@
+"""Parity of the CUDA ragged<->dense / mask kernels with the CPU oracle: bit-exact, through the raw
+C ABI (ctypes on device pointers) and through the Python operator surface."""
+import math
+
+import pytest
+import torch
+
+import nestedtensor_b200 as nt
+from nestedtensor_b200 import workloads
+from oracle import ntref
+from _helpers import (assert_bit_equal, cabi_mask, cabi_pad, cabi_unpad, random_list, sizes_of)
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int64, torch.uint8, torch.bool, torch.int16]
+
+
+def _oracle_pad(tensors, padding):
+    if tensors[0].dtype == torch.bool:
+        return ntref.to_padded_tensor([t.to(torch.uint8) for t in tensors], padding).to(torch.bool)
+    return ntref.to_padded_tensor(tensors, padding)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=str)
+@pytest.mark.parametrize("tdim", [1, 2, 3])
+def test_cabi_pad_unpad_small(native_libs, cuda_device, dtype, tdim):
+    """5 random tensors with extents 3..30 per dim (test/test_nested_tensor_class.py:754-792), every
+    element width, odd extents so that rows start at every 16-byte phase."""
+    g = torch.Generator().manual_seed(1010 + tdim)
+    tensors = random_list(g, 5, tdim, 3, 30, dtype)
+    padding = 1
+    want = _oracle_pad(tensors, padding)
+    got = cabi_pad(tensors, padding, cuda_device)
+    assert_bit_equal(got, want, "pad")
+    buf = cabi_unpad(got, sizes_of(tensors))
+    assert_bit_equal(buf, torch.cat([t.reshape(-1) for t in tensors]), "unpad")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.uint8], ids=str)
+@pytest.mark.parametrize("tdim,regular_last", [(2, 8), (2, 7), (3, 5), (3, 16), (2, 1)])
+def test_cabi_pad_regular_last(native_libs, cuda_device, dtype, tdim, regular_last):
+    """(L_i, D) style constituents: trailing regular dims are folded into `inner`."""
+    g = torch.Generator().manual_seed(7 + tdim + regular_last)
+    tensors = random_list(g, 9, tdim, 1, 19, dtype, regular_last=regular_last)
+    for padding in (0, -1):
+        if dtype == torch.uint8 and padding < 0:
+            continue
+        want = _oracle_pad(tensors, padding)
+        got = cabi_pad(tensors, padding, cuda_device)
+        assert_bit_equal(got, want, "pad")
+        assert_bit_equal(cabi_unpad(got, sizes_of(tensors)), torch.cat([t.reshape(-1) for t in tensors]), "unpad")
+
+
+def test_exhaustive_tiny(native_libs, cuda_device):
+    """Every combination of lengths 1..5 for 3 sequences and row widths 1..5 (fp32 and bf16):
+    covers every alignment residue and vectors that span rows and entries."""
+    for dtype in (torch.float32, torch.bfloat16):
+        for D in range(1, 6):
+            for l0 in range(1, 6):
+                for l1 in range(1, 6):
+                    for l2 in (1, 3, 5):
+                        tensors = [torch.arange(l * D, dtype=torch.float32).reshape(l, D).add(100 * i).to(dtype)
+                                   for i, l in enumerate((l0, l1, l2))]
+                        want = ntref.to_padded_tensor(tensors, -1)
+                        got = cabi_pad(tensors, -1, cuda_device)
+                        assert_bit_equal(got, want, "pad D=%d L=%s" % (D, (l0, l1, l2)))
+                        back = cabi_unpad(got, sizes_of(tensors))
+                        assert_bit_equal(back, torch.cat([t.reshape(-1) for t in tensors]), "unpad")
+
+
+def test_negative_zero_and_nan_bits(native_libs, cuda_device):
+    a = torch.tensor([[-0.0, float("nan")], [1.0, -0.0]])
+    b = torch.tensor([[float("inf"), -0.0]])
+    got = cabi_pad([a, b], -0.0, cuda_device)
+    want = ntref.to_padded_tensor([a, b], -0.0)
+    assert_bit_equal(got, want, "special values")
+
+
+def test_empty_constituents(native_libs, cuda_device):
+    tensors = [torch.randn(0, 4), torch.randn(3, 4), torch.randn(0, 4), torch.randn(2, 4), torch.randn(0, 4)]
+    got = cabi_pad(tensors, 7, cuda_device)
+    want = torch.full((5, 3, 4), 7.0)
+    want[1] = tensors[1]
+    want[3, :2] = tensors[3]
+    assert_bit_equal(got, want, "pad with empty entries")
+    back = cabi_unpad(got, sizes_of(tensors))
+    assert_bit_equal(back, torch.cat([t.reshape(-1) for t in tensors]), "unpad with empty entries")
+
+
+@pytest.mark.parametrize("mask_nd", [1, 2, 3])
+def test_cabi_mask(native_libs, cuda_device, mask_nd):
+    g = torch.Generator().manual_seed(5)
+    tensors = random_list(g, 7, 3, 1, 21, torch.float32)
+    got = cabi_mask(sizes_of(tensors), mask_nd, cuda_device)
+    want = ntref.to_mask(tensors, mask_nd + 1) if mask_nd < 3 else ntref.to_tensor_mask(tensors, 4)[1]
+    assert_bit_equal(got, want.to(torch.uint8), "mask")
+
+
+def test_config1_roundtrip(native_libs, cuda_device):
+    """Configuration 1: 64 fp32 (L_i, 256): pad(0) -> mask -> from padded, bit-exact."""
+    w = workloads.config1()
+    tensors = w.tensors()
+    a = nt.nested_tensor(tensors, device=cuda_device, dtype=torch.float32)
+    padded = a.to_padded_tensor(padding=0)
+    assert_bit_equal(padded, ntref.to_padded_tensor(tensors, 0), "to_padded_tensor")
+    data, mask = a.to_tensor_mask(mask_dim=2)
+    odata, omask = ntref.to_tensor_mask(tensors, mask_dim=2)
+    assert_bit_equal(data, odata, "to_tensor_mask data")
+    assert mask.dtype == torch.bool and omask.dtype == torch.bool
+    assert_bit_equal(mask, omask, "to_tensor_mask mask")
+    back = nt.nested_tensor_from_padded_tensor(padded, padding=0)
+    assert back.nested_size() == a.nested_size()
+    assert_bit_equal(back._buffer, a._buffer, "nested_tensor_from_padded_tensor")
+    back2 = nt.from_padded_tensor(padded, a)
+    assert_bit_equal(back2._buffer, a._buffer, "from_padded_tensor")
+    # default padding of the API is -1
+    assert_bit_equal(a.to_padded_tensor(), ntref.to_padded_tensor(tensors, -1), "padding=-1")
+
+
+def test_config3_images(native_libs, cuda_device):
+    """Configuration 3: 32 fp32 images (3, H_i, W_i): 4-D pad, the un-collapsible 4-D mask, and the
+    DETR (B, maxH, maxW) mask = channel 0 of it."""
+    w = workloads.config3()
+    tensors = w.tensors()
+    a = nt.nested_tensor(tensors, device=cuda_device, dtype=torch.float32)
+    padded = a.to_padded_tensor(padding=0)
+    want = ntref.to_padded_tensor(tensors, 0)
+    assert_bit_equal(padded, want, "to_padded_tensor 4-D")
+    data, mask = a.to_tensor_mask()
+    odata, omask = ntref.to_tensor_mask(tensors)
+    assert mask.dtype == omask.dtype == torch.uint8 and mask.dim() == 4
+    assert_bit_equal(mask, omask, "4-D mask")
+    assert_bit_equal(data, odata, "4-D data")
+    with pytest.raises(RuntimeError, match="Mask dimension is too small"):
+        a.to_tensor_mask(mask_dim=3)
+    back = nt.from_padded_tensor(padded, a)
+    assert_bit_equal(back._buffer, a._buffer, "unpad 4-D")
+    m3 = nt.to_mask(a, 3)  # leading dims (B, C, maxH)
+    assert_bit_equal(m3, ntref.to_mask(tensors, 3), "to_mask(3)")
+
+
+def test_config2_properties_full_size(native_libs, cuda_device):
+    """Configuration 2 at full size (4096 bf16 sequences, 8.6 GB dense): the oracle cannot run it in
+    seconds, so check size-independent properties: unpad(pad(x)) == x bit-exactly, the padding region
+    holds only the padding value (count and checksum), and a sampled set of rows equals the source."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 14 * (1 << 30):
+        pytest.skip("needs 14 GB of free device memory")
+    w = workloads.config2(with_values=False)
+    L = w.sizes[:, 0]
+    T = int(L.sum())
+    g = torch.Generator(device="cuda").manual_seed(2)
+    buf = torch.randn(T * 1024, generator=g, device=cuda_device, dtype=torch.float32).to(torch.bfloat16)
+    a = nt.NestedTensor(buf, w.sizes)
+    pad_value = 3.0
+    padded = a.to_padded_tensor(padding=pad_value)
+    assert tuple(padded.shape) == (4096, int(L.max()), 1024)
+    back = nt.from_padded_tensor(padded, a)
+    assert torch.equal(back._buffer.view(torch.int16), buf.view(torch.int16))
+    # padding region: number of elements equal to the padding value >= padded - valid, and the sum of the
+    # integer views is the valid checksum plus pad_bits * (number of padding elements)
+    n_pad = padded.numel() - buf.numel()
+    pad_bits = int(torch.tensor(pad_value, dtype=torch.bfloat16).view(torch.int16))
+    chk_valid = int(buf.view(torch.int16).to(torch.int64).sum())
+    chk = 0
+    for b0 in range(0, 4096, 256):
+        chk += int(padded[b0:b0 + 256].view(torch.int16).to(torch.int64).sum())
+    assert chk == chk_valid + pad_bits * n_pad
+    offs = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(L, 0)])
+    for b in (0, 1, 17, 2048, 4095):
+        l = int(L[b])
+        src = buf[int(offs[b]) * 1024:(int(offs[b]) + l) * 1024].reshape(l, 1024)
+        assert torch.equal(padded[b, :l].view(torch.int16), src.view(torch.int16))
+        assert bool((padded[b, l:] == pad_value).all())
+    del padded, back
+    # mask
+    m = nt.to_mask(a, 2)
+    assert int(m.sum()) == T and bool((m.sum(1).cpu() == L).all())
+
+
+def test_big_index_path(native_libs, cuda_device):
+    """One padded entry above 2^30 elements takes the 64-bit division path of the kernels."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 6 * (1 << 30):
+        pytest.skip("needs 6 GB of free device memory")
+    big = (1 << 30) + 4096 + 3
+    x = torch.arange(big, device=cuda_device, dtype=torch.int32).to(torch.uint8)
+    y = x[:1000].clone()
+    a = nt.NestedTensor(torch.cat([x, y]), torch.tensor([[big], [1000]], dtype=torch.int64))
+    padded = a.to_padded_tensor(padding=9)
+    assert torch.equal(padded[0], x)
+    assert torch.equal(padded[1, :1000], y) and bool((padded[1, 1000:] == 9).all())
+    back = nt.from_padded_tensor(padded, a)
+    assert torch.equal(back._buffer, a._buffer)
