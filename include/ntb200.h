@@ -148,6 +148,63 @@ int ntb200_offsets_from_sizes(const int64_t* sizes, int64_t size_stride, int nd,
 int ntb200_token_index(const int64_t* token_offsets, int64_t batch, int64_t total_tokens,
                        int32_t* batch_idx, int32_t* word_idx, void* stream);
 
+
+/* ------------------------------------------------------------------ packed projection
+ * C[M,N] = A[M,K] * W[N,K]^T + bias[N] (bias may be NULL); all row-major, element type `dtype`,
+ * fp32 accumulation.  A is the packed token buffer [sum(L_i), K] of a nested tensor, so the
+ * grouped variable-length projection is a single GEMM.  fp16/bf16 with K % 8 == 0, N % 8 == 0 and
+ * 16-byte aligned pointers run on tcgen05/TMEM fed by TMA; other cases on a SIMT kernel
+ * (force_simt != 0 selects it explicitly, for cross-checks).
+ * Replaces NestedTensor_matmul's packed path (nestedtensor/csrc/matmul.cpp:12-45) and the bias add of
+ * NestedTensor_add_Tensor (nestedtensor/csrc/BinaryOps.cpp:97-107), i.e. steps 1 and 9 of bt_min_mha
+ * (nestedtensor/csrc/cuda/mha.cpp:57,106).
+ */
+int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, int64_t M, int64_t N,
+                     int64_t K, int dtype, int force_simt, void* stream);
+
+/* Bit mask of device-side wait time-outs recorded by the tcgen05 kernels since the last call
+ * (0 = none; bit 0 TMA producer, bit 1 MMA issuer, bit 2 epilogue); synchronises the device;
+ * negative on a CUDA error.  No counterpart in the reference. */
+int ntb200_device_error_flags(void);
+
+/* ------------------------------------------------------------------ varlen self-attention
+ * out[t, h*d:(h+1)*d] = softmax(scaling * Q_b,h K_b,h^T) V_b,h for token t of sequence b, reading
+ * q|k|v of token t from row t of the packed qkv buffer [total_tokens, 3*H*d] and attending only
+ * to the tokens of the same sequence; `offsets` are the ELEMENT offsets of the sequences in the
+ * [total_tokens, H*d] input (B+1 entries, multiples of H*d), max_len the longest sequence.
+ * Padded tokens are never materialised.  head_dim 64 in fp16/bf16 uses tensor cores.
+ * Replaces steps 2-8 of bt_min_mha (nestedtensor/csrc/cuda/mha.cpp:59-105) including
+ * softmax_kernel_kernelLauncher (nestedtensor/csrc/cuda/attention.h:25-33).
+ */
+int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, int64_t batch,
+                            int64_t total_tokens, int num_heads, int head_dim, int64_t max_len,
+                            float scaling, int dtype, int force_simt, void* stream);
+
+/* ------------------------------------------------------------------ reference-shaped helpers
+ * q/k/v_buf[b, h, l, :] = qkv[tok(b,l), {0,E,2E} + h*d + :] + bias  for valid tokens (padded
+ * positions are left untouched): bias add fused with packed -> padded head-major scatter.
+ * Replaces add_QKV_bias_padding_kernelLauncher (nestedtensor/csrc/cuda/attention.cu:107-174,
+ * attention.h:35-44).
+ */
+int ntb200_add_qkv_bias_pad(const void* qkv, const void* bias, void* q_buf, void* k_buf, void* v_buf,
+                            const int64_t* offsets, int64_t batch, int64_t total_tokens,
+                            int num_heads, int head_dim, int64_t max_len, int dtype, void* stream);
+
+/* dst[t, h*d + :] = src[b, h, l, :]: padded head-major -> packed token-major.
+ * Replaces transpose_rm_padding_kernelLauncher (nestedtensor/csrc/cuda/attention.cu:488-538,
+ * attention.h:46-52). */
+int ntb200_transpose_rm_padding(const void* src, void* dst, const int64_t* offsets, int64_t batch,
+                                int64_t total_tokens, int num_heads, int head_dim, int64_t max_len,
+                                int dtype, void* stream);
+
+/* In-place masked softmax over the last dim of padded scores [B, H, len_q, len_k] with the reference's
+ * arithmetic: logits*scaling + (1-mask)*-10000, row sum + 1e-6; mask[b,i,j] = i < len_b && j < len_b
+ * with len_b = (offsets[b+1]-offsets[b]) / row_elems.
+ * Replaces softmax_kernel_kernelLauncher (nestedtensor/csrc/cuda/attention.cu:182-482). */
+int ntb200_softmax_masked(void* scores, const int64_t* offsets, int64_t row_elems, int64_t batch,
+                          int num_heads, int64_t len_q, int64_t len_k, float scaling, int dtype,
+                          void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,6 +20,14 @@ from .sharding import token_balanced_partition
 
 __version__ = "0.1.0"
 
+# Register torch.ops.nestedtensor.* at import when the native libraries are built, like the reference's
+# `import nestedtensor` does.  If they are not, the first operator call raises with the build command.
+import os as _os
+from . import _build as _b, _ops as _o
+if _os.path.exists(_b.CABI_LIB) and _os.path.exists(_b.DISPATCH_LIB):
+    _o.load()
+del _os, _b, _o
+
 
 def is_nested_tensor(obj):
     return isinstance(obj, NestedTensor)

@@ -67,7 +67,7 @@ def build_cabi(force: bool = False, verbose: bool = False) -> str:
             _run([_nvcc(), "-O3", "-std=c++17", *NVCC_ARCH, "-lineinfo", "-Xcompiler", "-fPIC",
                   "-Xptxas", "-v" if verbose else "-warn-spills",
                   "-I", INCLUDE_DIR, "-I", CSRC_DIR, "-c", cu, "-o", obj], verbose)
-    _run([_nvcc(), "-shared", *NVCC_ARCH, "-o", CABI_LIB, *objs, "-lcuda"], verbose)
+    _run([_nvcc(), "-shared", *NVCC_ARCH, "-o", CABI_LIB, *objs], verbose)
     return CABI_LIB
 
 

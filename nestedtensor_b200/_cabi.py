@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_uint64, c_void_p, c_double
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_uint64, c_void_p
 
 from . import _build
 
@@ -32,7 +32,20 @@ SIGNATURES = {
     "ntb200_offsets_from_sizes": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                           c_size_t, c_void_p]),
     "ntb200_token_index": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "ntb200_gemm_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
+                                 c_void_p]),
+    "ntb200_device_error_flags": (c_int, []),
+    "ntb200_varlen_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int64,
+                                        c_float, c_int, c_int, c_void_p]),
+    "ntb200_add_qkv_bias_pad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                        c_int, c_int, c_int64, c_int, c_void_p]),
+    "ntb200_transpose_rm_padding": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int64,
+                                            c_int, c_void_p]),
+    "ntb200_softmax_masked": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int64, c_float, c_int,
+                                      c_void_p]),
 }
+
+DTYPE_CODES = {"float32": 0, "float16": 1, "bfloat16": 2}
 
 
 def lib_path() -> str:

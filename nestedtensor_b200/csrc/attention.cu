@@ -1,0 +1,524 @@
+// Variable-length self-attention on the packed QKV buffer of a nested tensor, and the standalone
+// B200 equivalents of the reference's attention helper kernels.
+//
+//   qkv   [T, 3E]  token-major, row t = (q | k | v) of token t, heads contiguous inside each third
+//   out   [T, E]   token-major: softmax(scale * Q_b K_b^T) V_b for every sequence b and head h
+//
+// Padded tokens never exist: a CTA works on one (sequence, head, 64-query tile) and walks only that
+// sequence's keys, so the "transpose + remove padding" step of the reference
+// (transpose_rm_padding, nestedtensor/csrc/cuda/attention.cu:488-530) is the kernel's own store.
+// Replaces steps 2-8 of bt_min_mha (nestedtensor/csrc/cuda/mha.cpp:59-105): pad to (B, maxL, 3E),
+// padded batched QK^T, host-built mask, masked softmax kernel (attention.cu:182-482), padded PV, unpad.
+//
+// Paths: head_dim 64 in fp16/bf16 -> tensor-core flash kernel (mma.sync m16n8k16, fp32 online softmax);
+// anything else (fp32, other head sizes) -> a warp-per-(token, head) SIMT kernel with fp32 math.
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace ntb200 {
+namespace {
+
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// largest b in [0, batch) with offsets[b] <= e
+__device__ __forceinline__ int64_t find_entry(const int64_t* __restrict__ offsets, int64_t batch, int64_t e) {
+  int64_t lo = 0, hi = batch - 1;
+  while (lo < hi) {
+    const int64_t mid = (lo + hi + 1) >> 1;
+    if (offsets[mid] <= e) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+// ------------------------------------------------------------------ generic SIMT attention
+constexpr int kSimtWarps = 8;
+constexpr int kMaxHeadDim = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
+                                                                    const int64_t* __restrict__ offsets, int64_t batch,
+                                                                    int64_t total_tokens, int H, int d, float scale) {
+  __shared__ float s_q[kSimtWarps][kMaxHeadDim];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t wg = (int64_t)blockIdx.x * kSimtWarps + warp;
+  if (wg >= total_tokens * H) return;
+  const int64_t t = wg / H;
+  const int h = (int)(wg % H);
+  const int64_t E = (int64_t)H * d;
+  const int64_t b = find_entry(offsets, batch, t * E);
+  const int64_t tok0 = offsets[b] / E;
+  const int L = (int)((offsets[b + 1] - offsets[b]) / E);
+  const T* qrow = qkv + t * 3 * E + (int64_t)h * d;
+  for (int i = lane; i < d; i += 32) s_q[warp][i] = Cvt<T>::to_f(qrow[i]) * scale;
+  __syncwarp();
+  const T* kbase = qkv + tok0 * 3 * E + E + (int64_t)h * d;
+  const T* vbase = kbase + E;
+  constexpr int DPL = kMaxHeadDim / 32;
+  float acc[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
+  float m = -INFINITY, l = 0.0f;
+  for (int c0 = 0; c0 < L; c0 += 32) {
+    const int j = c0 + lane;
+    float s = -INFINITY;
+    if (j < L) {
+      const T* krow = kbase + (int64_t)j * 3 * E;
+      float dot = 0.0f;
+      for (int i = 0; i < d; ++i) dot = fmaf(s_q[warp][i], Cvt<T>::to_f(krow[i]), dot);
+      s = dot;
+    }
+    float cm = s;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+    const float m_new = fmaxf(m, cm);
+    const float corr = __expf(m - m_new);  // 0 on the first chunk (m = -inf)
+    const float p = (j < L) ? __expf(s - m_new) : 0.0f;
+    float ps = p;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+    l = l * corr + ps;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] *= corr;
+    const int nj = (L - c0) < 32 ? (L - c0) : 32;
+    for (int jj = 0; jj < nj; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const T* vrow = vbase + (int64_t)(c0 + jj) * 3 * E;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        const int dim = lane + 32 * i;
+        if (dim < d) acc[i] = fmaf(pj, Cvt<T>::to_f(vrow[dim]), acc[i]);
+      }
+    }
+    m = m_new;
+  }
+  const float inv = 1.0f / l;
+  T* orow = out + t * E + (int64_t)h * d;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) {
+    const int dim = lane + 32 * i;
+    if (dim < d) orow[dim] = Cvt<T>::from_f(acc[i] * inv);
+  }
+}
+
+// ------------------------------------------------------- tensor-core flash kernel, head_dim 64
+constexpr int kBQ = 64, kBKV = 64, kD = 64, kFaThreads = 128;
+
+template <typename T>
+struct MmaOp;
+template <>
+struct MmaOp<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float x, float y) {
+    __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+};
+template <>
+struct MmaOp<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float x, float y) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// byte offset of 16-byte chunk `c` of row `r` in a [rows][64] two-byte tile (128-byte rows, XOR swizzle)
+__device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+// copy rows [row0, row0+64) (clamped to last_row) x 64 columns of one head from global into a swizzled tile
+template <typename T>
+__device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const T* __restrict__ gbase, int64_t ld, int row0,
+                                                int last_row) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = threadIdx.x + i * kFaThreads;  // 512 chunks
+    const int r = idx >> 3, c = idx & 7;
+    int gr = row0 + r;
+    gr = gr > last_row ? last_row : gr;
+    cp_async_16(smem_tile + tile_off(r, c), gbase + (int64_t)gr * ld + c * 8);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kFaThreads) attn_fa_d64_kernel(const T* __restrict__ qkv, T* __restrict__ out,
+                                                                  const int64_t* __restrict__ offsets, int H,
+                                                                  float scale_log2e) {
+  __shared__ __align__(128) uint8_t s_q[kBQ * kD * 2];
+  __shared__ __align__(128) uint8_t s_k[2][kBKV * kD * 2];
+  __shared__ __align__(128) uint8_t s_v[2][kBKV * kD * 2];
+
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int64_t E = (int64_t)H * kD;
+  const int64_t off_b = offsets[b];
+  const int L = (int)((offsets[b + 1] - off_b) / E);
+  const int q0 = blockIdx.x * kBQ;
+  if (q0 >= L) return;
+  const int64_t tok0 = off_b / E;
+  const int64_t ld = 3 * E;
+  const T* qbase = qkv + tok0 * ld + (int64_t)h * kD;
+  const T* kbase = qbase + E;
+  const T* vbase = kbase + E;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t sq = (uint32_t)__cvta_generic_to_shared(s_q);
+  const uint32_t sk = (uint32_t)__cvta_generic_to_shared(s_k);
+  const uint32_t sv = (uint32_t)__cvta_generic_to_shared(s_v);
+  constexpr uint32_t kTileBytes = kBKV * kD * 2;
+
+  const int n_kv = (L + kBKV - 1) / kBKV;
+  load_tile_async<T>(sq, qbase, ld, q0, L - 1);
+  load_tile_async<T>(sk, kbase, ld, 0, L - 1);
+  load_tile_async<T>(sv, vbase, ld, 0, L - 1);
+  cp_async_commit();
+
+  uint32_t qf[4][4];  // Q fragments: 4 k-steps of 16 head dims
+  float o[8][4];      // O accumulator: 8 n-tiles of 8 head dims
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // rows g and g+8 of this warp's 16
+
+  for (int it = 0; it < n_kv; ++it) {
+    const int buf = it & 1;
+    if (it + 1 < n_kv) {
+      load_tile_async<T>(sk + (buf ^ 1) * kTileBytes, kbase, ld, (it + 1) * kBKV, L - 1);
+      load_tile_async<T>(sv + (buf ^ 1) * kTileBytes, vbase, ld, (it + 1) * kBKV, L - 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        ldmatrix_x4(qf[ks], sq + tile_off(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+    }
+    // S = Q K^T for this warp's 16 rows x 64 keys
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
+    const uint32_t kt = sk + buf * kTileBytes, vt = sv + buf * kTileBytes;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {  // pairs of key n-tiles
+        uint32_t kf[4];
+        ldmatrix_x4(kf, kt + tile_off(np * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+        MmaOp<T>::mma(s[np * 2], qf[ks], kf[0], kf[1]);
+        MmaOp<T>::mma(s[np * 2 + 1], qf[ks], kf[2], kf[3]);
+      }
+    }
+    // mask keys beyond the sequence (only the last tile can have any)
+    const int kv0 = it * kBKV;
+    if (kv0 + kBKV > L) {
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int key = kv0 + nt * 8 + 2 * (lane & 3);
+        if (key >= L) s[nt][0] = s[nt][2] = -INFINITY;
+        if (key + 1 >= L) s[nt][1] = s[nt][3] = -INFINITY;
+      }
+    }
+    // online softmax in the exp2 domain
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0 * scale_log2e), mn1 = fmaxf(m1, mx1 * scale_log2e);
+    const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+    float rs0 = 0.0f, rs1 = 0.0f;
+    uint32_t pf[4][4];  // P as A fragments: 4 k-steps of 16 keys
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float p0 = exp2f(fmaf(s[nt][0], scale_log2e, -mn0));
+      const float p1 = exp2f(fmaf(s[nt][1], scale_log2e, -mn0));
+      const float p2 = exp2f(fmaf(s[nt][2], scale_log2e, -mn1));
+      const float p3 = exp2f(fmaf(s[nt][3], scale_log2e, -mn1));
+      rs0 += p0 + p1;
+      rs1 += p2 + p3;
+      pf[nt >> 1][(nt & 1) * 2] = MmaOp<T>::pack(p0, p1);
+      pf[nt >> 1][(nt & 1) * 2 + 1] = MmaOp<T>::pack(p2, p3);
+    }
+    l0 = l0 * c0 + rs0;
+    l1 = l1 * c1 + rs1;
+    m0 = mn0;
+    m1 = mn1;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      o[nt][0] *= c0;
+      o[nt][1] *= c0;
+      o[nt][2] *= c1;
+      o[nt][3] *= c1;
+    }
+    // O += P V
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {  // pairs of head-dim n-tiles
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, vt + tile_off(ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
+        MmaOp<T>::mma(o[np * 2], pf[ks], vf[0], vf[1]);
+        MmaOp<T>::mma(o[np * 2 + 1], pf[ks], vf[2], vf[3]);
+      }
+    }
+    __syncthreads();  // everyone is done with this K/V buffer before it is refilled
+  }
+
+  // finish the row sums across the quad, normalise, store token-major
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+  const int r0 = q0 + warp * 16 + (lane >> 2), r1 = r0 + 8;
+  uint32_t* obase = reinterpret_cast<uint32_t*>(out + (tok0 + r0) * E + (int64_t)h * kD);
+  uint32_t* obase1 = reinterpret_cast<uint32_t*>(out + (tok0 + r1) * E + (int64_t)h * kD);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    const int col2 = nt * 4 + (lane & 3);  // index in 32-bit pairs
+    if (r0 < L) obase[col2] = MmaOp<T>::pack(o[nt][0] * i0, o[nt][1] * i0);
+    if (r1 < L) obase1[col2] = MmaOp<T>::pack(o[nt][2] * i1, o[nt][3] * i1);
+  }
+}
+
+// ---------------------------------------------------- packed QKV + bias -> padded head-major
+// q/k/v_buf[b, h, l, :] = qkv[tok, {0,E,2E} + h*d + :] + bias, zero elsewhere is NOT written (the caller
+// zero-fills if it needs it, as the reference's caller would).  One warp per (token, head, third).
+template <typename T>
+__global__ void __launch_bounds__(256) add_qkv_bias_pad_kernel(const T* __restrict__ qkv, const T* __restrict__ bias,
+                                                               T* __restrict__ q_buf, T* __restrict__ k_buf,
+                                                               T* __restrict__ v_buf, const int64_t* __restrict__ offsets,
+                                                               int64_t batch, int64_t total_tokens, int H, int d,
+                                                               int64_t max_len) {
+  const int64_t E = (int64_t)H * d;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // over T * 3E
+  if (idx >= total_tokens * 3 * E) return;
+  const int64_t t = idx / (3 * E);
+  const int64_t c = idx - t * 3 * E;
+  const int which = (int)(c / E);
+  const int64_t e = c - which * E;
+  const int h = (int)(e / d), i = (int)(e - (int64_t)h * d);
+  const int64_t b = find_entry(offsets, batch, t * E);
+  const int64_t l = t - offsets[b] / E;
+  T* dst = which == 0 ? q_buf : (which == 1 ? k_buf : v_buf);
+  const float v = Cvt<T>::to_f(qkv[idx]) + (bias != nullptr ? Cvt<T>::to_f(bias[c]) : 0.0f);
+  dst[((b * H + h) * max_len + l) * d + i] = Cvt<T>::from_f(v);
+}
+
+// padded head-major [B, H, maxL, d] -> packed token-major [T, H*d]
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_rm_padding_kernel(const T* __restrict__ src, T* __restrict__ dst,
+                                                                   const int64_t* __restrict__ offsets, int64_t batch,
+                                                                   int64_t total_tokens, int H, int d, int64_t max_len) {
+  const int64_t E = (int64_t)H * d;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // over T * E
+  if (idx >= total_tokens * E) return;
+  const int64_t t = idx / E;
+  const int64_t e = idx - t * E;
+  const int h = (int)(e / d), i = (int)(e - (int64_t)h * d);
+  const int64_t b = find_entry(offsets, batch, t * E);
+  const int64_t l = t - offsets[b] / E;
+  dst[idx] = src[((b * H + h) * max_len + l) * d + i];
+}
+
+// ---------------------------------------------------- masked softmax on padded scores
+// In place over the last dim of scores [B, H, Lq, Lk]; the valid region of batch b is lens[b] x lens[b].
+// Same arithmetic as the reference (attention.cu:182-225): masked logits get -10000 added, the row sum
+// gets 1e-6.  One warp per row.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_masked_kernel(T* __restrict__ scores, const int64_t* __restrict__ offsets,
+                                                             int64_t row_elems, int64_t rows_total, int H, int Lq, int Lk,
+                                                             float scale) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= rows_total) return;
+  const int64_t b = row / ((int64_t)H * Lq);
+  const int qi = (int)(row % Lq);
+  const int len = (int)((offsets[b + 1] - offsets[b]) / row_elems);
+  T* p = scores + row * Lk;
+  const bool qvalid = qi < len;
+  float mx = -1e20f;
+  for (int j = lane; j < Lk; j += 32) {
+    const float mask = (qvalid && j < len) ? 1.0f : 0.0f;
+    const float v = Cvt<T>::to_f(p[j]) * scale + (1.0f - mask) * -10000.0f;
+    mx = fmaxf(mx, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.0f;
+  for (int j = lane; j < Lk; j += 32) {
+    const float mask = (qvalid && j < len) ? 1.0f : 0.0f;
+    const float v = Cvt<T>::to_f(p[j]) * scale + (1.0f - mask) * -10000.0f;
+    sum += __expf(v - mx);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.0f / (sum + 1e-6f);
+  for (int j = lane; j < Lk; j += 32) {
+    const float mask = (qvalid && j < len) ? 1.0f : 0.0f;
+    const float v = Cvt<T>::to_f(p[j]) * scale + (1.0f - mask) * -10000.0f;
+    p[j] = Cvt<T>::from_f(__expf(v - mx) * inv);
+  }
+}
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T>
+int launch_attn_simt(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t T_tokens, int H, int d,
+                     float scale, cudaStream_t st) {
+  const int64_t blocks = ceil_div(T_tokens * H, kSimtWarps);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  attn_simt_kernel<T><<<(unsigned)blocks, kSimtWarps * 32, 0, st>>>(static_cast<const T*>(qkv), static_cast<T*>(out), offsets,
+                                                                    batch, T_tokens, H, d, scale);
+  return status_from_cuda(cudaGetLastError());
+}
+
+template <typename T>
+int launch_attn_fa(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int H, int64_t max_len, float scale,
+                   cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div(max_len, kBQ), (unsigned)H, (unsigned)batch);
+  attn_fa_d64_kernel<T><<<grid, kFaThreads, 0, st>>>(static_cast<const T*>(qkv), static_cast<T*>(out), offsets, H,
+                                                     scale * 1.4426950408889634f);
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace ntb200
+
+using namespace ntb200;
+
+extern "C" {
+
+int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens,
+                            int num_heads, int head_dim, int64_t max_len, float scaling, int dtype, int force_simt,
+                            void* stream) {
+  if (batch < 0 || total_tokens < 0 || num_heads < 1 || head_dim < 1 || max_len < 0) return NTB200_INVALID_ARG;
+  if (dtype != NTB200_F32 && dtype != NTB200_F16 && dtype != NTB200_BF16) return NTB200_UNSUPPORTED_DTYPE;
+  if (head_dim > kMaxHeadDim) return NTB200_UNSUPPORTED_SHAPE;
+  if (batch == 0 || total_tokens == 0) return NTB200_OK;
+  if (qkv == nullptr || out == nullptr || offsets == nullptr) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fa = !force_simt && dtype != NTB200_F32 && head_dim == kD && aligned16(qkv) && aligned16(out) && batch <= 65535 &&
+                  num_heads <= 65535 && max_len > 0;
+  if (fa) {
+    if (dtype == NTB200_F16) return launch_attn_fa<__half>(qkv, out, offsets, batch, num_heads, max_len, scaling, st);
+    return launch_attn_fa<__nv_bfloat16>(qkv, out, offsets, batch, num_heads, max_len, scaling, st);
+  }
+  switch (dtype) {
+    case NTB200_F32: return launch_attn_simt<float>(qkv, out, offsets, batch, total_tokens, num_heads, head_dim, scaling, st);
+    case NTB200_F16: return launch_attn_simt<__half>(qkv, out, offsets, batch, total_tokens, num_heads, head_dim, scaling, st);
+    case NTB200_BF16:
+      return launch_attn_simt<__nv_bfloat16>(qkv, out, offsets, batch, total_tokens, num_heads, head_dim, scaling, st);
+  }
+  return NTB200_UNSUPPORTED_DTYPE;
+}
+
+#define NTB200_DISPATCH_DTYPE(dtype, CALL)                 \
+  switch (dtype) {                                         \
+    case NTB200_F32: { using T = float; CALL; } break;     \
+    case NTB200_F16: { using T = __half; CALL; } break;    \
+    case NTB200_BF16: { using T = __nv_bfloat16; CALL; } break; \
+    default: return NTB200_UNSUPPORTED_DTYPE;              \
+  }
+
+int ntb200_add_qkv_bias_pad(const void* qkv, const void* bias, void* q_buf, void* k_buf, void* v_buf, const int64_t* offsets,
+                            int64_t batch, int64_t total_tokens, int num_heads, int head_dim, int64_t max_len, int dtype,
+                            void* stream) {
+  if (batch < 0 || total_tokens < 0 || num_heads < 1 || head_dim < 1 || max_len < 0) return NTB200_INVALID_ARG;
+  if (batch == 0 || total_tokens == 0) return NTB200_OK;
+  if (qkv == nullptr || q_buf == nullptr || k_buf == nullptr || v_buf == nullptr || offsets == nullptr) return NTB200_INVALID_ARG;
+  const int64_t n = total_tokens * 3 * num_heads * head_dim;
+  const int64_t blocks = ceil_div(n, 256);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  NTB200_DISPATCH_DTYPE(dtype, (add_qkv_bias_pad_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(
+                                   static_cast<const T*>(qkv), static_cast<const T*>(bias), static_cast<T*>(q_buf),
+                                   static_cast<T*>(k_buf), static_cast<T*>(v_buf), offsets, batch, total_tokens, num_heads,
+                                   head_dim, max_len)));
+  return status_from_cuda(cudaGetLastError());
+}
+
+int ntb200_transpose_rm_padding(const void* src, void* dst, const int64_t* offsets, int64_t batch, int64_t total_tokens,
+                                int num_heads, int head_dim, int64_t max_len, int dtype, void* stream) {
+  if (batch < 0 || total_tokens < 0 || num_heads < 1 || head_dim < 1 || max_len < 0) return NTB200_INVALID_ARG;
+  if (batch == 0 || total_tokens == 0) return NTB200_OK;
+  if (src == nullptr || dst == nullptr || offsets == nullptr) return NTB200_INVALID_ARG;
+  const int64_t n = total_tokens * num_heads * head_dim;
+  const int64_t blocks = ceil_div(n, 256);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  NTB200_DISPATCH_DTYPE(dtype, (transpose_rm_padding_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(
+                                   static_cast<const T*>(src), static_cast<T*>(dst), offsets, batch, total_tokens, num_heads,
+                                   head_dim, max_len)));
+  return status_from_cuda(cudaGetLastError());
+}
+
+int ntb200_softmax_masked(void* scores, const int64_t* offsets, int64_t row_elems, int64_t batch, int num_heads,
+                          int64_t len_q, int64_t len_k, float scaling, int dtype, void* stream) {
+  if (batch < 0 || num_heads < 1 || len_q < 0 || len_k < 0 || row_elems < 1) return NTB200_INVALID_ARG;
+  if (batch == 0 || len_q == 0 || len_k == 0) return NTB200_OK;
+  if (scores == nullptr || offsets == nullptr) return NTB200_INVALID_ARG;
+  if (len_q > 0x7fffffffll || len_k > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  const int64_t rows = batch * num_heads * len_q;
+  const int64_t blocks = ceil_div(rows, 8);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  NTB200_DISPATCH_DTYPE(dtype, (softmax_masked_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(
+                                   static_cast<T*>(scores), offsets, row_elems, rows, num_heads, (int)len_q, (int)len_k,
+                                   scaling)));
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // extern "C"

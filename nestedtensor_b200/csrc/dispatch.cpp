@@ -405,6 +405,65 @@ std::tuple<Tensor, Tensor> token_index(const Tensor& token_offsets, int64_t tota
   return std::make_tuple(bi, wi);
 }
 
+// ------------------------------------------------------------------ self-attention
+int dtype_code(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return NTB200_F32;
+    case at::kHalf: return NTB200_F16;
+    case at::kBFloat16: return NTB200_BF16;
+    default: TORCH_CHECK(false, "nestedtensor_b200: attention supports float32, float16 and bfloat16, got ", t);
+  }
+}
+
+// bt_min_mha (nestedtensor/csrc/cuda/mha.cpp:22-107) on the packed token buffer:
+//   qkv = x W_in^T + b_in   ->  varlen softmax(scaling * q k^T) v per sequence and head  ->  out W_out^T + b_out
+// Dropout arguments are accepted and ignored exactly as in the reference (inference path).  Unlike the
+// reference (mha.cpp:106) the output projection bias IS added, as in min_mha (nestedtensor/csrc/mha.cpp:66-67).
+Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, bool /*training*/, const Tensor& buffer,
+                  const Tensor& sizes, const Tensor& meta, const Tensor& attr_kernel, const Tensor& attr_bias,
+                  double scaling, const Tensor& out_proj_weight, const c10::optional<Tensor>& out_proj_bias) {
+  Record r = make_record(sizes, meta);
+  TORCH_CHECK(r.tdim == 2, "query needs to be 3 dim.");
+  check_buffer(buffer, r, "bt_min_mha");
+  const int64_t E = num_heads * head_dim;
+  TORCH_CHECK(r.B == 0 || (r.regular[1] && r.max_sizes[1] == E), "query's third dimension must be regular.");
+  TORCH_CHECK(num_heads >= 1 && head_dim >= 1 && head_dim <= 256, "nestedtensor_b200: head_dim must be in [1, 256]");
+  const int dt = dtype_code(buffer.scalar_type());
+  auto same = [&](const Tensor& w, const char* name) {
+    TORCH_CHECK(w.is_cuda() && w.device() == buffer.device() && w.scalar_type() == buffer.scalar_type(),
+                "nestedtensor_b200: ", name, " must be on the input's device and of its dtype");
+  };
+  same(attr_kernel, "in_proj_weight");
+  same(attr_bias, "in_proj_bias");
+  same(out_proj_weight, "out_proj_weight");
+  TORCH_CHECK(attr_kernel.dim() == 2 && attr_kernel.size(0) == 3 * E && attr_kernel.size(1) == E, "in_proj_weight must be [3E, E]");
+  TORCH_CHECK(attr_bias.numel() == 3 * E, "in_proj_bias must have 3E entries");
+  TORCH_CHECK(out_proj_weight.dim() == 2 && out_proj_weight.size(0) == E && out_proj_weight.size(1) == E, "out_proj_weight must be [E, E]");
+  c10::cuda::CUDAGuard guard(buffer.device());
+  const int64_t T = r.numel / (E > 0 ? E : 1);
+  Tensor out = at::empty({T * E}, buffer.options());
+  if (T == 0) return out;
+  Tensor w_in = attr_kernel.contiguous(), b_in = attr_bias.contiguous(), w_out = out_proj_weight.contiguous();
+  const void* b_out = nullptr;
+  Tensor b_out_t;
+  if (out_proj_bias && out_proj_bias->defined()) {
+    same(*out_proj_bias, "out_proj_bias");
+    TORCH_CHECK(out_proj_bias->numel() == E, "out_proj_bias must have E entries");
+    b_out_t = out_proj_bias->contiguous();
+    b_out = b_out_t.data_ptr();
+  }
+  Tensor qkv = at::empty({T, 3 * E}, buffer.options());
+  Tensor attn = at::empty({T, E}, buffer.options());
+  void* st = cur_stream();
+  check_rc(ntb200_gemm_bias(buffer.data_ptr(), w_in.data_ptr(), b_in.data_ptr(), qkv.data_ptr(), T, 3 * E, E, dt, 0, st),
+           "ntb200_gemm_bias");
+  check_rc(ntb200_varlen_attention(qkv.data_ptr(), attn.data_ptr(), r.d_offsets, r.B, T, (int)num_heads, (int)head_dim,
+                                   r.max_sizes[0], (float)scaling, dt, 0, st),
+           "ntb200_varlen_attention");
+  check_rc(ntb200_gemm_bias(attn.data_ptr(), w_out.data_ptr(), b_out, out.data_ptr(), T, E, E, dt, 0, st), "ntb200_gemm_bias");
+  return out;
+}
+
 }  // namespace
 
 // The operator names follow the reference's `nestedtensor` namespace
@@ -419,4 +478,8 @@ TORCH_LIBRARY(nestedtensor, m) {
   m.def("sizes_from_mask(Tensor mask) -> (Tensor, Tensor)", &sizes_from_mask);
   m.def("meta_from_device_sizes(Tensor sizes) -> Tensor", &meta_from_device_sizes);
   m.def("token_index(Tensor token_offsets, int total_tokens) -> (Tensor, Tensor)", &token_index);
+  m.def(
+      "bt_min_mha(int num_heads, int head_dim, float dropout_p, bool training, Tensor buffer, Tensor sizes, Tensor meta, "
+      "Tensor attr_kernel, Tensor attr_bias, float scaling, Tensor out_proj_weight, Tensor? out_proj_bias) -> Tensor",
+      &bt_min_mha);
 }

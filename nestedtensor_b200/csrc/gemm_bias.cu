@@ -1,0 +1,419 @@
+// C[M,N] = A[M,K] * W[N,K]^T + bias[N] on the packed token buffer of a nested tensor: the QKV and
+// output projections of self-attention.  Tokens of all sequences are contiguous, so the "grouped
+// varlen" projection is one M = sum(L_i) GEMM whose last row tile is predicated.
+//
+// Two code paths in one backend:
+//   * fp16 / bf16, K % 8 == 0, N % 8 == 0: persistent warp-specialised tcgen05 kernel — TMA (128-byte
+//     swizzle, no multicast) feeds a 4-stage shared-memory ring, one thread issues
+//     tcgen05.mma.cta_group::1 (128 x 256 x 16) into two 256-column TMEM accumulators, four epilogue warps
+//     drain one accumulator (tcgen05.ld), add the bias and store while the other is being filled;
+//   * everything else (fp32, odd shapes): a tiled SIMT kernel with fp32 accumulation.
+// Replaces NestedTensor_matmul's packed fast path (nestedtensor/csrc/matmul.cpp:12-45, one cuBLAS GEMM)
+// plus the separate bias pass of NestedTensor_add_Tensor (nestedtensor/csrc/BinaryOps.cpp:97-107).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ntb200 {
+namespace {
+
+// Set by a kernel whose bounded wait ran out (bit 0: producer, 1: MMA issuer, 2: epilogue).
+__device__ int g_gemm_error = 0;
+
+// ------------------------------------------------------------------------ tcgen05 path
+constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;            // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;    // 48 KB
+constexpr int kAccCols = kBN;                     // fp32 accumulator columns per stage
+constexpr int kTmemCols = 2 * kAccCols;           // 512: the whole TMEM, two accumulator stages
+constexpr int kGemmThreads = 192;                 // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kCtrlBytes = 256 + kBN * 4;         // barriers + tmem slot + abort flag, bias tile
+constexpr int kGemmSmem = 1024 + kStages * kStageBytes + kCtrlBytes;
+
+struct Ctrl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint64_t done;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+static_assert(sizeof(Ctrl) <= 256, "control block");
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = ptx::globaltimer_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+      if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) return false;
+  }
+}
+
+template <int FMT>
+struct OutPack;
+template <>
+struct OutPack<0> {  // fp16
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float load(const void* p, int i) { return __half2float(reinterpret_cast<const __half*>(p)[i]); }
+};
+template <>
+struct OutPack<1> {  // bf16
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float load(const void* p, int i) {
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  }
+};
+
+template <int FMT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const void* __restrict__ bias, void* __restrict__ C, int M, int N, int K) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kStages * kStageBytes);
+  float* s_bias = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (M + kBM - 1) / kBM, num_n = (N + kBN - 1) / kBN, num_k = (K + kBK - 1) / kBK;
+  const int num_tiles = num_m * num_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tfull[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tempty[a]), 4);
+    }
+    ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
+    ctrl->abort = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctrl->tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+    ptx::tc_fence_before_sync();
+  }
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const uint32_t smem_base = ptx::smem_u32(smem);
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / num_n) * kBM, n0 = (tile % num_n) * kBN;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->empty[s]), ph ^ 1, &ctrl->abort)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&ctrl->full[s]);
+          ptx::mbar_arrive_expect_tx(full, kStageBytes);
+          ptx::tma_load_2d(smem_base + s * kStageBytes, &map_a, full, kb * kBK, m0);
+          ptx::tma_load_2d(smem_base + s * kStageBytes + kABytes, &map_w, full, kb * kBK, n0);
+        }
+      }
+      if (!ok) {
+        ctrl->abort = 1;
+        atomicOr(&g_gemm_error, 1);
+      }
+      // drain: every load issued must have landed before this CTA's shared memory is released
+      const uint32_t first = it > (uint32_t)kStages ? it - kStages : 0;
+      for (uint32_t i = first; i < it; ++i)
+        ptx::mbar_wait(ptx::smem_u32(&ctrl->full[i % kStages]), (i / kStages) & 1);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc_f16(FMT, kBM, kBN);
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1;
+        if (!wait_or_abort(ptx::smem_u32(&ctrl->tempty[acc]), ((tile_iter >> 1) & 1) ^ 1, &ctrl->abort)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kAccCols;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->full[s]), ph, &ctrl->abort)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + s * kStageBytes, b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            ptx::umma_f16(d_tmem, ptx::umma_desc_kmajor_sw128(a_addr + k * 32), ptx::umma_desc_kmajor_sw128(b_addr + k * 32),
+                          idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(ptx::smem_u32(&ctrl->empty[s]));  // frees the stage when these MMAs retire
+        }
+        if (ok) ptx::umma_commit(ptx::smem_u32(&ctrl->tfull[acc]));
+      }
+      if (!ok) {
+        ctrl->abort = 1;
+        atomicOr(&g_gemm_error, 2);
+      }
+      // all MMAs must have retired before TMEM is freed
+      ptx::umma_commit(ptx::smem_u32(&ctrl->done));
+      ptx::mbar_wait(ptx::smem_u32(&ctrl->done), 0);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (128 threads)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int et = threadIdx.x - 64;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
+      const int m0 = (tile / num_n) * kBM, n0 = (tile % num_n) * kBN;
+      const uint32_t acc = tile_iter & 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // previous tile's bias reads are done
+      for (int i = et; i < kBN; i += 128) {
+        const int n = n0 + i;
+        s_bias[i] = (bias != nullptr && n < N) ? OutPack<FMT>::load(bias, n) : 0.0f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
+      if (!ok) continue;  // keep taking the named barriers with the other epilogue warps
+      ptx::tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
+#pragma unroll 1
+      for (int c = 0; c < kBN; c += 32) {
+        if (n0 + c >= N) break;
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + acc * kAccCols + c + ((uint32_t)(q * 32) << 16), r);
+        ptx::tmem_ld_wait();
+        if (row < M) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {  // 8 columns = 16 bytes per store
+            if (n0 + c + g * 8 < N) {
+              uint4 v;
+              v.x = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 0]) + s_bias[c + g * 8 + 0],
+                                       __uint_as_float(r[g * 8 + 1]) + s_bias[c + g * 8 + 1]);
+              v.y = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 2]) + s_bias[c + g * 8 + 2],
+                                       __uint_as_float(r[g * 8 + 3]) + s_bias[c + g * 8 + 3]);
+              v.z = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 4]) + s_bias[c + g * 8 + 4],
+                                       __uint_as_float(r[g * 8 + 5]) + s_bias[c + g * 8 + 5]);
+              v.w = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 6]) + s_bias[c + g * 8 + 6],
+                                       __uint_as_float(r[g * 8 + 7]) + s_bias[c + g * 8 + 7]);
+              *reinterpret_cast<uint4*>(crow + c + g * 8) = v;
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->tempty[acc]));
+    }
+    if (!ok && lane == 0) {
+      ctrl->abort = 1;
+      atomicOr(&g_gemm_error, 4);
+    }
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// row-major [rows, cols] two-byte matrix, box = box_rows x 64 columns, 128-byte swizzle, zero fill
+bool make_map_2d(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t gdim[2] = {cols, rows};
+  const cuuint64_t gstride[1] = {cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == NTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(map, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int FMT>
+int launch_tcgen05(const void* A, const void* W, const void* bias, void* C, int M, int N, int K, int dtype, cudaStream_t st) {
+  CUtensorMap map_a, map_w;
+  if (!make_map_2d(&map_a, A, dtype, (uint64_t)M, (uint64_t)K, kBM)) return NTB200_LAUNCH_FAILED;
+  if (!make_map_2d(&map_w, W, dtype, (uint64_t)N, (uint64_t)K, kBN)) return NTB200_LAUNCH_FAILED;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_bias_tcgen05_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
+      return NTB200_LAUNCH_FAILED;
+    attr_set = true;
+  }
+  const int num_tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+  int dev = 0, sms = kNumSMs;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = num_tiles < sms ? num_tiles : sms;
+  gemm_bias_tcgen05_kernel<FMT><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_w, bias, C, M, N, K);
+  return status_from_cuda(cudaGetLastError());
+}
+
+// --------------------------------------------------------------------------- SIMT path
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+constexpr int kSimtTile = 64, kSimtK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_bias_simt_kernel(const T* __restrict__ A, const T* __restrict__ W,
+                                                             const T* __restrict__ bias, T* __restrict__ C, int64_t M,
+                                                             int64_t N, int64_t K) {
+  __shared__ float sA[kSimtK][kSimtTile + 1];
+  __shared__ float sW[kSimtK][kSimtTile + 1];
+  const int64_t m0 = (int64_t)blockIdx.y * kSimtTile, n0 = (int64_t)blockIdx.x * kSimtTile;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int64_t k0 = 0; k0 < K; k0 += kSimtK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      const int r = idx >> 4, kk = idx & 15;
+      const int64_t k = k0 + kk;
+      sA[kk][r] = (m0 + r < M && k < K) ? Cvt<T>::to_f(A[(m0 + r) * K + k]) : 0.0f;
+      sW[kk][r] = (n0 + r < N && k < K) ? Cvt<T>::to_f(W[(n0 + r) * K + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kSimtK; ++kk) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = sA[kk][ty * 4 + i];
+        w[i] = sW[kk][tx * 4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t n = n0 + tx * 4 + j;
+      if (n < N) C[m * N + n] = Cvt<T>::from_f(acc[i][j] + (bias != nullptr ? Cvt<T>::to_f(bias[n]) : 0.0f));
+    }
+  }
+}
+
+template <typename T>
+int launch_simt(const void* A, const void* W, const void* bias, void* C, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+  const int64_t gx = (N + kSimtTile - 1) / kSimtTile, gy = (M + kSimtTile - 1) / kSimtTile;
+  if (gx > 0x7fffffffll || gy > 65535) return NTB200_UNSUPPORTED_SHAPE;
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  gemm_bias_simt_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(A), static_cast<const T*>(W),
+                                                 static_cast<const T*>(bias), static_cast<T*>(C), M, N, K);
+  return status_from_cuda(cudaGetLastError());
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+int gemm_error_flags_read_and_clear() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace ntb200
+
+using namespace ntb200;
+
+extern "C" {
+
+int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, int64_t M, int64_t N, int64_t K, int dtype,
+                     int force_simt, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return NTB200_INVALID_ARG;
+  if (dtype != NTB200_F32 && dtype != NTB200_F16 && dtype != NTB200_BF16) return NTB200_UNSUPPORTED_DTYPE;
+  if (M == 0 || N == 0) return NTB200_OK;
+  if (A == nullptr || W == nullptr || C == nullptr) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool tc = !force_simt && dtype != NTB200_F32 && K >= 8 && (K % 8) == 0 && (N % 8) == 0 && aligned16(A) && aligned16(W) &&
+                  aligned16(C) && M < (1ll << 31) - kBM && N < (1ll << 31) - kBN && K < (1ll << 31) - kBK;
+  if (tc) {
+    if (dtype == NTB200_F16) return launch_tcgen05<0>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
+    return launch_tcgen05<1>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
+  }
+  const size_t es = dtype == NTB200_F32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(A) % es) || (reinterpret_cast<uintptr_t>(W) % es) || (reinterpret_cast<uintptr_t>(C) % es))
+    return NTB200_MISALIGNED;
+  switch (dtype) {
+    case NTB200_F32: return launch_simt<float>(A, W, bias, C, M, N, K, st);
+    case NTB200_F16: return launch_simt<__half>(A, W, bias, C, M, N, K, st);
+    case NTB200_BF16: return launch_simt<__nv_bfloat16>(A, W, bias, C, M, N, K, st);
+  }
+  return NTB200_UNSUPPORTED_DTYPE;
+}
+
+int ntb200_device_error_flags(void) { return gemm_error_flags_read_and_clear(); }
+
+}  // extern "C"

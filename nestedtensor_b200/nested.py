@@ -76,6 +76,15 @@ class NestedTensor(object):
         return False
 
     @property
+    def is_cuda(self):
+        return self._buffer.is_cuda
+
+    @property
+    def is_nested(self):
+        # not a core torch.nested tensor: stock modules must not take their torch.nested branches
+        return False
+
+    @property
     def shape(self):
         return self.size()
 

@@ -1,18 +1,100 @@
-"""Self-attention on nested tensors (nestedtensor/nn/mha.py:7-83, nestedtensor/csrc/cuda/mha.cpp:22-107)."""
+"""Self-attention on nested tensors (nestedtensor/nn/mha.py:7-83 over bt_min_mha,
+nestedtensor/csrc/cuda/mha.cpp:22-107)."""
 from __future__ import annotations
 
 import torch
 
+from .. import _ops
+from ..nested import NestedTensor
+
 
 def bt_min_mha(num_heads, head_dim, dropout_p, training, query, key, value, attr_kernel, attr_bias, scaling,
                out_proj_weight, out_proj_bias):
-    raise NotImplementedError("nestedtensor_b200: the attention kernels are not built yet")
+    """``torch.ops.nestedtensor.bt_min_mha`` with the reference's argument list.  query, key and value
+    must be the same NestedTensor (self-attention); returns a NestedTensor of the same nested size."""
+    if not (query is key and key is value):
+        raise NotImplementedError("nestedtensor_b200: bt_min_mha implements self-attention (query is key is value)")
+    if query.dim() != 3:
+        raise RuntimeError("query needs to be 3 dim.")
+    buf, sizes, meta = query._record()
+    out = _ops.ops().bt_min_mha(num_heads, head_dim, float(dropout_p), bool(training), buf, sizes, meta, attr_kernel,
+                                attr_bias, float(scaling), out_proj_weight, out_proj_bias)
+    return NestedTensor(out, sizes, meta)
 
 
-def multi_head_attention_forward(*args, **kwargs):
-    raise NotImplementedError("nestedtensor_b200: the attention kernels are not built yet")
+def multi_head_attention_forward(query,
+                                 key,
+                                 value,
+                                 embed_dim_to_check,
+                                 num_heads,
+                                 in_proj_weight,
+                                 in_proj_bias,
+                                 bias_k,
+                                 bias_v,
+                                 add_zero_attn,
+                                 dropout_p,
+                                 out_proj_weight,
+                                 out_proj_bias,
+                                 training=True,
+                                 key_padding_mask=None,
+                                 need_weights=True,
+                                 attn_mask=None,
+                                 use_separate_proj_weight=False,
+                                 q_proj_weight=None,
+                                 k_proj_weight=None,
+                                 v_proj_weight=None,
+                                 static_k=None,
+                                 static_v=None,
+                                 average_attn_weights=True,
+                                 is_causal=False):
+    """Stock signature; the unsupported options are rejected exactly as the reference does
+    (nestedtensor/nn/mha.py:37-45).  Returns ``(output, None)``.  The output projection bias is applied
+    (the reference's CUDA path drops it, nestedtensor/csrc/cuda/mha.cpp:106 and nn/mha.py:69; its generic
+    path adds it, nestedtensor/csrc/mha.cpp:66-67)."""
+    assert isinstance(query, NestedTensor)
+    assert isinstance(key, NestedTensor)
+    assert isinstance(value, NestedTensor)
+    assert torch.is_tensor(out_proj_weight)
+    assert torch.is_tensor(out_proj_bias)
+    assert not use_separate_proj_weight
+    assert attn_mask is None
+    assert key_padding_mask is None
+    assert bias_k is None
+    assert bias_v is None
+    assert static_k is None
+    assert static_v is None
+    assert not add_zero_attn
+    assert not is_causal
+
+    bsz, tgt_len, embed_dim = query.size()
+    assert embed_dim == embed_dim_to_check
+    assert key.size(0) == value.size(0) and key.size(1) == value.size(1)
+    head_dim = embed_dim // num_heads
+    assert head_dim * num_heads == embed_dim, "embed_dim must be divisible by num_heads"
+    scaling = float(head_dim) ** -0.5
+
+    if query is key and key is value:
+        if not in_proj_weight.is_cuda:
+            raise RuntimeError("nestedtensor_b200: attention needs CUDA weights (this build has no CPU implementation)")
+        return bt_min_mha(num_heads, head_dim, dropout_p, False, query, query, query, in_proj_weight, in_proj_bias,
+                          scaling, out_proj_weight, out_proj_bias), None
+    raise NotImplementedError(
+        "nestedtensor_b200: only self-attention (query is key is value) is implemented; cross-attention is outside "
+        "the accelerated path")
 
 
 class MultiheadAttention(torch.nn.MultiheadAttention):
-    """Stock ``torch.nn.MultiheadAttention``; called with NestedTensor inputs its forward reaches
-    ``multi_head_attention_forward`` above through ``NestedTensor.__torch_function__``."""
+    """``torch.nn.MultiheadAttention`` whose forward accepts NestedTensor inputs.  The reference relies on
+    the stock module plus ``NestedTensor.__torch_function__``; this subclass makes the route explicit so
+    that it does not depend on the stock forward's pre-checks."""
+
+    def forward(self, query, key, value, key_padding_mask=None, need_weights=True, attn_mask=None,
+                average_attn_weights=True, is_causal=False):
+        if isinstance(query, NestedTensor):
+            return multi_head_attention_forward(
+                query, key, value, self.embed_dim, self.num_heads, self.in_proj_weight, self.in_proj_bias, self.bias_k,
+                self.bias_v, self.add_zero_attn, self.dropout, self.out_proj.weight, self.out_proj.bias,
+                training=self.training, key_padding_mask=key_padding_mask, need_weights=need_weights,
+                attn_mask=attn_mask, is_causal=is_causal)
+        return super().forward(query, key, value, key_padding_mask=key_padding_mask, need_weights=need_weights,
+                               attn_mask=attn_mask, average_attn_weights=average_attn_weights, is_causal=is_causal)

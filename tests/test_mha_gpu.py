@@ -1,0 +1,295 @@
+"""Parity of the CUDA projection / varlen attention kernels and of the MHA operator with the fp32
+oracle (oracle.ntref.min_mha = nestedtensor/csrc/mha.cpp:18-69).  Tolerances: max-abs 2e-2 for
+fp16/bf16 and 1e-5 for fp32, against the oracle evaluated in fp32 on the same (cast) inputs."""
+import ctypes
+
+import pytest
+import torch
+
+import nestedtensor_b200 as nt
+from nestedtensor_b200 import _cabi, workloads
+from nestedtensor_b200.nested import build_meta
+from oracle import ntref
+from _helpers import stream_ptr
+
+pytestmark = pytest.mark.gpu
+
+CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+TOL = {torch.float32: 1e-5, torch.float16: 2e-2, torch.bfloat16: 2e-2}
+
+
+def _gemm(A, W, bias, force_simt=0):
+    lib = _cabi.load()
+    M, K = A.shape
+    N = W.shape[0]
+    C = torch.empty(M, N, dtype=A.dtype, device=A.device)
+    rc = lib.ntb200_gemm_bias(A.data_ptr(), W.data_ptr(), bias.data_ptr() if bias is not None else None, C.data_ptr(),
+                              M, N, K, CODE[A.dtype], force_simt, stream_ptr())
+    _cabi.check("ntb200_gemm_bias", rc)
+    torch.cuda.synchronize()
+    assert lib.ntb200_device_error_flags() == 0
+    return C
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 512, 256), (1000, 3072, 1024), (129, 264, 72), (5, 8, 64),
+                                   (4099, 1024, 1024), (20000, 768, 768)])
+def test_gemm_bias_tensor_core(native_libs, cuda_device, dtype, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    A = torch.randn(M, K, generator=g).to(dtype).to(cuda_device)
+    W = (torch.randn(N, K, generator=g) * K ** -0.5).to(dtype).to(cuda_device)
+    b = (torch.randn(N, generator=g) * 0.1).to(dtype).to(cuda_device)
+    want = A.float() @ W.float().t() + b.float()
+    got = _gemm(A, W, b)
+    err = (got.float() - want).abs().max().item()
+    assert err <= 2e-2, "tensor-core path max-abs %g" % err
+    got2 = _gemm(A, W, b, force_simt=1)
+    err2 = (got2.float() - want).abs().max().item()
+    assert err2 <= 2e-2, "SIMT path max-abs %g" % err2
+    got3 = _gemm(A, W, None)
+    assert (got3.float() - (want - b.float())).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(7, 5, 3), (130, 66, 100), (1000, 768, 256)])
+def test_gemm_bias_fp32(native_libs, cuda_device, M, N, K):
+    g = torch.Generator().manual_seed(M)
+    A = torch.randn(M, K, generator=g).to(cuda_device)
+    W = (torch.randn(N, K, generator=g) * K ** -0.5).to(cuda_device)
+    b = torch.randn(N, generator=g).to(cuda_device)
+    want = (A.double() @ W.double().t() + b.double()).float()
+    got = _gemm(A, W, b)
+    assert (got - want).abs().max().item() <= 1e-5
+
+
+def _attention(qkv, lengths, H, d, force_simt=0):
+    lib = _cabi.load()
+    E = H * d
+    T = qkv.shape[0]
+    sizes = torch.tensor([[l, E] for l in lengths], dtype=torch.int64)
+    meta = build_meta(sizes, qkv.device)
+    out = torch.empty(T, E, dtype=qkv.dtype, device=qkv.device)
+    rc = lib.ntb200_varlen_attention(qkv.data_ptr(), out.data_ptr(), meta.data_ptr(), len(lengths), T, H, d, max(lengths),
+                                     float(d) ** -0.5, CODE[qkv.dtype], force_simt, stream_ptr())
+    _cabi.check("ntb200_varlen_attention", rc)
+    torch.cuda.synchronize()
+    return out
+
+
+def _attention_oracle(qkv, lengths, H, d):
+    E = H * d
+    x = qkv.float().cpu()
+    out, off = [], 0
+    for l in lengths:
+        blk = x[off:off + l]
+        q = blk[:, :E].reshape(l, H, d).transpose(0, 1) * float(d) ** -0.5
+        k = blk[:, E:2 * E].reshape(l, H, d).transpose(0, 1)
+        v = blk[:, 2 * E:].reshape(l, H, d).transpose(0, 1)
+        w = torch.softmax(q @ k.transpose(1, 2), -1)
+        out.append((w @ v).transpose(0, 1).reshape(l, E))
+        off += l
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+def test_varlen_attention_d64(native_libs, cuda_device, dtype):
+    lengths = [1, 63, 64, 65, 128, 200, 512, 7, 129, 16]
+    H, d = 4, 64
+    g = torch.Generator().manual_seed(4)
+    qkv = torch.randn(sum(lengths), 3 * H * d, generator=g).to(dtype).to(cuda_device)
+    want = _attention_oracle(qkv, lengths, H, d)
+    got = _attention(qkv, lengths, H, d)
+    err = (got.float().cpu() - want).abs().max().item()
+    assert err <= 2e-2, "tensor-core attention max-abs %g" % err
+    got2 = _attention(qkv, lengths, H, d, force_simt=1)
+    err2 = (got2.float().cpu() - want).abs().max().item()
+    assert err2 <= 2e-2, "SIMT attention max-abs %g" % err2
+
+
+@pytest.mark.parametrize("H,d", [(2, 1), (1, 4), (2, 2), (8, 16), (4, 256), (3, 40), (16, 64)])
+def test_varlen_attention_fp32(native_libs, cuda_device, H, d):
+    lengths = [5, 1, 33, 50, 2, 64, 100]
+    g = torch.Generator().manual_seed(H * 100 + d)
+    qkv = torch.randn(sum(lengths), 3 * H * d, generator=g).to(cuda_device)
+    want = _attention_oracle(qkv, lengths, H, d)
+    got = _attention(qkv, lengths, H, d)
+    assert (got.cpu() - want).abs().max().item() <= 1e-5
+
+
+def _run_mha(tensors, H, w, dtype, device):
+    a = nt.nested_tensor(tensors, device=device, dtype=dtype)
+    E = tensors[0].shape[1]
+    d = E // H
+    wd = {k: v.to(dtype).to(device) for k, v in w.items()}
+    out = torch.ops.nestedtensor.bt_min_mha(H, d, 0.5, False, a, a, a, wd["in_proj_weight"], wd["in_proj_bias"],
+                                            float(d) ** -0.5, wd["out_proj_weight"], wd["out_proj_bias"])
+    torch.cuda.synchronize()
+    assert _cabi.load().ntb200_device_error_flags() == 0
+    cast = [t.to(dtype) for t in tensors]
+    wc = {k: v.to(dtype) for k, v in w.items()}
+    want = ntref.min_mha(H, d, cast, cast, cast, wc["in_proj_weight"], wc["in_proj_bias"], float(d) ** -0.5,
+                         wc["out_proj_weight"], wc["out_proj_bias"])
+    return out, want
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=str)
+@pytest.mark.parametrize("H,B,Lmax,d", [(2, 1, 2, 1), (1, 3, 5, 4), (2, 3, 5, 2), (2, 1, 2, 2), (8, 8, 50, 16),
+                                         (16, 64, 50, 16), (16, 128, 50, 16), (4, 64, 50, 256), (16, 64, 50, 64)])
+def test_bt_min_mha_reference_shapes(native_libs, cuda_device, dtype, H, B, Lmax, d):
+    """Shape list of test/test_nested_tensor_functional.py:1149-1161 (largest batches reduced to keep the CPU
+    oracle in seconds)."""
+    g = torch.Generator().manual_seed(1010 + H + B + d)
+    E = H * d
+    tensors = [torch.randn(int(torch.randint(1, Lmax + 1, (1,), generator=g)), E, generator=g) for _ in range(B)]
+    w = {"in_proj_weight": torch.randn(3 * E, E, generator=g) * E ** -0.5,
+         "in_proj_bias": torch.randn(3 * E, generator=g) * 0.02,
+         "out_proj_weight": torch.randn(E, E, generator=g) * E ** -0.5,
+         "out_proj_bias": torch.randn(E, generator=g) * 0.02}
+    out, want = _run_mha(tensors, H, w, dtype, cuda_device)
+    assert out.nested_size() == tuple(torch.Size(t.shape) for t in tensors)
+    for o, r in zip(out.unbind(), want):
+        err = (o.float().cpu() - r).abs().max().item()
+        assert err <= TOL[dtype], "max-abs %g" % err
+
+
+def test_config4_bert_base_fp16(native_libs, cuda_device):
+    """Configuration 4: batch 128, L ~ U[32,512], E=768, 12 heads x 64, fp16, non-zero biases."""
+    w = workloads.config4()
+    tensors = w.tensors()
+    out, want = _run_mha([t.float() for t in tensors], 12, {k: v.float() for k, v in w.weights.items()}, torch.float16,
+                         cuda_device)
+    worst = max((o.float().cpu() - r).abs().max().item() for o, r in zip(out.unbind(), want))
+    assert worst <= 2e-2, "max-abs %g" % worst
+
+
+def test_config5_bert_large_bf16_sampled(native_libs, cuda_device):
+    """Configuration 5 at full size on the GPU (batch 1024, bf16, E=1024, 16 x 64); the fp32 oracle is
+    evaluated on every 16th sequence only (sequences are independent)."""
+    w = workloads.config5()
+    a = nt.NestedTensor(w.buffer.to(cuda_device), w.sizes)
+    wd = {k: v.to(cuda_device) for k, v in w.weights.items()}
+    mha = nt.nn.MultiheadAttention(1024, 16).to(torch.bfloat16).to(cuda_device)
+    with torch.no_grad():
+        mha.in_proj_weight.copy_(wd["in_proj_weight"])
+        mha.in_proj_bias.copy_(wd["in_proj_bias"])
+        mha.out_proj.weight.copy_(wd["out_proj_weight"])
+        mha.out_proj.bias.copy_(wd["out_proj_bias"])
+        out, none = mha(a, a, a, need_weights=False)
+    assert none is None
+    torch.cuda.synchronize()
+    assert _cabi.load().ntb200_device_error_flags() == 0
+    tensors = w.tensors()
+    idx = list(range(0, w.batch, 16))
+    sample = [tensors[i] for i in idx]
+    want = ntref.min_mha(16, 64, sample, sample, sample, w.weights["in_proj_weight"], w.weights["in_proj_bias"],
+                         64 ** -0.5, w.weights["out_proj_weight"], w.weights["out_proj_bias"])
+    outs = out.unbind()
+    worst = max((outs[i].float().cpu() - r).abs().max().item() for i, r in zip(idx, want))
+    assert worst <= 2e-2, "max-abs %g" % worst
+
+
+def test_stock_module_matches_dense_attention(native_libs, cuda_device):
+    """test/test_nested_tensor_functional.py:1103-1140: stock torch.nn.MultiheadAttention on NestedTensor inputs
+    equals the dense module with key_padding_mask on the zero-padded batch (atol 5e-4, fp32)."""
+    torch.manual_seed(1010)
+    E, H = 128, 8
+    g = torch.Generator().manual_seed(5)
+    tensors = [torch.randn(int(torch.randint(1, 51, (1,), generator=g)), E, generator=g) for _ in range(8)]
+    a = nt.nested_tensor(tensors, device=cuda_device, dtype=torch.float32)
+    mha = torch.nn.MultiheadAttention(E, H).to(cuda_device).eval()
+    with torch.no_grad():
+        mha.in_proj_bias.normal_(0, 0.02)
+        mha.out_proj.bias.normal_(0, 0.02)
+        got, _ = mha(a, a, a, need_weights=False)
+        data, mask = a.to_tensor_mask(mask_dim=2)
+        x = data.transpose(0, 1)
+        dense, _ = mha(x, x, x, key_padding_mask=~mask, need_weights=False)
+    dense = dense.transpose(0, 1) * mask.unsqueeze(-1)
+    assert torch.allclose(got.to_padded_tensor(padding=0), dense, atol=5e-4, rtol=1e-8)
+
+
+def test_cross_attention_is_rejected(native_libs, cuda_device):
+    a = nt.nested_tensor([torch.randn(3, 8)], device=cuda_device)
+    b = nt.nested_tensor([torch.randn(4, 8)], device=cuda_device)
+    mha = torch.nn.MultiheadAttention(8, 2).to(cuda_device)
+    with pytest.raises(NotImplementedError):
+        mha(a, b, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=str)
+def test_reference_shaped_helpers(native_libs, cuda_device, dtype):
+    """add_qkv_bias_pad / transpose_rm_padding / softmax_masked against plain torch."""
+    lib = _cabi.load()
+    H, d = 3, 8
+    E = H * d
+    lengths = [4, 1, 6, 3]
+    B, T, maxL = len(lengths), sum(lengths), max(lengths)
+    g = torch.Generator().manual_seed(9)
+    qkv = torch.randn(T, 3 * E, generator=g).to(dtype).to(cuda_device)
+    bias = torch.randn(3 * E, generator=g).to(dtype).to(cuda_device)
+    meta = build_meta(torch.tensor([[l, E] for l in lengths], dtype=torch.int64), cuda_device)
+    bufs = [torch.zeros(B, H, maxL, d, dtype=dtype, device=cuda_device) for _ in range(3)]
+    rc = lib.ntb200_add_qkv_bias_pad(qkv.data_ptr(), bias.data_ptr(), bufs[0].data_ptr(), bufs[1].data_ptr(),
+                                     bufs[2].data_ptr(), meta.data_ptr(), B, T, H, d, maxL, CODE[dtype], stream_ptr())
+    _cabi.check("ntb200_add_qkv_bias_pad", rc)
+    torch.cuda.synchronize()
+    biased = (qkv.float() + bias.float()).to(dtype)
+    off = 0
+    for b, l in enumerate(lengths):
+        for which in range(3):
+            want = biased[off:off + l, which * E:(which + 1) * E].reshape(l, H, d).transpose(0, 1)
+            assert torch.equal(bufs[which][b, :, :l], want)
+            assert bool((bufs[which][b, :, l:] == 0).all())
+        off += l
+    back = torch.empty(T, E, dtype=dtype, device=cuda_device)
+    rc = lib.ntb200_transpose_rm_padding(bufs[0].data_ptr(), back.data_ptr(), meta.data_ptr(), B, T, H, d, maxL,
+                                         CODE[dtype], stream_ptr())
+    _cabi.check("ntb200_transpose_rm_padding", rc)
+    torch.cuda.synchronize()
+    assert torch.equal(back, biased[:, :E])
+    # masked softmax with the reference's arithmetic
+    scores = torch.randn(B, H, maxL, maxL, generator=g).to(dtype).to(cuda_device)
+    m = torch.zeros(B, maxL)
+    for b, l in enumerate(lengths):
+        m[b, :l] = 1
+    want = ntref.masked_softmax(scores.cpu(), m.unsqueeze(1) * m.unsqueeze(2), 0.35)
+    rc = lib.ntb200_softmax_masked(scores.data_ptr(), meta.data_ptr(), E, B, H, maxL, maxL, 0.35, CODE[dtype], stream_ptr())
+    _cabi.check("ntb200_softmax_masked", rc)
+    torch.cuda.synchronize()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for b, l in enumerate(lengths):
+        assert (scores[b, :, :l, :l].float().cpu() - want[b, :, :l, :l]).abs().max().item() <= tol
+
+
+def test_offsets_scan_and_token_index(native_libs, cuda_device):
+    """Device-side offsets (exclusive scan, with and without the block-sum workspace) and token index."""
+    for B in (1, 7, 1024, 1025, 5000, 70000):
+        g = torch.Generator().manual_seed(B)
+        sizes = torch.randint(0, 9, (B, 2), generator=g)
+        d_sizes = sizes.to(cuda_device)
+        meta = torch.ops.nestedtensor.meta_from_device_sizes(d_sizes)
+        want = build_meta(sizes, "cpu")
+        assert torch.equal(meta.cpu(), want)
+    lengths = torch.tensor([3, 0, 5, 1, 0, 2])
+    offs = torch.cat([torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)]).to(cuda_device)
+    bi, wi = torch.ops.nestedtensor.token_index(offs, int(lengths.sum()))
+    assert bi.cpu().tolist() == [0, 0, 0, 2, 2, 2, 2, 2, 3, 5, 5]
+    assert wi.cpu().tolist() == [0, 1, 2, 0, 1, 2, 3, 4, 0, 0, 1]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.uint8],
+                         ids=str)
+def test_sizes_from_padded_semantics(native_libs, cuda_device, dtype):
+    """`tensor != padding` follows the dtype's comparison: -0.0 counts as padding 0.0, NaN never does."""
+    t = torch.zeros(3, 4, 6, dtype=dtype)
+    t[0, :2, :3] = 1
+    t[1, :4, :6] = 2
+    t[2, :1, :1] = 3
+    if dtype.is_floating_point:
+        t[0, 3, 5] = -0.0            # still padding
+    a = nt.nested_tensor_from_padded_tensor(t.to(cuda_device), padding=0)
+    assert a.nested_size() == (torch.Size([2, 3]), torch.Size([4, 6]), torch.Size([1, 1]))
+    if dtype.is_floating_point:
+        t2 = t.clone()
+        t2[2, 0, 1] = float("nan")   # NaN != 0 -> valid
+        b = nt.nested_tensor_from_padded_tensor(t2.to(cuda_device), padding=0)
+        assert b.nested_size()[2] == torch.Size([1, 2])
