@@ -38,7 +38,8 @@ typedef enum ntb200_status {
   NTB200_LAUNCH_FAILED = -4,
   NTB200_DEVICE_TIMEOUT = -5,
   NTB200_WORKSPACE_TOO_SMALL = -6,
-  NTB200_UNSUPPORTED_SHAPE = -7
+  NTB200_UNSUPPORTED_SHAPE = -7,
+  NTB200_STATIC_SCRATCH_EXCEEDED = -8
 } ntb200_status;
 
 /* element types of the MHA entry points (copies take an element size instead) */
@@ -139,6 +140,28 @@ size_t ntb200_offsets_workspace_bytes(int64_t batch);
 int ntb200_offsets_from_sizes(const int64_t* sizes, int64_t size_stride, int nd, int64_t inner,
                               int64_t batch, int64_t* offsets, void* workspace,
                               size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ offsets, no allocation anywhere
+ * Same result as ntb200_offsets_from_sizes, for hosts that cannot hand the library a workspace:
+ * runtimes that carve one fixed device arena at start-up and forbid any later cudaMalloc (a
+ * database or inference server with a hard memory budget, an embedded control loop), and foreign
+ * language bindings that have no device allocator to call at all.  The block sums that the
+ * multi-block scan needs are kept in a 32 KB array compiled into the library (one copy on every
+ * GPU that loads it, for the life of the process), so this call takes no workspace and performs
+ * no cudaMalloc / cudaFree / allocating library call.
+ *   limit        batch <= ntb200_offsets_static_max_batch() (4 194 304); larger batches return
+ *                NTB200_STATIC_SCRATCH_EXCEEDED and launch nothing - use ntb200_offsets_from_sizes
+ *   first call   on each device looks up the array's device address once (cudaGetSymbolAddress, with
+ *                that device current); make that first call before starting any stream capture
+ *   sharing      every call on a device uses the same array: two calls whose kernels can overlap
+ *                on the GPU (different streams, no dependency between them) race and may both
+ *                return wrong offsets; calls on one stream are safe.  Nothing needs clearing
+ *                between calls: each call overwrites every entry it later reads.
+ * This entry point has no counterpart in the reference.
+ */
+int64_t ntb200_offsets_static_max_batch(void);
+int ntb200_offsets_from_sizes_static(const int64_t* sizes, int64_t size_stride, int nd, int64_t inner,
+                                     int64_t batch, int64_t* offsets, void* stream);
 
 /* ------------------------------------------------------------------ token index
  * For token t in [0, total_tokens): batch_idx[t] = b and word_idx[t] = t - token_offsets[b]

@@ -31,6 +31,8 @@ SIGNATURES = {
     "ntb200_offsets_workspace_bytes": (c_size_t, [c_int64]),
     "ntb200_offsets_from_sizes": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                           c_size_t, c_void_p]),
+    "ntb200_offsets_static_max_batch": (c_int64, []),
+    "ntb200_offsets_from_sizes_static": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "ntb200_token_index": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ntb200_gemm_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                                  c_void_p]),

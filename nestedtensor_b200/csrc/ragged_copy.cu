@@ -574,6 +574,32 @@ __global__ void __launch_bounds__(kScanThreads) offsets_phase3(int64_t* offsets,
   if (b < batch) offsets[b] += block_sums[blockIdx.x];
 }
 
+// ---------------------------------------------------- built-in scratch for the no-allocation variant
+// Block sums for ntb200_offsets_from_sizes_static live here instead of in a caller-provided workspace.
+// 4096 entries of 8 bytes = 32 KB, held by every GPU that loads the library until the process exits.
+constexpr int64_t kStaticScanBlocks = 4096;
+constexpr int64_t kStaticScanMaxBatch = kStaticScanBlocks * kScanThreads;  // 4 194 304 constituents
+static __device__ __align__(256) int64_t g_static_block_sums[kStaticScanBlocks];
+
+// In host code `g_static_block_sums` is only a handle for the runtime, not a device address, so the
+// address the kernels receive is looked up once per device with cudaGetSymbolAddress.
+constexpr int kMaxDevices = 64;
+int64_t* g_static_block_sums_addr[kMaxDevices] = {};
+
+int static_block_sums_for_current_device(int64_t** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return NTB200_LAUNCH_FAILED;
+  int64_t* p = __atomic_load_n(&g_static_block_sums_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_static_block_sums) != cudaSuccess || sym == nullptr) return NTB200_LAUNCH_FAILED;
+    p = static_cast<int64_t*>(sym);
+    __atomic_store_n(&g_static_block_sums_addr[dev], p, __ATOMIC_RELEASE);  // same value from any thread
+  }
+  *out = p;
+  return NTB200_OK;
+}
+
 // ---------------------------------------------------------------------- token index
 __global__ void __launch_bounds__(kThreads) token_index_kernel(const int64_t* __restrict__ offsets, int64_t batch,
                                                                 int64_t total, int32_t* __restrict__ batch_idx,
@@ -707,6 +733,7 @@ const char* ntb200_status_string(int status) {
     case NTB200_DEVICE_TIMEOUT: return "device-side wait timed out";
     case NTB200_WORKSPACE_TOO_SMALL: return "workspace too small";
     case NTB200_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case NTB200_STATIC_SCRATCH_EXCEEDED: return "size exceeds the built-in scratch of the no-allocation entry point";
   }
   return "unknown status";
 }
@@ -903,6 +930,30 @@ int ntb200_offsets_from_sizes(const int64_t* sizes, int64_t size_stride, int nd,
     if (!aligned_to(workspace, 8)) return NTB200_MISALIGNED;
   }
   int64_t* block_sums = static_cast<int64_t*>(workspace);
+  offsets_phase1<<<(unsigned)nblk, kScanThreads, 0, st>>>(sizes, size_stride, nd, inner, batch, offsets, block_sums);
+  if (nblk > 1) {
+    offsets_phase2<<<1, kScanThreads, 0, st>>>(block_sums, nblk, offsets + batch);
+    offsets_phase3<<<(unsigned)nblk, kScanThreads, 0, st>>>(offsets, block_sums, batch);
+  }
+  return status_from_cuda(cudaGetLastError());
+}
+
+int64_t ntb200_offsets_static_max_batch(void) { return kStaticScanMaxBatch; }
+
+int ntb200_offsets_from_sizes_static(const int64_t* sizes, int64_t size_stride, int nd, int64_t inner, int64_t batch,
+                                     int64_t* offsets, void* stream) {
+  if (batch < 0 || nd < 0 || nd > 8 || size_stride < nd || inner < 0) return NTB200_INVALID_ARG;
+  if (batch > kStaticScanMaxBatch) return NTB200_STATIC_SCRATCH_EXCEEDED;
+  if (offsets == nullptr) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (batch == 0) return status_from_cuda(cudaMemsetAsync(offsets, 0, sizeof(int64_t), st));
+  if (sizes == nullptr && nd > 0) return NTB200_INVALID_ARG;
+  int64_t* block_sums = nullptr;
+  const int rc = static_block_sums_for_current_device(&block_sums);
+  if (rc != NTB200_OK) return rc;
+  const int64_t nblk = ceil_div(batch, kScanThreads);
+  // Every block sum that phase 2 and 3 read is written by phase 1 of this same call, so nothing
+  // left in the array by an earlier call can leak into the result and no clearing is needed.
   offsets_phase1<<<(unsigned)nblk, kScanThreads, 0, st>>>(sizes, size_stride, nd, inner, batch, offsets, block_sums);
   if (nblk > 1) {
     offsets_phase2<<<1, kScanThreads, 0, st>>>(block_sums, nblk, offsets + batch);
