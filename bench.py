@@ -348,7 +348,7 @@ def run_reference(args, kind, rank, world):
         _, nbytes, fn = cpu_unpad_sample(L, hidden, dtype, seqs)
         metric = "from_padded_tensor HBM GB/s"
     else:
-        return run_reference_mha(args)
+        return run_reference_mha(args, world)
     for _ in range(max(1, min(args.warmup, 2))):
         fn()
     steps = max(1, min(args.steps, 10))
@@ -367,12 +367,145 @@ def run_reference(args, kind, rank, world):
             "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
-def run_reference_mha(args):
-    return {"impl": "reference", "unavailable": "mha reference arm not wired yet"}
+def cpu_mha_sample(L, E, H, dtype, seqs):
+    """The reference's generic (CPU-capable) MHA, nestedtensor/csrc/mha.cpp:18-69, on the first `seqs` sequences."""
+    from oracle import ntref
+    from nestedtensor_b200 import workloads
+    Ls = L[:seqs].tolist()
+    g = torch.Generator().manual_seed(13)
+    tensors = [torch.randn(l, E, generator=g).to(dtype) for l in Ls]
+    w = workloads._mha_weights(g, E, dtype)
+    d = E // H
+    fn = lambda: ntref.min_mha(H, d, tensors, tensors, tensors, w["in_proj_weight"], w["in_proj_bias"], float(d) ** -0.5,
+                               w["out_proj_weight"], w["out_proj_bias"])
+    return sum(Ls), fn
 
 
-def run_mha(args, rank, world, local):
-    raise SystemExit("mha workload not built yet")
+def run_reference_mha(args, world):
+    L, _ = shard_lengths("mha", 1, 0)
+    E, H, dtype, seqs = 1024, 16, torch.bfloat16, 64
+    tokens, fn = cpu_mha_sample(L, E, H, dtype, seqs)
+    for _ in range(max(1, min(args.warmup, 2))):
+        fn()
+    steps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    v = tokens / dt
+    sample = "each step = the first %d sequences of configuration 5 (%d tokens), per-sequence fp32 loop" % (seqs, tokens)
+    return {"impl": "reference", "metric": "varlen MHA valid tokens/s", "value": v, "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 inputs, fp32 math", "data": "synthetic",
+            "config": {"workload": "config5 (CPU sample): " + sample},
+            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def run_mha(args, rank, world, local, brief=False):
+    """Configuration 5: BERT-large varlen self-attention forward (bf16, E=1024, 16 heads x 64)."""
+    import ctypes
+    import nestedtensor_b200 as nt
+    from nestedtensor_b200 import _ops, _cabi, workloads
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    E, H, d, dtype = 1024, 16, 64, torch.bfloat16
+    L, imb = shard_lengths("mha", world, rank)
+    B, T, maxL = int(L.numel()), int(L.sum()), int(L.max())
+    sizes = torch.stack([L, torch.full_like(L, E)], 1).contiguous()
+    flops = workloads.mha_flops(L, E)
+    gemm_flops = 2.0 * T * 3 * E * E
+    host = host_values(T * E, dtype, 20245 + rank)
+    w = workloads._mha_weights(workloads._gen(5), E, dtype)
+    wd = {k: v.to(device) for k, v in w.items()}
+    x = nt.NestedTensor(host.to(device), sizes)
+    ops = _ops.ops()
+    buf, sz, meta = x._record()
+    scaling = float(d) ** -0.5
+    step = lambda: ops.bt_min_mha(H, d, 0.0, False, buf, sz, meta, wd["in_proj_weight"], wd["in_proj_bias"], scaling,
+                                  wd["out_proj_weight"], wd["out_proj_bias"])
+    steps = args.steps if not brief else min(args.steps, 20)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    with ClockSampler(local) as clocks:
+        ms = timed_region(step, steps, world, device)
+        ms = min(ms, timed_region(step, steps, world, device))
+        # the dominant kernel alone: QKV projection through the C ABI, same stream, same events
+        lib = _cabi.load()
+        qkv = torch.empty(T, 3 * E, dtype=dtype, device=device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        gemm = lambda: lib.ntb200_gemm_bias(buf.data_ptr(), wd["in_proj_weight"].data_ptr(), wd["in_proj_bias"].data_ptr(),
+                                            qkv.data_ptr(), T, 3 * E, E, 2, 0, stream)
+        for _ in range(3):
+            gemm()
+        gms = timed_region(gemm, steps, world, device) / steps
+        attn_out = torch.empty(T, E, dtype=dtype, device=device)
+        attn = lambda: lib.ntb200_varlen_attention(qkv.data_ptr(), attn_out.data_ptr(), meta.data_ptr(), B, T, H, d, maxL,
+                                                   scaling, 2, 0, stream)
+        for _ in range(3):
+            attn()
+        ams = timed_region(attn, steps, world, device) / steps
+    step_ms = ms / steps
+    total_tokens = all_sum(T, world, device)
+    value = total_tokens / (step_ms * 1e-3)
+    flags = lib.ntb200_device_error_flags()
+
+    e2e = None
+    if not brief:
+        h_in = torch.empty(T * E, dtype=dtype).pin_memory()
+        h_in.copy_(host)
+        h_out = torch.empty(T * E, dtype=dtype).pin_memory()
+        d_in = torch.empty(T * E, dtype=dtype, device=device)
+
+        def e2e_step():
+            d_in.copy_(h_in, non_blocking=True)
+            r = ops.bt_min_mha(H, d, 0.0, False, d_in, sz, meta, wd["in_proj_weight"], wd["in_proj_bias"], scaling,
+                               wd["out_proj_weight"], wd["out_proj_bias"])
+            h_out.copy_(r, non_blocking=True)
+
+        e2e_steps = max(3, min(steps, 20))
+        e2e_step()
+        with ClockSampler(local) as clocks2:
+            ems = timed_region(e2e_step, e2e_steps, world, device) / e2e_steps
+        clocks.samples += clocks2.samples
+        clocks.reasons |= clocks2.reasons
+        e2e = {"value": total_tokens / (ems * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * T * E,
+               "d2h_bytes_per_step": 2 * T * E, "ms_per_step": ems, "steps": e2e_steps}
+
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    tf = flops / (step_ms * 1e-3) / 1e12
+    gtf = gemm_flops / (gms * 1e-3) / 1e12
+    atf = 4.0 * E * float((L.double() ** 2).sum()) / (ams * 1e-3) / 1e12
+    line = {
+        "metric": "varlen MHA valid tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config5: BERT-large varlen self-attention forward, batch 1024 per GPU, 70% L~U[16,128] / "
+                               "30% L~U[128,512], E=1024, 16 heads x 64, bf16",
+                   "batch_per_gpu": B, "tokens_per_gpu": T, "max_len": maxL, "flops_per_gpu": flops,
+                   "token_imbalance": imb,
+                   "l2": "activations per step (x, qkv, attn, out = %.2f GB) exceed the 126 MB L2" % (12 * T * E / 1e9)},
+        "step_tflops": tf, "step_frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+        "step_frac_of_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
+        "kernels_ms": {"qkv_gemm": gms, "attention": ams, "step": step_ms},
+        "attention_tflops_valid": atf,
+        "roofline": {"bound": "tensor", "kernel": "gemm_bias_tcgen05_kernel (QKV projection, M=%d N=3072 K=1024)" % T,
+                     "achieved": gtf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": gtf / peaks["bf16_tflops"],
+                     "frac_of_sustained": gtf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
+                     "traffic": NCU_TRAFFIC.get("mha")},
+        "e2e": e2e, "gpu_launches": 3 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
+    }
+    if not brief:
+        torch.set_num_threads(os.cpu_count() or 1)
+        tokens, fn = cpu_mha_sample(L, E, H, dtype, 32)
+        t = time_cpu(fn, 1, 3)
+        line["cpu_baseline"] = {"value": tokens / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": "first 32 sequences (%d tokens), median of 3, per-sequence fp32 loop of the "
+                                          "reference's generic MHA" % tokens}
+    return line
 
 
 # ------------------------------------------------------------------------------- main
@@ -383,6 +516,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="pad", choices=["pad", "unpad", "mha"])
+    ap.add_argument("--no-mha", action="store_true", help="pad workload only: skip the attached MHA measurement")
     args = ap.parse_args()
 
     rank, world, local = dist_env()
@@ -407,6 +541,13 @@ def main():
     try:
         if args.workload in ("pad", "unpad"):
             line = run_copy(args, args.workload, rank, world, local)
+            if args.workload == "pad" and not args.no_mha:
+                # the metric has two halves; attach a short MHA (configuration 5) measurement to the same line
+                torch.cuda.empty_cache()
+                mha = run_mha(args, rank, world, local, brief=True)
+                if line is not None and mha is not None:
+                    line["mha"] = {k: mha[k] for k in ("metric", "value", "unit", "ms_per_step", "step_tflops",
+                                                        "step_frac_of_bf16_peak", "kernels_ms", "roofline", "config")}
         else:
             line = run_mha(args, rank, world, local)
         if rank == 0 and line is not None:

@@ -45,3 +45,34 @@ def imbalance(lengths: Sequence[int], parts: Sequence[Tuple[int, int]]) -> float
     toks = [sum(int(v) for v in lengths[a:b]) for a, b in parts]
     mean = sum(toks) / max(len(toks), 1)
     return max(toks) / mean if mean > 0 else 1.0
+
+
+def gather_ragged(local_buffer, local_sizes, group=None):
+    """All-gather the per-rank pieces of a sharded nested tensor for VERIFICATION (never on the data
+    path): every rank contributes its 1-D buffer and its CPU int64 sizes matrix; returns
+    (buffer, sizes) of the whole batch in rank order.  Buffers are padded to the largest per-rank
+    element count for the fixed-size collective.  Works with NCCL (device buffers) and gloo (CPU)."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    dev = local_buffer.device
+    tdim = local_sizes.size(1)
+    counts = torch.tensor([local_buffer.numel(), local_sizes.size(0)], dtype=torch.int64, device=dev)
+    all_counts = [torch.zeros_like(counts) for _ in range(world)]
+    dist.all_gather(all_counts, counts, group=group)
+    all_counts = [c.cpu().tolist() for c in all_counts]
+    max_elems = max(c[0] for c in all_counts)
+    max_rows = max(c[1] for c in all_counts)
+    pad_buf = torch.zeros(max(max_elems, 1), dtype=local_buffer.dtype, device=dev)
+    pad_buf[:local_buffer.numel()] = local_buffer
+    bufs = [torch.empty_like(pad_buf) for _ in range(world)]
+    dist.all_gather(bufs, pad_buf, group=group)
+    pad_sz = torch.zeros((max(max_rows, 1), max(tdim, 1)), dtype=torch.int64, device=dev)
+    if local_sizes.numel():
+        pad_sz[:local_sizes.size(0), :tdim] = local_sizes.to(dev)
+    szs = [torch.empty_like(pad_sz) for _ in range(world)]
+    dist.all_gather(szs, pad_sz, group=group)
+    buffer = torch.cat([b[:c[0]] for b, c in zip(bufs, all_counts)])
+    sizes = torch.cat([s[:c[1], :tdim].cpu() for s, c in zip(szs, all_counts)]).contiguous()
+    return buffer, sizes
