@@ -329,7 +329,7 @@ def run_copy(args, kind, rank, world, local):
 
 # Per-launch DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from the
 # ncu capture summarised under profiles/; None until a capture exists for that workload.
-NCU_TRAFFIC = {"pad": None, "unpad": None, "mha": None}
+NCU_TRAFFIC = {"pad": 10.48e9, "unpad": None, "mha": None}
 
 
 # ---------------------------------------------------------------------- reference arm
@@ -441,8 +441,10 @@ def run_mha(args, rank, world, local, brief=False):
             gemm()
         gms = timed_region(gemm, steps, world, device) / steps
         attn_out = torch.empty(T, E, dtype=dtype, device=device)
+        ws_bytes = lib.ntb200_varlen_attention_workspace_bytes(B, T, H, d, 2)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
         attn = lambda: lib.ntb200_varlen_attention(qkv.data_ptr(), attn_out.data_ptr(), meta.data_ptr(), B, T, H, d, maxL,
-                                                   scaling, 2, 0, stream)
+                                                   scaling, 2, 0, ws.data_ptr() if ws_bytes else None, ws_bytes, stream)
         for _ in range(3):
             attn()
         ams = timed_region(attn, steps, world, device) / steps
@@ -496,7 +498,7 @@ def run_mha(args, rank, world, local, brief=False):
                      "achieved": gtf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": gtf / peaks["bf16_tflops"],
                      "frac_of_sustained": gtf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
                      "traffic": NCU_TRAFFIC.get("mha")},
-        "e2e": e2e, "gpu_launches": 3 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
+        "e2e": e2e, "gpu_launches": 4 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
     }
     if not brief:
         torch.set_num_threads(os.cpu_count() or 1)

@@ -186,8 +186,9 @@ int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, in
                      int64_t K, int dtype, int force_simt, void* stream);
 
 /* Bit mask of device-side wait time-outs recorded by the tcgen05 kernels since the last call
- * (0 = none; bit 0 TMA producer, bit 1 MMA issuer, bit 2 epilogue); synchronises the device;
- * negative on a CUDA error.  No counterpart in the reference. */
+ * (0 = none; projection GEMM: bit 0 TMA producer, bit 1 MMA issuer, bit 2 epilogue; attention: the
+ * same roles in bits 8-10); synchronises the device; negative on a CUDA error.  No counterpart in the
+ * reference. */
 int ntb200_device_error_flags(void);
 
 /* ------------------------------------------------------------------ varlen self-attention
@@ -195,13 +196,21 @@ int ntb200_device_error_flags(void);
  * q|k|v of token t from row t of the packed qkv buffer [total_tokens, 3*H*d] and attending only
  * to the tokens of the same sequence; `offsets` are the ELEMENT offsets of the sequences in the
  * [total_tokens, H*d] input (B+1 entries, multiples of H*d), max_len the longest sequence.
- * Padded tokens are never materialised.  head_dim 64 in fp16/bf16 uses tensor cores.
+ * Padded tokens are never materialised.
+ *   path       0 = best available: head_dim 64 in fp16/bf16 runs on tcgen05/TMEM fed by TMA when a
+ *              workspace is supplied, on an mma.sync flash kernel when it is not, everything else on
+ *              a SIMT kernel;  1 = SIMT;  2 = mma.sync kernel;  3 = tcgen05 kernel (for cross-checks)
+ *   workspace  device scratch of ntb200_varlen_attention_workspace_bytes(...) bytes, 16-byte aligned
+ *              (holds the device-built list of (sequence, query tile) work items); may be NULL
  * Replaces steps 2-8 of bt_min_mha (nestedtensor/csrc/cuda/mha.cpp:59-105) including
  * softmax_kernel_kernelLauncher (nestedtensor/csrc/cuda/attention.h:25-33).
  */
+size_t ntb200_varlen_attention_workspace_bytes(int64_t batch, int64_t total_tokens, int num_heads,
+                                               int head_dim, int dtype);
 int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, int64_t batch,
                             int64_t total_tokens, int num_heads, int head_dim, int64_t max_len,
-                            float scaling, int dtype, int force_simt, void* stream);
+                            float scaling, int dtype, int path, void* workspace,
+                            size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ reference-shaped helpers
  * q/k/v_buf[b, h, l, :] = qkv[tok(b,l), {0,E,2E} + h*d + :] + bias  for valid tokens (padded

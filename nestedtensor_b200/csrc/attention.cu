@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "attention_internal.cuh"
 #include "common.cuh"
 
 namespace ntb200 {
@@ -441,17 +442,36 @@ using namespace ntb200;
 
 extern "C" {
 
+size_t ntb200_varlen_attention_workspace_bytes(int64_t batch, int64_t total_tokens, int num_heads, int head_dim, int dtype) {
+  if (batch <= 0 || total_tokens <= 0) return 0;
+  if (!attn_tcgen05_supported(batch, total_tokens, num_heads, head_dim, dtype)) return 0;
+  return attn_tcgen05_workspace_bytes(batch, total_tokens);
+}
+
 int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens,
-                            int num_heads, int head_dim, int64_t max_len, float scaling, int dtype, int force_simt,
-                            void* stream) {
+                            int num_heads, int head_dim, int64_t max_len, float scaling, int dtype, int path,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  const int force_simt = path == 1;
   if (batch < 0 || total_tokens < 0 || num_heads < 1 || head_dim < 1 || max_len < 0) return NTB200_INVALID_ARG;
   if (dtype != NTB200_F32 && dtype != NTB200_F16 && dtype != NTB200_BF16) return NTB200_UNSUPPORTED_DTYPE;
   if (head_dim > kMaxHeadDim) return NTB200_UNSUPPORTED_SHAPE;
   if (batch == 0 || total_tokens == 0) return NTB200_OK;
   if (qkv == nullptr || out == nullptr || offsets == nullptr) return NTB200_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // path 0: best available (tcgen05 when a workspace is given and the shape is supported, else mma.sync,
+  // else SIMT); 1: SIMT; 2: mma.sync flash kernel; 3: tcgen05 (error if unsupported)
+  const bool tc_ok = dtype != NTB200_F32 && (num_heads * (int64_t)head_dim) % 8 == 0 && aligned16(qkv) && aligned16(out) &&
+                     attn_tcgen05_supported(batch, total_tokens, num_heads, head_dim, dtype);
+  if (path == 3 || (path == 0 && tc_ok && workspace != nullptr)) {
+    if (!tc_ok) return NTB200_UNSUPPORTED_SHAPE;
+    const size_t need = attn_tcgen05_workspace_bytes(batch, total_tokens);
+    if (workspace == nullptr || workspace_bytes < need) return NTB200_WORKSPACE_TOO_SMALL;
+    if (!aligned16(workspace)) return NTB200_MISALIGNED;
+    return attn_tcgen05_launch(qkv, out, offsets, batch, total_tokens, num_heads, scaling, dtype, workspace, st);
+  }
   const bool fa = !force_simt && dtype != NTB200_F32 && head_dim == kD && aligned16(qkv) && aligned16(out) && batch <= 65535 &&
                   num_heads <= 65535 && max_len > 0;
+  if (path == 2 && !fa) return NTB200_UNSUPPORTED_SHAPE;
   if (fa) {
     if (dtype == NTB200_F16) return launch_attn_fa<__half>(qkv, out, offsets, batch, num_heads, max_len, scaling, st);
     return launch_attn_fa<__nv_bfloat16>(qkv, out, offsets, batch, num_heads, max_len, scaling, st);

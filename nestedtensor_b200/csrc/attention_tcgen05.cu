@@ -1,0 +1,474 @@
+// Variable-length self-attention on tcgen05 tensor cores, head_dim 64, fp16 / bf16.
+//
+// One CTA = one (sequence, head, 128-query tile).  For every block of 128 keys:
+//     S[128 x n]   = Q K^T          tcgen05.mma, both operands K-major in shared memory (TMA, 128-B swizzle)
+//     P            = exp2(scale*log2e*S - m)   one softmax thread per query ROW (TMEM lane = row, so no
+//                                   cross-thread reduction); P is written back over S as packed 16-bit
+//     O[128 x 64] += P V            tcgen05.mma with A = P read from tensor memory, B = V tile as MN-major
+// S / P (128 columns) and O (64 columns) live in tensor memory (256 columns per CTA, two CTAs per SM so
+// one CTA's softmax overlaps the other's MMAs).  Q, K and V tiles come straight out of the packed
+// [T, 3E] projection output through ONE 2-D tensor map (row = token, column = which third + head), so
+// padded tokens are never materialised; rows past the end of a sequence belong to the next sequence
+// (or are zero-filled past the end of the buffer) and are masked / never stored.
+// The list of (sequence, query tile) work items is built on the device, longest sequences first.
+// Every wait is bounded; a wait that runs out sets an error flag, the CTA drains and frees its TMEM.
+// Replaces steps 2-8 of bt_min_mha (nestedtensor/csrc/cuda/mha.cpp:59-105).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "attention_internal.cuh"
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ntb200 {
+namespace {
+
+__device__ int g_attn_error = 0;  // bit 0 producer, 1 MMA issuer, 2 softmax
+
+constexpr int kQT = 128;   // query rows per CTA (TMEM lanes)
+constexpr int kKV = 128;   // keys per block
+constexpr int kHD = 64;    // head dim
+constexpr int kTile = kQT * kHD * 2;  // 16 KB: one 128 x 64 two-byte tile
+constexpr int kStages = 2;
+constexpr int kTmemCols = 256;        // S/P: columns [0,128), O of even items: [128,192), of odd items: [192,256)
+constexpr int kOCol = 128;
+constexpr int kAttnThreads = 192;     // warp 0 TMA, warp 1 MMA, warps 2-5 softmax
+constexpr int kAttnSmem = 1024 + kTile * (2 + 2 * kStages) + 256;  // 2 Q buffers + 2 stages of (K, V)
+
+struct Ctrl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t s_ready;
+  uint64_t p_ready;
+  uint64_t o_ready;
+  uint64_t done;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = ptx::globaltimer_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (ptx::mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
+    if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) return false;
+  }
+}
+
+template <int FMT>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (FMT == 0) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+// ------------------------------------------------------------------ work list
+// items[i] = (sequence, first query row) for every 128-query tile, ordered by decreasing number of key
+// blocks so that the longest CTAs start first; *count = number of items.  One block.
+constexpr int kListThreads = 1024;
+constexpr int kBuckets = 9;  // key blocks 1..8+, (0 unused)
+
+__global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t* __restrict__ offsets, int64_t batch,
+                                                                   int64_t row_elems, int2* __restrict__ items,
+                                                                   int* __restrict__ count, int64_t capacity) {
+  __shared__ int s_cnt[kBuckets];
+  __shared__ int s_base[kBuckets];
+  if (threadIdx.x < kBuckets) s_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
+    const int64_t L = (offsets[b + 1] - offsets[b]) / row_elems;
+    if (L <= 0) continue;
+    const int nq = (int)((L + kQT - 1) / kQT);
+    int nb = (int)((L + kKV - 1) / kKV);
+    nb = nb >= kBuckets ? kBuckets - 1 : nb;
+    atomicAdd(&s_cnt[nb], nq);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int k = kBuckets - 1; k >= 1; --k) {
+      s_base[k] = acc;
+      acc += s_cnt[k];
+    }
+    *count = acc < capacity ? acc : (int)capacity;
+  }
+  __syncthreads();
+  for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
+    const int64_t L = (offsets[b + 1] - offsets[b]) / row_elems;
+    if (L <= 0) continue;
+    const int nq = (int)((L + kQT - 1) / kQT);
+    int nb = (int)((L + kKV - 1) / kKV);
+    nb = nb >= kBuckets ? kBuckets - 1 : nb;
+    const int pos = atomicAdd(&s_base[nb], nq);
+    for (int t = 0; t < nq; ++t)
+      if (pos + t < capacity) items[pos + t] = make_int2((int)b, t * kQT);
+  }
+}
+
+// ------------------------------------------------------------------ attention
+// Persistent: CTA c works on items c, c + gridDim.x, ... of the flattened (work item, head) list.  All
+// barriers run on one global block counter g (one phase per 128-key block), Q and O alternate between two
+// buffers per item, K/V between two stages per block, so the producer and the MMA warp run ahead into the
+// next item while the softmax warps finish the current one.
+template <int FMT>
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restrict__ out, const int64_t* __restrict__ offsets,
+                    const int2* __restrict__ items, const int* __restrict__ count, int H, float scale_log2e) {
+  const int64_t total = (int64_t)(*count) * H;
+  if ((int64_t)blockIdx.x >= total) return;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kTile * (2 + 2 * kStages));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t E = (int64_t)H * kHD;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(&ctrl->s_ready), 1);
+    ptx::mbar_init(ptx::smem_u32(&ctrl->p_ready), 4);
+    ptx::mbar_init(ptx::smem_u32(&ctrl->o_ready), 1);
+    ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
+    ctrl->abort = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_qkv);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&ctrl->tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+    ptx::tc_fence_before_sync();
+  }
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const uint32_t s_q = ptx::smem_u32(smem);          // two Q buffers
+  const uint32_t s_kv = s_q + 2 * kTile;             // stage s: K at s_kv + s*2*kTile, V right after it
+
+  // decode of flattened item i -> sequence geometry
+  struct Item {
+    int q0, h, L, tok0, n_blk;
+  };
+  auto decode = [&](int64_t i) {
+    Item it;
+    const int2 w = items[i / H];
+    it.h = (int)(i % H);
+    it.q0 = w.y;
+    const int64_t off_b = offsets[w.x];
+    it.L = (int)((offsets[w.x + 1] - off_b) / E);
+    it.tok0 = (int)(off_b / E);
+    it.n_blk = (it.L + kKV - 1) / kKV;
+    return it;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t g = 0, n = 0;
+      for (int64_t i = blockIdx.x; i < total && ok; i += gridDim.x, ++n) {
+        const Item it = decode(i);
+        for (int j = 0; j < it.n_blk; ++j, ++g) {
+          const uint32_t s = g % kStages, ph = (g / kStages) & 1;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->empty[s]), ph ^ 1, &ctrl->abort)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&ctrl->full[s]);
+          ptx::mbar_arrive_expect_tx(full, (j == 0 ? 3 : 2) * kTile);
+          // the Q buffer of item n was last read by item n-2, whose MMAs all precede the release of this stage
+          if (j == 0) ptx::tma_load_2d(s_q + (n & 1) * kTile, &map_qkv, full, it.h * kHD, it.tok0 + it.q0);
+          ptx::tma_load_2d(s_kv + s * 2 * kTile, &map_qkv, full, (int)E + it.h * kHD, it.tok0 + j * kKV);
+          ptx::tma_load_2d(s_kv + s * 2 * kTile + kTile, &map_qkv, full, 2 * (int)E + it.h * kHD, it.tok0 + j * kKV);
+        }
+      }
+      if (!ok) {
+        ctrl->abort = 1;
+        atomicOr(&g_attn_error, 1);
+      }
+      const uint32_t first = g > (uint32_t)kStages ? g - kStages : 0;  // every issued load must land before exit
+      for (uint32_t k = first; k < g; ++k) ptx::mbar_wait(ptx::smem_u32(&ctrl->full[k % kStages]), (k / kStages) & 1);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t g = 0, n = 0;
+      constexpr uint32_t idesc_pv = ptx::umma_idesc_f16(FMT, kQT, kHD, 0, 1);  // B = V is MN-major
+      for (int64_t i = blockIdx.x; i < total && ok; i += gridDim.x, ++n) {
+        const Item it = decode(i);
+        const uint32_t t_s = tmem_base, t_o = tmem_base + kOCol + (n & 1) * kHD;
+        const uint32_t q_addr = s_q + (n & 1) * kTile;
+        for (int j = 0; j < it.n_blk && ok; ++j, ++g) {
+          const uint32_t s = g % kStages, ph = (g / kStages) & 1;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->full[s]), ph, &ctrl->abort)) { ok = false; break; }
+          // S aliases P of the previous block (possibly of the previous item): its PV must have retired
+          if (g > 0 && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          int nvalid = it.L - j * kKV;
+          nvalid = nvalid > kKV ? kKV : nvalid;
+          const int n1 = (nvalid + 15) & ~15;
+          const uint32_t idesc_qk = ptx::umma_idesc_f16(FMT, kQT, n1);
+          const uint32_t k_addr = s_kv + s * 2 * kTile, v_addr = k_addr + kTile;
+#pragma unroll
+          for (int k = 0; k < kHD / 16; ++k)
+            ptx::umma_f16(t_s, ptx::umma_desc_kmajor_sw128(q_addr + k * 32), ptx::umma_desc_kmajor_sw128(k_addr + k * 32),
+                          idesc_qk, k != 0 ? 1u : 0u);
+          ptx::umma_commit(ptx::smem_u32(&ctrl->s_ready));
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->p_ready), g & 1, &ctrl->abort)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const int ksteps = n1 >> 4;
+          for (int ks = 0; ks < ksteps; ++ks)
+            ptx::umma_f16_ts(t_o, t_s + ks * 8, ptx::umma_desc_mnmajor_sw128(v_addr + ks * 2048), idesc_pv,
+                             (j | ks) != 0 ? 1u : 0u);
+          ptx::umma_commit(ptx::smem_u32(&ctrl->empty[s]));
+          ptx::umma_commit(ptx::smem_u32(&ctrl->o_ready));
+        }
+      }
+      if (!ok) {
+        ctrl->abort = 1;
+        atomicOr(&g_attn_error, 2);
+      }
+      // every MMA issued must have retired before tensor memory is freed
+      ptx::umma_commit(ptx::smem_u32(&ctrl->done));
+      ptx::mbar_wait(ptx::smem_u32(&ctrl->done), 0);
+    }
+  } else {
+    // ------------------------------------------------------------ softmax, one thread per query row
+    const int q = warp & 3;
+    const int row = q * 32 + lane;                   // row inside the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_addr;
+    bool ok = true;
+    uint32_t g = 0, n = 0;
+    for (int64_t i = blockIdx.x; i < total; i += gridDim.x, ++n) {
+      const Item it = decode(i);
+      const bool warp_active = it.q0 + q * 32 < it.L;  // warp-uniform
+      const uint32_t t_o = tmem_base + kOCol + (n & 1) * kHD + lane_addr;
+      float m = -INFINITY, l = 0.0f;
+      for (int j = 0; j < it.n_blk; ++j, ++g) {
+        if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->s_ready), g & 1, &ctrl->abort)) ok = false;
+        if (ok && warp_active) {
+          ptx::tc_fence_after_sync();
+          int nvalid = it.L - j * kKV;
+          nvalid = nvalid > kKV ? kKV : nvalid;
+          const int nchunks = (nvalid + 31) >> 5;
+          // pass 1: row maximum over the valid keys of this block (next chunk's load in flight)
+          float mx = -INFINITY;
+          {
+            uint32_t ra[32], rb[32];
+            ptx::tmem_ld_32x32b_x32(t_s, ra);
+            ptx::tmem_ld_wait();
+            for (int c = 0; c < nchunks; c += 2) {
+              if (c + 1 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 1) * 32, rb);
+#pragma unroll
+              for (int k = 0; k < 32; ++k)
+                if (c * 32 + k < nvalid) mx = fmaxf(mx, __uint_as_float(ra[k]));
+              ptx::tmem_ld_wait();
+              if (c + 2 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 2) * 32, ra);
+              if (c + 1 < nchunks) {
+#pragma unroll
+                for (int k = 0; k < 32; ++k)
+                  if ((c + 1) * 32 + k < nvalid) mx = fmaxf(mx, __uint_as_float(rb[k]));
+              }
+              ptx::tmem_ld_wait();
+            }
+          }
+          const float m_new = fmaxf(m, mx * scale_log2e);
+          const float corr = ptx::ex2_approx(m - m_new);  // 0 for the first block
+          if (j > 0 && __any_sync(0xffffffffu, m_new > m)) {
+            // rescale the running output; PV of the previous block has retired (the MMA warp waited for it
+            // before it issued this block's QK^T).  Skipped when no row of the warp raised its maximum.
+            uint32_t r0[32], r1[32];
+            ptx::tmem_ld_32x32b_x32(t_o, r0);
+            ptx::tmem_ld_32x32b_x32(t_o + 32, r1);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              r0[k] = __float_as_uint(__uint_as_float(r0[k]) * corr);
+              r1[k] = __float_as_uint(__uint_as_float(r1[k]) * corr);
+            }
+            ptx::tmem_st_32x32b_x32(t_o, r0);
+            ptx::tmem_st_32x32b_x32(t_o + 32, r1);
+          }
+          // pass 2: P = exp2(S*scale*log2e - m_new), packed two per column over S columns already consumed
+          float rs = 0.0f;
+          {
+            uint32_t ra[32], rb[32];
+            ptx::tmem_ld_32x32b_x32(t_s, ra);
+            ptx::tmem_ld_wait();
+            for (int c = 0; c < nchunks; c += 2) {
+              if (c + 1 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 1) * 32, rb);
+              uint32_t pk[16];
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                const int k0 = c * 32 + 2 * k;
+                const float p0 = k0 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(ra[2 * k]), scale_log2e, -m_new)) : 0.0f;
+                const float p1 =
+                    k0 + 1 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(ra[2 * k + 1]), scale_log2e, -m_new)) : 0.0f;
+                rs += p0 + p1;
+                pk[k] = pack2<FMT>(p0, p1);
+              }
+              ptx::tmem_ld_wait();  // chunk c+1 is in registers before P overwrites columns [16c, 16c+16)
+              ptx::tmem_st_32x32b_x16(t_s + c * 16, pk);
+              if (c + 1 < nchunks) {
+                if (c + 2 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 2) * 32, ra);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                  const int k0 = (c + 1) * 32 + 2 * k;
+                  const float p0 = k0 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(rb[2 * k]), scale_log2e, -m_new)) : 0.0f;
+                  const float p1 =
+                      k0 + 1 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(rb[2 * k + 1]), scale_log2e, -m_new)) : 0.0f;
+                  rs += p0 + p1;
+                  pk[k] = pack2<FMT>(p0, p1);
+                }
+                ptx::tmem_ld_wait();
+                ptx::tmem_st_32x32b_x16(t_s + (c + 1) * 16, pk);
+              }
+            }
+          }
+          l = l * corr + rs;
+          m = m_new;
+          ptx::tmem_st_wait();
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->p_ready));
+      }
+      // final: O / l -> token-major output rows of this sequence (O buffer n&1; the next item uses the other)
+      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
+      if (ok && warp_active) {
+        ptx::tc_fence_after_sync();
+        const float inv = 1.0f / l;
+        const bool row_valid = it.q0 + row < it.L;
+        uint16_t* orow = reinterpret_cast<uint16_t*>(out) + ((int64_t)it.tok0 + it.q0 + row) * E + (int64_t)it.h * kHD;
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld_32x32b_x32(t_o, r0);
+        ptx::tmem_ld_32x32b_x32(t_o + 32, r1);
+        ptx::tmem_ld_wait();
+        if (row_valid) {
+#pragma unroll
+          for (int gg = 0; gg < 4; ++gg) {
+            uint4 v;
+            v.x = pack2<FMT>(__uint_as_float(r0[gg * 8 + 0]) * inv, __uint_as_float(r0[gg * 8 + 1]) * inv);
+            v.y = pack2<FMT>(__uint_as_float(r0[gg * 8 + 2]) * inv, __uint_as_float(r0[gg * 8 + 3]) * inv);
+            v.z = pack2<FMT>(__uint_as_float(r0[gg * 8 + 4]) * inv, __uint_as_float(r0[gg * 8 + 5]) * inv);
+            v.w = pack2<FMT>(__uint_as_float(r0[gg * 8 + 6]) * inv, __uint_as_float(r0[gg * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + gg * 8) = v;
+          }
+#pragma unroll
+          for (int gg = 0; gg < 4; ++gg) {
+            uint4 v;
+            v.x = pack2<FMT>(__uint_as_float(r1[gg * 8 + 0]) * inv, __uint_as_float(r1[gg * 8 + 1]) * inv);
+            v.y = pack2<FMT>(__uint_as_float(r1[gg * 8 + 2]) * inv, __uint_as_float(r1[gg * 8 + 3]) * inv);
+            v.z = pack2<FMT>(__uint_as_float(r1[gg * 8 + 4]) * inv, __uint_as_float(r1[gg * 8 + 5]) * inv);
+            v.w = pack2<FMT>(__uint_as_float(r1[gg * 8 + 6]) * inv, __uint_as_float(r1[gg * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + 32 + gg * 8) = v;
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      ctrl->abort = 1;
+      atomicOr(&g_attn_error, 4);
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+template <int FMT>
+int launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens, int H, float scaling,
+           int dtype, void* workspace, cudaStream_t st) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return NTB200_LAUNCH_FAILED;
+  const int64_t E = (int64_t)H * kHD;
+  CUtensorMap map;
+  const cuuint64_t gdim[2] = {(cuuint64_t)(3 * E), (cuuint64_t)total_tokens};
+  const cuuint64_t gstride[1] = {(cuuint64_t)(3 * E * 2)};
+  const cuuint32_t box[2] = {(cuuint32_t)kHD, (cuuint32_t)kQT};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == NTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (fn(&map, dt, 2, const_cast<void*>(qkv), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return NTB200_LAUNCH_FAILED;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_tcgen05_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess)
+      return NTB200_LAUNCH_FAILED;
+    attr_set = true;
+  }
+  const int64_t capacity = attn_tcgen05_item_capacity(batch, total_tokens);
+  int* count = static_cast<int*>(workspace);
+  int2* items = reinterpret_cast<int2*>(static_cast<uint8_t*>(workspace) + 16);
+  build_items_kernel<<<1, kListThreads, 0, st>>>(offsets, batch, E, items, count, capacity);
+  int dev = 0, sms = kNumSMs;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t grid = 2ll * sms;  // two resident CTAs per SM, each loops over its share of the items
+  if (grid > capacity * H) grid = capacity * H;
+  attn_tcgen05_kernel<FMT><<<(unsigned)grid, kAttnThreads, kAttnSmem, st>>>(map, out, offsets, items, count, H,
+                                                                            scaling * 1.4426950408889634f);
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // namespace
+
+int64_t attn_tcgen05_item_capacity(int64_t batch, int64_t total_tokens) { return batch + total_tokens / kQT + 1; }
+
+size_t attn_tcgen05_workspace_bytes(int64_t batch, int64_t total_tokens) {
+  return 16 + sizeof(int2) * (size_t)attn_tcgen05_item_capacity(batch, total_tokens);
+}
+
+bool attn_tcgen05_supported(int64_t batch, int64_t total_tokens, int num_heads, int head_dim, int dtype) {
+  return head_dim == kHD && (dtype == NTB200_F16 || dtype == NTB200_BF16) && num_heads <= 65535 &&
+         total_tokens < (1ll << 31) - kQT && 3ll * num_heads * kHD < (1ll << 31) &&
+         attn_tcgen05_item_capacity(batch, total_tokens) < (1ll << 31);
+}
+
+int attn_tcgen05_launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens, int H,
+                        float scaling, int dtype, void* workspace, cudaStream_t st) {
+  if (dtype == NTB200_F16) return launch<0>(qkv, out, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
+  return launch<1>(qkv, out, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
+}
+
+int attn_tcgen05_error_flags_read_and_clear() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace ntb200

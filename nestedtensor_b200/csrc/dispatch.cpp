@@ -457,8 +457,11 @@ Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, boo
   void* st = cur_stream();
   check_rc(ntb200_gemm_bias(buffer.data_ptr(), w_in.data_ptr(), b_in.data_ptr(), qkv.data_ptr(), T, 3 * E, E, dt, 0, st),
            "ntb200_gemm_bias");
+  const size_t ws_bytes = ntb200_varlen_attention_workspace_bytes(r.B, T, (int)num_heads, (int)head_dim, dt);
+  Tensor ws;
+  if (ws_bytes > 0) ws = at::empty({(int64_t)ws_bytes}, buffer.options().dtype(at::kByte));
   check_rc(ntb200_varlen_attention(qkv.data_ptr(), attn.data_ptr(), r.d_offsets, r.B, T, (int)num_heads, (int)head_dim,
-                                   r.max_sizes[0], (float)scaling, dt, 0, st),
+                                   r.max_sizes[0], (float)scaling, dt, 0, ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, st),
            "ntb200_varlen_attention");
   check_rc(ntb200_gemm_bias(attn.data_ptr(), w_out.data_ptr(), b_out, out.data_ptr(), T, E, E, dt, 0, st), "ntb200_gemm_bias");
   return out;

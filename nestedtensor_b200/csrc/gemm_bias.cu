@@ -14,6 +14,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "attention_internal.cuh"
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -414,6 +415,11 @@ int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, in
   return NTB200_UNSUPPORTED_DTYPE;
 }
 
-int ntb200_device_error_flags(void) { return gemm_error_flags_read_and_clear(); }
+int ntb200_device_error_flags(void) {
+  const int g = gemm_error_flags_read_and_clear();
+  const int a = attn_tcgen05_error_flags_read_and_clear();
+  if (g < 0 || a < 0) return -1;
+  return g | (a << 8);
+}
 
 }  // extern "C"

@@ -61,17 +61,22 @@ def test_gemm_bias_fp32(native_libs, cuda_device, M, N, K):
     assert (got - want).abs().max().item() <= 1e-5
 
 
-def _attention(qkv, lengths, H, d, force_simt=0):
+def _attention(qkv, lengths, H, d, path=0):
+    """path 0 = best available, 1 = SIMT, 2 = mma.sync flash kernel, 3 = tcgen05 kernel"""
     lib = _cabi.load()
     E = H * d
     T = qkv.shape[0]
     sizes = torch.tensor([[l, E] for l in lengths], dtype=torch.int64)
     meta = build_meta(sizes, qkv.device)
-    out = torch.empty(T, E, dtype=qkv.dtype, device=qkv.device)
+    out = torch.full((T, E), float("nan"), dtype=qkv.dtype, device=qkv.device)
+    nbytes = lib.ntb200_varlen_attention_workspace_bytes(len(lengths), T, H, d, CODE[qkv.dtype])
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=qkv.device)
     rc = lib.ntb200_varlen_attention(qkv.data_ptr(), out.data_ptr(), meta.data_ptr(), len(lengths), T, H, d, max(lengths),
-                                     float(d) ** -0.5, CODE[qkv.dtype], force_simt, stream_ptr())
+                                     float(d) ** -0.5, CODE[qkv.dtype], path, ws.data_ptr() if nbytes else None, nbytes,
+                                     stream_ptr())
     _cabi.check("ntb200_varlen_attention", rc)
     torch.cuda.synchronize()
+    assert lib.ntb200_device_error_flags() == 0
     return out
 
 
@@ -97,12 +102,23 @@ def test_varlen_attention_d64(native_libs, cuda_device, dtype):
     g = torch.Generator().manual_seed(4)
     qkv = torch.randn(sum(lengths), 3 * H * d, generator=g).to(dtype).to(cuda_device)
     want = _attention_oracle(qkv, lengths, H, d)
-    got = _attention(qkv, lengths, H, d)
+    for path, name in ((3, "tcgen05"), (2, "mma.sync"), (1, "SIMT"), (0, "default")):
+        got = _attention(qkv, lengths, H, d, path=path)
+        err = (got.float().cpu() - want).abs().max().item()
+        assert err <= 2e-2, "%s attention max-abs %g" % (name, err)
+
+
+@pytest.mark.parametrize("lengths", [[1], [128], [129], [256, 1, 255], [300, 512, 700, 1024, 33], [16] * 40 + [1000]],
+                         ids=lambda l: "L" + "_".join(map(str, l[:5])))
+def test_varlen_attention_tcgen05_lengths(native_libs, cuda_device, lengths):
+    """Block boundaries (128 keys / 128 queries), multi-block online softmax and the work-list order."""
+    H, d = 2, 64
+    g = torch.Generator().manual_seed(sum(lengths))
+    qkv = (torch.randn(sum(lengths), 3 * H * d, generator=g) * 1.5).to(torch.bfloat16).to(cuda_device)
+    want = _attention_oracle(qkv, lengths, H, d)
+    got = _attention(qkv, lengths, H, d, path=3)
     err = (got.float().cpu() - want).abs().max().item()
-    assert err <= 2e-2, "tensor-core attention max-abs %g" % err
-    got2 = _attention(qkv, lengths, H, d, force_simt=1)
-    err2 = (got2.float().cpu() - want).abs().max().item()
-    assert err2 <= 2e-2, "SIMT attention max-abs %g" % err2
+    assert err <= 2e-2, "tcgen05 attention max-abs %g" % err
 
 
 @pytest.mark.parametrize("H,d", [(2, 1), (1, 4), (2, 2), (8, 16), (4, 256), (3, 40), (16, 64)])
