@@ -26,20 +26,34 @@ namespace {
 
 __device__ int g_attn_error = 0;  // bit 0 producer, 1 MMA issuer, 2 softmax
 
+#ifdef NTB200_ATTN_TRACE
+// Timing probe (development builds only): SM clock at the phase boundaries of CTA 0's first blocks.
+constexpr int kTraceBlocks = 96, kTraceSlots = 12;
+__device__ long long g_trace[kTraceBlocks * kTraceSlots];
+__device__ long long g_cta_info[1024 * 3];  // per CTA: SM id, start and end time (ns)
+__device__ long long g_pv_issue[32 * 12];   // SM clock before each PV MMA of CTA 0's first blocks
+#define NTB200_TRACE(g, slot) \
+  do { if (blockIdx.x == 0 && (g) < (uint32_t)kTraceBlocks) g_trace[(g) * kTraceSlots + (slot)] = clock64(); } while (0)
+#else
+#define NTB200_TRACE(g, slot) do { } while (0)
+#endif
+
 constexpr int kQT = 128;   // query rows per CTA (TMEM lanes)
 constexpr int kKV = 128;   // keys per block
 constexpr int kHD = 64;    // head dim
 constexpr int kTile = kQT * kHD * 2;  // 16 KB: one 128 x 64 two-byte tile
 constexpr int kStages = 2;
-constexpr int kTmemCols = 256;        // S/P: columns [0,128), O of even items: [128,192), of odd items: [192,256)
-constexpr int kOCol = 128;
-constexpr int kAttnThreads = 192;     // warp 0 TMA, warp 1 MMA, warps 2-5 softmax
+constexpr int kTmemCols = 256;        // S: columns [0,128), P: [128,192), O: [192,256)
+constexpr int kPCol = 128;
+constexpr int kOCol = 192;
+constexpr int kAttnThreads = 256;     // warps 0-3 softmax, warp 4 TMA, warp 5 MMA, warps 6-7 idle
 constexpr int kAttnSmem = 1024 + kTile * (2 + 2 * kStages) + 256;  // 2 Q buffers + 2 stages of (K, V)
 
 struct Ctrl {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t s_ready;
+  uint64_t s_free;
   uint64_t p_ready;
   uint64_t o_ready;
   uint64_t done;
@@ -71,13 +85,14 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // ------------------------------------------------------------------ work list
-// items[i] = (sequence, first query row) for every 128-query tile, ordered by decreasing number of key
-// blocks so that the longest CTAs start first; *count = number of items.  One block.
+// items[i] = (first token of the sequence, first query row, sequence length, sequence index) for every
+// 128-query tile, ordered by decreasing number of key blocks so that the longest items start first;
+// *count = number of items.  One block.
 constexpr int kListThreads = 1024;
 constexpr int kBuckets = 9;  // key blocks 1..8+, (0 unused)
 
 __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t* __restrict__ offsets, int64_t batch,
-                                                                   int64_t row_elems, int2* __restrict__ items,
+                                                                   int64_t row_elems, int4* __restrict__ items,
                                                                    int* __restrict__ count, int64_t capacity) {
   __shared__ int s_cnt[kBuckets];
   __shared__ int s_base[kBuckets];
@@ -108,22 +123,37 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
     int nb = (int)((L + kKV - 1) / kKV);
     nb = nb >= kBuckets ? kBuckets - 1 : nb;
     const int pos = atomicAdd(&s_base[nb], nq);
+    const int tok0 = (int)(offsets[b] / row_elems);
     for (int t = 0; t < nq; ++t)
-      if (pos + t < capacity) items[pos + t] = make_int2((int)b, t * kQT);
+      if (pos + t < capacity) items[pos + t] = make_int4(tok0, t * kQT, (int)L, (int)b);
   }
 }
 
 // ------------------------------------------------------------------ attention
 // Persistent: CTA c works on items c, c + gridDim.x, ... of the flattened (work item, head) list.  All
-// barriers run on one global block counter g (one phase per 128-key block), Q and O alternate between two
-// buffers per item, K/V between two stages per block, so the producer and the MMA warp run ahead into the
-// next item while the softmax warps finish the current one.
+// barriers run on one global block counter g (one phase per 128-key block).
+//   warps 0-3  softmax warpgroup (one thread per query row; registers raised with setmaxnreg so a whole
+//              128-key row of S lives in registers: S is read from tensor memory ONCE per block)
+//   warp 4     TMA producer   warp 5  MMA issuer   warps 6-7  idle (they only give their registers away)
+// Tensor memory (256 columns): S [0,128) fp32, P [128,192) packed 16-bit, O [192,256) fp32.  P has its own
+// columns, so QK^T of block g+1 is issued as soon as the softmax warps have read S of block g
+// (s_free), before PV of block g: the tensor pipe works under the softmax of the same CTA.
+// Two 256-thread CTAs per SM at 128 registers per thread; the control warpgroup then drops to 48 and the
+// softmax warpgroup rises to 208.
 template <int FMT>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restrict__ out, const int64_t* __restrict__ offsets,
-                    const int2* __restrict__ items, const int* __restrict__ count, int H, float scale_log2e) {
+                    const int4* __restrict__ items, const int* __restrict__ count, int H, float scale_log2e) {
   const int64_t total = (int64_t)(*count) * H;
   if ((int64_t)blockIdx.x >= total) return;
+#ifdef NTB200_ATTN_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    g_cta_info[blockIdx.x * 3 + 0] = smid;
+    g_cta_info[blockIdx.x * 3 + 1] = (long long)ptx::globaltimer_ns();
+  }
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kTile * (2 + 2 * kStages));
@@ -136,6 +166,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
     }
     ptx::mbar_init(ptx::smem_u32(&ctrl->s_ready), 1);
+    ptx::mbar_init(ptx::smem_u32(&ctrl->s_free), 4);
     ptx::mbar_init(ptx::smem_u32(&ctrl->p_ready), 4);
     ptx::mbar_init(ptx::smem_u32(&ctrl->o_ready), 1);
     ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
@@ -143,7 +174,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_qkv);
   }
-  if (warp == 1) {
+  if (warp == 5) {
     ptx::tmem_alloc(ptx::smem_u32(&ctrl->tmem_base), kTmemCols);
     ptx::tmem_relinquish();
     ptx::tc_fence_before_sync();
@@ -154,29 +185,33 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
   const uint32_t s_q = ptx::smem_u32(smem);          // two Q buffers
   const uint32_t s_kv = s_q + 2 * kTile;             // stage s: K at s_kv + s*2*kTile, V right after it
 
-  // decode of flattened item i -> sequence geometry
+  // One 16-byte record per work item; every role fetches the record of its NEXT item while it works on
+  // the current one, so the load latency never sits on a critical path.
   struct Item {
     int q0, h, L, tok0, n_blk;
   };
-  auto decode = [&](int64_t i) {
+  auto fetch = [&](int64_t i) { return i < total ? __ldg(items + i / H) : make_int4(0, 0, 1, 0); };
+  auto decode = [&](int64_t i, const int4& w) {
     Item it;
-    const int2 w = items[i / H];
     it.h = (int)(i % H);
+    it.tok0 = w.x;
     it.q0 = w.y;
-    const int64_t off_b = offsets[w.x];
-    it.L = (int)((offsets[w.x + 1] - off_b) / E);
-    it.tok0 = (int)(off_b / E);
-    it.n_blk = (it.L + kKV - 1) / kKV;
+    it.L = w.z;
+    it.n_blk = (w.z + kKV - 1) / kKV;
     return it;
   };
+  const int64_t G = gridDim.x;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+  if (warp >= 4) {
+    ptx::setmaxnreg_dec<48>();
+    if (warp == 4 && ptx::elect_one()) {
+      // ------------------------------------------------------------ TMA producer
       bool ok = true;
       uint32_t g = 0, n = 0;
-      for (int64_t i = blockIdx.x; i < total && ok; i += gridDim.x, ++n) {
-        const Item it = decode(i);
+      int4 rec = fetch(blockIdx.x);
+      for (int64_t i = blockIdx.x; i < total && ok; i += G, ++n) {
+        const Item it = decode(i, rec);
+        rec = fetch(i + G);
         for (int j = 0; j < it.n_blk; ++j, ++g) {
           const uint32_t s = g % kStages, ph = (g / kStages) & 1;
           if (!wait_or_abort(ptx::smem_u32(&ctrl->empty[s]), ph ^ 1, &ctrl->abort)) {
@@ -185,7 +220,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           }
           const uint32_t full = ptx::smem_u32(&ctrl->full[s]);
           ptx::mbar_arrive_expect_tx(full, (j == 0 ? 3 : 2) * kTile);
-          // the Q buffer of item n was last read by item n-2, whose MMAs all precede the release of this stage
+          // Q buffer n&1 was last read by item n-2; every MMA of that item precedes the release of this stage
           if (j == 0) ptx::tma_load_2d(s_q + (n & 1) * kTile, &map_qkv, full, it.h * kHD, it.tok0 + it.q0);
           ptx::tma_load_2d(s_kv + s * 2 * kTile, &map_qkv, full, (int)E + it.h * kHD, it.tok0 + j * kKV);
           ptx::tma_load_2d(s_kv + s * 2 * kTile + kTile, &map_qkv, full, 2 * (int)E + it.h * kHD, it.tok0 + j * kKV);
@@ -197,41 +232,84 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       }
       const uint32_t first = g > (uint32_t)kStages ? g - kStages : 0;  // every issued load must land before exit
       for (uint32_t k = first; k < g; ++k) ptx::mbar_wait(ptx::smem_u32(&ctrl->full[k % kStages]), (k / kStages) & 1);
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    } else if (warp == 5 && ptx::elect_one()) {
+      // ------------------------------------------------------------ MMA issuer
       bool ok = true;
-      uint32_t g = 0, n = 0;
+      const uint32_t t_s = tmem_base, t_p = tmem_base + kPCol, t_o = tmem_base + kOCol;
       constexpr uint32_t idesc_pv = ptx::umma_idesc_f16(FMT, kQT, kHD, 0, 1);  // B = V is MN-major
-      for (int64_t i = blockIdx.x; i < total && ok; i += gridDim.x, ++n) {
-        const Item it = decode(i);
-        const uint32_t t_s = tmem_base, t_o = tmem_base + kOCol + (n & 1) * kHD;
-        const uint32_t q_addr = s_q + (n & 1) * kTile;
-        for (int j = 0; j < it.n_blk && ok; ++j, ++g) {
-          const uint32_t s = g % kStages, ph = (g / kStages) & 1;
-          if (!wait_or_abort(ptx::smem_u32(&ctrl->full[s]), ph, &ctrl->abort)) { ok = false; break; }
-          // S aliases P of the previous block (possibly of the previous item): its PV must have retired
-          if (g > 0 && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
-          int nvalid = it.L - j * kKV;
-          nvalid = nvalid > kKV ? kKV : nvalid;
-          const int n1 = (nvalid + 15) & ~15;
-          const uint32_t idesc_qk = ptx::umma_idesc_f16(FMT, kQT, n1);
-          const uint32_t k_addr = s_kv + s * 2 * kTile, v_addr = k_addr + kTile;
+      const uint64_t desc_q0 = ptx::umma_desc_kmajor_sw128(s_q);
+      const uint64_t desc_k0 = ptx::umma_desc_kmajor_sw128(s_kv);
+      const uint64_t desc_v0 = ptx::umma_desc_mnmajor_sw128(s_kv + kTile);
+      // cursor A: the block whose QK^T is issued next (runs one block ahead of cursor B: PV)
+      int64_t ia = blockIdx.x;
+      uint32_t ga = 0, na = 0;
+      int ja = 0;
+      Item a = decode(ia, fetch(ia));
+      int4 rec_a = fetch(ia + G);
+      auto issue_qk = [&]() -> bool {
+        const uint32_t s = ga % kStages, ph = (ga / kStages) & 1;
+        NTB200_TRACE(ga, 0);
+        if (!wait_or_abort(ptx::smem_u32(&ctrl->full[s]), ph, &ctrl->abort)) return false;
+        NTB200_TRACE(ga, 1);
+        ptx::tc_fence_after_sync();
+        int nvalid = a.L - ja * kKV;
+        nvalid = nvalid > kKV ? kKV : nvalid;
+        const uint32_t idesc_qk = ptx::umma_idesc_f16(FMT, kQT, (nvalid + 15) & ~15);
+        const uint64_t dq = desc_q0 + (uint64_t)((na & 1) * (kTile >> 4));
+        const uint64_t dk = desc_k0 + (uint64_t)(s * (2 * kTile >> 4));
 #pragma unroll
-          for (int k = 0; k < kHD / 16; ++k)
-            ptx::umma_f16(t_s, ptx::umma_desc_kmajor_sw128(q_addr + k * 32), ptx::umma_desc_kmajor_sw128(k_addr + k * 32),
-                          idesc_qk, k != 0 ? 1u : 0u);
-          ptx::umma_commit(ptx::smem_u32(&ctrl->s_ready));
-          if (!wait_or_abort(ptx::smem_u32(&ctrl->p_ready), g & 1, &ctrl->abort)) { ok = false; break; }
+        for (int k = 0; k < kHD / 16; ++k) ptx::umma_f16(t_s, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0 ? 1u : 0u);
+        ptx::umma_commit(ptx::smem_u32(&ctrl->s_ready));
+        NTB200_TRACE(ga, 2);
+        ++ga;
+        if (++ja == a.n_blk) {
+          ja = 0;
+          ++na;
+          ia += G;
+          a = decode(ia, rec_a);
+          rec_a = fetch(ia + G);
+        }
+        return true;
+      };
+      ok = issue_qk();
+      uint32_t gb = 0;
+      int4 rec_b = fetch(blockIdx.x);
+      for (int64_t ib = blockIdx.x; ib < total && ok; ib += G) {
+        const Item b = decode(ib, rec_b);
+        rec_b = fetch(ib + G);
+        for (int jb = 0; jb < b.n_blk && ok; ++jb, ++gb) {
+          // S of block gb is in the softmax warps' registers: the next QK^T may overwrite it
+          if (ia < total) {
+            if (!wait_or_abort(ptx::smem_u32(&ctrl->s_free), gb & 1, &ctrl->abort)) { ok = false; break; }
+            if (!issue_qk()) { ok = false; break; }
+          }
+          NTB200_TRACE(gb, 3);
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->p_ready), gb & 1, &ctrl->abort)) { ok = false; break; }
+          NTB200_TRACE(gb, 4);
           ptx::tc_fence_after_sync();
-          const int ksteps = n1 >> 4;
-          for (int ks = 0; ks < ksteps; ++ks)
-            ptx::umma_f16_ts(t_o, t_s + ks * 8, ptx::umma_desc_mnmajor_sw128(v_addr + ks * 2048), idesc_pv,
-                             (j | ks) != 0 ? 1u : 0u);
+          const uint32_t s = gb % kStages;
+          int nvalid = b.L - jb * kKV;
+          nvalid = nvalid > kKV ? kKV : nvalid;
+          const int ksteps = (nvalid + 15) >> 4;
+          const uint64_t dv = desc_v0 + (uint64_t)(s * (2 * kTile >> 4));
+          for (int ks = 0; ks < ksteps; ++ks) {
+#ifdef NTB200_ATTN_TRACE
+            if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + ks] = clock64();
+#endif
+            ptx::umma_f16_ts(t_o, t_p + ks * 8, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (jb | ks) != 0 ? 1u : 0u);
+          }
+#ifdef NTB200_ATTN_TRACE
+          if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 8] = clock64();
+#endif
           ptx::umma_commit(ptx::smem_u32(&ctrl->empty[s]));
+#ifdef NTB200_ATTN_TRACE
+          if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 9] = clock64();
+#endif
           ptx::umma_commit(ptx::smem_u32(&ctrl->o_ready));
+#ifdef NTB200_ATTN_TRACE
+          if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 10] = clock64();
+#endif
+          NTB200_TRACE(gb, 5);
         }
       }
       if (!ok) {
@@ -244,107 +322,125 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
     }
   } else {
     // ------------------------------------------------------------ softmax, one thread per query row
-    const int q = warp & 3;
+    ptx::setmaxnreg_inc<208>();
+    const int q = warp;                              // TMEM lane quarter of this warp
     const int row = q * 32 + lane;                   // row inside the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_addr;
+    const uint32_t t_s = tmem_base + lane_addr, t_p = tmem_base + kPCol + lane_addr, t_o = tmem_base + kOCol + lane_addr;
     bool ok = true;
-    uint32_t g = 0, n = 0;
-    for (int64_t i = blockIdx.x; i < total; i += gridDim.x, ++n) {
-      const Item it = decode(i);
+    uint32_t g = 0;
+    int4 rec = fetch(blockIdx.x);
+    for (int64_t i = blockIdx.x; i < total; i += G) {
+      const Item it = decode(i, rec);
+      rec = fetch(i + G);
       const bool warp_active = it.q0 + q * 32 < it.L;  // warp-uniform
-      const uint32_t t_o = tmem_base + kOCol + (n & 1) * kHD + lane_addr;
       float m = -INFINITY, l = 0.0f;
       for (int j = 0; j < it.n_blk; ++j, ++g) {
+        if (threadIdx.x == 0) NTB200_TRACE(g, 6);
         if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->s_ready), g & 1, &ctrl->abort)) ok = false;
+        if (threadIdx.x == 0) NTB200_TRACE(g, 7);
+        int nvalid = it.L - j * kKV;
+        nvalid = nvalid > kKV ? kKV : nvalid;
+        const int nchunks = (nvalid + 31) >> 5;
+        uint32_t sv[4][32];  // the whole row of S (up to 128 keys) in registers
         if (ok && warp_active) {
           ptx::tc_fence_after_sync();
-          int nvalid = it.L - j * kKV;
-          nvalid = nvalid > kKV ? kKV : nvalid;
-          const int nchunks = (nvalid + 31) >> 5;
-          // pass 1: row maximum over the valid keys of this block (next chunk's load in flight)
-          float mx = -INFINITY;
-          {
-            uint32_t ra[32], rb[32];
-            ptx::tmem_ld_32x32b_x32(t_s, ra);
-            ptx::tmem_ld_wait();
-            for (int c = 0; c < nchunks; c += 2) {
-              if (c + 1 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 1) * 32, rb);
+          ptx::tmem_ld_32x32b_x32(t_s, sv[0]);
+          if (nchunks > 1) ptx::tmem_ld_32x32b_x32(t_s + 32, sv[1]);
+          if (nchunks > 2) ptx::tmem_ld_32x32b_x32(t_s + 64, sv[2]);
+          if (nchunks > 3) ptx::tmem_ld_32x32b_x32(t_s + 96, sv[3]);
+          ptx::tmem_ld_wait();
+        }
+        // S has been consumed: the MMA warp may issue the next block's QK^T
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->s_free));
+        if (threadIdx.x == 0) NTB200_TRACE(g, 8);
+        float m_new = m, corr = 1.0f;
+        bool any_up = false;
+        if (ok && warp_active) {
+          // row maximum over the valid keys, four independent chains
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-              for (int k = 0; k < 32; ++k)
-                if (c * 32 + k < nvalid) mx = fmaxf(mx, __uint_as_float(ra[k]));
-              ptx::tmem_ld_wait();
-              if (c + 2 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 2) * 32, ra);
-              if (c + 1 < nchunks) {
+          for (int c = 0; c < 4; ++c) {
+            if (c < nchunks) {
+              if ((c + 1) * 32 <= nvalid) {
+#pragma unroll
+                for (int k = 0; k < 32; k += 4) {
+                  mx0 = fmaxf(mx0, __uint_as_float(sv[c][k]));
+                  mx1 = fmaxf(mx1, __uint_as_float(sv[c][k + 1]));
+                  mx2 = fmaxf(mx2, __uint_as_float(sv[c][k + 2]));
+                  mx3 = fmaxf(mx3, __uint_as_float(sv[c][k + 3]));
+                }
+              } else {
 #pragma unroll
                 for (int k = 0; k < 32; ++k)
-                  if ((c + 1) * 32 + k < nvalid) mx = fmaxf(mx, __uint_as_float(rb[k]));
+                  if (c * 32 + k < nvalid) mx0 = fmaxf(mx0, __uint_as_float(sv[c][k]));
               }
+            }
+          }
+          const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+          m_new = fmaxf(m, mx * scale_log2e);
+          corr = ptx::ex2_approx(m - m_new);  // 0 for the first block
+          any_up = __any_sync(0xffffffffu, m_new > m);
+        }
+        if (threadIdx.x == 0) NTB200_TRACE(g, 9);
+        // PV of the previous block must have retired before P is overwritten / O is rescaled
+        if (ok && g > 0 && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
+        if (ok && warp_active) {
+          ptx::tc_fence_after_sync();
+          if (j > 0 && any_up) {
+            // rescale the running output (skipped when no row of the warp raised its maximum)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {  // 16 columns at a time: the S row stays live in registers
+              uint32_t r0[16];
+              ptx::tmem_ld_32x32b_x16(t_o + c * 16, r0);
               ptx::tmem_ld_wait();
-            }
-          }
-          const float m_new = fmaxf(m, mx * scale_log2e);
-          const float corr = ptx::ex2_approx(m - m_new);  // 0 for the first block
-          if (j > 0 && __any_sync(0xffffffffu, m_new > m)) {
-            // rescale the running output; PV of the previous block has retired (the MMA warp waited for it
-            // before it issued this block's QK^T).  Skipped when no row of the warp raised its maximum.
-            uint32_t r0[32], r1[32];
-            ptx::tmem_ld_32x32b_x32(t_o, r0);
-            ptx::tmem_ld_32x32b_x32(t_o + 32, r1);
-            ptx::tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 32; ++k) {
-              r0[k] = __float_as_uint(__uint_as_float(r0[k]) * corr);
-              r1[k] = __float_as_uint(__uint_as_float(r1[k]) * corr);
+              for (int k = 0; k < 16; ++k) r0[k] = __float_as_uint(__uint_as_float(r0[k]) * corr);
+              ptx::tmem_st_32x32b_x16(t_o + c * 16, r0);
             }
-            ptx::tmem_st_32x32b_x32(t_o, r0);
-            ptx::tmem_st_32x32b_x32(t_o + 32, r1);
           }
-          // pass 2: P = exp2(S*scale*log2e - m_new), packed two per column over S columns already consumed
+          if (threadIdx.x == 0) NTB200_TRACE(g, 10);
+          // P = exp2(S*scale*log2e - m_new), packed two per column
           float rs = 0.0f;
-          {
-            uint32_t ra[32], rb[32];
-            ptx::tmem_ld_32x32b_x32(t_s, ra);
-            ptx::tmem_ld_wait();
-            for (int c = 0; c < nchunks; c += 2) {
-              if (c + 1 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 1) * 32, rb);
-              uint32_t pk[16];
 #pragma unroll
-              for (int k = 0; k < 16; ++k) {
-                const int k0 = c * 32 + 2 * k;
-                const float p0 = k0 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(ra[2 * k]), scale_log2e, -m_new)) : 0.0f;
-                const float p1 =
-                    k0 + 1 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(ra[2 * k + 1]), scale_log2e, -m_new)) : 0.0f;
-                rs += p0 + p1;
-                pk[k] = pack2<FMT>(p0, p1);
-              }
-              ptx::tmem_ld_wait();  // chunk c+1 is in registers before P overwrites columns [16c, 16c+16)
-              ptx::tmem_st_32x32b_x16(t_s + c * 16, pk);
-              if (c + 1 < nchunks) {
-                if (c + 2 < nchunks) ptx::tmem_ld_32x32b_x32(t_s + (c + 2) * 32, ra);
+          for (int c = 0; c < 4; ++c) {
+            if (c < nchunks) {
+              uint32_t pk[16];
+              if ((c + 1) * 32 <= nvalid) {
 #pragma unroll
                 for (int k = 0; k < 16; ++k) {
-                  const int k0 = (c + 1) * 32 + 2 * k;
-                  const float p0 = k0 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(rb[2 * k]), scale_log2e, -m_new)) : 0.0f;
-                  const float p1 =
-                      k0 + 1 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(rb[2 * k + 1]), scale_log2e, -m_new)) : 0.0f;
+                  const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k]), scale_log2e, -m_new));
+                  const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k + 1]), scale_log2e, -m_new));
                   rs += p0 + p1;
                   pk[k] = pack2<FMT>(p0, p1);
                 }
-                ptx::tmem_ld_wait();
-                ptx::tmem_st_32x32b_x16(t_s + (c + 1) * 16, pk);
+              } else {
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                  const int k0 = c * 32 + 2 * k;
+                  const float p0 = k0 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k]), scale_log2e, -m_new)) : 0.0f;
+                  const float p1 =
+                      k0 + 1 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k + 1]), scale_log2e, -m_new)) : 0.0f;
+                  rs += p0 + p1;
+                  pk[k] = pack2<FMT>(p0, p1);
+                }
               }
+              ptx::tmem_st_32x32b_x16(t_p + c * 16, pk);
             }
           }
           l = l * corr + rs;
           m = m_new;
           ptx::tmem_st_wait();
+          if (threadIdx.x == 0) NTB200_TRACE(g, 11);
         }
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->p_ready));
       }
-      // final: O / l -> token-major output rows of this sequence (O buffer n&1; the next item uses the other)
+      // final: O / l -> token-major output rows of this sequence.  The next item's first PV (which
+      // overwrites O) is issued only after these warps arrive at its p_ready, i.e. after this read.
       if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
       if (ok && warp_active) {
         ptx::tc_fence_after_sync();
@@ -385,7 +481,10 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+#ifdef NTB200_ATTN_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta_info[blockIdx.x * 3 + 2] = (long long)ptx::globaltimer_ns();
+#endif
+  if (warp == 5) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -430,7 +529,7 @@ int launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, in
   }
   const int64_t capacity = attn_tcgen05_item_capacity(batch, total_tokens);
   int* count = static_cast<int*>(workspace);
-  int2* items = reinterpret_cast<int2*>(static_cast<uint8_t*>(workspace) + 16);
+  int4* items = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + 16);
   build_items_kernel<<<1, kListThreads, 0, st>>>(offsets, batch, E, items, count, capacity);
   int dev = 0, sms = kNumSMs;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -446,7 +545,7 @@ int launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, in
 int64_t attn_tcgen05_item_capacity(int64_t batch, int64_t total_tokens) { return batch + total_tokens / kQT + 1; }
 
 size_t attn_tcgen05_workspace_bytes(int64_t batch, int64_t total_tokens) {
-  return 16 + sizeof(int2) * (size_t)attn_tcgen05_item_capacity(batch, total_tokens);
+  return 16 + sizeof(int4) * (size_t)attn_tcgen05_item_capacity(batch, total_tokens);
 }
 
 bool attn_tcgen05_supported(int64_t batch, int64_t total_tokens, int num_heads, int head_dim, int dtype) {
@@ -460,6 +559,33 @@ int attn_tcgen05_launch(const void* qkv, void* out, const int64_t* offsets, int6
   if (dtype == NTB200_F16) return launch<0>(qkv, out, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
   return launch<1>(qkv, out, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
 }
+
+#ifdef NTB200_ATTN_TRACE
+extern "C" int ntb200_attn_occupancy2(int threads, int smem) {
+  int nb = -1;
+  cudaFuncSetAttribute(attn_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, attn_tcgen05_kernel<1>, threads, smem);
+  return nb;
+}
+extern "C" int ntb200_attn_occupancy(void) {
+  int nb = -1;
+  cudaFuncSetAttribute(attn_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, attn_tcgen05_kernel<1>, kAttnThreads, kAttnSmem);
+  cudaFuncAttributes fa;
+  cudaFuncGetAttributes(&fa, attn_tcgen05_kernel<1>);
+  return nb * 1000 + fa.numRegs;
+}
+extern "C" int ntb200_attn_pv_issue_read(long long* h_out, int n) {
+  return cudaMemcpyFromSymbol(h_out, g_pv_issue, sizeof(long long) * (n < 384 ? n : 384)) == cudaSuccess ? 0 : -1;
+}
+extern "C" int ntb200_attn_cta_info_read(long long* h_out, int n) {
+  return cudaMemcpyFromSymbol(h_out, g_cta_info, sizeof(long long) * (n < 3072 ? n : 3072)) == cudaSuccess ? 0 : -1;
+}
+extern "C" int ntb200_attn_trace_read(long long* h_out, int n) {
+  const int total = kTraceBlocks * kTraceSlots;
+  return cudaMemcpyFromSymbol(h_out, g_trace, sizeof(long long) * (n < total ? n : total)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int attn_tcgen05_error_flags_read_and_clear() {
   int v = 0;

@@ -119,7 +119,7 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (ptx::elect_one()) {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -147,7 +147,7 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (ptx::elect_one()) {
       constexpr uint32_t idesc = ptx::umma_idesc_f16(FMT, kBM, kBN);
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
