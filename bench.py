@@ -291,7 +291,7 @@ def run_copy(args, kind, rank, world, local):
     line = None
     if rank == 0:
         cpu = None
-        if world == 1 or True:
+        if world == 1:  # the CPU baseline is a single-GPU-run figure; other ranks would compete for the cores
             seqs = 256
             if kind == "pad":
                 _, nbytes, fn = cpu_pad_sample(L, hidden, dtype, seqs)

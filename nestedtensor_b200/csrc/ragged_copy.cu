@@ -16,8 +16,14 @@
 namespace ntb200 {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kVecPerThread = 4;  // 16-byte vectors per thread per tile
+#ifndef NTB200_COPY_THREADS
+#define NTB200_COPY_THREADS 256
+#endif
+#ifndef NTB200_COPY_VECS
+#define NTB200_COPY_VECS 8
+#endif
+constexpr int kThreads = NTB200_COPY_THREADS;
+constexpr int kVecPerThread = NTB200_COPY_VECS;  // 16-byte vectors per thread per tile (32 KB tiles measured best)
 
 // ------------------------------------------------------------------------------ pad
 struct PadParams {
