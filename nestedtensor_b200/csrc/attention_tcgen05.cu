@@ -28,7 +28,7 @@ __device__ int g_attn_error = 0;  // bit 0 producer, 1 MMA issuer, 2 softmax
 
 #ifdef NTB200_ATTN_TRACE
 // Timing probe (development builds only): SM clock at the phase boundaries of CTA 0's first blocks.
-constexpr int kTraceBlocks = 96, kTraceSlots = 12;
+constexpr int kTraceBlocks = 96, kTraceSlots = 16;
 __device__ long long g_trace[kTraceBlocks * kTraceSlots];
 __device__ long long g_cta_info[1024 * 3];  // per CTA: SM id, start and end time (ns)
 __device__ long long g_pv_issue[32 * 12];   // SM clock before each PV MMA of CTA 0's first blocks
@@ -50,8 +50,10 @@ constexpr int kAttnThreads = 256;     // warps 0-3 softmax, warp 4 TMA, warp 5 M
 constexpr int kAttnSmem = 1024 + kTile * (2 + 2 * kStages) + 256;  // 2 Q buffers + 2 stages of (K, V)
 
 struct Ctrl {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full_k[kStages];   // K tile (plus Q with the first block of an item) landed
+  uint64_t empty_k[kStages];  // QK^T of that stage retired: K (and the Q buffer two items back) reusable
+  uint64_t full_v[kStages];
+  uint64_t empty_v[kStages];  // PV of that stage retired and the softmax warps are done with it (output staging)
   uint64_t s_ready;
   uint64_t s_free;
   uint64_t p_ready;
@@ -162,8 +164,10 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->full_k[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->empty_k[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->full_v[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->empty_v[s]), 5);  // PV commit + the four softmax warps
     }
     ptx::mbar_init(ptx::smem_u32(&ctrl->s_ready), 1);
     ptx::mbar_init(ptx::smem_u32(&ctrl->s_free), 4);
@@ -183,7 +187,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
   const uint32_t s_q = ptx::smem_u32(smem);          // two Q buffers
-  const uint32_t s_kv = s_q + 2 * kTile;             // stage s: K at s_kv + s*2*kTile, V right after it
+  const uint32_t s_k = s_q + 2 * kTile;              // K ring: stage s at s_k + s*kTile
+  const uint32_t s_v = s_k + kStages * kTile;        // V ring: stage s at s_v + s*kTile
 
   // One 16-byte record per work item; every role fetches the record of its NEXT item while it works on
   // the current one, so the load latency never sits on a critical path.
@@ -214,32 +219,46 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         rec = fetch(i + G);
         for (int j = 0; j < it.n_blk; ++j, ++g) {
           const uint32_t s = g % kStages, ph = (g / kStages) & 1;
-          if (!wait_or_abort(ptx::smem_u32(&ctrl->empty[s]), ph ^ 1, &ctrl->abort)) {
+          // K (and Q) as soon as the QK^T that last read this stage has retired ...
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->empty_k[s]), ph ^ 1, &ctrl->abort)) {
             ok = false;
             break;
           }
-          const uint32_t full = ptx::smem_u32(&ctrl->full[s]);
-          ptx::mbar_arrive_expect_tx(full, (j == 0 ? 3 : 2) * kTile);
-          // Q buffer n&1 was last read by item n-2; every MMA of that item precedes the release of this stage
-          if (j == 0) ptx::tma_load_2d(s_q + (n & 1) * kTile, &map_qkv, full, it.h * kHD, it.tok0 + it.q0);
-          ptx::tma_load_2d(s_kv + s * 2 * kTile, &map_qkv, full, (int)E + it.h * kHD, it.tok0 + j * kKV);
-          ptx::tma_load_2d(s_kv + s * 2 * kTile + kTile, &map_qkv, full, 2 * (int)E + it.h * kHD, it.tok0 + j * kKV);
+          const uint32_t fk = ptx::smem_u32(&ctrl->full_k[s]);
+          ptx::mbar_arrive_expect_tx(fk, (j == 0 ? 2 : 1) * kTile);
+          // Q buffer n&1 was last read by item n-2, all of whose QK^T precede the release of this stage
+          if (j == 0) ptx::tma_load_2d(s_q + (n & 1) * kTile, &map_qkv, fk, it.h * kHD, it.tok0 + it.q0);
+          ptx::tma_load_2d(s_k + s * kTile, &map_qkv, fk, (int)E + it.h * kHD, it.tok0 + j * kKV);
+          // ... V only once the PV that last read its stage has retired
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->empty_v[s]), ph ^ 1, &ctrl->abort)) {
+            ok = false;
+            ++g;  // the K load of this block was issued: include it in the drain below
+            break;
+          }
+          const uint32_t fv = ptx::smem_u32(&ctrl->full_v[s]);
+          ptx::mbar_arrive_expect_tx(fv, kTile);
+          ptx::tma_load_2d(s_v + s * kTile, &map_qkv, fv, 2 * (int)E + it.h * kHD, it.tok0 + j * kKV);
         }
       }
       if (!ok) {
         ctrl->abort = 1;
         atomicOr(&g_attn_error, 1);
       }
-      const uint32_t first = g > (uint32_t)kStages ? g - kStages : 0;  // every issued load must land before exit
-      for (uint32_t k = first; k < g; ++k) ptx::mbar_wait(ptx::smem_u32(&ctrl->full[k % kStages]), (k / kStages) & 1);
+      // every issued load must land before exit (a V load that was never issued after an abort cannot
+      // complete; that wait is bounded and runs out)
+      const uint32_t first = g > (uint32_t)kStages ? g - kStages : 0;
+      for (uint32_t k = first; k < g; ++k) {
+        ptx::mbar_wait(ptx::smem_u32(&ctrl->full_k[k % kStages]), (k / kStages) & 1);
+        if (ok) ptx::mbar_wait(ptx::smem_u32(&ctrl->full_v[k % kStages]), (k / kStages) & 1);
+      }
     } else if (warp == 5 && ptx::elect_one()) {
       // ------------------------------------------------------------ MMA issuer
       bool ok = true;
       const uint32_t t_s = tmem_base, t_p = tmem_base + kPCol, t_o = tmem_base + kOCol;
       constexpr uint32_t idesc_pv = ptx::umma_idesc_f16(FMT, kQT, kHD, 0, 1);  // B = V is MN-major
       const uint64_t desc_q0 = ptx::umma_desc_kmajor_sw128(s_q);
-      const uint64_t desc_k0 = ptx::umma_desc_kmajor_sw128(s_kv);
-      const uint64_t desc_v0 = ptx::umma_desc_mnmajor_sw128(s_kv + kTile);
+      const uint64_t desc_k0 = ptx::umma_desc_kmajor_sw128(s_k);
+      const uint64_t desc_v0 = ptx::umma_desc_mnmajor_sw128(s_v);
       // cursor A: the block whose QK^T is issued next (runs one block ahead of cursor B: PV)
       int64_t ia = blockIdx.x;
       uint32_t ga = 0, na = 0;
@@ -249,16 +268,17 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       auto issue_qk = [&]() -> bool {
         const uint32_t s = ga % kStages, ph = (ga / kStages) & 1;
         NTB200_TRACE(ga, 0);
-        if (!wait_or_abort(ptx::smem_u32(&ctrl->full[s]), ph, &ctrl->abort)) return false;
+        if (!wait_or_abort(ptx::smem_u32(&ctrl->full_k[s]), ph, &ctrl->abort)) return false;
         NTB200_TRACE(ga, 1);
         ptx::tc_fence_after_sync();
         int nvalid = a.L - ja * kKV;
         nvalid = nvalid > kKV ? kKV : nvalid;
         const uint32_t idesc_qk = ptx::umma_idesc_f16(FMT, kQT, (nvalid + 15) & ~15);
         const uint64_t dq = desc_q0 + (uint64_t)((na & 1) * (kTile >> 4));
-        const uint64_t dk = desc_k0 + (uint64_t)(s * (2 * kTile >> 4));
+        const uint64_t dk = desc_k0 + (uint64_t)(s * (kTile >> 4));
 #pragma unroll
         for (int k = 0; k < kHD / 16; ++k) ptx::umma_f16(t_s, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0 ? 1u : 0u);
+        ptx::umma_commit(ptx::smem_u32(&ctrl->empty_k[s]));
         ptx::umma_commit(ptx::smem_u32(&ctrl->s_ready));
         NTB200_TRACE(ga, 2);
         ++ga;
@@ -286,12 +306,13 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           NTB200_TRACE(gb, 3);
           if (!wait_or_abort(ptx::smem_u32(&ctrl->p_ready), gb & 1, &ctrl->abort)) { ok = false; break; }
           NTB200_TRACE(gb, 4);
-          ptx::tc_fence_after_sync();
           const uint32_t s = gb % kStages;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->full_v[s]), (gb / kStages) & 1, &ctrl->abort)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
           int nvalid = b.L - jb * kKV;
           nvalid = nvalid > kKV ? kKV : nvalid;
           const int ksteps = (nvalid + 15) >> 4;
-          const uint64_t dv = desc_v0 + (uint64_t)(s * (2 * kTile >> 4));
+          const uint64_t dv = desc_v0 + (uint64_t)(s * (kTile >> 4));
           for (int ks = 0; ks < ksteps; ++ks) {
 #ifdef NTB200_ATTN_TRACE
             if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + ks] = clock64();
@@ -301,7 +322,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
 #ifdef NTB200_ATTN_TRACE
           if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 8] = clock64();
 #endif
-          ptx::umma_commit(ptx::smem_u32(&ctrl->empty[s]));
+          ptx::umma_commit(ptx::smem_u32(&ctrl->empty_v[s]));
 #ifdef NTB200_ATTN_TRACE
           if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 9] = clock64();
 #endif
@@ -329,6 +350,63 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
     const uint32_t t_s = tmem_base + lane_addr, t_p = tmem_base + kPCol + lane_addr, t_o = tmem_base + kOCol + lane_addr;
     bool ok = true;
     uint32_t g = 0;
+
+    // The output rows of an item go through the V stage that its last PV just released (128 rows x 128
+    // bytes, XOR-swizzled) so that every global store instruction writes four full 128-byte rows instead of
+    // 32 scattered 16-byte pieces; the stage is handed back to the producer afterwards.
+    struct Pending {
+      bool any;          // an item is waiting for its output
+      bool warp_active;  // this warp owns valid rows of it
+      float inv;         // 1 / softmax denominator of this thread's row
+      int rows;          // valid rows in the tile
+      int64_t out_row0;  // element offset of (first token of the tile, head) in the output
+      uint32_t vstage;   // V stage to hand back to the producer afterwards
+    } pend = {false, false, 0.0f, 0, 0, 0};
+    auto write_pending = [&]() {
+      if (pend.warp_active) {
+        const uint32_t stage = s_v + pend.vstage * kTile;
+        {
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld_32x32b_x32(t_o, r0);
+          ptx::tmem_ld_32x32b_x32(t_o + 32, r1);
+          ptx::tmem_ld_wait();
+          const float inv = pend.inv;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t a0 = stage + row * 128 + ((c ^ (row & 7)) << 4);
+            const uint32_t a1 = stage + row * 128 + (((c + 4) ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a0),
+                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 0]) * inv, __uint_as_float(r0[c * 8 + 1]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 2]) * inv, __uint_as_float(r0[c * 8 + 3]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 4]) * inv, __uint_as_float(r0[c * 8 + 5]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 6]) * inv, __uint_as_float(r0[c * 8 + 7]) * inv))
+                         : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a1),
+                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 0]) * inv, __uint_as_float(r1[c * 8 + 1]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 2]) * inv, __uint_as_float(r1[c * 8 + 3]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 4]) * inv, __uint_as_float(r1[c * 8 + 5]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 6]) * inv, __uint_as_float(r1[c * 8 + 7]) * inv))
+                         : "memory");
+          }
+        }
+        __syncwarp();  // a warp reads back only the 32 rows it wrote itself
+        uint16_t* obase = reinterpret_cast<uint16_t*>(out) + pend.out_row0;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int rr = q * 32 + 4 * jj + (lane >> 3), cc = lane & 7;
+          uint4 v;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                       : "r"(stage + rr * 128 + ((cc ^ (rr & 7)) << 4))
+                       : "memory");
+          if (rr < pend.rows) *reinterpret_cast<uint4*>(obase + (int64_t)rr * E + cc * 8) = v;
+        }
+        ptx::fence_proxy_async();  // the stage is refilled by TMA (async proxy) after this
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->empty_v[pend.vstage]));
+      pend.any = false;
+    };
     int4 rec = fetch(blockIdx.x);
     for (int64_t i = blockIdx.x; i < total; i += G) {
       const Item it = decode(i, rec);
@@ -411,8 +489,11 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
               if ((c + 1) * 32 <= nvalid) {
 #pragma unroll
                 for (int k = 0; k < 16; ++k) {
-                  const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k]), scale_log2e, -m_new));
-                  const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k + 1]), scale_log2e, -m_new));
+                  // every fourth exponential goes to the FMA pipe (polynomial) instead of the MUFU unit
+                  const float x0 = fmaf(__uint_as_float(sv[c][2 * k]), scale_log2e, -m_new);
+                  const float x1 = fmaf(__uint_as_float(sv[c][2 * k + 1]), scale_log2e, -m_new);
+                  const float p0 = ptx::ex2_approx(x0);
+                  const float p1 = (k & 1) ? ptx::ex2_poly(x1) : ptx::ex2_approx(x1);
                   rs += p0 + p1;
                   pk[k] = pack2<FMT>(p0, p1);
                 }
@@ -437,40 +518,23 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         }
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->p_ready));
-      }
-      // final: O / l -> token-major output rows of this sequence.  The next item's first PV (which
-      // overwrites O) is issued only after these warps arrive at its p_ready, i.e. after this read.
-      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
-      if (ok && warp_active) {
-        ptx::tc_fence_after_sync();
-        const float inv = 1.0f / l;
-        const bool row_valid = it.q0 + row < it.L;
-        uint16_t* orow = reinterpret_cast<uint16_t*>(out) + ((int64_t)it.tok0 + it.q0 + row) * E + (int64_t)it.h * kHD;
-        uint32_t r0[32], r1[32];
-        ptx::tmem_ld_32x32b_x32(t_o, r0);
-        ptx::tmem_ld_32x32b_x32(t_o + 32, r1);
-        ptx::tmem_ld_wait();
-        if (row_valid) {
-#pragma unroll
-          for (int gg = 0; gg < 4; ++gg) {
-            uint4 v;
-            v.x = pack2<FMT>(__uint_as_float(r0[gg * 8 + 0]) * inv, __uint_as_float(r0[gg * 8 + 1]) * inv);
-            v.y = pack2<FMT>(__uint_as_float(r0[gg * 8 + 2]) * inv, __uint_as_float(r0[gg * 8 + 3]) * inv);
-            v.z = pack2<FMT>(__uint_as_float(r0[gg * 8 + 4]) * inv, __uint_as_float(r0[gg * 8 + 5]) * inv);
-            v.w = pack2<FMT>(__uint_as_float(r0[gg * 8 + 6]) * inv, __uint_as_float(r0[gg * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + gg * 8) = v;
-          }
-#pragma unroll
-          for (int gg = 0; gg < 4; ++gg) {
-            uint4 v;
-            v.x = pack2<FMT>(__uint_as_float(r1[gg * 8 + 0]) * inv, __uint_as_float(r1[gg * 8 + 1]) * inv);
-            v.y = pack2<FMT>(__uint_as_float(r1[gg * 8 + 2]) * inv, __uint_as_float(r1[gg * 8 + 3]) * inv);
-            v.z = pack2<FMT>(__uint_as_float(r1[gg * 8 + 4]) * inv, __uint_as_float(r1[gg * 8 + 5]) * inv);
-            v.w = pack2<FMT>(__uint_as_float(r1[gg * 8 + 6]) * inv, __uint_as_float(r1[gg * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + 32 + gg * 8) = v;
-          }
+        if (lane == 0) {
+          ptx::mbar_arrive(ptx::smem_u32(&ctrl->p_ready));
+          // the V stage of the item's last block doubles as the output staging buffer and is released later
+          if (j + 1 < it.n_blk) ptx::mbar_arrive(ptx::smem_u32(&ctrl->empty_v[g % kStages]));
         }
+      }
+      // output of this item: wait for its last PV, then write through the staging buffer
+      pend.any = true;
+      pend.warp_active = warp_active;
+      pend.inv = 1.0f / l;
+      pend.rows = it.L - it.q0 < kQT ? it.L - it.q0 : kQT;
+      pend.out_row0 = ((int64_t)it.tok0 + it.q0) * E + (int64_t)it.h * kHD;
+      pend.vstage = (g - 1) % kStages;
+      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
+      if (ok) {
+        ptx::tc_fence_after_sync();
+        write_pending();
       }
     }
     if (!ok && lane == 0) {

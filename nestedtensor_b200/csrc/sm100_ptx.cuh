@@ -85,6 +85,18 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for x <= 0 on the FMA/ALU pipes (no MUFU): round-to-nearest split x = n + f, f in [-0.5, 0.5], a
+// degree-3 polynomial for 2^f (max relative error 1.9e-4, far below fp16/bf16 rounding) and n added
+// to the exponent field.  Lets part of a softmax row bypass the 16-per-clock-per-SM MUFU unit.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.0f);
+  const float t = x + 12582912.0f;        // 1.5 * 2^23: round(x) lands in the low mantissa bits
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(0.054898810f, f, 0.24193299f);
+  p = fmaf(p, f, 0.69324845f);
+  p = fmaf(p, f, 0.99997652f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 // Warpgroup-wide register re-allocation (all four warps of an aligned warpgroup execute it): the control
 // warps give registers back, the math warps take them.
 template <int N>
