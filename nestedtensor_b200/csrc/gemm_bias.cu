@@ -245,6 +245,209 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
+// ------------------------------------------------------------- tcgen05 path, CTA pairs (cta_group::2)
+// A cluster of two CTAs computes a 256 x 256 tile: CTA r loads rows [r*128, r*128+128) of the A tile and
+// rows [r*128, r*128+128) of the W tile (half of N) into its own shared memory; one thread of CTA 0 issues
+// tcgen05.mma.cta_group::2 (M = 256), which reads both CTAs' operands and writes each CTA's 128 accumulator
+// rows into that CTA's tensor memory.  Per FLOP this moves 1.5x fewer bytes from L2 into the SMs than the
+// single-CTA 128 x 256 tile.  No load is multicast: every CTA fetches what it needs itself, the TMA
+// completion bytes of both CTAs land on CTA 0's barrier, and CTA 0 releases stages / publishes
+// accumulators with one commit per CTA.
+constexpr int k2Stages = 6;
+constexpr int k2HalfBytes = 128 * kBK * 2;          // 16 KB: 128 rows x 64 columns
+constexpr int k2StageBytes = 2 * k2HalfBytes;       // A half + W half
+constexpr int k2Smem = 1024 + k2Stages * k2StageBytes + kCtrlBytes;
+
+struct Ctrl2 {
+  uint64_t full[k2Stages];    // used in CTA 0: bytes of both CTAs
+  uint64_t empty[k2Stages];   // one per CTA
+  uint64_t tfull[2];          // one per CTA
+  uint64_t tempty[2];         // used in CTA 0: 4 epilogue warps of each CTA
+  uint64_t done;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+static_assert(sizeof(Ctrl2) <= 256, "control block");
+
+template <int FMT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                              const void* __restrict__ bias, void* __restrict__ C, int M, int N, int K) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Ctrl2* ctrl = reinterpret_cast<Ctrl2*>(smem + k2Stages * k2StageBytes);
+  float* s_bias = reinterpret_cast<float*>(smem + k2Stages * k2StageBytes + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_m = (M + 255) / 256, num_n = (N + 255) / 256, num_k = (K + kBK - 1) / kBK;
+  const int num_tiles = num_m * num_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < k2Stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tfull[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tempty[a]), 8);
+    }
+    ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
+    ctrl->abort = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(&ctrl->tmem_base), kTmemCols);
+    ptx::tmem_relinquish_pair();
+    ptx::tc_fence_before_sync();
+  }
+  // both CTAs' barriers exist before either signals the other
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  const uint32_t smem_base = ptx::smem_u32(smem);
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (ptx::elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile / num_n) * 256 + (int)rank * 128, n0 = (tile % num_n) * 256 + (int)rank * 128;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const uint32_t s = it % k2Stages, ph = (it / k2Stages) & 1;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->empty[s]), ph ^ 1, &ctrl->abort)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = ptx::smem_u32(&ctrl->full[s]);
+          const uint32_t full_leader = ptx::mapa_shared(full_local, 0);
+          if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * k2StageBytes);
+          ptx::tma_load_2d_pair(smem_base + s * k2StageBytes, &map_a, full_leader, kb * kBK, m0);
+          ptx::tma_load_2d_pair(smem_base + s * k2StageBytes + k2HalfBytes, &map_w, full_leader, kb * kBK, n0);
+        }
+      }
+      if (!ok) {
+        ctrl->abort = 1;
+        atomicOr(&g_gemm_error, 1);
+      }
+      if (rank == 0) {  // CTA 0 sees the landing of both CTAs' loads on its own barriers
+        const uint32_t first = it > (uint32_t)k2Stages ? it - k2Stages : 0;
+        for (uint32_t i = first; i < it; ++i) ptx::mbar_wait(ptx::smem_u32(&ctrl->full[i % k2Stages]), (i / k2Stages) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (CTA 0 only)
+    if (rank == 0 && ptx::elect_one()) {
+      constexpr uint32_t idesc = ptx::umma_idesc_f16(FMT, 256, kBN);
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1;
+        if (!wait_or_abort(ptx::smem_u32(&ctrl->tempty[acc]), ((tile_iter >> 1) & 1) ^ 1, &ctrl->abort)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kAccCols;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const uint32_t s = it % k2Stages, ph = (it / k2Stages) & 1;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->full[s]), ph, &ctrl->abort)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + s * k2StageBytes, b_addr = a_addr + k2HalfBytes;
+          const uint64_t da = ptx::umma_desc_kmajor_sw128(a_addr), db = ptx::umma_desc_kmajor_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) ptx::umma_f16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          // free the stage in both CTAs once these MMAs retire
+          const uint32_t e = ptx::smem_u32(&ctrl->empty[s]);
+          ptx::umma_commit_pair(e);
+          ptx::umma_commit_pair(ptx::mapa_shared(e, 1));
+        }
+        if (ok) {
+          const uint32_t t = ptx::smem_u32(&ctrl->tfull[acc]);
+          ptx::umma_commit_pair(t);
+          ptx::umma_commit_pair(ptx::mapa_shared(t, 1));
+        }
+      }
+      if (!ok) {
+        ctrl->abort = 1;
+        atomicOr(&g_gemm_error, 2);
+      }
+      ptx::umma_commit_pair(ptx::smem_u32(&ctrl->done));
+      ptx::mbar_wait(ptx::smem_u32(&ctrl->done), 0);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (128 threads per CTA)
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tile_iter) {
+      const int m0 = (tile / num_n) * 256 + (int)rank * 128, n0 = (tile % num_n) * 256;
+      const uint32_t acc = tile_iter & 1;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int i = et; i < kBN; i += 128) {
+        const int n = n0 + i;
+        s_bias[i] = (bias != nullptr && n < N) ? OutPack<FMT>::load(bias, n) : 0.0f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
+      if (!ok) continue;
+      ptx::tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
+#pragma unroll 1
+      for (int c = 0; c < kBN; c += 32) {
+        if (n0 + c >= N) break;
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + acc * kAccCols + c + ((uint32_t)(q * 32) << 16), r);
+        ptx::tmem_ld_wait();
+        if (row < M) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (n0 + c + g * 8 < N) {
+              uint4 v;
+              v.x = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 0]) + s_bias[c + g * 8 + 0],
+                                       __uint_as_float(r[g * 8 + 1]) + s_bias[c + g * 8 + 1]);
+              v.y = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 2]) + s_bias[c + g * 8 + 2],
+                                       __uint_as_float(r[g * 8 + 3]) + s_bias[c + g * 8 + 3]);
+              v.z = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 4]) + s_bias[c + g * 8 + 4],
+                                       __uint_as_float(r[g * 8 + 5]) + s_bias[c + g * 8 + 5]);
+              v.w = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 6]) + s_bias[c + g * 8 + 6],
+                                       __uint_as_float(r[g * 8 + 7]) + s_bias[c + g * 8 + 7]);
+              *reinterpret_cast<uint4*>(crow + c + g * 8) = v;
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      // the accumulator stage is free when the epilogue warps of BOTH CTAs have read it: all arrive at CTA 0
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(&ctrl->tempty[acc]), 0));
+    }
+    if (!ok && lane == 0) {
+      ctrl->abort = 1;
+      atomicOr(&g_gemm_error, 4);
+    }
+  }
+
+  // neither CTA may free tensor memory or leave (its barriers are signalled remotely) before both are done
+  ptx::tc_fence_before_sync();
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ---------------------------------------------------------------------- tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -291,6 +494,49 @@ int launch_tcgen05(const void* A, const void* W, const void* bias, void* C, int 
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = num_tiles < sms ? num_tiles : sms;
   gemm_bias_tcgen05_kernel<FMT><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_w, bias, C, M, N, K);
+  return status_from_cuda(cudaGetLastError());
+}
+
+template <int FMT>
+int launch_tcgen05_pair(const void* A, const void* W, const void* bias, void* C, int M, int N, int K, int dtype, cudaStream_t st) {
+  CUtensorMap map_a, map_w;
+  if (!make_map_2d(&map_a, A, dtype, (uint64_t)M, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
+  if (!make_map_2d(&map_w, W, dtype, (uint64_t)N, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_bias_tcgen05_pair_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, k2Smem) != cudaSuccess)
+      return NTB200_LAUNCH_FAILED;
+    attr_set = true;
+  }
+  const int num_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  int dev = 0, sms = kNumSMs;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = k2Smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // how many CTA pairs can be resident at once (GPCs with an odd SM count leave one SM without a partner)
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cfg.gridDim = dim3(2 * (sms / 2));
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bias_tcgen05_pair_kernel<FMT>, &cfg) == cudaSuccess && n > 0) max_pairs = n;
+    else max_pairs = sms / 2;
+    (void)cudaGetLastError();
+  }
+  const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
+  cfg.gridDim = dim3(2 * pairs);
+  if (cudaLaunchKernelEx(&cfg, gemm_bias_tcgen05_pair_kernel<FMT>, map_a, map_w, bias, C, M, N, K) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return NTB200_LAUNCH_FAILED;
+  }
   return status_from_cuda(cudaGetLastError());
 }
 
@@ -398,9 +644,16 @@ int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, in
   if (M == 0 || N == 0) return NTB200_OK;
   if (A == nullptr || W == nullptr || C == nullptr) return NTB200_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool tc = !force_simt && dtype != NTB200_F32 && K >= 8 && (K % 8) == 0 && (N % 8) == 0 && aligned16(A) && aligned16(W) &&
-                  aligned16(C) && M < (1ll << 31) - kBM && N < (1ll << 31) - kBN && K < (1ll << 31) - kBK;
+  // force_simt: 0 = best available, 1 = SIMT, 2 = single-CTA tcgen05 kernel, 3 = CTA-pair tcgen05 kernel
+  const bool tc = force_simt != 1 && dtype != NTB200_F32 && K >= 8 && (K % 8) == 0 && (N % 8) == 0 && aligned16(A) && aligned16(W) &&
+                  aligned16(C) && M < (1ll << 31) - 256 && N < (1ll << 31) - 256 && K < (1ll << 31) - kBK;
+  if ((force_simt == 2 || force_simt == 3) && !tc) return NTB200_UNSUPPORTED_SHAPE;
   if (tc) {
+    const bool pair = force_simt == 3 || (force_simt == 0 && M > 128);
+    if (pair) {
+      if (dtype == NTB200_F16) return launch_tcgen05_pair<0>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
+      return launch_tcgen05_pair<1>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
+    }
     if (dtype == NTB200_F16) return launch_tcgen05<0>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
     return launch_tcgen05<1>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
   }

@@ -40,12 +40,10 @@ def test_gemm_bias_tensor_core(native_libs, cuda_device, dtype, M, N, K):
     W = (torch.randn(N, K, generator=g) * K ** -0.5).to(dtype).to(cuda_device)
     b = (torch.randn(N, generator=g) * 0.1).to(dtype).to(cuda_device)
     want = A.float() @ W.float().t() + b.float()
-    got = _gemm(A, W, b)
-    err = (got.float() - want).abs().max().item()
-    assert err <= 2e-2, "tensor-core path max-abs %g" % err
-    got2 = _gemm(A, W, b, force_simt=1)
-    err2 = (got2.float() - want).abs().max().item()
-    assert err2 <= 2e-2, "SIMT path max-abs %g" % err2
+    for path, name in ((3, "CTA-pair tcgen05"), (2, "single-CTA tcgen05"), (1, "SIMT"), (0, "default")):
+        got = _gemm(A, W, b, force_simt=path)
+        err = (got.float() - want).abs().max().item()
+        assert err <= 2e-2, "%s path max-abs %g" % (name, err)
     got3 = _gemm(A, W, None)
     assert (got3.float() - (want - b.float())).abs().max().item() <= 2e-2
 
