@@ -510,6 +510,98 @@ def run_mha(args, rank, world, local, brief=False):
     return line
 
 
+def run_kernels(args, local):
+    """Every operator of the path at the configuration that exercises it, CUDA-event timed on one GPU:
+    algorithmic bytes (copies, masks) or FLOPs (MHA) per call divided by the mean call time."""
+    import nestedtensor_b200 as nt
+    from nestedtensor_b200 import _ops, workloads
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    ops = _ops.ops()
+    peaks = measured_peaks()
+    rows = []
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        ms = timed_region(fn, n, 1, device) / n
+        return ms
+
+    def add(name, config, ms, nbytes=None, flops=None):
+        r = {"op": name, "config": config, "ms": ms}
+        if nbytes is not None:
+            r["GB/s"] = nbytes / ms / 1e6
+            r["frac_hbm_measured"] = r["GB/s"] / peaks["hbm_gbs"]
+        if flops is not None:
+            r["TFLOP/s"] = flops / ms / 1e9
+            r["frac_bf16_burst"] = r["TFLOP/s"] / peaks["bf16_tflops"]
+        rows.append(r)
+
+    n = max(args.steps, 5)
+    # configuration 1: 64 fp32 (L_i, 256)
+    w = workloads.config1()
+    a = nt.NestedTensor(w.buffer.to(device), w.sizes)
+    b, sz, meta = a._record()
+    es, nv = 4, w.buffer.numel()
+    padded = ops.to_padded_tensor(b, sz, meta, 0.0)
+    npad = padded.numel()
+    add("to_padded_tensor", "c1", timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0), n), es * (nv + npad))
+    add("to_tensor_mask(mask_dim=2)", "c1", timed(lambda: ops.to_tensor_mask(b, sz, meta, 2), n), es * (nv + npad) + npad // 256)
+    add("from_padded_tensor", "c1", timed(lambda: ops.from_padded_tensor(padded, sz, meta), n), 2 * es * nv)
+    add("nested_tensor_from_padded_tensor", "c1 (includes the one host sync of the API)",
+        timed(lambda: nt.nested_tensor_from_padded_tensor(padded, padding=0), n), es * (npad + nv))
+    # configuration 3: 32 fp32 images (3, H_i, W_i)
+    w = workloads.config3()
+    a = nt.NestedTensor(w.buffer.to(device), w.sizes)
+    b, sz, meta = a._record()
+    nv = w.buffer.numel()
+    padded = ops.to_padded_tensor(b, sz, meta, 0.0)
+    npad = padded.numel()
+    add("to_padded_tensor (4-D)", "c3", timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0), n), es * (nv + npad))
+    add("to_tensor_mask (4-D uint8 mask)", "c3", timed(lambda: ops.to_tensor_mask(b, sz, meta, None), n), es * (nv + npad) + npad)
+    add("to_mask(mask_dim=3)", "c3", timed(lambda: ops.to_mask(sz, meta, 3), n), None)
+    add("from_padded_tensor (4-D)", "c3", timed(lambda: ops.from_padded_tensor(padded, sz, meta), n), 2 * es * nv)
+    add("sizes_from_padded (scan)", "c3", timed(lambda: ops.sizes_from_padded(padded, 0.0), n), es * npad)
+    del padded
+    # configuration 2: 4096 bf16 (L_i, 1024)
+    L, _ = shard_lengths("pad", 1, 0)
+    sizes = torch.stack([L, torch.full_like(L, 1024)], 1).contiguous()
+    nv = int(L.sum()) * 1024
+    buf = torch.randn(nv // 2, device=device).to(torch.bfloat16).repeat(2)[:nv].contiguous()
+    a = nt.NestedTensor(buf, sizes)
+    b, sz, meta = a._record()
+    padded = ops.to_padded_tensor(b, sz, meta, 0.0)
+    npad = padded.numel()
+    add("to_padded_tensor", "c2", timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0), n), 2 * (nv + npad))
+    add("from_padded_tensor", "c2", timed(lambda: ops.from_padded_tensor(padded, sz, meta), n), 4 * nv)
+    add("to_mask(mask_dim=2)", "c2", timed(lambda: ops.to_mask(sz, meta, 2), n), npad // 1024)
+    add("sizes_from_padded (scan)", "c2", timed(lambda: ops.sizes_from_padded(padded, 0.0), n), 2 * npad)
+    d_sizes = sizes.to(device)
+    add("meta_from_device_sizes (offsets scan)", "c2", timed(lambda: ops.meta_from_device_sizes(d_sizes), n), None)
+    del padded, buf, a
+    torch.cuda.empty_cache()
+    # configurations 4 and 5: MHA
+    for name, wl, dtype, E, H in (("c4", workloads.config4(), torch.float16, 768, 12),
+                                  ("c5", workloads.config5(), torch.bfloat16, 1024, 16)):
+        a = nt.NestedTensor(wl.buffer.to(device), wl.sizes)
+        b, sz, meta = a._record()
+        wd = {k: v.to(device) for k, v in wl.weights.items()}
+        d = E // H
+        fn = lambda: ops.bt_min_mha(H, d, 0.0, False, b, sz, meta, wd["in_proj_weight"], wd["in_proj_bias"], float(d) ** -0.5,
+                                    wd["out_proj_weight"], wd["out_proj_bias"])
+        ms = timed(fn, n)
+        Ls = wl.sizes[:, 0]
+        r_flops = workloads.mha_flops(Ls, E)
+        add("bt_min_mha", name, ms, None, r_flops)
+        rows[-1]["tokens/s"] = float(Ls.sum()) / (ms * 1e-3)
+        T = int(Ls.sum())
+        bi = lambda: ops.token_index(meta[:wl.batch + 1] // E, T)
+        add("token_index", name, timed(bi, n), None)
+    from nestedtensor_b200 import _cabi
+    return {"metric": "per-operator timings", "unit": "ms", "n_gpus": 1, "steps": n, "data": "synthetic",
+            "peaks": peaks, "rows": rows, "device_error_flags": _cabi.load().ntb200_device_error_flags()}
+
+
 # ------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -517,7 +609,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="pad", choices=["pad", "unpad", "mha"])
+    ap.add_argument("--workload", default="pad", choices=["pad", "unpad", "mha", "kernels"])
     ap.add_argument("--no-mha", action="store_true", help="pad workload only: skip the attached MHA measurement")
     args = ap.parse_args()
 
@@ -541,7 +633,9 @@ def main():
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     try:
-        if args.workload in ("pad", "unpad"):
+        if args.workload == "kernels":
+            line = run_kernels(args, local) if rank == 0 else None
+        elif args.workload in ("pad", "unpad"):
             line = run_copy(args, args.workload, rank, world, local)
             if args.workload == "pad" and not args.no_mha:
                 # the metric has two halves; attach a short MHA (configuration 5) measurement to the same line
