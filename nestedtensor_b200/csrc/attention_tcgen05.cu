@@ -437,23 +437,28 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         float m_new = m, corr = 1.0f;
         bool any_up = false;
         if (ok && warp_active) {
-          // row maximum over the valid keys, four independent chains
+          // Keys past the end of the sequence become -inf once, here, so that the maximum and the exponentials
+          // below need no per-element predicate (only the last 32-key chunk of a block can be ragged).
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            // (a range test, not "c == nchunks - 1": the latter is turned into a run-time index and sends the
+            // row to local memory)
+            if (nvalid > c * 32 && nvalid < (c + 1) * 32) {
+#pragma unroll
+              for (int k = 0; k < 32; ++k) sv[c][k] = (c * 32 + k >= nvalid) ? 0xff800000u : sv[c][k];
+            }
+          }
+          // row maximum, four independent chains of three-input maxima
           float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             if (c < nchunks) {
-              if ((c + 1) * 32 <= nvalid) {
 #pragma unroll
-                for (int k = 0; k < 32; k += 4) {
-                  mx0 = fmaxf(mx0, __uint_as_float(sv[c][k]));
-                  mx1 = fmaxf(mx1, __uint_as_float(sv[c][k + 1]));
-                  mx2 = fmaxf(mx2, __uint_as_float(sv[c][k + 2]));
-                  mx3 = fmaxf(mx3, __uint_as_float(sv[c][k + 3]));
-                }
-              } else {
-#pragma unroll
-                for (int k = 0; k < 32; ++k)
-                  if (c * 32 + k < nvalid) mx0 = fmaxf(mx0, __uint_as_float(sv[c][k]));
+              for (int k = 0; k < 32; k += 8) {
+                mx0 = ptx::fmax3(mx0, __uint_as_float(sv[c][k]), __uint_as_float(sv[c][k + 1]));
+                mx1 = ptx::fmax3(mx1, __uint_as_float(sv[c][k + 2]), __uint_as_float(sv[c][k + 3]));
+                mx2 = ptx::fmax3(mx2, __uint_as_float(sv[c][k + 4]), __uint_as_float(sv[c][k + 5]));
+                mx3 = ptx::fmax3(mx3, __uint_as_float(sv[c][k + 6]), __uint_as_float(sv[c][k + 7]));
               }
             }
           }
@@ -480,37 +485,42 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
             }
           }
           if (threadIdx.x == 0) NTB200_TRACE(g, 10);
-          // P = exp2(S*scale*log2e - m_new), packed two per column
-          float rs = 0.0f;
+          // P = exp2(S*scale*log2e - m_new), packed two per column.  Of every four keys two go through the
+          // MUFU unit and two through a polynomial on the FMA pipe (16 MUFU results per clock per SM would
+          // otherwise bound the block); the scaling, the polynomial and the row sum run on packed fp32 pairs.
+          const uint64_t sc2 = ptx::f32x2_pack(scale_log2e, scale_log2e);
+          const uint64_t nm2 = ptx::f32x2_pack(-m_new, -m_new);
+          uint64_t acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;  // four packed partial row sums
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             if (c < nchunks) {
               uint32_t pk[16];
-              if ((c + 1) * 32 <= nvalid) {
 #pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                  // every fourth exponential goes to the FMA pipe (polynomial) instead of the MUFU unit
-                  const float x0 = fmaf(__uint_as_float(sv[c][2 * k]), scale_log2e, -m_new);
-                  const float x1 = fmaf(__uint_as_float(sv[c][2 * k + 1]), scale_log2e, -m_new);
-                  const float p0 = ptx::ex2_approx(x0);
-                  const float p1 = (k & 1) ? ptx::ex2_poly(x1) : ptx::ex2_approx(x1);
-                  rs += p0 + p1;
-                  pk[k] = pack2<FMT>(p0, p1);
+              for (int k = 0; k < 8; ++k) {
+                const uint64_t xa = ptx::f32x2_fma(ptx::f32x2_pack(__uint_as_float(sv[c][4 * k]), __uint_as_float(sv[c][4 * k + 1])), sc2, nm2);
+                const uint64_t xb = ptx::f32x2_fma(ptx::f32x2_pack(__uint_as_float(sv[c][4 * k + 2]), __uint_as_float(sv[c][4 * k + 3])), sc2, nm2);
+                float a0, a1, b0, b1;
+                ptx::f32x2_unpack(xa, a0, a1);
+                ptx::f32x2_unpack(xb, b0, b1);
+                const float p0 = ptx::ex2_approx(a0), p1 = ptx::ex2_approx(a1);
+                float p2, p3;
+                ptx::ex2_poly_x2(ptx::f32x2_pack(fmaxf(b0, -126.0f), fmaxf(b1, -126.0f)), p2, p3);
+                if (k & 1) {
+                  acc2 = ptx::f32x2_add(acc2, ptx::f32x2_pack(p0, p1));
+                  acc3 = ptx::f32x2_add(acc3, ptx::f32x2_pack(p2, p3));
+                } else {
+                  acc0 = ptx::f32x2_add(acc0, ptx::f32x2_pack(p0, p1));
+                  acc1 = ptx::f32x2_add(acc1, ptx::f32x2_pack(p2, p3));
                 }
-              } else {
-#pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                  const int k0 = c * 32 + 2 * k;
-                  const float p0 = k0 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k]), scale_log2e, -m_new)) : 0.0f;
-                  const float p1 =
-                      k0 + 1 < nvalid ? ptx::ex2_approx(fmaf(__uint_as_float(sv[c][2 * k + 1]), scale_log2e, -m_new)) : 0.0f;
-                  rs += p0 + p1;
-                  pk[k] = pack2<FMT>(p0, p1);
-                }
+                pk[2 * k] = pack2<FMT>(p0, p1);
+                pk[2 * k + 1] = pack2<FMT>(p2, p3);
               }
               ptx::tmem_st_32x32b_x16(t_p + c * 16, pk);
             }
           }
+          float rs, rs_hi;
+          ptx::f32x2_unpack(ptx::f32x2_add(ptx::f32x2_add(acc0, acc1), ptx::f32x2_add(acc2, acc3)), rs, rs_hi);
+          rs += rs_hi;
           l = l * corr + rs;
           m = m_new;
           ptx::tmem_st_wait();

@@ -97,6 +97,50 @@ __device__ __forceinline__ float ex2_poly(float x) {
   p = fmaf(p, f, 0.99997652f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
+// Packed pairs of fp32 (sm_100 issues add/sub/fma on two fp32 values held in a 64-bit register pair with
+// one instruction) and the three-input maximum: they halve the issue slots of the softmax inner loops.
+__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.ftz.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f32x2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t f32x2_sub(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.ftz.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for a pair, same polynomial as ex2_poly; x must already be >= -126 (the caller clamps).
+__device__ __forceinline__ void ex2_poly_x2(uint64_t x, float& r0, float& r1) {
+  const uint64_t magic = f32x2_pack(12582912.0f, 12582912.0f);
+  const uint64_t t = f32x2_add(x, magic);
+  const uint64_t f = f32x2_sub(x, f32x2_sub(t, magic));
+  uint64_t p = f32x2_fma(f32x2_pack(0.054898810f, 0.054898810f), f, f32x2_pack(0.24193299f, 0.24193299f));
+  p = f32x2_fma(p, f, f32x2_pack(0.69324845f, 0.69324845f));
+  p = f32x2_fma(p, f, f32x2_pack(0.99997652f, 0.99997652f));
+  float p0, p1, t0, t1;
+  f32x2_unpack(p, p0, p1);
+  f32x2_unpack(t, t0, t1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
 // Warpgroup-wide register re-allocation (all four warps of an aligned warpgroup execute it): the control
 // warps give registers back, the math warps take them.
 template <int N>
