@@ -146,8 +146,8 @@ template <int FMT>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restrict__ out, const int64_t* __restrict__ offsets,
                     const int4* __restrict__ items, const int* __restrict__ count, int H, float scale_log2e) {
-  const int64_t total = (int64_t)(*count) * H;
-  if ((int64_t)blockIdx.x >= total) return;
+  const int n_items = *count;
+  if ((int64_t)blockIdx.x >= (int64_t)n_items * H) return;
 #ifdef NTB200_ATTN_TRACE
   if (threadIdx.x == 0 && blockIdx.x < 1024) {
     unsigned smid;
@@ -195,17 +195,32 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
   struct Item {
     int q0, h, L, tok0, n_blk;
   };
-  auto fetch = [&](int64_t i) { return i < total ? __ldg(items + i / H) : make_int4(0, 0, 1, 0); };
-  auto decode = [&](int64_t i, const int4& w) {
+  // Position in the flattened (work item, head) list; a CTA steps through it by gridDim.x without a
+  // division per item.
+  struct Pos {
+    int item, h;
+  };
+  const int step_items = (int)(gridDim.x / (unsigned)H), step_heads = (int)(gridDim.x % (unsigned)H);
+  const Pos first = {(int)(blockIdx.x / (unsigned)H), (int)(blockIdx.x % (unsigned)H)};
+  auto next = [&](Pos p) {
+    p.item += step_items;
+    p.h += step_heads;
+    if (p.h >= H) {
+      p.h -= H;
+      ++p.item;
+    }
+    return p;
+  };
+  auto fetch = [&](const Pos& p) { return p.item < n_items ? __ldg(items + p.item) : make_int4(0, 0, 1, 0); };
+  auto decode = [&](const Pos& p, const int4& w) {
     Item it;
-    it.h = (int)(i % H);
+    it.h = p.h;
     it.tok0 = w.x;
     it.q0 = w.y;
     it.L = w.z;
     it.n_blk = (w.z + kKV - 1) / kKV;
     return it;
   };
-  const int64_t G = gridDim.x;
 
   if (warp >= 4) {
     ptx::setmaxnreg_dec<48>();
@@ -213,10 +228,10 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       // ------------------------------------------------------------ TMA producer
       bool ok = true;
       uint32_t g = 0, n = 0;
-      int4 rec = fetch(blockIdx.x);
-      for (int64_t i = blockIdx.x; i < total && ok; i += G, ++n) {
+      int4 rec = fetch(first);
+      for (Pos i = first; i.item < n_items && ok; i = next(i), ++n) {
         const Item it = decode(i, rec);
-        rec = fetch(i + G);
+        rec = fetch(next(i));
         for (int j = 0; j < it.n_blk; ++j, ++g) {
           const uint32_t s = g % kStages, ph = (g / kStages) & 1;
           // K (and Q) as soon as the QK^T that last read this stage has retired ...
@@ -260,11 +275,11 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       const uint64_t desc_k0 = ptx::umma_desc_kmajor_sw128(s_k);
       const uint64_t desc_v0 = ptx::umma_desc_mnmajor_sw128(s_v);
       // cursor A: the block whose QK^T is issued next (runs one block ahead of cursor B: PV)
-      int64_t ia = blockIdx.x;
+      Pos ia = first;
       uint32_t ga = 0, na = 0;
       int ja = 0;
       Item a = decode(ia, fetch(ia));
-      int4 rec_a = fetch(ia + G);
+      int4 rec_a = fetch(next(ia));
       auto issue_qk = [&]() -> bool {
         const uint32_t s = ga % kStages, ph = (ga / kStages) & 1;
         NTB200_TRACE(ga, 0);
@@ -285,21 +300,21 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         if (++ja == a.n_blk) {
           ja = 0;
           ++na;
-          ia += G;
+          ia = next(ia);
           a = decode(ia, rec_a);
-          rec_a = fetch(ia + G);
+          rec_a = fetch(next(ia));
         }
         return true;
       };
       ok = issue_qk();
       uint32_t gb = 0;
-      int4 rec_b = fetch(blockIdx.x);
-      for (int64_t ib = blockIdx.x; ib < total && ok; ib += G) {
+      int4 rec_b = fetch(first);
+      for (Pos ib = first; ib.item < n_items && ok; ib = next(ib)) {
         const Item b = decode(ib, rec_b);
-        rec_b = fetch(ib + G);
+        rec_b = fetch(next(ib));
         for (int jb = 0; jb < b.n_blk && ok; ++jb, ++gb) {
           // S of block gb is in the softmax warps' registers: the next QK^T may overwrite it
-          if (ia < total) {
+          if (ia.item < n_items) {
             if (!wait_or_abort(ptx::smem_u32(&ctrl->s_free), gb & 1, &ctrl->abort)) { ok = false; break; }
             if (!issue_qk()) { ok = false; break; }
           }
@@ -313,11 +328,13 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           nvalid = nvalid > kKV ? kKV : nvalid;
           const int ksteps = (nvalid + 15) >> 4;
           const uint64_t dv = desc_v0 + (uint64_t)(s * (kTile >> 4));
-          for (int ks = 0; ks < ksteps; ++ks) {
+#pragma unroll
+          for (int ks = 0; ks < kKV / 16; ++ks) {
 #ifdef NTB200_ATTN_TRACE
             if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + ks] = clock64();
 #endif
-            ptx::umma_f16_ts(t_o, t_p + ks * 8, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (jb | ks) != 0 ? 1u : 0u);
+            if (ks < ksteps)
+              ptx::umma_f16_ts(t_o, t_p + ks * 8, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (jb | ks) != 0 ? 1u : 0u);
           }
 #ifdef NTB200_ATTN_TRACE
           if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 8] = clock64();
@@ -407,10 +424,10 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->empty_v[pend.vstage]));
       pend.any = false;
     };
-    int4 rec = fetch(blockIdx.x);
-    for (int64_t i = blockIdx.x; i < total; i += G) {
+    int4 rec = fetch(first);
+    for (Pos i = first; i.item < n_items; i = next(i)) {
       const Item it = decode(i, rec);
-      rec = fetch(i + G);
+      rec = fetch(next(i));
       const bool warp_active = it.q0 + q * 32 < it.L;  // warp-uniform
       float m = -INFINITY, l = 0.0f;
       for (int j = 0; j < it.n_blk; ++j, ++g) {
@@ -490,7 +507,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           // otherwise bound the block); the scaling, the polynomial and the row sum run on packed fp32 pairs.
           const uint64_t sc2 = ptx::f32x2_pack(scale_log2e, scale_log2e);
           const uint64_t nm2 = ptx::f32x2_pack(-m_new, -m_new);
-          uint64_t acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;  // four packed partial row sums
+          uint64_t acc0 = 0, acc1 = 0;  // packed partial row sums (four independent chains)
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             if (c < nchunks) {
@@ -505,13 +522,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
                 const float p0 = ptx::ex2_approx(a0), p1 = ptx::ex2_approx(a1);
                 float p2, p3;
                 ptx::ex2_poly_x2(ptx::f32x2_pack(fmaxf(b0, -126.0f), fmaxf(b1, -126.0f)), p2, p3);
-                if (k & 1) {
-                  acc2 = ptx::f32x2_add(acc2, ptx::f32x2_pack(p0, p1));
-                  acc3 = ptx::f32x2_add(acc3, ptx::f32x2_pack(p2, p3));
-                } else {
-                  acc0 = ptx::f32x2_add(acc0, ptx::f32x2_pack(p0, p1));
-                  acc1 = ptx::f32x2_add(acc1, ptx::f32x2_pack(p2, p3));
-                }
+                acc0 = ptx::f32x2_add(acc0, ptx::f32x2_pack(p0, p1));
+                acc1 = ptx::f32x2_add(acc1, ptx::f32x2_pack(p2, p3));
                 pk[2 * k] = pack2<FMT>(p0, p1);
                 pk[2 * k + 1] = pack2<FMT>(p2, p3);
               }
@@ -519,7 +531,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
             }
           }
           float rs, rs_hi;
-          ptx::f32x2_unpack(ptx::f32x2_add(ptx::f32x2_add(acc0, acc1), ptx::f32x2_add(acc2, acc3)), rs, rs_hi);
+          ptx::f32x2_unpack(ptx::f32x2_add(acc0, acc1), rs, rs_hi);
           rs += rs_hi;
           l = l * corr + rs;
           m = m_new;
