@@ -136,6 +136,36 @@ Tensor to_padded_tensor(const Tensor& buffer, const Tensor& sizes, const Tensor&
   return out;
 }
 
+// Same operator writing into a caller-provided dense tensor whose extents may exceed the batch maxima
+// (slices of one large padded tensor filled batch range by batch range, e.g. by the host-buffer pipeline).
+// No counterpart in the reference, whose to_padded_tensor always allocates (masking.cpp:558-650).
+Tensor& to_padded_tensor_out(const Tensor& buffer, const Tensor& sizes, const Tensor& meta, double padding, Tensor& out) {
+  Record r = make_record(sizes, meta);
+  check_buffer(buffer, r, "to_padded_tensor_out");
+  TORCH_CHECK(r.B > 0 && r.tdim >= 1, "nestedtensor_b200: to_padded_tensor_out needs a non-empty batch of tensors");
+  TORCH_CHECK(out.is_cuda() && out.device() == buffer.device() && out.scalar_type() == buffer.scalar_type() &&
+                  out.is_contiguous(),
+              "nestedtensor_b200: out must be a contiguous tensor on the input's device and of its dtype");
+  TORCH_CHECK(out.dim() == r.tdim + 1 && out.size(0) == r.B, "nestedtensor_b200: out must have shape (batch, extents...)");
+  std::vector<int64_t> dense(r.tdim);
+  for (int64_t d = 0; d < r.tdim; ++d) {
+    dense[d] = out.size(d + 1);
+    TORCH_CHECK(dense[d] >= r.max_sizes[d], "nestedtensor_b200: out extent ", dense[d], " of dim ", d + 1,
+                " is smaller than the largest constituent (", r.max_sizes[d], ")");
+  }
+  if (out.numel() == 0) return out;
+  c10::cuda::CUDAGuard guard(buffer.device());
+  int nd;
+  int64_t inner;
+  fold_dims(r, dense.data(), &nd, &inner);
+  const int64_t es = buffer.element_size();
+  const uint64_t bits = scalar_bits(at::Scalar(padding), buffer.scalar_type(), es);
+  check_rc(ntb200_pad_nd(buffer.data_ptr(), out.data_ptr(), r.d_offsets, r.d_sizes, r.tdim, nd, inner, r.B, dense.data(),
+                         (int)es, bits, cur_stream()),
+           "ntb200_pad_nd");
+  return out;
+}
+
 // Number of mask dims left after the reference's collapse rule (merge_tensor_mask,
 // nestedtensor/csrc/masking.cpp:12-43), derived from the sizes alone: a trailing mask dim can be
 // dropped iff that tensor dim is regular (every slice is then all-1 or all-0); the batch dim can
@@ -474,6 +504,8 @@ Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, boo
 // record (buffer, sizes, meta) and the Python wrapper's __torch_function__ does the spelling.
 TORCH_LIBRARY(nestedtensor, m) {
   m.def("to_padded_tensor(Tensor buffer, Tensor sizes, Tensor meta, float padding) -> Tensor", &to_padded_tensor);
+  m.def("to_padded_tensor_out(Tensor buffer, Tensor sizes, Tensor meta, float padding, Tensor(a!) out) -> Tensor(a!)",
+        &to_padded_tensor_out);
   m.def("to_tensor_mask(Tensor buffer, Tensor sizes, Tensor meta, int? mask_dim) -> (Tensor, Tensor)", &to_tensor_mask);
   m.def("to_mask(Tensor sizes, Tensor meta, int? mask_dim) -> Tensor", &to_mask);
   m.def("from_padded_tensor(Tensor padded, Tensor sizes, Tensor meta) -> Tensor", &from_padded_tensor);

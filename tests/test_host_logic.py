@@ -130,3 +130,25 @@ def test_workloads_are_deterministic():
     assert c5.batch == 1024 and c5.weights["in_proj_weight"].shape == (3072, 1024) and c5.dtype == torch.bfloat16
     s = c5.slice(10, 20)
     assert s.batch == 10 and s.buffer.numel() == int(c5.sizes[10:20].prod(1).sum())
+
+
+def test_host_pipeline_range_plan():
+    """Ranges are contiguous, non-empty, cover the batch in order and never outnumber the sequences."""
+    from nestedtensor_b200.host_pipeline import plan_ranges
+    w = [5, 1, 1, 1, 8, 2, 2, 40, 1, 1]
+    for n in (1, 2, 3, 8, 50):
+        parts = plan_ranges(w, n)
+        assert parts[0][0] == 0 and parts[-1][1] == len(w)
+        assert all(b > a for a, b in parts)
+        assert all(parts[i][1] == parts[i + 1][0] for i in range(len(parts) - 1))
+        assert len(parts) <= min(n, len(w))
+    assert plan_ranges([3], 8) == [(0, 1)]
+
+
+def test_host_pipeline_rejects_pageable_memory_before_touching_the_gpu():
+    import nestedtensor_b200 as nt
+    sizes = torch.tensor([[2, 4], [3, 4]], dtype=torch.int64)
+    with pytest.raises(ValueError, match="pinned"):
+        nt.to_padded_tensor_host(torch.zeros(20), sizes, 0)
+    with pytest.raises(ValueError, match="pinned"):
+        nt.from_padded_tensor_host(torch.zeros(2, 3, 4), sizes)
