@@ -148,6 +148,10 @@ def all_sum(x, world, device):
 
 
 # --------------------------------------------------------------------------- workloads
+SEQUENCE_LIMIT = 0   # --sequences: keep only the first N sequences of each shard (small cases for profiler captures)
+KERNEL_ONLY = False  # --kernel-only: skip the end-to-end pass, the CPU baseline and the parity spot check
+
+
 def shard_lengths(kind, world, rank):
     """Lengths of this rank's shard: N batches of the configuration drawn as ONE list (generator of the
     configuration, batch = N * config batch) and cut token-balanced into N contiguous slices."""
@@ -158,6 +162,8 @@ def shard_lengths(kind, world, rank):
         L = workloads.lengths_c5(workloads._gen(5), 1024 * world)
     parts = sharding.token_balanced_partition(L.tolist(), world)
     a, b = parts[rank]
+    if SEQUENCE_LIMIT:
+        b = min(b, a + SEQUENCE_LIMIT)
     return L[a:b].contiguous(), sharding.imbalance(L.tolist(), parts)
 
 
@@ -240,9 +246,11 @@ def run_copy(args, kind, rank, world, local):
     kernel_ms = ms / args.steps
 
     # parity spot check in the same run (size-independent property): round trip is the identity
-    chk = ops.from_padded_tensor(ops.to_padded_tensor(buf, sz, meta, 0.0), sz, meta)
-    parity_ok = bool(torch.equal(chk.view(torch.int16), ragged.view(torch.int16)))
-    del chk
+    parity_ok = None
+    if not KERNEL_ONLY:
+        chk = ops.from_padded_tensor(ops.to_padded_tensor(buf, sz, meta, 0.0), sz, meta)
+        parity_ok = bool(torch.equal(chk.view(torch.int16), ragged.view(torch.int16)))
+        del chk
 
     # end to end: pinned host input -> device -> kernel -> pinned host output, every step
     e2e = None
@@ -254,7 +262,9 @@ def run_copy(args, kind, rank, world, local):
     out_elems = n_pad if kind == "pad" else n_valid
     in_elems = n_valid if kind == "pad" else n_pad
     need = es * (out_elems + in_elems)
-    if avail > 3 * need * max(world, 1):
+    if KERNEL_ONLY:
+        e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "sample": "skipped: --kernel-only"}
+    elif avail > 3 * need * max(world, 1):
         if kind == "unpad":
             del padded
         torch.cuda.empty_cache()
@@ -302,7 +312,7 @@ def run_copy(args, kind, rank, world, local):
     line = None
     if rank == 0:
         cpu = None
-        if world == 1:  # the CPU baseline is a single-GPU-run figure; other ranks would compete for the cores
+        if world == 1 and not KERNEL_ONLY:  # a single-GPU-run figure; other ranks would compete for the cores
             seqs = 256
             if kind == "pad":
                 _, nbytes, fn = cpu_pad_sample(L, hidden, dtype, seqs)
@@ -319,7 +329,8 @@ def run_copy(args, kind, rank, world, local):
             "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 (bit copy, u16)", "data": "synthetic",
-            "config": {"workload": "config2: %d bf16 sequences (L_i,1024), L_i=clip(round(lognormal(ln200,0.6)),1,1024) "
+            "config": {"workload": ("FIRST %d SEQUENCES ONLY of " % SEQUENCE_LIMIT if SEQUENCE_LIMIT else "") +
+                                   "config2: %d bf16 sequences (L_i,1024), L_i=clip(round(lognormal(ln200,0.6)),1,1024) "
                                    "per GPU; %s" % (4096, "to_padded_tensor(padding=0)" if kind == "pad" else
                                                     "from_padded_tensor with known sizes"),
                        "batch_per_gpu": B, "tokens_per_gpu": T, "max_len": maxL, "hidden": hidden,
@@ -464,6 +475,7 @@ def run_mha(args, rank, world, local, brief=False):
     value = total_tokens / (step_ms * 1e-3)
     flags = lib.ntb200_device_error_flags()
 
+    brief = brief or KERNEL_ONLY
     e2e = None
     if not brief:
         h_in = torch.empty(T * E, dtype=dtype).pin_memory()
@@ -504,7 +516,8 @@ def run_mha(args, rank, world, local, brief=False):
         "metric": "varlen MHA valid tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
         "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "config5: BERT-large varlen self-attention forward, batch 1024 per GPU, 70% L~U[16,128] / "
+        "config": {"workload": ("FIRST %d SEQUENCES ONLY of " % SEQUENCE_LIMIT if SEQUENCE_LIMIT else "") +
+                               "config5: BERT-large varlen self-attention forward, batch 1024 per GPU, 70% L~U[16,128] / "
                                "30% L~U[128,512], E=1024, 16 heads x 64, bf16",
                    "batch_per_gpu": B, "tokens_per_gpu": T, "max_len": maxL, "flops_per_gpu": flops,
                    "token_imbalance": imb,
@@ -630,7 +643,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="pad", choices=["pad", "unpad", "mha", "kernels"])
     ap.add_argument("--no-mha", action="store_true", help="pad workload only: skip the attached MHA measurement")
+    ap.add_argument("--sequences", type=int, default=0,
+                    help="use only the first N sequences of each GPU's batch (small cases for profiler captures; "
+                         "the line then does not describe the named configuration)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end pass, the CPU baseline and the parity spot check")
     args = ap.parse_args()
+    global SEQUENCE_LIMIT, KERNEL_ONLY
+    SEQUENCE_LIMIT, KERNEL_ONLY = max(args.sequences, 0), bool(args.kernel_only)
 
     rank, world, local = dist_env()
     if world == 1 and args.gpus > 1 and args.impl == "ours":

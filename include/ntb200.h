@@ -176,8 +176,10 @@ int ntb200_token_index(const int64_t* token_offsets, int64_t batch, int64_t tota
  * C[M,N] = A[M,K] * W[N,K]^T + bias[N] (bias may be NULL); all row-major, element type `dtype`,
  * fp32 accumulation.  A is the packed token buffer [sum(L_i), K] of a nested tensor, so the
  * grouped variable-length projection is a single GEMM.  fp16/bf16 with K % 8 == 0, N % 8 == 0 and
- * 16-byte aligned pointers run on tcgen05/TMEM fed by TMA; other cases on a SIMT kernel
- * (force_simt != 0 selects it explicitly, for cross-checks).
+ * 16-byte aligned pointers run on tcgen05/TMEM fed by TMA; other cases on a SIMT kernel.
+ *   force_simt  0 = best available (M > 128: pairs of CTAs on 256x256 tiles with cta_group::2 MMAs,
+ *               else one CTA per 128x256 tile);  1 = SIMT kernel;  2 = single-CTA tcgen05 kernel;
+ *               3 = CTA-pair tcgen05 kernel (1-3 for cross-checks)
  * Replaces NestedTensor_matmul's packed path (nestedtensor/csrc/matmul.cpp:12-45) and the bias add of
  * NestedTensor_add_Tensor (nestedtensor/csrc/BinaryOps.cpp:97-107), i.e. steps 1 and 9 of bt_min_mha
  * (nestedtensor/csrc/cuda/mha.cpp:57,106).
