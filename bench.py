@@ -349,9 +349,13 @@ def run_copy(args, kind, rank, world, local):
     return line
 
 
-# Per-launch DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from the
-# ncu capture summarised under profiles/; None until a capture exists for that workload.
-NCU_TRAFFIC = {"pad": 10.48e9, "unpad": None, "mha": None}
+# Per-launch DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the ncu
+# captures summarised under profiles/.  The captures ran on the first 512 (copies) / 256 (MHA) sequences;
+# reads equalled the algorithmic bytes and writes fell short of them only by the 50-55 MB still dirty in
+# L2 at kernel end, which does not grow with the batch, so the full-size figure is algorithmic - residue:
+#   pad   1.950 + 8.590 - 0.055 GB      unpad 1.950 + 1.950 - 0.051 GB
+#   QKV projection (A 310.9 MB + W 6.3 MB read, C 932.6 MB written) - 0.052 GB
+NCU_TRAFFIC = {"pad": 10.48e9, "unpad": 3.85e9, "mha": 1.20e9}
 
 
 # ---------------------------------------------------------------------- reference arm
@@ -526,7 +530,7 @@ def run_mha(args, rank, world, local, brief=False):
         "step_frac_of_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
         "kernels_ms": {"qkv_gemm": gms, "attention": ams, "step": step_ms},
         "attention_tflops_valid": atf,
-        "roofline": {"bound": "tensor", "kernel": "gemm_bias_tcgen05_kernel (QKV projection, M=%d N=3072 K=1024)" % T,
+        "roofline": {"bound": "tensor", "kernel": "gemm_bias_tcgen05_pair_kernel (QKV projection, M=%d N=3072 K=1024)" % T,
                      "achieved": gtf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": gtf / peaks["bf16_tflops"],
                      "frac_of_sustained": gtf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
                      "traffic": NCU_TRAFFIC.get("mha")},
