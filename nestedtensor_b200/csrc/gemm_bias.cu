@@ -79,6 +79,31 @@ struct OutPack<1> {  // bf16
   }
 };
 
+// 32 accumulator columns of one output row: + bias, packed to 16 bits, stored.  With `wide` (row stride and
+// base 32-byte aligned) each store is one full 32-byte sector (st.global.v8); a warp-wide 16-byte store per
+// row would touch every sector twice.
+template <int FMT>
+__device__ __forceinline__ void store_chunk32(uint16_t* dst, const uint32_t (&r)[32], const float* bias32, int n_left,
+                                              bool wide) {
+  uint32_t p[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k)
+    p[k] = OutPack<FMT>::pack(__uint_as_float(r[2 * k]) + bias32[2 * k], __uint_as_float(r[2 * k + 1]) + bias32[2 * k + 1]);
+  if (wide) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+      if (g * 16 < n_left)
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + g * 16), "r"(p[g * 8 + 0]),
+                     "r"(p[g * 8 + 1]), "r"(p[g * 8 + 2]), "r"(p[g * 8 + 3]), "r"(p[g * 8 + 4]), "r"(p[g * 8 + 5]),
+                     "r"(p[g * 8 + 6]), "r"(p[g * 8 + 7])
+                     : "memory");
+  } else {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (g * 8 < n_left) *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(p[g * 4], p[g * 4 + 1], p[g * 4 + 2], p[g * 4 + 3]);
+  }
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -188,6 +213,7 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // ---------------------------------------------------------------- epilogue (128 threads)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int et = threadIdx.x - 64;
+    const bool wide = (N % 16 == 0) && (reinterpret_cast<uintptr_t>(C) % 32 == 0);
     uint32_t tile_iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
@@ -204,29 +230,22 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       ptx::tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
+      // two register buffers: the tensor-memory load of the next 32 columns runs under the bias add, the
+      // packing and the stores of the current ones
+      const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
+      uint32_t ra[32], rb[32];
+      ptx::tmem_ld_32x32b_x32(tacc, ra);
 #pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
+      for (int c = 0; c < kBN; c += 64) {
         if (n0 + c >= N) break;
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + acc * kAccCols + c + ((uint32_t)(q * 32) << 16), r);
         ptx::tmem_ld_wait();
-        if (row < M) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {  // 8 columns = 16 bytes per store
-            if (n0 + c + g * 8 < N) {
-              uint4 v;
-              v.x = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 0]) + s_bias[c + g * 8 + 0],
-                                       __uint_as_float(r[g * 8 + 1]) + s_bias[c + g * 8 + 1]);
-              v.y = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 2]) + s_bias[c + g * 8 + 2],
-                                       __uint_as_float(r[g * 8 + 3]) + s_bias[c + g * 8 + 3]);
-              v.z = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 4]) + s_bias[c + g * 8 + 4],
-                                       __uint_as_float(r[g * 8 + 5]) + s_bias[c + g * 8 + 5]);
-              v.w = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 6]) + s_bias[c + g * 8 + 6],
-                                       __uint_as_float(r[g * 8 + 7]) + s_bias[c + g * 8 + 7]);
-              *reinterpret_cast<uint4*>(crow + c + g * 8) = v;
-            }
-          }
-        }
+        const bool second = n0 + c + 32 < N;
+        if (second) ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
+        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide);
+        if (!second) break;
+        ptx::tmem_ld_wait();
+        if (c + 64 < kBN && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
+        if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide);
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -387,6 +406,7 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     // ---------------------------------------------------------------- epilogue (128 threads per CTA)
     const int q = warp & 3;
     const int et = threadIdx.x - 64;
+    const bool wide = (N % 16 == 0) && (reinterpret_cast<uintptr_t>(C) % 32 == 0);
     uint32_t tile_iter = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tile_iter) {
@@ -403,29 +423,22 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
       ptx::tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
+      // two register buffers: the tensor-memory load of the next 32 columns runs under the bias add, the
+      // packing and the stores of the current ones
+      const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
+      uint32_t ra[32], rb[32];
+      ptx::tmem_ld_32x32b_x32(tacc, ra);
 #pragma unroll 1
-      for (int c = 0; c < kBN; c += 32) {
+      for (int c = 0; c < kBN; c += 64) {
         if (n0 + c >= N) break;
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + acc * kAccCols + c + ((uint32_t)(q * 32) << 16), r);
         ptx::tmem_ld_wait();
-        if (row < M) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (n0 + c + g * 8 < N) {
-              uint4 v;
-              v.x = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 0]) + s_bias[c + g * 8 + 0],
-                                       __uint_as_float(r[g * 8 + 1]) + s_bias[c + g * 8 + 1]);
-              v.y = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 2]) + s_bias[c + g * 8 + 2],
-                                       __uint_as_float(r[g * 8 + 3]) + s_bias[c + g * 8 + 3]);
-              v.z = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 4]) + s_bias[c + g * 8 + 4],
-                                       __uint_as_float(r[g * 8 + 5]) + s_bias[c + g * 8 + 5]);
-              v.w = OutPack<FMT>::pack(__uint_as_float(r[g * 8 + 6]) + s_bias[c + g * 8 + 6],
-                                       __uint_as_float(r[g * 8 + 7]) + s_bias[c + g * 8 + 7]);
-              *reinterpret_cast<uint4*>(crow + c + g * 8) = v;
-            }
-          }
-        }
+        const bool second = n0 + c + 32 < N;
+        if (second) ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
+        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide);
+        if (!second) break;
+        ptx::tmem_ld_wait();
+        if (c + 64 < kBN && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
+        if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide);
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
