@@ -5,7 +5,7 @@
 // Two code paths in one backend:
 //   * fp16 / bf16, K % 8 == 0, N % 8 == 0: persistent warp-specialised tcgen05 kernel — TMA (128-byte
 //     swizzle, no multicast) feeds a 4-stage shared-memory ring, one thread issues
-//     tcgen05.mma.cta_group::1 (128 x 256 x 16) into two 256-column TMEM accumulators, four epilogue warps
+//     tcgen05.mma.cta_group::1 (128 x 256 x 16) into two 256-column TMEM accumulators, eight epilogue warps
 //     drain one accumulator (tcgen05.ld), add the bias and store while the other is being filled;
 //   * everything else (fp32, odd shapes): a tiled SIMT kernel with fp32 accumulation.
 // Replaces NestedTensor_matmul's packed fast path (nestedtensor/csrc/matmul.cpp:12-45, one cuBLAS GEMM)
@@ -31,7 +31,9 @@ constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;    // 48 KB
 constexpr int kAccCols = kBN;                     // fp32 accumulator columns per stage
 constexpr int kTmemCols = 2 * kAccCols;           // 512: the whole TMEM, two accumulator stages
-constexpr int kGemmThreads = 192;                 // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kEpiWarps = 8;                      // two warps per tensor-memory lane quarter, 128 columns each
+constexpr int kEpiThreads = 32 * kEpiWarps;
+constexpr int kGemmThreads = 64 + kEpiThreads;    // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int kCtrlBytes = 256 + kBN * 4;         // barriers + tmem slot + abort flag, bias tile
 constexpr int kGemmSmem = 1024 + kStages * kStageBytes + kCtrlBytes;
 
@@ -124,7 +126,7 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(ptx::smem_u32(&ctrl->tfull[a]), 1);
-      ptx::mbar_init(ptx::smem_u32(&ctrl->tempty[a]), 4);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tempty[a]), kEpiWarps);
     }
     ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
     ctrl->abort = 0;
@@ -210,7 +212,7 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       ptx::mbar_wait(ptx::smem_u32(&ctrl->done), 0);
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (128 threads)
+    // ---------------------------------------------------------------- epilogue (256 threads)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int et = threadIdx.x - 64;
     const bool wide = (N % 16 == 0) && (reinterpret_cast<uintptr_t>(C) % 32 == 0);
@@ -219,12 +221,12 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
       const int m0 = (tile / num_n) * kBM, n0 = (tile % num_n) * kBN;
       const uint32_t acc = tile_iter & 1;
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // previous tile's bias reads are done
-      for (int i = et; i < kBN; i += 128) {
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // previous tile's bias reads are done
+      for (int i = et; i < kBN; i += kEpiThreads) {
         const int n = n0 + i;
         s_bias[i] = (bias != nullptr && n < N) ? OutPack<FMT>::load(bias, n) : 0.0f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
       if (!ok) continue;  // keep taking the named barriers with the other epilogue warps
       ptx::tc_fence_after_sync();
@@ -234,9 +236,10 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       // packing and the stores of the current ones
       const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
       uint32_t ra[32], rb[32];
-      ptx::tmem_ld_32x32b_x32(tacc, ra);
+      const int c_begin = ((warp - 2) >> 2) * (kBN / 2), c_end = c_begin + kBN / 2;  // this warp's 128 columns
+      if (n0 + c_begin < N) ptx::tmem_ld_32x32b_x32(tacc + c_begin, ra);
 #pragma unroll 1
-      for (int c = 0; c < kBN; c += 64) {
+      for (int c = c_begin; c < c_end; c += 64) {
         if (n0 + c >= N) break;
         ptx::tmem_ld_wait();
         const bool second = n0 + c + 32 < N;
@@ -244,7 +247,7 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide);
         if (!second) break;
         ptx::tmem_ld_wait();
-        if (c + 64 < kBN && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
+        if (c + 64 < c_end && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
         if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide);
       }
       ptx::tc_fence_before_sync();
@@ -281,7 +284,7 @@ struct Ctrl2 {
   uint64_t full[k2Stages];    // used in CTA 0: bytes of both CTAs
   uint64_t empty[k2Stages];   // one per CTA
   uint64_t tfull[2];          // one per CTA
-  uint64_t tempty[2];         // used in CTA 0: 4 epilogue warps of each CTA
+  uint64_t tempty[2];         // used in CTA 0: the epilogue warps of both CTAs arrive
   uint64_t done;
   uint32_t tmem_base;
   volatile int abort;
@@ -310,7 +313,7 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(ptx::smem_u32(&ctrl->tfull[a]), 1);
-      ptx::mbar_init(ptx::smem_u32(&ctrl->tempty[a]), 8);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tempty[a]), 2 * kEpiWarps);
     }
     ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
     ctrl->abort = 0;
@@ -403,7 +406,7 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
       ptx::mbar_wait(ptx::smem_u32(&ctrl->done), 0);
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (128 threads per CTA)
+    // ---------------------------------------------------------------- epilogue (256 threads per CTA)
     const int q = warp & 3;
     const int et = threadIdx.x - 64;
     const bool wide = (N % 16 == 0) && (reinterpret_cast<uintptr_t>(C) % 32 == 0);
@@ -412,12 +415,12 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tile_iter) {
       const int m0 = (tile / num_n) * 256 + (int)rank * 128, n0 = (tile % num_n) * 256;
       const uint32_t acc = tile_iter & 1;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int i = et; i < kBN; i += 128) {
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      for (int i = et; i < kBN; i += kEpiThreads) {
         const int n = n0 + i;
         s_bias[i] = (bias != nullptr && n < N) ? OutPack<FMT>::load(bias, n) : 0.0f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
       if (!ok) continue;
       ptx::tc_fence_after_sync();
@@ -427,9 +430,10 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
       // packing and the stores of the current ones
       const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
       uint32_t ra[32], rb[32];
-      ptx::tmem_ld_32x32b_x32(tacc, ra);
+      const int c_begin = ((warp - 2) >> 2) * (kBN / 2), c_end = c_begin + kBN / 2;  // this warp's 128 columns
+      if (n0 + c_begin < N) ptx::tmem_ld_32x32b_x32(tacc + c_begin, ra);
 #pragma unroll 1
-      for (int c = 0; c < kBN; c += 64) {
+      for (int c = c_begin; c < c_end; c += 64) {
         if (n0 + c >= N) break;
         ptx::tmem_ld_wait();
         const bool second = n0 + c + 32 < N;
@@ -437,7 +441,7 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
         if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide);
         if (!second) break;
         ptx::tmem_ld_wait();
-        if (c + 64 < kBN && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
+        if (c + 64 < c_end && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
         if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide);
       }
       ptx::tc_fence_before_sync();
