@@ -79,6 +79,7 @@ def run_pipeline(n: int, upload: Callable[[int, int], None], compute: Callable[[
             ev_down[c].record(s_down)
     for c in range(max(0, n - slots), n):
         caller.wait_event(ev_down[c])
+        s_comp.wait_event(ev_down[c])  # memory that compute callbacks allocated may be released after this point
 
 
 def _check_host(t: torch.Tensor, name: str) -> None:
@@ -194,9 +195,9 @@ def from_padded_tensor_host(h_padded: torch.Tensor, sizes: torch.Tensor, out: Op
 
         def download(c, slot):
             a, b = parts[c]
-            r = results[slot]
-            r.record_stream(torch.cuda.current_stream(device))  # produced on the compute stream, read on this one
-            out[int(offs[a]):int(offs[b])].copy_(r, non_blocking=True)
+            # results[slot] stays referenced until range c + 2 replaces it, which the compute stream does only
+            # after waiting for this download: its memory cannot be handed out again before the copy has run
+            out[int(offs[a]):int(offs[b])].copy_(results[slot], non_blocking=True)
 
         run_pipeline(len(parts), upload, compute, download, device)
     return out
@@ -262,11 +263,9 @@ def multi_head_attention_host(h_x: torch.Tensor, sizes: torch.Tensor, num_heads:
 
         def download(c, slot):
             a, b = parts[c]
-            r = results[slot]
-            # produced on the compute stream, read here on the download stream: keep its memory from being
-            # handed out again before this copy has run
-            r.record_stream(torch.cuda.current_stream(device))
-            o2[int(toff[a]):int(toff[b])].copy_(r.reshape(-1, E), non_blocking=True)
+            # results[slot] stays referenced until range c + 2 replaces it, which the compute stream does only
+            # after waiting for this download: its memory cannot be handed out again before the copy has run
+            o2[int(toff[a]):int(toff[b])].copy_(results[slot].reshape(-1, E), non_blocking=True)
 
         run_pipeline(len(parts), upload, compute, download, device)
     return out
