@@ -187,6 +187,16 @@ int ntb200_token_index(const int64_t* token_offsets, int64_t batch, int64_t tota
 int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, int64_t M, int64_t N,
                      int64_t K, int dtype, int force_simt, void* stream);
 
+/* The same projection with the rest of a transformer layer's epilogue fused into the store:
+ *   C = act(A W^T + bias) + residual      act: 0 = identity, 1 = GELU (tanh form), 2 = ReLU; residual [M,N] or NULL
+ * so the feed-forward up-projection (bias + GELU) and the two down-projections (bias + residual) make no
+ * separate pass over their [sum(L_i), N] outputs.  Replaces add_bias_act_kernelLauncher
+ * (nestedtensor/csrc/cuda/cuda_kernels.cu:73-104) and add_bias_input_kernelLauncher
+ * (nestedtensor/csrc/cuda/transformer_kernels.cu:235-258) run after a cuBLAS GEMM.
+ */
+int ntb200_gemm_bias_act(const void* A, const void* W, const void* bias, const void* residual, void* C,
+                         int64_t M, int64_t N, int64_t K, int dtype, int act, int force_simt, void* stream);
+
 /* Bit mask of device-side wait time-outs recorded by the tcgen05 kernels since the last call
  * (0 = none; projection GEMM: bit 0 TMA producer, bit 1 MMA issuer, bit 2 epilogue; attention: the
  * same roles in bits 8-10); synchronises the device; negative on a CUDA error.  No counterpart in the
@@ -213,6 +223,28 @@ int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, 
                             int64_t total_tokens, int num_heads, int head_dim, int64_t max_len,
                             float scaling, int dtype, int path, void* workspace,
                             size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ packed row operators
+ * Rows are the tokens of the packed [rows = sum(L_i), cols] matrix of a nested tensor; arithmetic in fp32,
+ * one read and one write per element; `out` may be `x` (in place).
+ *
+ * out = (x - mean(x)) * rsqrt(var(x) + eps) * gamma + beta per row (gamma and beta both NULL: no affine).
+ * Replaces fastertransformer::layer_norm (nestedtensor/csrc/cuda/transformer_kernels.cu:260-335) behind
+ * cuda::NestedTensor_layer_norm (nestedtensor/csrc/cuda/layernorm.cpp:14-76).
+ */
+int ntb200_layer_norm(const void* x, const void* gamma, const void* beta, float eps, void* out,
+                      int64_t rows, int64_t cols, int dtype, void* stream);
+/* The same on x + residual + bias (residual [rows,cols] and bias [cols], either may be NULL).
+ * Replaces add_bias_input_layernorm_kernelLauncher (nestedtensor/csrc/cuda/transformer_kernels.cu:64-156,
+ * nestedtensor/csrc/cuda/cuda_kernels.cu:114-159), whose eps is fixed at 1e-6. */
+int ntb200_add_bias_residual_layer_norm(const void* x, const void* residual, const void* bias,
+                                        const void* gamma, const void* beta, float eps, void* out,
+                                        int64_t rows, int64_t cols, int dtype, void* stream);
+/* out = gelu_tanh(x + bias) (bias [cols] or NULL).  Replaces add_bias_act_kernelLauncher
+ * (nestedtensor/csrc/cuda/cuda_kernels.cu:73-104) and add_bias_gelu
+ * (nestedtensor/csrc/cuda/transformer_kernels.cu:52-62). */
+int ntb200_add_bias_gelu(const void* x, const void* bias, void* out, int64_t rows, int64_t cols,
+                         int dtype, void* stream);
 
 /* ------------------------------------------------------------------ reference-shaped helpers
  * q/k/v_buf[b, h, l, :] = qkv[tok(b,l), {0,E,2E} + h*d + :] + bias  for valid tokens (padded

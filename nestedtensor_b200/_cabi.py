@@ -36,6 +36,12 @@ SIGNATURES = {
     "ntb200_token_index": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "ntb200_gemm_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                                  c_void_p]),
+    "ntb200_gemm_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                     c_int, c_int, c_void_p]),
+    "ntb200_layer_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "ntb200_add_bias_residual_layer_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                                                    c_int64, c_int64, c_int, c_void_p]),
+    "ntb200_add_bias_gelu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "ntb200_device_error_flags": (c_int, []),
     "ntb200_varlen_attention_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int, c_int]),
     "ntb200_varlen_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int64,

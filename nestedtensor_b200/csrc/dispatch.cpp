@@ -441,7 +441,7 @@ int dtype_code(at::ScalarType t) {
     case at::kFloat: return NTB200_F32;
     case at::kHalf: return NTB200_F16;
     case at::kBFloat16: return NTB200_BF16;
-    default: TORCH_CHECK(false, "nestedtensor_b200: attention supports float32, float16 and bfloat16, got ", t);
+    default: TORCH_CHECK(false, "nestedtensor_b200: this operator supports float32, float16 and bfloat16, got ", t);
   }
 }
 
@@ -449,9 +449,9 @@ int dtype_code(at::ScalarType t) {
 //   qkv = x W_in^T + b_in   ->  varlen softmax(scaling * q k^T) v per sequence and head  ->  out W_out^T + b_out
 // Dropout arguments are accepted and ignored exactly as in the reference (inference path).  Unlike the
 // reference (mha.cpp:106) the output projection bias IS added, as in min_mha (nestedtensor/csrc/mha.cpp:66-67).
-Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, bool /*training*/, const Tensor& buffer,
-                  const Tensor& sizes, const Tensor& meta, const Tensor& attr_kernel, const Tensor& attr_bias,
-                  double scaling, const Tensor& out_proj_weight, const c10::optional<Tensor>& out_proj_bias) {
+// QKV projection and the varlen attention core: returns the [T, E] context (before the output projection).
+Tensor bt_min_mha_core(int64_t num_heads, int64_t head_dim, const Tensor& buffer, const Tensor& sizes, const Tensor& meta,
+                       const Tensor& attr_kernel, const Tensor& attr_bias, double scaling) {
   Record r = make_record(sizes, meta);
   TORCH_CHECK(r.tdim == 2, "query needs to be 3 dim.");
   check_buffer(buffer, r, "bt_min_mha");
@@ -465,25 +465,14 @@ Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, boo
   };
   same(attr_kernel, "in_proj_weight");
   same(attr_bias, "in_proj_bias");
-  same(out_proj_weight, "out_proj_weight");
   TORCH_CHECK(attr_kernel.dim() == 2 && attr_kernel.size(0) == 3 * E && attr_kernel.size(1) == E, "in_proj_weight must be [3E, E]");
   TORCH_CHECK(attr_bias.numel() == 3 * E, "in_proj_bias must have 3E entries");
-  TORCH_CHECK(out_proj_weight.dim() == 2 && out_proj_weight.size(0) == E && out_proj_weight.size(1) == E, "out_proj_weight must be [E, E]");
   c10::cuda::CUDAGuard guard(buffer.device());
   const int64_t T = r.numel / (E > 0 ? E : 1);
-  Tensor out = at::empty({T * E}, buffer.options());
-  if (T == 0) return out;
-  Tensor w_in = attr_kernel.contiguous(), b_in = attr_bias.contiguous(), w_out = out_proj_weight.contiguous();
-  const void* b_out = nullptr;
-  Tensor b_out_t;
-  if (out_proj_bias && out_proj_bias->defined()) {
-    same(*out_proj_bias, "out_proj_bias");
-    TORCH_CHECK(out_proj_bias->numel() == E, "out_proj_bias must have E entries");
-    b_out_t = out_proj_bias->contiguous();
-    b_out = b_out_t.data_ptr();
-  }
-  Tensor qkv = at::empty({T, 3 * E}, buffer.options());
   Tensor attn = at::empty({T, E}, buffer.options());
+  if (T == 0) return attn;
+  Tensor w_in = attr_kernel.contiguous(), b_in = attr_bias.contiguous();
+  Tensor qkv = at::empty({T, 3 * E}, buffer.options());
   void* st = cur_stream();
   check_rc(ntb200_gemm_bias(buffer.data_ptr(), w_in.data_ptr(), b_in.data_ptr(), qkv.data_ptr(), T, 3 * E, E, dt, 0, st),
            "ntb200_gemm_bias");
@@ -493,7 +482,121 @@ Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, boo
   check_rc(ntb200_varlen_attention(qkv.data_ptr(), attn.data_ptr(), r.d_offsets, r.B, T, (int)num_heads, (int)head_dim,
                                    r.max_sizes[0], (float)scaling, dt, 0, ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, st),
            "ntb200_varlen_attention");
-  check_rc(ntb200_gemm_bias(attn.data_ptr(), w_out.data_ptr(), b_out, out.data_ptr(), T, E, E, dt, 0, st), "ntb200_gemm_bias");
+  return attn;
+}
+
+Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, bool /*training*/, const Tensor& buffer,
+                  const Tensor& sizes, const Tensor& meta, const Tensor& attr_kernel, const Tensor& attr_bias,
+                  double scaling, const Tensor& out_proj_weight, const c10::optional<Tensor>& out_proj_bias) {
+  const int64_t E = num_heads * head_dim;
+  TORCH_CHECK(out_proj_weight.is_cuda() && out_proj_weight.device() == buffer.device() &&
+                  out_proj_weight.scalar_type() == buffer.scalar_type(),
+              "nestedtensor_b200: out_proj_weight must be on the input's device and of its dtype");
+  TORCH_CHECK(out_proj_weight.dim() == 2 && out_proj_weight.size(0) == E && out_proj_weight.size(1) == E, "out_proj_weight must be [E, E]");
+  Tensor attn = bt_min_mha_core(num_heads, head_dim, buffer, sizes, meta, attr_kernel, attr_bias, scaling);
+  const int64_t T = attn.size(0);
+  c10::cuda::CUDAGuard guard(buffer.device());
+  Tensor out = at::empty({T * E}, buffer.options());
+  if (T == 0) return out;
+  Tensor w_out = out_proj_weight.contiguous();
+  const void* b_out = nullptr;
+  Tensor b_out_t;
+  if (out_proj_bias && out_proj_bias->defined()) {
+    TORCH_CHECK(out_proj_bias->is_cuda() && out_proj_bias->device() == buffer.device() &&
+                    out_proj_bias->scalar_type() == buffer.scalar_type(),
+                "nestedtensor_b200: out_proj_bias must be on the input's device and of its dtype");
+    TORCH_CHECK(out_proj_bias->numel() == E, "out_proj_bias must have E entries");
+    b_out_t = out_proj_bias->contiguous();
+    b_out = b_out_t.data_ptr();
+  }
+  check_rc(ntb200_gemm_bias(attn.data_ptr(), w_out.data_ptr(), b_out, out.data_ptr(), T, E, E, dtype_code(buffer.scalar_type()), 0,
+                            cur_stream()),
+           "ntb200_gemm_bias");
+  return out;
+}
+
+// ------------------------------------------------------------------ packed row operators and projections
+// Dense CUDA [T, cols] views of a packed buffer go straight to the C ABI.
+void check_rows(const Tensor& x, const char* op) {
+  TORCH_CHECK(x.is_cuda(), "nestedtensor_b200: ", op, " needs CUDA tensors (this build has no CPU implementation)");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous(), "nestedtensor_b200: ", op, " expects a contiguous [tokens, features] tensor");
+  dtype_code(x.scalar_type());
+}
+
+const void* opt_vec(const c10::optional<Tensor>& t, const Tensor& like, int64_t n, const char* name, Tensor* keep) {
+  if (!t || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->device() == like.device() && t->scalar_type() == like.scalar_type(), "nestedtensor_b200: ",
+              name, " must be on the input's device and of its dtype");
+  TORCH_CHECK(t->numel() == n, "nestedtensor_b200: ", name, " must have ", n, " entries");
+  *keep = t->contiguous();
+  return keep->data_ptr();
+}
+
+// out = LayerNorm(x + residual + bias) * weight + beta over the last dim of the packed [T, E] matrix
+Tensor add_bias_residual_layer_norm(const Tensor& x, const c10::optional<Tensor>& residual, const c10::optional<Tensor>& bias,
+                                    const c10::optional<Tensor>& weight, const c10::optional<Tensor>& beta, double eps) {
+  check_rows(x, "add_bias_residual_layer_norm");
+  const int64_t T = x.size(0), E = x.size(1);
+  TORCH_CHECK((weight && weight->defined()) == (beta && beta->defined()), "Either both weight and bias are used or not.");
+  Tensor keep_r, keep_b, keep_g, keep_be;
+  const void* r = opt_vec(residual, x, T * E, "residual", &keep_r);
+  const void* b = opt_vec(bias, x, E, "bias", &keep_b);
+  const void* g = opt_vec(weight, x, E, "weight", &keep_g);
+  const void* be = opt_vec(beta, x, E, "beta", &keep_be);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = at::empty_like(x);
+  check_rc(ntb200_add_bias_residual_layer_norm(x.data_ptr(), r, b, g, be, (float)eps, out.data_ptr(), T, E,
+                                               dtype_code(x.scalar_type()), cur_stream()),
+           "ntb200_add_bias_residual_layer_norm");
+  return out;
+}
+
+// nestedtensor/csrc/functions.cpp:65-110 + nestedtensor/csrc/cuda/layernorm.cpp:14-76, on the record
+Tensor layer_norm(const Tensor& buffer, const Tensor& sizes, const Tensor& meta, at::IntArrayRef normalized_shape,
+                  const c10::optional<Tensor>& weight, const c10::optional<Tensor>& bias, double eps) {
+  Record r = make_record(sizes, meta);
+  TORCH_CHECK(normalized_shape.size() == 1, "Currently only singleton tuples of integers supported for layer_norm.");
+  TORCH_CHECK(r.tdim >= 1, "Cannot normalize across irregular dimension ", r.tdim);
+  TORCH_CHECK(r.B == 0 || r.regular[r.tdim - 1], "Cannot normalize across irregular dimension ", r.tdim);
+  const int64_t E = r.B > 0 ? r.max_sizes[r.tdim - 1] : normalized_shape[0];
+  TORCH_CHECK(E == normalized_shape[0], "Normalized shape [", normalized_shape[0],
+              "] does not match the size of the last dimension (", E, ") of input.");
+  const bool has_w = weight && weight->defined(), has_b = bias && bias->defined();
+  TORCH_CHECK(has_w == has_b, "Either both weight and bias are used or not.");
+  check_buffer(buffer, r, "layer_norm");
+  if (buffer.numel() == 0) return buffer.clone();
+  TORCH_CHECK(E > 0, "nestedtensor_b200: layer_norm over an empty dimension");
+  return add_bias_residual_layer_norm(buffer.view({buffer.numel() / E, E}), c10::nullopt, c10::nullopt, weight, bias, eps)
+      .view({buffer.numel()});
+}
+
+// C = act(x W^T + bias) + residual on the packed [T, K] matrix (act: 0 identity, 1 GELU tanh form, 2 ReLU)
+Tensor packed_linear(const Tensor& x, const Tensor& weight, const c10::optional<Tensor>& bias, int64_t act,
+                     const c10::optional<Tensor>& residual) {
+  check_rows(x, "packed_linear");
+  TORCH_CHECK(weight.is_cuda() && weight.device() == x.device() && weight.scalar_type() == x.scalar_type() && weight.dim() == 2 &&
+                  weight.size(1) == x.size(1),
+              "nestedtensor_b200: weight must be [out_features, in_features] on the input's device and of its dtype");
+  const int64_t T = x.size(0), K = x.size(1), N = weight.size(0);
+  Tensor w = weight.contiguous(), keep_b, keep_r;
+  const void* b = opt_vec(bias, x, N, "bias", &keep_b);
+  const void* r = opt_vec(residual, x, T * N, "residual", &keep_r);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = at::empty({T, N}, x.options());
+  check_rc(ntb200_gemm_bias_act(x.data_ptr(), w.data_ptr(), b, r, out.data_ptr(), T, N, K, dtype_code(x.scalar_type()), (int)act,
+                                0, cur_stream()),
+           "ntb200_gemm_bias_act");
+  return out;
+}
+
+Tensor add_bias_gelu(const Tensor& x, const c10::optional<Tensor>& bias) {
+  check_rows(x, "add_bias_gelu");
+  Tensor keep_b;
+  const void* b = opt_vec(bias, x, x.size(1), "bias", &keep_b);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = at::empty_like(x);
+  check_rc(ntb200_add_bias_gelu(x.data_ptr(), b, out.data_ptr(), x.size(0), x.size(1), dtype_code(x.scalar_type()), cur_stream()),
+           "ntb200_add_bias_gelu");
   return out;
 }
 
@@ -517,4 +620,14 @@ TORCH_LIBRARY(nestedtensor, m) {
       "bt_min_mha(int num_heads, int head_dim, float dropout_p, bool training, Tensor buffer, Tensor sizes, Tensor meta, "
       "Tensor attr_kernel, Tensor attr_bias, float scaling, Tensor out_proj_weight, Tensor? out_proj_bias) -> Tensor",
       &bt_min_mha);
+  m.def(
+      "bt_min_mha_core(int num_heads, int head_dim, Tensor buffer, Tensor sizes, Tensor meta, Tensor attr_kernel, "
+      "Tensor attr_bias, float scaling) -> Tensor",
+      &bt_min_mha_core);
+  m.def("layer_norm(Tensor buffer, Tensor sizes, Tensor meta, int[] normalized_shape, Tensor? weight, Tensor? bias, float eps) -> Tensor",
+        &layer_norm);
+  m.def("add_bias_residual_layer_norm(Tensor x, Tensor? residual, Tensor? bias, Tensor? weight, Tensor? beta, float eps) -> Tensor",
+        &add_bias_residual_layer_norm);
+  m.def("packed_linear(Tensor x, Tensor weight, Tensor? bias, int act, Tensor? residual) -> Tensor", &packed_linear);
+  m.def("add_bias_gelu(Tensor x, Tensor? bias) -> Tensor", &add_bias_gelu);
 }

@@ -69,6 +69,8 @@ struct OutPack<0> {  // fp16
     return *reinterpret_cast<uint32_t*>(&h);
   }
   static __device__ __forceinline__ float load(const void* p, int i) { return __half2float(reinterpret_cast<const __half*>(p)[i]); }
+  static __device__ __forceinline__ float lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
 };
 template <>
 struct OutPack<1> {  // bf16
@@ -79,18 +81,52 @@ struct OutPack<1> {  // bf16
   static __device__ __forceinline__ float load(const void* p, int i) {
     return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
   }
+  static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 };
 
-// 32 accumulator columns of one output row: + bias, packed to 16 bits, stored.  With `wide` (row stride and
-// base 32-byte aligned) each store is one full 32-byte sector (st.global.v8); a warp-wide 16-byte store per
-// row would touch every sector twice.
+// tanh form of GELU (the one the reference's fused kernels use, nestedtensor/csrc/cuda/cuda_kernels.cu:29-36)
+// with the hardware tanh approximation (relative error 2^-11, below the 16-bit output rounding).
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+  return 0.5f * x * (1.0f + t);
+}
+
+// 32 accumulator columns of one output row: + bias, optional GELU, optional + residual (the same 32 columns
+// of the residual row, `res`, or nullptr), packed to 16 bits, stored.  With `wide` (row stride and base
+// 32-byte aligned) each store is one full 32-byte sector (st.global.v8); a warp-wide 16-byte store per row
+// would touch every sector twice.
 template <int FMT>
 __device__ __forceinline__ void store_chunk32(uint16_t* dst, const uint32_t (&r)[32], const float* bias32, int n_left,
-                                              bool wide) {
+                                              bool wide, int act, const uint16_t* res) {
+  float v[32];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]) + bias32[k];
+  if (act == 1) {
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = gelu_tanh_fast(v[k]);
+  } else if (act == 2) {
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = fmaxf(v[k], 0.0f);
+  }
+  if (res != nullptr) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < n_left) {
+        const uint4 q = *reinterpret_cast<const uint4*>(res + g * 8);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          v[g * 8 + 2 * k] += OutPack<FMT>::lo(w[k]);
+          v[g * 8 + 2 * k + 1] += OutPack<FMT>::hi(w[k]);
+        }
+      }
+    }
+  }
   uint32_t p[16];
 #pragma unroll
-  for (int k = 0; k < 16; ++k)
-    p[k] = OutPack<FMT>::pack(__uint_as_float(r[2 * k]) + bias32[2 * k], __uint_as_float(r[2 * k + 1]) + bias32[2 * k + 1]);
+  for (int k = 0; k < 16; ++k) p[k] = OutPack<FMT>::pack(v[2 * k], v[2 * k + 1]);
   if (wide) {
 #pragma unroll
     for (int g = 0; g < 2; ++g)
@@ -109,7 +145,8 @@ __device__ __forceinline__ void store_chunk32(uint16_t* dst, const uint32_t (&r)
 template <int FMT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                         const void* __restrict__ bias, void* __restrict__ C, int M, int N, int K) {
+                         const void* __restrict__ bias, const void* __restrict__ residual, int act, void* __restrict__ C,
+                         int M, int N, int K) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kStages * kStageBytes);
@@ -232,6 +269,7 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       ptx::tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
+      const uint16_t* rrow = residual != nullptr ? reinterpret_cast<const uint16_t*>(residual) + (size_t)row * N + n0 : nullptr;
       // two register buffers: the tensor-memory load of the next 32 columns runs under the bias add, the
       // packing and the stores of the current ones
       const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
@@ -244,11 +282,12 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         ptx::tmem_ld_wait();
         const bool second = n0 + c + 32 < N;
         if (second) ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
-        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide);
+        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide, act, rrow != nullptr ? rrow + c : nullptr);
         if (!second) break;
         ptx::tmem_ld_wait();
         if (c + 64 < c_end && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
-        if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide);
+        if (row < M)
+          store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide, act, rrow != nullptr ? rrow + c + 32 : nullptr);
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -294,7 +333,8 @@ static_assert(sizeof(Ctrl2) <= 256, "control block");
 template <int FMT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                              const void* __restrict__ bias, void* __restrict__ C, int M, int N, int K) {
+                              const void* __restrict__ bias, const void* __restrict__ residual, int act, void* __restrict__ C,
+                         int M, int N, int K) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Ctrl2* ctrl = reinterpret_cast<Ctrl2*>(smem + k2Stages * k2StageBytes);
@@ -426,6 +466,7 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
       ptx::tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
+      const uint16_t* rrow = residual != nullptr ? reinterpret_cast<const uint16_t*>(residual) + (size_t)row * N + n0 : nullptr;
       // two register buffers: the tensor-memory load of the next 32 columns runs under the bias add, the
       // packing and the stores of the current ones
       const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
@@ -438,11 +479,12 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
         ptx::tmem_ld_wait();
         const bool second = n0 + c + 32 < N;
         if (second) ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
-        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide);
+        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide, act, rrow != nullptr ? rrow + c : nullptr);
         if (!second) break;
         ptx::tmem_ld_wait();
         if (c + 64 < c_end && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
-        if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide);
+        if (row < M)
+          store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide, act, rrow != nullptr ? rrow + c + 32 : nullptr);
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -496,7 +538,8 @@ bool make_map_2d(CUtensorMap* map, const void* base, int dtype, uint64_t rows, u
 }
 
 template <int FMT>
-int launch_tcgen05(const void* A, const void* W, const void* bias, void* C, int M, int N, int K, int dtype, cudaStream_t st) {
+int launch_tcgen05(const void* A, const void* W, const void* bias, const void* residual, int act, void* C, int M, int N, int K,
+                   int dtype, cudaStream_t st) {
   CUtensorMap map_a, map_w;
   if (!make_map_2d(&map_a, A, dtype, (uint64_t)M, (uint64_t)K, kBM)) return NTB200_LAUNCH_FAILED;
   if (!make_map_2d(&map_w, W, dtype, (uint64_t)N, (uint64_t)K, kBN)) return NTB200_LAUNCH_FAILED;
@@ -510,12 +553,13 @@ int launch_tcgen05(const void* A, const void* W, const void* bias, void* C, int 
   int dev = 0, sms = kNumSMs;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = num_tiles < sms ? num_tiles : sms;
-  gemm_bias_tcgen05_kernel<FMT><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_w, bias, C, M, N, K);
+  gemm_bias_tcgen05_kernel<FMT><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_w, bias, residual, act, C, M, N, K);
   return status_from_cuda(cudaGetLastError());
 }
 
 template <int FMT>
-int launch_tcgen05_pair(const void* A, const void* W, const void* bias, void* C, int M, int N, int K, int dtype, cudaStream_t st) {
+int launch_tcgen05_pair(const void* A, const void* W, const void* bias, const void* residual, int act, void* C, int M, int N,
+                        int K, int dtype, cudaStream_t st) {
   CUtensorMap map_a, map_w;
   if (!make_map_2d(&map_a, A, dtype, (uint64_t)M, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
   if (!make_map_2d(&map_w, W, dtype, (uint64_t)N, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
@@ -550,7 +594,7 @@ int launch_tcgen05_pair(const void* A, const void* W, const void* bias, void* C,
   }
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
   cfg.gridDim = dim3(2 * pairs);
-  if (cudaLaunchKernelEx(&cfg, gemm_bias_tcgen05_pair_kernel<FMT>, map_a, map_w, bias, C, M, N, K) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemm_bias_tcgen05_pair_kernel<FMT>, map_a, map_w, bias, residual, act, C, M, N, K) != cudaSuccess) {
     (void)cudaGetLastError();
     return NTB200_LAUNCH_FAILED;
   }
@@ -580,8 +624,8 @@ constexpr int kSimtTile = 64, kSimtK = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(256) gemm_bias_simt_kernel(const T* __restrict__ A, const T* __restrict__ W,
-                                                             const T* __restrict__ bias, T* __restrict__ C, int64_t M,
-                                                             int64_t N, int64_t K) {
+                                                             const T* __restrict__ bias, const T* __restrict__ residual,
+                                                             int act, T* __restrict__ C, int64_t M, int64_t N, int64_t K) {
   __shared__ float sA[kSimtK][kSimtTile + 1];
   __shared__ float sW[kSimtK][kSimtTile + 1];
   const int64_t m0 = (int64_t)blockIdx.y * kSimtTile, n0 = (int64_t)blockIdx.x * kSimtTile;
@@ -619,18 +663,26 @@ __global__ void __launch_bounds__(256) gemm_bias_simt_kernel(const T* __restrict
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int64_t n = n0 + tx * 4 + j;
-      if (n < N) C[m * N + n] = Cvt<T>::from_f(acc[i][j] + (bias != nullptr ? Cvt<T>::to_f(bias[n]) : 0.0f));
+      if (n < N) {
+        float v = acc[i][j] + (bias != nullptr ? Cvt<T>::to_f(bias[n]) : 0.0f);
+        if (act == 1) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        if (act == 2) v = fmaxf(v, 0.0f);
+        if (residual != nullptr) v += Cvt<T>::to_f(residual[m * N + n]);
+        C[m * N + n] = Cvt<T>::from_f(v);
+      }
     }
   }
 }
 
 template <typename T>
-int launch_simt(const void* A, const void* W, const void* bias, void* C, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+int launch_simt(const void* A, const void* W, const void* bias, const void* residual, int act, void* C, int64_t M, int64_t N,
+                int64_t K, cudaStream_t st) {
   const int64_t gx = (N + kSimtTile - 1) / kSimtTile, gy = (M + kSimtTile - 1) / kSimtTile;
   if (gx > 0x7fffffffll || gy > 65535) return NTB200_UNSUPPORTED_SHAPE;
   dim3 grid((unsigned)gx, (unsigned)gy);
   gemm_bias_simt_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(A), static_cast<const T*>(W),
-                                                 static_cast<const T*>(bias), static_cast<T*>(C), M, N, K);
+                                                 static_cast<const T*>(bias), static_cast<const T*>(residual), act,
+                                                 static_cast<T*>(C), M, N, K);
   return status_from_cuda(cudaGetLastError());
 }
 
@@ -654,35 +706,41 @@ using namespace ntb200;
 
 extern "C" {
 
-int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, int64_t M, int64_t N, int64_t K, int dtype,
-                     int force_simt, void* stream) {
-  if (M < 0 || N < 0 || K < 0) return NTB200_INVALID_ARG;
+int ntb200_gemm_bias_act(const void* A, const void* W, const void* bias, const void* residual, void* C, int64_t M, int64_t N,
+                         int64_t K, int dtype, int act, int force_simt, void* stream) {
+  if (M < 0 || N < 0 || K < 0 || act < 0 || act > 2) return NTB200_INVALID_ARG;
   if (dtype != NTB200_F32 && dtype != NTB200_F16 && dtype != NTB200_BF16) return NTB200_UNSUPPORTED_DTYPE;
   if (M == 0 || N == 0) return NTB200_OK;
   if (A == nullptr || W == nullptr || C == nullptr) return NTB200_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // force_simt: 0 = best available, 1 = SIMT, 2 = single-CTA tcgen05 kernel, 3 = CTA-pair tcgen05 kernel
   const bool tc = force_simt != 1 && dtype != NTB200_F32 && K >= 8 && (K % 8) == 0 && (N % 8) == 0 && aligned16(A) && aligned16(W) &&
-                  aligned16(C) && M < (1ll << 31) - 256 && N < (1ll << 31) - 256 && K < (1ll << 31) - kBK;
+                  aligned16(C) && (residual == nullptr || aligned16(residual)) && M < (1ll << 31) - 256 && N < (1ll << 31) - 256 && K < (1ll << 31) - kBK;
   if ((force_simt == 2 || force_simt == 3) && !tc) return NTB200_UNSUPPORTED_SHAPE;
   if (tc) {
     const bool pair = force_simt == 3 || (force_simt == 0 && M > 128);
     if (pair) {
-      if (dtype == NTB200_F16) return launch_tcgen05_pair<0>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
-      return launch_tcgen05_pair<1>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
+      if (dtype == NTB200_F16) return launch_tcgen05_pair<0>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
+      return launch_tcgen05_pair<1>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
     }
-    if (dtype == NTB200_F16) return launch_tcgen05<0>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
-    return launch_tcgen05<1>(A, W, bias, C, (int)M, (int)N, (int)K, dtype, st);
+    if (dtype == NTB200_F16) return launch_tcgen05<0>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
+    return launch_tcgen05<1>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
   }
   const size_t es = dtype == NTB200_F32 ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(A) % es) || (reinterpret_cast<uintptr_t>(W) % es) || (reinterpret_cast<uintptr_t>(C) % es))
+  if ((reinterpret_cast<uintptr_t>(A) % es) || (reinterpret_cast<uintptr_t>(W) % es) || (reinterpret_cast<uintptr_t>(C) % es) ||
+      (reinterpret_cast<uintptr_t>(residual) % es))
     return NTB200_MISALIGNED;
   switch (dtype) {
-    case NTB200_F32: return launch_simt<float>(A, W, bias, C, M, N, K, st);
-    case NTB200_F16: return launch_simt<__half>(A, W, bias, C, M, N, K, st);
-    case NTB200_BF16: return launch_simt<__nv_bfloat16>(A, W, bias, C, M, N, K, st);
+    case NTB200_F32: return launch_simt<float>(A, W, bias, residual, act, C, M, N, K, st);
+    case NTB200_F16: return launch_simt<__half>(A, W, bias, residual, act, C, M, N, K, st);
+    case NTB200_BF16: return launch_simt<__nv_bfloat16>(A, W, bias, residual, act, C, M, N, K, st);
   }
   return NTB200_UNSUPPORTED_DTYPE;
+}
+
+int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, int64_t M, int64_t N, int64_t K, int dtype,
+                     int force_simt, void* stream) {
+  return ntb200_gemm_bias_act(A, W, bias, nullptr, C, M, N, K, dtype, 0, force_simt, stream);
 }
 
 int ntb200_device_error_flags(void) {

@@ -1,0 +1,357 @@
+// Row operators on the packed token matrix [T = sum(L_i), E] of a nested tensor: the steps of a
+// transformer encoder layer that sit between the projections.  All of them stream every element once
+// (HBM-bound), never see padding, and keep their arithmetic in fp32 whatever the storage type.
+//
+//   layer_norm                    out = (x - mean) * rsqrt(var + eps) * gamma + beta          per row
+//   add_bias_residual_layer_norm  the same on x + residual + bias (one pass instead of three)
+//   add_bias_gelu                 out = gelu_tanh(x + bias)
+//
+// Replaces fastertransformer::layer_norm (nestedtensor/csrc/cuda/transformer_kernels.cu:260-335) as used by
+// cuda::NestedTensor_layer_norm (nestedtensor/csrc/cuda/layernorm.cpp:14-76), add_bias_input_layernorm
+// (transformer_kernels.cu:64-156, cuda_kernels.cu:114-159) and add_bias_act / add_bias_gelu
+// (cuda_kernels.cu:73-104, transformer_kernels.cu:52-62).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace ntb200 {
+namespace {
+
+// 16 bytes of storage <-> fp32 lanes
+template <int DT>
+struct Vec16;
+template <>
+struct Vec16<NTB200_F32> {
+  static constexpr int kElems = 4;
+  static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+    f[0] = __uint_as_float(r.x), f[1] = __uint_as_float(r.y), f[2] = __uint_as_float(r.z), f[3] = __uint_as_float(r.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+  static __device__ __forceinline__ float load1(const void* p, int64_t i) { return reinterpret_cast<const float*>(p)[i]; }
+  static __device__ __forceinline__ void store1(void* p, int64_t i, float v) { reinterpret_cast<float*>(p)[i] = v; }
+};
+template <>
+struct Vec16<NTB200_F16> {
+  static constexpr int kElems = 8;
+  static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+      f[2 * k] = t.x, f[2 * k + 1] = t.y;
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __half2 h = __floats2half2_rn(f[2 * k], f[2 * k + 1]);
+      w[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  static __device__ __forceinline__ float load1(const void* p, int64_t i) { return __half2float(reinterpret_cast<const __half*>(p)[i]); }
+  static __device__ __forceinline__ void store1(void* p, int64_t i, float v) { reinterpret_cast<__half*>(p)[i] = __float2half_rn(v); }
+};
+template <>
+struct Vec16<NTB200_BF16> {
+  static constexpr int kElems = 8;
+  static __device__ __forceinline__ void unpack(const uint4& r, float* f) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {  // a bf16 is the upper half of an fp32
+      f[2 * k] = __uint_as_float(w[k] << 16);
+      f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+      w[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  static __device__ __forceinline__ float load1(const void* p, int64_t i) {
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  }
+  static __device__ __forceinline__ void store1(void* p, int64_t i, float v) {
+    reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sum over the GROUP threads that share a row: a warp (GROUP == 32) or the whole block.
+template <int GROUP>
+__device__ __forceinline__ float group_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  if (GROUP == 32) return v;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // scratch may still be read from the previous reduction
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = lane < GROUP / 32 ? scratch[lane] : 0.0f;
+  return warp_sum(t);
+}
+
+constexpr int kLnThreads = 256;
+
+// One row per GROUP threads, the row held in registers between the passes (one global read, one global
+// write per element).  VPL = 16-byte vectors per thread; vector v of the row belongs to thread v % GROUP.
+// Mean and variance are the two-pass forms of the reference kernel (sum, then sum of squared deviations).
+template <int DT, int VPL, int GROUP, bool FUSED>
+__global__ void __launch_bounds__(kLnThreads)
+layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* __restrict__ bias,
+                  const void* __restrict__ gamma, const void* __restrict__ beta, float eps, void* out, int64_t rows,
+                  int cols) {  // out may alias x: a thread has read all it needs of the row before it writes
+  constexpr int EPV = Vec16<DT>::kElems;
+  constexpr int kRowsPerBlock = kLnThreads / GROUP;
+  __shared__ float scratch[kLnThreads / 32];
+  const int t = threadIdx.x % GROUP;
+  const int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + threadIdx.x / GROUP;
+  const bool live = row < rows;  // whole groups are live or not (a group is a warp or the block)
+  if (GROUP == 32 && !live) return;
+  const int nv = cols / EPV;
+  const uint4* xr = reinterpret_cast<const uint4*>(x) + row * nv;
+  const uint4* rr = reinterpret_cast<const uint4*>(residual) + row * nv;
+  float v[VPL][EPV];
+  float sum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int vec = t + j * GROUP;
+    if (vec < nv) {
+      Vec16<DT>::unpack(xr[vec], v[j]);
+      if (FUSED) {
+        float a[EPV];
+        if (residual != nullptr) {
+          Vec16<DT>::unpack(rr[vec], a);
+#pragma unroll
+          for (int k = 0; k < EPV; ++k) v[j][k] += a[k];
+        }
+        if (bias != nullptr) {
+          Vec16<DT>::unpack(reinterpret_cast<const uint4*>(bias)[vec], a);
+#pragma unroll
+          for (int k = 0; k < EPV; ++k) v[j][k] += a[k];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) sum += v[j][k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) v[j][k] = 0.0f;
+    }
+  }
+  const float mean = group_sum<GROUP>(sum, scratch) / (float)cols;
+  float sq = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    if (t + j * GROUP < nv) {
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) {
+        const float d = v[j][k] - mean;
+        sq += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(group_sum<GROUP>(sq, scratch) / (float)cols + eps);
+  uint4* orow = reinterpret_cast<uint4*>(out) + row * nv;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int vec = t + j * GROUP;
+    if (vec < nv) {
+      float g[EPV], b[EPV], o[EPV];
+      if (gamma != nullptr) {
+        Vec16<DT>::unpack(reinterpret_cast<const uint4*>(gamma)[vec], g);
+        Vec16<DT>::unpack(reinterpret_cast<const uint4*>(beta)[vec], b);
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) o[k] = (v[j][k] - mean) * rstd * g[k] + b[k];
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) o[k] = (v[j][k] - mean) * rstd;
+      }
+      orow[vec] = Vec16<DT>::pack(o);
+    }
+  }
+}
+
+// Any row length and alignment: one block per row, three passes over global memory.
+template <int DT>
+__global__ void __launch_bounds__(kLnThreads)
+layer_norm_generic_kernel(const void* x, const void* __restrict__ residual, const void* __restrict__ bias,
+                          const void* __restrict__ gamma, const void* __restrict__ beta, float eps, void* out, int64_t rows,
+                          int cols) {
+  __shared__ float scratch[kLnThreads / 32];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int64_t base = row * cols;
+    auto value = [&](int i) {
+      float a = Vec16<DT>::load1(x, base + i);
+      if (residual != nullptr) a += Vec16<DT>::load1(residual, base + i);
+      if (bias != nullptr) a += Vec16<DT>::load1(bias, i);
+      return a;
+    };
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < cols; i += kLnThreads) sum += value(i);
+    const float mean = group_sum<kLnThreads>(sum, scratch) / (float)cols;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < cols; i += kLnThreads) {
+      const float d = value(i) - mean;
+      sq += d * d;
+    }
+    const float rstd = rsqrtf(group_sum<kLnThreads>(sq, scratch) / (float)cols + eps);
+    for (int i = threadIdx.x; i < cols; i += kLnThreads) {
+      float o = (value(i) - mean) * rstd;
+      if (gamma != nullptr) o = o * Vec16<DT>::load1(gamma, i) + Vec16<DT>::load1(beta, i);
+      Vec16<DT>::store1(out, base + i, o);  // out may alias x: every thread rereads only what it writes itself
+    }
+  }
+}
+
+// tanh form of GELU, the one the reference's fused kernels use (cuda_kernels.cu:29-36)
+__device__ __forceinline__ float gelu_tanh(float x) {
+  return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+add_bias_gelu_kernel(const void* x, const void* __restrict__ bias, void* out, int64_t n_vec,
+                     int vec_per_row) {
+  constexpr int EPV = Vec16<DT>::kElems;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * 256) {
+    float a[EPV], b[EPV];
+    Vec16<DT>::unpack(reinterpret_cast<const uint4*>(x)[i], a);
+    if (bias != nullptr) {
+      Vec16<DT>::unpack(reinterpret_cast<const uint4*>(bias)[i % vec_per_row], b);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) a[k] += b[k];
+    }
+#pragma unroll
+    for (int k = 0; k < EPV; ++k) a[k] = gelu_tanh(a[k]);
+    reinterpret_cast<uint4*>(out)[i] = Vec16<DT>::pack(a);
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+add_bias_gelu_scalar_kernel(const void* x, const void* __restrict__ bias, void* out, int64_t n,
+                            int cols) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    float a = Vec16<DT>::load1(x, i);
+    if (bias != nullptr) a += Vec16<DT>::load1(bias, i % cols);
+    Vec16<DT>::store1(out, i, gelu_tanh(a));
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <int DT, bool FUSED>
+int launch_layer_norm(const void* x, const void* residual, const void* bias, const void* gamma, const void* beta, float eps,
+                      void* out, int64_t rows, int64_t cols, cudaStream_t st) {
+  constexpr int EPV = Vec16<DT>::kElems;
+  const bool vec_ok = cols % EPV == 0 && aligned16(x) && aligned16(out) && (residual == nullptr || aligned16(residual)) &&
+                      (bias == nullptr || aligned16(bias)) && (gamma == nullptr || (aligned16(gamma) && aligned16(beta)));
+  const int64_t nv = cols / EPV;
+#define NTB200_LN_LAUNCH(VPL, GROUP)                                                                              \
+  do {                                                                                                            \
+    const int64_t rpb = kLnThreads / GROUP;                                                                       \
+    const int64_t grid = (rows + rpb - 1) / rpb;                                                                  \
+    if (grid > 0x7fffffff) return NTB200_INVALID_ARG;                                                             \
+    layer_norm_kernel<DT, VPL, GROUP, FUSED><<<(unsigned)grid, kLnThreads, 0, st>>>(x, residual, bias, gamma, beta, \
+                                                                                   eps, out, rows, (int)cols);     \
+  } while (0)
+  if (vec_ok && nv <= 32) NTB200_LN_LAUNCH(1, 32);
+  else if (vec_ok && nv <= 64) NTB200_LN_LAUNCH(2, 32);
+  else if (vec_ok && nv <= 128) NTB200_LN_LAUNCH(4, 32);
+  else if (vec_ok && nv <= 256) NTB200_LN_LAUNCH(8, 32);
+  else if (vec_ok && nv <= 512) NTB200_LN_LAUNCH(2, kLnThreads);
+  else if (vec_ok && nv <= 1024) NTB200_LN_LAUNCH(4, kLnThreads);
+  else if (vec_ok && nv <= 2048) NTB200_LN_LAUNCH(8, kLnThreads);
+  else {
+    const int64_t grid = rows < 148 * 32 ? rows : 148 * 32;
+    layer_norm_generic_kernel<DT><<<(unsigned)grid, kLnThreads, 0, st>>>(x, FUSED ? residual : nullptr,
+                                                                        FUSED ? bias : nullptr, gamma, beta, eps, out, rows,
+                                                                        (int)cols);
+  }
+#undef NTB200_LN_LAUNCH
+  return status_from_cuda(cudaGetLastError());
+}
+
+int layer_norm_entry(const void* x, const void* residual, const void* bias, const void* gamma, const void* beta, float eps,
+                     void* out, int64_t rows, int64_t cols, int dtype, void* stream) {
+  if (rows < 0 || cols < 0 || cols > 0x7fffffff || !(eps >= 0.0f)) return NTB200_INVALID_ARG;
+  if ((gamma == nullptr) != (beta == nullptr)) return NTB200_INVALID_ARG;
+  if (rows == 0 || cols == 0) return NTB200_OK;
+  if (x == nullptr || out == nullptr) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fused = residual != nullptr || bias != nullptr;
+  switch (dtype) {
+    case NTB200_F32:
+      return fused ? launch_layer_norm<NTB200_F32, true>(x, residual, bias, gamma, beta, eps, out, rows, cols, st)
+                   : launch_layer_norm<NTB200_F32, false>(x, residual, bias, gamma, beta, eps, out, rows, cols, st);
+    case NTB200_F16:
+      return fused ? launch_layer_norm<NTB200_F16, true>(x, residual, bias, gamma, beta, eps, out, rows, cols, st)
+                   : launch_layer_norm<NTB200_F16, false>(x, residual, bias, gamma, beta, eps, out, rows, cols, st);
+    case NTB200_BF16:
+      return fused ? launch_layer_norm<NTB200_BF16, true>(x, residual, bias, gamma, beta, eps, out, rows, cols, st)
+                   : launch_layer_norm<NTB200_BF16, false>(x, residual, bias, gamma, beta, eps, out, rows, cols, st);
+    default:
+      return NTB200_UNSUPPORTED_DTYPE;
+  }
+}
+
+template <int DT>
+int launch_bias_gelu(const void* x, const void* bias, void* out, int64_t rows, int64_t cols, cudaStream_t st) {
+  constexpr int EPV = Vec16<DT>::kElems;
+  const int64_t n = rows * cols;
+  if (cols % EPV == 0 && aligned16(x) && aligned16(out) && (bias == nullptr || aligned16(bias))) {
+    const int64_t n_vec = n / EPV;
+    int64_t grid = (n_vec + 255) / 256;
+    if (grid > 148 * 64) grid = 148 * 64;
+    add_bias_gelu_kernel<DT><<<(unsigned)grid, 256, 0, st>>>(x, bias, out, n_vec, (int)(cols / EPV));
+  } else {
+    int64_t grid = (n + 255) / 256;
+    if (grid > 148 * 64) grid = 148 * 64;
+    add_bias_gelu_scalar_kernel<DT><<<(unsigned)grid, 256, 0, st>>>(x, bias, out, n, (int)cols);
+  }
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace ntb200
+
+extern "C" {
+
+int ntb200_layer_norm(const void* x, const void* gamma, const void* beta, float eps, void* out, int64_t rows, int64_t cols,
+                      int dtype, void* stream) {
+  return ntb200::layer_norm_entry(x, nullptr, nullptr, gamma, beta, eps, out, rows, cols, dtype, stream);
+}
+
+int ntb200_add_bias_residual_layer_norm(const void* x, const void* residual, const void* bias, const void* gamma,
+                                        const void* beta, float eps, void* out, int64_t rows, int64_t cols, int dtype,
+                                        void* stream) {
+  return ntb200::layer_norm_entry(x, residual, bias, gamma, beta, eps, out, rows, cols, dtype, stream);
+}
+
+int ntb200_add_bias_gelu(const void* x, const void* bias, void* out, int64_t rows, int64_t cols, int dtype, void* stream) {
+  if (rows < 0 || cols < 0 || cols > 0x7fffffff) return NTB200_INVALID_ARG;
+  if (rows == 0 || cols == 0) return NTB200_OK;
+  if (x == nullptr || out == nullptr) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case NTB200_F32: return ntb200::launch_bias_gelu<NTB200_F32>(x, bias, out, rows, cols, st);
+    case NTB200_F16: return ntb200::launch_bias_gelu<NTB200_F16>(x, bias, out, rows, cols, st);
+    case NTB200_BF16: return ntb200::launch_bias_gelu<NTB200_BF16>(x, bias, out, rows, cols, st);
+    default: return NTB200_UNSUPPORTED_DTYPE;
+  }
+}
+
+}  // extern "C"

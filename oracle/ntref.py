@@ -335,3 +335,62 @@ def masked_softmax(scores: torch.Tensor, mask: torch.Tensor, scaling: float) -> 
     s = s - s.max(-1, keepdim=True).values
     e = torch.exp(s)
     return e / (e.sum(-1, keepdim=True) + 1e-6)
+
+
+# ------------------------------------------------------- layer norm and the encoder layer
+def layer_norm(tensors: NTList, normalized_shape, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+               eps: float = 1e-5) -> NTList:
+    """nestedtensor/csrc/functions.cpp:65-110 (CPU branch: ``at::layer_norm`` mapped over the constituents),
+    with its checks; evaluated in fp32."""
+    if isinstance(normalized_shape, int):
+        normalized_shape = (normalized_shape,)
+    if len(normalized_shape) != 1:
+        raise RuntimeError("Currently only singleton tuples of integers supported for layer_norm.")
+    if len(tensors) == 0:
+        return []
+    last = tensors[0].dim()  # index of the last dimension of the nested tensor
+    if any(t.size(-1) != tensors[0].size(-1) for t in tensors):
+        raise RuntimeError("Cannot normalize across irregular dimension %d" % last)
+    if tensors[0].size(-1) != normalized_shape[0]:
+        raise RuntimeError("Normalized shape [%d] does not match the size of the last dimension (%d) of input."
+                           % (normalized_shape[0], tensors[0].size(-1)))
+    if (weight is None) != (bias is None):
+        raise RuntimeError("Either both weight and bias are used or not.")
+    w = None if weight is None else weight.float()
+    b = None if bias is None else bias.float()
+    return [F.layer_norm(t.float(), tuple(normalized_shape), w, b, eps) for t in tensors]
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    """The GELU of the reference's fused kernels (nestedtensor/csrc/cuda/cuda_kernels.cu:29-36)."""
+    x = x.float()
+    return 0.5 * x * (1.0 + torch.tanh(0.7978845608028654 * (x + 0.044715 * x * x * x)))
+
+
+def encoder_layer(tensors: NTList, num_heads: int, p: dict, activation: str = "gelu_tanh", norm_first: bool = False,
+                  eps: float = 1e-5) -> NTList:
+    """One transformer encoder layer (self-attention + feed-forward, inference) per constituent in fp32, built
+    from ``min_mha`` (nestedtensor/csrc/mha.cpp:18-69) and ``layer_norm`` above, in the order of
+    ``torch.nn.TransformerEncoderLayer``.  ``p`` holds in_proj_weight/bias, out_proj_weight/bias,
+    linear1_weight/bias, linear2_weight/bias, norm1_weight/bias, norm2_weight/bias."""
+    f = {k: v.float() for k, v in p.items()}
+    E = f["out_proj_weight"].size(0)
+    head_dim = E // num_heads
+    act = {"gelu_tanh": gelu_tanh, "relu": torch.relu}[activation]
+
+    def sa(xs):
+        return min_mha(num_heads, head_dim, xs, xs, xs, f["in_proj_weight"], f["in_proj_bias"], float(head_dim) ** -0.5,
+                       f["out_proj_weight"], f["out_proj_bias"])
+
+    def ff(xs):
+        return [act(x @ f["linear1_weight"].t() + f["linear1_bias"]) @ f["linear2_weight"].t() + f["linear2_bias"] for x in xs]
+
+    def ln(xs, which):
+        return layer_norm(xs, (E,), f[which + "_weight"], f[which + "_bias"], eps)
+
+    xs = [t.float() for t in tensors]
+    if norm_first:
+        xs = [x + a for x, a in zip(xs, sa(ln(xs, "norm1")))]
+        return [x + h for x, h in zip(xs, ff(ln(xs, "norm2")))]
+    xs = ln([x + a for x, a in zip(xs, sa(xs))], "norm1")
+    return ln([x + h for x, h in zip(xs, ff(xs))], "norm2")

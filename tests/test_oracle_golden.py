@@ -146,3 +146,55 @@ def test_masked_softmax_matches_exact():
     for b, l in enumerate(lens):
         exact = torch.softmax(s[b, :, :l, :l] * 0.5, -1)
         assert torch.allclose(p[b, :, :l, :l], exact, atol=2e-6)
+
+
+# ------------------------------------------------------------------ layer norm / encoder layer
+@pytest.mark.parametrize("size", [1024, 512, 256, 128, 2, 4, 32])
+def test_oracle_layer_norm_matches_module_per_constituent(size):
+    """test/test_nested_tensor_functional.py:895-957: LayerNorm of the nested tensor equals the module applied
+    to each constituent."""
+    g = torch.Generator().manual_seed(size)
+    ts = [torch.randn(2, size, generator=g), torch.randn(3, size, generator=g)]
+    m = torch.nn.LayerNorm(size)
+    with torch.no_grad():
+        m.weight.copy_(torch.randn(size, generator=g))
+        m.bias.copy_(torch.randn(size, generator=g))
+        want = [m(t) for t in ts]
+    got = ntref.layer_norm(ts, (size,), m.weight.detach(), m.bias.detach(), m.eps)
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=1e-6, rtol=1e-6)
+
+
+def test_oracle_layer_norm_errors():
+    ts = [torch.randn(3, 4), torch.randn(2, 4)]
+    with pytest.raises(RuntimeError, match="Currently only singleton tuples"):
+        ntref.layer_norm(ts, (2, 4), None, None)
+    with pytest.raises(RuntimeError, match=r"Normalized shape \[3\] does not match the size of the last dimension \(4\)"):
+        ntref.layer_norm(ts, (3,), None, None)
+    with pytest.raises(RuntimeError, match="Either both weight and bias"):
+        ntref.layer_norm(ts, (4,), torch.ones(4), None)
+    with pytest.raises(RuntimeError, match="Cannot normalize across irregular dimension 2"):
+        ntref.layer_norm([torch.randn(3, 4), torch.randn(2, 5)], (4,), None, None)
+
+
+@pytest.mark.parametrize("norm_first", [False, True])
+@pytest.mark.parametrize("act", ["gelu_tanh", "relu"])
+def test_oracle_encoder_layer_matches_stock_module(act, norm_first):
+    """The oracle's encoder layer is pinned to torch.nn.TransformerEncoderLayer evaluated per sequence (with
+    gradients enabled the stock module takes its plain Python path; its fused inference path replaces the
+    tanh GELU by the erf form)."""
+    torch.manual_seed(5)
+    activation = torch.nn.GELU(approximate="tanh") if act == "gelu_tanh" else torch.nn.functional.relu
+    layer = torch.nn.TransformerEncoderLayer(64, 4, dim_feedforward=128, dropout=0.0, activation=activation, batch_first=True,
+                                             norm_first=norm_first).eval()
+    p = {"in_proj_weight": layer.self_attn.in_proj_weight, "in_proj_bias": layer.self_attn.in_proj_bias,
+         "out_proj_weight": layer.self_attn.out_proj.weight, "out_proj_bias": layer.self_attn.out_proj.bias,
+         "linear1_weight": layer.linear1.weight, "linear1_bias": layer.linear1.bias, "linear2_weight": layer.linear2.weight,
+         "linear2_bias": layer.linear2.bias, "norm1_weight": layer.norm1.weight, "norm1_bias": layer.norm1.bias,
+         "norm2_weight": layer.norm2.weight, "norm2_bias": layer.norm2.bias}
+    p = {k: v.detach() for k, v in p.items()}
+    xs = [torch.randn(l, 64) for l in (5, 17, 1)]
+    got = ntref.encoder_layer(xs, 4, p, act, norm_first)
+    want = [layer(x.unsqueeze(0)).squeeze(0).detach() for x in xs]
+    for a, b in zip(got, want):
+        assert (a - b).abs().max().item() <= 2e-6
