@@ -365,7 +365,7 @@ def run_reference(args, kind, rank, world):
     if rank != 0:
         return None
     torch.set_num_threads(os.cpu_count() or 1)
-    L, _ = shard_lengths("pad" if kind in ("pad", "unpad") else kind, 1, 0)
+    L, _ = shard_lengths("pad" if kind in ("pad", "unpad") else "mha", 1, 0)
     hidden, dtype = 1024, torch.bfloat16
     seqs = 256
     if kind == "pad":
@@ -375,7 +375,7 @@ def run_reference(args, kind, rank, world):
         _, nbytes, fn = cpu_unpad_sample(L, hidden, dtype, seqs)
         metric = "from_padded_tensor HBM GB/s"
     else:
-        return run_reference_mha(args, world)
+        return run_reference_mha(args, world, encoder=(kind == "encoder"))
     for _ in range(max(1, min(args.warmup, 2))):
         fn()
     steps = max(1, min(args.steps, 10))
@@ -408,10 +408,19 @@ def cpu_mha_sample(L, E, H, dtype, seqs):
     return sum(Ls), fn
 
 
-def run_reference_mha(args, world):
+def run_reference_mha(args, world, encoder=False):
     L, _ = shard_lengths("mha", 1, 0)
     E, H, dtype, seqs = 1024, 16, torch.bfloat16, 64
-    tokens, fn = cpu_mha_sample(L, E, H, dtype, seqs)
+    if encoder:
+        from oracle import ntref
+        seqs = 32
+        Ls = L[:seqs].tolist()
+        g = torch.Generator().manual_seed(13)
+        tensors = [torch.randn(l, E, generator=g).to(dtype) for l in Ls]
+        params = _layer_params(_bert_large_layer(torch.float32, "cpu"))
+        tokens, fn = sum(Ls), (lambda: ntref.encoder_layer(tensors, H, params, "gelu_tanh", False, 1e-5))
+    else:
+        tokens, fn = cpu_mha_sample(L, E, H, dtype, seqs)
     for _ in range(max(1, min(args.warmup, 2))):
         fn()
     steps = max(1, min(args.steps, 10))
@@ -421,7 +430,8 @@ def run_reference_mha(args, world):
     dt = (time.perf_counter() - t0) / steps
     v = tokens / dt
     sample = "each step = the first %d sequences of configuration 5 (%d tokens), per-sequence fp32 loop" % (seqs, tokens)
-    return {"impl": "reference", "metric": "varlen MHA valid tokens/s", "value": v, "unit": "tokens/s", "n_gpus": world,
+    return {"impl": "reference", "metric": "varlen encoder layer valid tokens/s" if encoder else "varlen MHA valid tokens/s",
+            "value": v, "unit": "tokens/s", "n_gpus": world,
             "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 inputs, fp32 math", "data": "synthetic",
             "config": {"workload": "config5 (CPU sample): " + sample},
@@ -640,6 +650,130 @@ def run_kernels(args, local):
             "peaks": peaks, "rows": rows, "device_error_flags": _cabi.load().ntb200_device_error_flags()}
 
 
+# ------------------------------------------------------------------- encoder layer (next row)
+def _bert_large_layer(dtype, device):
+    torch.manual_seed(20246)
+    layer = torch.nn.TransformerEncoderLayer(1024, 16, dim_feedforward=4096, dropout=0.0,
+                                             activation=torch.nn.GELU(approximate="tanh"))
+    return layer.eval().to(dtype).to(device)
+
+
+def _layer_params(layer):
+    p = {"in_proj_weight": layer.self_attn.in_proj_weight, "in_proj_bias": layer.self_attn.in_proj_bias,
+         "out_proj_weight": layer.self_attn.out_proj.weight, "out_proj_bias": layer.self_attn.out_proj.bias,
+         "linear1_weight": layer.linear1.weight, "linear1_bias": layer.linear1.bias, "linear2_weight": layer.linear2.weight,
+         "linear2_bias": layer.linear2.bias, "norm1_weight": layer.norm1.weight, "norm1_bias": layer.norm1.bias,
+         "norm2_weight": layer.norm2.weight, "norm2_bias": layer.norm2.bias}
+    return {k: v.detach().float().cpu() for k, v in p.items()}
+
+
+def run_encoder(args, rank, world, local):
+    """Configuration 5 through one BERT-large encoder layer (E=1024, 16 heads x 64, FFN 4096, tanh GELU, post-norm,
+    bf16) on packed tokens: the row after MHA in the scope table."""
+    import ctypes
+    import nestedtensor_b200 as nt
+    from nestedtensor_b200 import _cabi
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    E, H, F, dtype = 1024, 16, 4096, torch.bfloat16
+    L, imb = shard_lengths("mha", world, rank)
+    B, T, maxL = int(L.numel()), int(L.sum()), int(L.max())
+    sizes = torch.stack([L, torch.full_like(L, E)], 1).contiguous()
+    attn_flops = 4.0 * E * float((L.double() ** 2).sum())
+    gemm_flops = 2.0 * T * E * (3 * E + E + 2 * F)
+    flops = attn_flops + gemm_flops
+    host = host_values(T * E, dtype, 20246 + rank)
+    layer = _bert_large_layer(dtype, device)
+    x = nt.NestedTensor(host.to(device), sizes)
+    x._record()
+    step = lambda: nt.nn.transformer_encoder_layer(layer, x)
+    steps = args.steps
+    for _ in range(max(args.warmup, 3)):
+        step()
+    lib = _cabi.load()
+    with ClockSampler(local) as clocks:
+        ms = timed_region(step, steps, world, device)
+        ms = min(ms, timed_region(step, steps, world, device))
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        # the dominant kernel alone: feed-forward up-projection with the fused bias + GELU epilogue
+        a = torch.randn(T, E, device=device).to(dtype)
+        h = torch.empty(T, F, dtype=dtype, device=device)
+        w1, b1 = layer.linear1.weight, layer.linear1.bias
+        ffn1 = lambda: lib.ntb200_gemm_bias_act(a.data_ptr(), w1.data_ptr(), b1.data_ptr(), None, h.data_ptr(), T, F, E, 2, 1, 0, stream)
+        for _ in range(3):
+            ffn1()
+        f1ms = timed_region(ffn1, steps, world, device) / steps
+        # the row operator alone: LayerNorm over [T, E]
+        o = torch.empty_like(a)
+        g, be = layer.norm1.weight, layer.norm1.bias
+        ln = lambda: lib.ntb200_layer_norm(a.data_ptr(), g.data_ptr(), be.data_ptr(), 1e-5, o.data_ptr(), T, E, 2, stream)
+        for _ in range(3):
+            ln()
+        lnms = timed_region(ln, steps, world, device) / steps
+        del h
+    step_ms = ms / steps
+    total_tokens = all_sum(T, world, device)
+    value = total_tokens / (step_ms * 1e-3)
+    flags = lib.ntb200_device_error_flags()
+
+    e2e = None
+    if not KERNEL_ONLY:
+        h_in = torch.empty(T * E, dtype=dtype).pin_memory()
+        h_in.copy_(host)
+        h_out = torch.empty(T * E, dtype=dtype).pin_memory()
+        e2e_step = lambda: nt.transformer_encoder_layer_host(layer, h_in, sizes, out=h_out)
+        e2e_steps = max(3, min(steps, 20))
+        for _ in range(3):
+            e2e_step()
+        with ClockSampler(local) as clocks2:
+            ems = timed_region(e2e_step, e2e_steps, world, device) / e2e_steps
+        clocks.samples += clocks2.samples
+        clocks.reasons |= clocks2.reasons
+        e2e = {"value": total_tokens / (ems * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * T * E,
+               "d2h_bytes_per_step": 2 * T * E, "ms_per_step": ems, "steps": e2e_steps,
+               "api": "transformer_encoder_layer_host (pinned host in/out, 8 ranges pipelined on 3 streams)"}
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    tf = flops / (step_ms * 1e-3) / 1e12
+    f1tf = 2.0 * T * E * F / (f1ms * 1e-3) / 1e12
+    ln_gbs = 4.0 * T * E / (lnms * 1e-3) / 1e9
+    line = {
+        "metric": "varlen encoder layer valid tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": ("FIRST %d SEQUENCES ONLY of " % SEQUENCE_LIMIT if SEQUENCE_LIMIT else "") +
+                               "config5 batch (1024 sequences per GPU, 70% L~U[16,128] / 30% L~U[128,512]) through one BERT-large "
+                               "encoder layer: E=1024, 16 heads x 64, FFN 4096, tanh GELU, post-norm, bf16, inference",
+                   "batch_per_gpu": B, "tokens_per_gpu": T, "max_len": maxL, "flops_per_gpu": flops, "token_imbalance": imb,
+                   "l2": "activations per step (%.2f GB) exceed the 126 MB L2" % (2 * T * (E * 9 + F * 2) / 1e9)},
+        "step_tflops": tf, "step_frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+        "step_frac_of_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
+        "kernels_ms": {"ffn_up_gemm_gelu": f1ms, "layer_norm": lnms, "step": step_ms},
+        "layer_norm_hbm": {"achieved": ln_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ln_gbs / peaks["hbm_gbs"],
+                           "bytes": 4.0 * T * E},
+        "roofline": {"bound": "tensor", "kernel": "gemm_bias_tcgen05_pair_kernel (feed-forward up-projection + bias + GELU, "
+                                                  "M=%d N=4096 K=1024)" % T,
+                     "achieved": f1tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": f1tf / peaks["bf16_tflops"],
+                     "frac_of_sustained": f1tf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"], "traffic": None},
+        "e2e": e2e, "gpu_launches": 8 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
+    }
+    if not KERNEL_ONLY:
+        from oracle import ntref
+        torch.set_num_threads(os.cpu_count() or 1)
+        seqs = 16
+        Ls = L[:seqs].tolist()
+        g2 = torch.Generator().manual_seed(13)
+        tensors = [torch.randn(l, E, generator=g2).to(dtype) for l in Ls]
+        params = _layer_params(layer)
+        fn = lambda: ntref.encoder_layer(tensors, H, params, "gelu_tanh", False, 1e-5)
+        t = time_cpu(fn, 1, 3)
+        line["cpu_baseline"] = {"value": sum(Ls) / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": "first %d sequences (%d tokens), median of 3, per-sequence fp32 loop (reference's generic "
+                                          "MHA + ATen layer_norm / linear per constituent)" % (seqs, sum(Ls))}
+    return line
+
+
 # ------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -647,7 +781,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="pad", choices=["pad", "unpad", "mha", "kernels"])
+    ap.add_argument("--workload", default="pad", choices=["pad", "unpad", "mha", "kernels", "encoder"])
     ap.add_argument("--no-mha", action="store_true", help="pad workload only: skip the attached MHA measurement")
     ap.add_argument("--sequences", type=int, default=0,
                     help="use only the first N sequences of each GPU's batch (small cases for profiler captures; "
@@ -689,6 +823,8 @@ def main():
                 if line is not None and mha is not None:
                     line["mha"] = {k: mha[k] for k in ("metric", "value", "unit", "ms_per_step", "step_tflops",
                                                         "step_frac_of_bf16_peak", "kernels_ms", "roofline", "config")}
+        elif args.workload == "encoder":
+            line = run_encoder(args, rank, world, local)
         else:
             line = run_mha(args, rank, world, local)
         if rank == 0 and line is not None:

@@ -17,7 +17,8 @@ from .masking import (nested_tensor_from_tensor_mask, nested_tensor_from_padded_
                       TensorMask)
 from . import nn
 from .sharding import token_balanced_partition
-from .host_pipeline import to_padded_tensor_host, from_padded_tensor_host, multi_head_attention_host
+from .host_pipeline import (to_padded_tensor_host, from_padded_tensor_host, multi_head_attention_host,
+                            transformer_encoder_layer_host)
 
 __version__ = "0.1.0"
 

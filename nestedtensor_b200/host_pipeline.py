@@ -10,6 +10,7 @@ so that a step costs about max(upload, download) instead of their sum.
     to_padded_tensor_host(h_ragged, sizes, padding)   -> pinned dense tensor (B, max_1, ..., max_k)
     from_padded_tensor_host(h_padded, sizes)          -> pinned 1-D ragged buffer
     multi_head_attention_host(h_x, sizes, ...)        -> pinned packed [T, E] output of bt_min_mha
+    transformer_encoder_layer_host(layer, h_x, sizes) -> pinned packed [T, E] output of an encoder layer
 
 The kernels are the ones behind ``torch.ops.nestedtensor.to_padded_tensor`` / ``bt_min_mha``; there is no
 CPU path.  The reference has no host-buffer API (its operators take device tensors only).
@@ -265,6 +266,66 @@ def multi_head_attention_host(h_x: torch.Tensor, sizes: torch.Tensor, num_heads:
             a, b = parts[c]
             # results[slot] stays referenced until range c + 2 replaces it, which the compute stream does only
             # after waiting for this download: its memory cannot be handed out again before the copy has run
+            o2[int(toff[a]):int(toff[b])].copy_(results[slot].reshape(-1, E), non_blocking=True)
+
+        run_pipeline(len(parts), upload, compute, download, device)
+    return out
+
+
+def transformer_encoder_layer_host(layer: torch.nn.TransformerEncoderLayer, h_x: torch.Tensor, sizes: torch.Tensor,
+                                   activation: Optional[str] = None, out: Optional[torch.Tensor] = None,
+                                   ranges: int = 8) -> torch.Tensor:
+    """``nn.transformer_encoder_layer`` over a packed token matrix held in pinned host memory (``h_x`` is
+    ``[T, E]`` or its 1-D buffer, ``sizes`` the ``(L_i, E)`` rows); the layer's parameters pick the device.
+    Returns the pinned ``[T, E]`` output (asynchronous, as above)."""
+    from .nested import NestedTensor
+    from .nn import transformer_encoder_layer
+    _check_host(h_x, "h_x")
+    _check_sizes(sizes)
+    device = layer.linear1.weight.device
+    if device.type != "cuda":
+        raise ValueError("the layer must be on a CUDA device (this build has no CPU implementation)")
+    B, tdim = sizes.shape
+    if tdim != 2 or B == 0:
+        raise ValueError("query needs to be 3 dim.")
+    E = int(sizes[0, 1])
+    if bool((sizes[:, 1] != E).any()):
+        raise ValueError("query's third dimension must be regular.")
+    lengths = sizes[:, 0]
+    T = int(lengths.sum())
+    if h_x.numel() != T * E:
+        raise ValueError("h_x must hold sum(L_i) * E elements")
+    x = h_x.reshape(T, E)
+    if out is None:
+        out = torch.empty((T, E), dtype=h_x.dtype).pin_memory()
+    else:
+        _check_host(out, "out")
+        if out.numel() != T * E or out.dtype != h_x.dtype:
+            raise ValueError("out must hold sum(L_i) * E elements of the input dtype")
+    o2 = out.reshape(T, E)
+    parts = plan_ranges([int(v) for v in lengths], ranges)
+    toff = torch.zeros(B + 1, dtype=torch.int64)
+    torch.cumsum(lengths, 0, out=toff[1:])
+    with torch.cuda.device(device):
+        metas = [build_meta(sizes[a:b], device) for a, b in parts]
+        subs = [sizes[a:b].contiguous() for a, b in parts]
+        t_max = max(int(toff[b] - toff[a]) for a, b in parts)
+        d_in = [torch.empty((max(t_max, 1), E), dtype=h_x.dtype, device=device) for _ in range(2)]
+        results = [None, None]
+
+        def upload(c, slot):
+            a, b = parts[c]
+            d_in[slot][:int(toff[b] - toff[a])].copy_(x[int(toff[a]):int(toff[b])], non_blocking=True)
+
+        def compute(c, slot):
+            a, b = parts[c]
+            n = int(toff[b] - toff[a])
+            src = NestedTensor(d_in[slot][:n].reshape(-1), subs[c], metas[c])
+            results[slot] = transformer_encoder_layer(layer, src, activation)._buffer
+
+        def download(c, slot):
+            a, b = parts[c]
+            # (kept alive by stream order, as in multi_head_attention_host)
             o2[int(toff[a]):int(toff[b])].copy_(results[slot].reshape(-1, E), non_blocking=True)
 
         run_pipeline(len(parts), upload, compute, download, device)
