@@ -628,6 +628,24 @@ def run_kernels(args, local):
     add("meta_from_device_sizes (offsets scan)", "c2", timed(lambda: ops.meta_from_device_sizes(d_sizes), n), None)
     del padded, buf, a
     torch.cuda.empty_cache()
+    # construction of configuration 2 from 4096 separately allocated device tensors, and a packed embedding lookup
+    parts = list(torch.split(b, (sz[:, 0] * sz[:, 1]).tolist()))
+    parts = [p.clone() for p in parts]  # separate allocations, as a data loader would hand them over
+    shaped = [p.view(int(l), 1024) for p, l in zip(parts, sz[:, 0].tolist())]
+    add("nested_tensor(list of device tensors)", "c2 (one gather kernel + one pinned table copy)",
+        timed(lambda: ops.pack_list(shaped), n), 4 * nv)
+    del parts, shaped
+    torch.cuda.empty_cache()
+    c5 = workloads.config5()
+    T5 = int(c5.sizes[:, 0].sum())
+    table = torch.randn(30522, 1024, device=device).to(torch.bfloat16)  # BERT vocabulary x hidden
+    idx = torch.randint(0, 30522, (T5,), device=device)
+    isz = c5.sizes[:, :1].contiguous()
+    from nestedtensor_b200.nested import build_meta
+    imeta = build_meta(isz, device)
+    add("embedding (packed gather)", "c5 tokens, 30522 x 1024 bf16 table",
+        timed(lambda: ops.embedding(table, idx, isz, imeta), n), 2 * 2 * T5 * 1024 + 8 * T5)
+    del table, idx
     # configurations 4 and 5: MHA
     for name, wl, dtype, E, H in (("c4", workloads.config4(), torch.float16, 768, 12),
                                   ("c5", workloads.config5(), torch.bfloat16, 1024, 16)):

@@ -197,10 +197,10 @@ int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, in
 int ntb200_gemm_bias_act(const void* A, const void* W, const void* bias, const void* residual, void* C,
                          int64_t M, int64_t N, int64_t K, int dtype, int act, int force_simt, void* stream);
 
-/* Bit mask of device-side wait time-outs recorded by the tcgen05 kernels since the last call
- * (0 = none; projection GEMM: bit 0 TMA producer, bit 1 MMA issuer, bit 2 epilogue; attention: the
- * same roles in bits 8-10); synchronises the device; negative on a CUDA error.  No counterpart in the
- * reference. */
+/* Bit mask of device-side conditions recorded since the last call (0 = none): bounded waits of the tcgen05
+ * kernels that ran out (projection GEMM: bit 0 TMA producer, bit 1 MMA issuer, bit 2 epilogue; attention:
+ * the same roles in bits 8-10) and bit 16 = ntb200_embedding met an index outside [0, vocab) (that row
+ * was zero-filled); synchronises the device; negative on a CUDA error.  No counterpart in the reference. */
 int ntb200_device_error_flags(void);
 
 /* ------------------------------------------------------------------ varlen self-attention
@@ -245,6 +245,23 @@ int ntb200_add_bias_residual_layer_norm(const void* x, const void* residual, con
  * (nestedtensor/csrc/cuda/transformer_kernels.cu:52-62). */
 int ntb200_add_bias_gelu(const void* x, const void* bias, void* out, int64_t rows, int64_t cols,
                          int dtype, void* stream);
+
+/* ------------------------------------------------------------------ construction
+ * out[offsets[b] + i] = srcs[b][i] for i < offsets[b+1] - offsets[b]: packs `batch` separately allocated
+ * device tensors into the one buffer of a nested tensor with a single launch.  `srcs` is a DEVICE array of
+ * `batch` device pointers (element-aligned), `offsets` the B+1 element offsets, `out` 16-byte aligned.
+ * Replaces the per-constituent copy loop of the packed storage constructor
+ * (nestedtensor/csrc/storage/Packed.h:75-98, nestedtensor/csrc/creation.cpp:191-222).
+ */
+int ntb200_pack_pointers(const void* const* srcs, const int64_t* offsets, int64_t batch, void* out,
+                         int64_t total_elems, int elem_size, void* stream);
+/* out[t, :] = weight[index[t], :] for the `tokens` entries of the packed index buffer of a nested tensor of
+ * 1-D index sequences (index_bytes 4 or 8).  An index outside [0, vocab) zero-fills its row and sets bit 16
+ * of ntb200_device_error_flags (the reference's at::embedding would trip a device assert).
+ * Replaces the packed fast path of NestedTensor_embedding (nestedtensor/csrc/functions.cpp:29-56).
+ */
+int ntb200_embedding(const void* weight, const void* index, int index_bytes, void* out, int64_t tokens,
+                     int64_t vocab, int64_t embed_dim, int elem_size, void* stream);
 
 /* ------------------------------------------------------------------ reference-shaped helpers
  * q/k/v_buf[b, h, l, :] = qkv[tok(b,l), {0,E,2E} + h*d + :] + bias  for valid tokens (padded

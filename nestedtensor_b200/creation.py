@@ -56,15 +56,37 @@ def nested_tensor(data, dtype=None, device=None, requires_grad=False, pin_memory
     if len(tensors) > 0:
         _verify(tensors)
     sizes = _sizes_from_list(tensors)
+    meta = None
     if len(tensors) == 0:
         buffer = torch.empty(0, dtype=dtype, device=device)
+    elif tensors[0].is_cuda and device.type == "cuda" and tensors[0].element_size() in (1, 2, 4, 8) \
+            and tensors[0].device.index == (device.index if device.index is not None else torch.cuda.current_device()) \
+            and not tensors[0].is_complex():
+        # constituents already on the target GPU: one pointer-array gather kernel packs them (and the same host
+        # copy that carries the pointer table carries the offsets and sizes, i.e. meta)
+        from . import _ops
+        buffer, sizes, meta = _ops.ops().pack_list([t.detach() for t in tensors])
+        if buffer.dtype != dtype:
+            buffer = buffer.to(dtype)
+    elif device.type == "cuda" and not tensors[0].is_cuda:
+        # host constituents: concatenated straight into pinned memory, then one asynchronous copy
+        src_dtype = tensors[0].dtype
+        total = int(sum(t.numel() for t in tensors))
+        staging = torch.empty(total, dtype=src_dtype).pin_memory()
+        torch.cat([t.detach().reshape(-1) for t in tensors], out=staging)
+        buffer = staging.to(device, non_blocking=True)
+        if buffer.dtype != dtype:
+            buffer = buffer.to(dtype)
+        # the pinned block goes back to torch's host allocator, which hands it out again only after the copy
+        # recorded on this stream has completed
     else:
         buffer = torch.cat([t.detach().reshape(-1) for t in tensors]).to(device=device, dtype=dtype)
         if buffer.data_ptr() == tensors[0].data_ptr():  # single contiguous constituent already in place
             buffer = buffer.clone()
     if pin_memory:
         buffer = buffer.pin_memory()
-    meta = build_meta(sizes, device) if device.type == "cuda" else None
+    if meta is None and device.type == "cuda":
+        meta = build_meta(sizes, device)
     return NestedTensor(buffer, sizes, meta)
 
 

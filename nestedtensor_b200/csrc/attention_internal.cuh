@@ -14,5 +14,6 @@ bool attn_tcgen05_supported(int64_t batch, int64_t total_tokens, int num_heads, 
 int attn_tcgen05_launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens, int H,
                         float scaling, int dtype, void* workspace, cudaStream_t st);
 int attn_tcgen05_error_flags_read_and_clear();
+int construct_error_flags_read_and_clear();  // construct.cu: bit 0 = embedding index out of range
 
 }  // namespace ntb200

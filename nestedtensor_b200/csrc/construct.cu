@@ -1,0 +1,167 @@
+// The step before the ragged path: building the packed buffer.
+//
+//   pack_pointers   out[offsets[b] + i] = src_b[i]   B separately allocated device tensors -> one buffer, one launch
+//   embedding       out[t, :] = weight[index[t], :]  on the packed index buffer of a nested tensor
+//
+// Both stream every byte once (HBM-bound).  pack_pointers replaces the per-constituent copy loop of the
+// packed storage constructor (nestedtensor/csrc/storage/Packed.h:75-98, nestedtensor/csrc/creation.cpp:191-222);
+// embedding replaces the packed fast path of NestedTensor_embedding (nestedtensor/csrc/functions.cpp:29-56,
+// at::embedding on the index buffer).
+
+#include "common.cuh"
+
+namespace ntb200 {
+namespace {
+
+__device__ int g_construct_error = 0;  // bit 0: an embedding index was out of range (its row was zero-filled)
+
+constexpr int kPackThreads = 256, kPackVecs = 8;  // 32 KB of output per tile, as in the pad / unpad kernels
+
+// last b in [lo, hi] with offsets[b] <= e
+__device__ __forceinline__ int64_t find_entry(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
+  while (lo < hi) {
+    const int64_t mid = (lo + hi + 1) >> 1;
+    if (offsets[mid] <= e) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+// Flat walk over 16-byte vectors of the OUTPUT.  A vector that lies inside one constituent whose source is
+// 16-byte aligned at that point is one 16-byte load; any other vector is assembled element by element
+// (it crosses constituents, or its source is not aligned).  The tile first narrows the range of entries it
+// can touch (two searches, through shared memory), so the per-vector search is over a handful of entries.
+template <int ES>
+__global__ void __launch_bounds__(kPackThreads)
+pack_pointers_kernel(const void* const* __restrict__ srcs, const int64_t* __restrict__ offsets, int64_t batch,
+                     void* __restrict__ out, int64_t total_elems) {
+  using T = typename ElemBits<ES>::T;
+  constexpr int EPV = 16 / ES;
+  __shared__ int64_t s_range[2];
+  const int64_t n_vec = (total_elems + EPV - 1) / EPV;
+  const int64_t tile0 = (int64_t)blockIdx.x * (kPackThreads * kPackVecs);
+  if (threadIdx.x < 2) {
+    int64_t e = (threadIdx.x == 0 ? tile0 : tile0 + kPackThreads * kPackVecs - 1) * EPV;
+    e = e < total_elems ? e : total_elems - 1;
+    s_range[threadIdx.x] = find_entry(offsets, 0, batch - 1, e);
+  }
+  __syncthreads();
+  const int64_t lo = s_range[0], hi = s_range[1];
+#pragma unroll
+  for (int j = 0; j < kPackVecs; ++j) {
+    const int64_t v = tile0 + (int64_t)j * kPackThreads + threadIdx.x;
+    if (v >= n_vec) break;
+    const int64_t e0 = v * EPV;
+    int64_t b = find_entry(offsets, lo, hi, e0);
+    const int64_t end_b = offsets[b + 1];
+    const T* src = static_cast<const T*>(srcs[b]) + (e0 - offsets[b]);
+    if (e0 + EPV <= end_b && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+      st_global_16_stream(static_cast<T*>(out) + e0, ld_global_16_stream(src));
+    } else {
+      T* dst = static_cast<T*>(out) + e0;
+      int64_t nxt = end_b;
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) {
+        const int64_t e = e0 + k;
+        if (e >= total_elems) break;
+        while (e >= nxt) {  // empty constituents are skipped here
+          ++b;
+          nxt = offsets[b + 1];
+        }
+        dst[k] = static_cast<const T*>(srcs[b])[e - offsets[b]];
+      }
+    }
+  }
+}
+
+constexpr int kEmbThreads = 256;
+
+// One warp per output row (token); 16-byte vectors when the row size and both bases allow it.
+template <typename IDX, bool VEC>
+__global__ void __launch_bounds__(kEmbThreads)
+embedding_kernel(const void* __restrict__ weight, const IDX* __restrict__ index, void* __restrict__ out, int64_t tokens,
+                 int64_t vocab, int64_t row_bytes) {
+  const int64_t t = (int64_t)blockIdx.x * (kEmbThreads / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const int64_t i = (int64_t)index[t];
+  const bool ok = i >= 0 && i < vocab;
+  if (!ok && lane == 0) atomicOr(&g_construct_error, 1);
+  const uint8_t* src = static_cast<const uint8_t*>(weight) + (ok ? i : 0) * row_bytes;
+  uint8_t* dst = static_cast<uint8_t*>(out) + t * row_bytes;
+  if (VEC) {
+    const int64_t nv = row_bytes >> 4;
+    for (int64_t v = lane; v < nv; v += 32) {
+      uint4 x = make_uint4(0, 0, 0, 0);
+      if (ok) x = ld_global_16_stream(src + (v << 4));
+      st_global_16_stream(dst + (v << 4), x);
+    }
+  } else {
+    for (int64_t k = lane; k < row_bytes; k += 32) dst[k] = ok ? src[k] : (uint8_t)0;
+  }
+}
+
+}  // namespace
+
+int construct_error_flags_read_and_clear() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_construct_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_construct_error, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace ntb200
+
+using namespace ntb200;
+
+extern "C" {
+
+int ntb200_pack_pointers(const void* const* srcs, const int64_t* offsets, int64_t batch, void* out, int64_t total_elems,
+                         int elem_size, void* stream) {
+  if (batch < 0 || total_elems < 0) return NTB200_INVALID_ARG;
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return NTB200_UNSUPPORTED_DTYPE;
+  if (batch == 0 || total_elems == 0) return NTB200_OK;
+  if (srcs == nullptr || offsets == nullptr || out == nullptr) return NTB200_INVALID_ARG;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return NTB200_MISALIGNED;
+  const int64_t epv = 16 / elem_size;
+  const int64_t n_vec = (total_elems + epv - 1) / epv;
+  const int64_t grid = (n_vec + kPackThreads * kPackVecs - 1) / (kPackThreads * kPackVecs);
+  if (grid > 0x7fffffff) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (elem_size) {
+    case 1: pack_pointers_kernel<1><<<(unsigned)grid, kPackThreads, 0, st>>>(srcs, offsets, batch, out, total_elems); break;
+    case 2: pack_pointers_kernel<2><<<(unsigned)grid, kPackThreads, 0, st>>>(srcs, offsets, batch, out, total_elems); break;
+    case 4: pack_pointers_kernel<4><<<(unsigned)grid, kPackThreads, 0, st>>>(srcs, offsets, batch, out, total_elems); break;
+    default: pack_pointers_kernel<8><<<(unsigned)grid, kPackThreads, 0, st>>>(srcs, offsets, batch, out, total_elems); break;
+  }
+  return status_from_cuda(cudaGetLastError());
+}
+
+int ntb200_embedding(const void* weight, const void* index, int index_bytes, void* out, int64_t tokens, int64_t vocab,
+                     int64_t embed_dim, int elem_size, void* stream) {
+  if (tokens < 0 || vocab < 0 || embed_dim < 0 || (index_bytes != 4 && index_bytes != 8)) return NTB200_INVALID_ARG;
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return NTB200_UNSUPPORTED_DTYPE;
+  if (tokens == 0 || embed_dim == 0) return NTB200_OK;
+  if (weight == nullptr || index == nullptr || out == nullptr || vocab == 0) return NTB200_INVALID_ARG;
+  const int64_t row_bytes = embed_dim * elem_size;
+  const bool vec = (row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const int64_t grid = (tokens + kEmbThreads / 32 - 1) / (kEmbThreads / 32);
+  if (grid > 0x7fffffff) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define NTB200_EMB(IDX, VEC) \
+  embedding_kernel<IDX, VEC><<<(unsigned)grid, kEmbThreads, 0, st>>>(weight, static_cast<const IDX*>(index), out, tokens, vocab, row_bytes)
+  if (index_bytes == 8) {
+    if (vec) NTB200_EMB(int64_t, true);
+    else NTB200_EMB(int64_t, false);
+  } else {
+    if (vec) NTB200_EMB(int32_t, true);
+    else NTB200_EMB(int32_t, false);
+  }
+#undef NTB200_EMB
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -600,6 +600,69 @@ Tensor add_bias_gelu(const Tensor& x, const c10::optional<Tensor>& bias) {
   return out;
 }
 
+// ------------------------------------------------------------------ construction
+// nested_tensor(list of CUDA tensors): one pointer-array gather instead of one copy per constituent
+// (nestedtensor/csrc/storage/Packed.h:75-98).  Returns (buffer, sizes on the host, meta); the pointer table,
+// the offsets and the sizes travel to the device in one pinned asynchronous copy, and meta is a view of it.
+std::tuple<Tensor, Tensor, Tensor> pack_list(at::TensorList tensors) {
+  const int64_t B = (int64_t)tensors.size();
+  TORCH_CHECK(B > 0, "nestedtensor_b200: pack_list needs at least one tensor");
+  const Tensor& first = tensors[0];
+  TORCH_CHECK(first.is_cuda(), "nestedtensor_b200: pack_list needs CUDA tensors (this build has no CPU implementation)");
+  const int64_t tdim = first.dim();
+  const int64_t es = first.element_size();
+  TORCH_CHECK(es == 1 || es == 2 || es == 4 || es == 8, "Input datatype ", first.dtype(), " is not supported.");
+  std::vector<Tensor> keep;
+  keep.reserve(B);
+  Tensor host = at::empty({B + (B + 1) + B * tdim}, at::TensorOptions().dtype(at::kLong).pinned_memory(true));
+  int64_t* h = host.data_ptr<int64_t>();
+  Tensor sizes = at::empty({B, tdim}, at::TensorOptions().dtype(at::kLong));
+  int64_t* hs = sizes.data_ptr<int64_t>();
+  int64_t total = 0;
+  for (int64_t b = 0; b < B; ++b) {
+    const Tensor& t = tensors[b];
+    TORCH_CHECK(t.is_cuda() && t.device() == first.device() && t.scalar_type() == first.scalar_type() && t.dim() == tdim,
+                "nestedtensor_b200: pack_list needs tensors of one device, dtype and dimension");
+    keep.push_back(t.contiguous());
+    h[b] = reinterpret_cast<int64_t>(keep.back().data_ptr());
+    h[B + b] = total;
+    total += t.numel();
+    for (int64_t j = 0; j < tdim; ++j) hs[b * tdim + j] = h[B + (B + 1) + b * tdim + j] = t.size(j);
+  }
+  h[B + B] = total;
+  c10::cuda::CUDAGuard guard(first.device());
+  Tensor dev = host.to(first.device(), /*non_blocking=*/true);
+  Tensor buffer = at::empty({total}, first.options());
+  check_rc(ntb200_pack_pointers(reinterpret_cast<const void* const*>(dev.data_ptr<int64_t>()), dev.data_ptr<int64_t>() + B, B,
+                                buffer.data_ptr(), total, (int)es, cur_stream()),
+           "ntb200_pack_pointers");
+  // `keep` (contiguous copies, if any were needed) is released here: the caching allocator orders reuse of that
+  // memory after this stream's work, which includes the gather
+  return std::make_tuple(buffer, sizes, dev.slice(0, B));
+}
+
+// nestedtensor/csrc/functions.cpp:29-56: embedding of a nested tensor of 1-D index sequences = one gather on
+// its packed index buffer; the result has sizes (L_i, embedding_dim).
+Tensor embedding(const Tensor& weight, const Tensor& index_buffer, const Tensor& sizes, const Tensor& meta) {
+  Record r = make_record(sizes, meta);
+  TORCH_CHECK(r.tdim == 1, "nestedtensor_b200: embedding expects a nested tensor of 1-D index sequences");
+  TORCH_CHECK(weight.is_cuda() && weight.dim() == 2, "nestedtensor_b200: embedding needs a 2-D CUDA weight");
+  TORCH_CHECK(index_buffer.is_cuda() && index_buffer.device() == weight.device() && index_buffer.dim() == 1 &&
+                  index_buffer.is_contiguous() && index_buffer.numel() == r.numel,
+              "nestedtensor_b200: the index buffer must be 1-D contiguous on the weight's device");
+  TORCH_CHECK(index_buffer.scalar_type() == at::kLong || index_buffer.scalar_type() == at::kInt,
+              "Expected tensor for argument #1 'indices' to have one of the following scalar types: Long, Int");
+  const int64_t es = weight.element_size();
+  TORCH_CHECK(es == 1 || es == 2 || es == 4 || es == 8, "Input datatype ", weight.dtype(), " is not supported.");
+  Tensor w = weight.contiguous();
+  c10::cuda::CUDAGuard guard(weight.device());
+  Tensor out = at::empty({r.numel * w.size(1)}, w.options());
+  check_rc(ntb200_embedding(w.data_ptr(), index_buffer.data_ptr(), (int)index_buffer.element_size(), out.data_ptr(), r.numel,
+                            w.size(0), w.size(1), (int)es, cur_stream()),
+           "ntb200_embedding");
+  return out;
+}
+
 }  // namespace
 
 // The operator names follow the reference's `nestedtensor` namespace
@@ -630,4 +693,6 @@ TORCH_LIBRARY(nestedtensor, m) {
         &add_bias_residual_layer_norm);
   m.def("packed_linear(Tensor x, Tensor weight, Tensor? bias, int act, Tensor? residual) -> Tensor", &packed_linear);
   m.def("add_bias_gelu(Tensor x, Tensor? bias) -> Tensor", &add_bias_gelu);
+  m.def("pack_list(Tensor[] tensors) -> (Tensor, Tensor, Tensor)", &pack_list);
+  m.def("embedding(Tensor weight, Tensor index_buffer, Tensor sizes, Tensor meta) -> Tensor", &embedding);
 }

@@ -746,8 +746,9 @@ int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, in
 int ntb200_device_error_flags(void) {
   const int g = gemm_error_flags_read_and_clear();
   const int a = attn_tcgen05_error_flags_read_and_clear();
-  if (g < 0 || a < 0) return -1;
-  return g | (a << 8);
+  const int c = construct_error_flags_read_and_clear();
+  if (g < 0 || a < 0 || c < 0) return -1;
+  return g | (a << 8) | (c << 16);
 }
 
 }  // extern "C"

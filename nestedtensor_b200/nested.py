@@ -214,6 +214,9 @@ class NestedTensor(object):
         if func is torch.nn.functional.multi_head_attention_forward:
             from .nn import multi_head_attention_forward
             return multi_head_attention_forward(*args, **kwargs)
+        if func is torch.nn.functional.embedding:
+            from .nn import embedding
+            return embedding(*args, **kwargs)
         if func is torch.nn.functional.layer_norm or func is torch.layer_norm:
             from .nn import layer_norm
             if func is torch.layer_norm:  # (input, normalized_shape, weight, bias, eps, cudnn_enable)
@@ -221,7 +224,7 @@ class NestedTensor(object):
                 kwargs = {k: v for k, v in kwargs.items() if k != "cudnn_enable"}
             return layer_norm(*args, **kwargs)
         raise NotImplementedError(
-            "nestedtensor_b200 implements the padding / mask / attention / layer-norm path only; %s is not supported on a "
+            "nestedtensor_b200 implements the construction / padding / mask / attention / layer-norm path only; %s is not supported on a "
             "NestedTensor" % getattr(func, "__name__", str(func)))
 
 

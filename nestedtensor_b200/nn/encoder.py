@@ -86,3 +86,20 @@ def transformer_encoder_layer(layer: torch.nn.TransformerEncoderLayer, src: Nest
         x1 = norm(layer.norm1, self_attention(x, x))
         out = norm(layer.norm2, feed_forward(x1, x1))
     return NestedTensor(out.reshape(-1), sizes, meta)
+
+
+def embedding(input: NestedTensor, weight: torch.Tensor, padding_idx=None, max_norm=None, norm_type=2.0,
+              scale_grad_by_freq=False, sparse=False) -> NestedTensor:
+    """``torch.nn.functional.embedding`` on a NestedTensor of 1-D index sequences
+    (nestedtensor/csrc/functions.cpp:29-56): one gather on the packed index buffer; the result holds
+    ``(L_i, embedding_dim)`` constituents.  ``padding_idx``, ``scale_grad_by_freq`` and ``sparse`` only
+    affect gradients and are ignored at inference; ``max_norm`` (which rewrites the weight) is not supported."""
+    if max_norm is not None:
+        raise NotImplementedError("nestedtensor_b200: embedding with max_norm is not supported")
+    if input.dim() != 2:
+        raise NotImplementedError("nestedtensor_b200: embedding expects a nested tensor of 1-D index sequences")
+    buf, sizes, meta = input._record()
+    out = _ops.ops().embedding(weight, buf, sizes, meta)
+    E = weight.size(1)
+    new_sizes = torch.cat([sizes, torch.full((sizes.size(0), 1), E, dtype=torch.int64)], 1).contiguous()
+    return NestedTensor(out, new_sizes)

@@ -394,3 +394,9 @@ def encoder_layer(tensors: NTList, num_heads: int, p: dict, activation: str = "g
         return [x + h for x, h in zip(xs, ff(ln(xs, "norm2")))]
     xs = ln([x + a for x, a in zip(xs, sa(xs))], "norm1")
     return ln([x + h for x, h in zip(xs, ff(xs))], "norm2")
+
+
+def embedding(indices: NTList, weight: torch.Tensor) -> NTList:
+    """nestedtensor/csrc/functions.cpp:57-63 (``at::embedding`` mapped over the constituents; the packed fast
+    path :29-56 is the same gather on the concatenated indices)."""
+    return [F.embedding(i.long(), weight) for i in indices]
