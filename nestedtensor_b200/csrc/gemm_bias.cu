@@ -94,12 +94,27 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {
 }
 
 // 32 accumulator columns of one output row: + bias, optional GELU, optional + residual (the same 32 columns
-// of the residual row, `res`, or nullptr), packed to 16 bits, stored.  With `wide` (row stride and base
+// of the residual row, already in registers: the caller loads them a chunk ahead), packed to 16 bits, stored.  With `wide` (row stride and base
 // 32-byte aligned) each store is one full 32-byte sector (st.global.v8); a warp-wide 16-byte store per row
 // would touch every sector twice.
+// The thread's own 64 bytes of the residual row for one 32-column chunk (zeros past the matrix edge).
+__device__ __forceinline__ void load_res32(const uint16_t* res, int n_left, bool live, uint4 (&q)[4]) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g)
+    q[g] = (live && g * 8 < n_left) ? *reinterpret_cast<const uint4*>(res + g * 8) : make_uint4(0, 0, 0, 0);
+}
+
+// Pulls this thread's 128 columns (256 bytes) of the residual row towards L2 while the tile is still being
+// accumulated, so that the loads in the epilogue find it there.
+__device__ __forceinline__ void prefetch_res_l2(const uint16_t* rrow, bool live, int c_begin, int n_left) {
+  if (rrow == nullptr || !live) return;
+  if (c_begin < n_left) asm volatile("prefetch.global.L2 [%0];" ::"l"(rrow + c_begin));
+  if (c_begin + 64 < n_left) asm volatile("prefetch.global.L2 [%0];" ::"l"(rrow + c_begin + 64));
+}
+
 template <int FMT>
 __device__ __forceinline__ void store_chunk32(uint16_t* dst, const uint32_t (&r)[32], const float* bias32, int n_left,
-                                              bool wide, int act, const uint16_t* res) {
+                                              bool wide, int act, const uint4 (&res)[4], bool has_res) {
   float v[32];
 #pragma unroll
   for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]) + bias32[k];
@@ -110,17 +125,14 @@ __device__ __forceinline__ void store_chunk32(uint16_t* dst, const uint32_t (&r)
 #pragma unroll
     for (int k = 0; k < 32; ++k) v[k] = fmaxf(v[k], 0.0f);
   }
-  if (res != nullptr) {
+  if (has_res) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      if (g * 8 < n_left) {
-        const uint4 q = *reinterpret_cast<const uint4*>(res + g * 8);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      const uint32_t w[4] = {res[g].x, res[g].y, res[g].z, res[g].w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          v[g * 8 + 2 * k] += OutPack<FMT>::lo(w[k]);
-          v[g * 8 + 2 * k + 1] += OutPack<FMT>::hi(w[k]);
-        }
+      for (int k = 0; k < 4; ++k) {
+        v[g * 8 + 2 * k] += OutPack<FMT>::lo(w[k]);
+        v[g * 8 + 2 * k + 1] += OutPack<FMT>::hi(w[k]);
       }
     }
   }
@@ -264,30 +276,41 @@ gemm_bias_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         s_bias[i] = (bias != nullptr && n < N) ? OutPack<FMT>::load(bias, n) : 0.0f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
-      if (!ok) continue;  // keep taking the named barriers with the other epilogue warps
-      ptx::tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
       const uint16_t* rrow = residual != nullptr ? reinterpret_cast<const uint16_t*>(residual) + (size_t)row * N + n0 : nullptr;
+      prefetch_res_l2(rrow, row < M, ((warp - 2) >> 2) * (kBN / 2), N - n0);  // while the main loop of this tile still runs
+      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
+      if (!ok) continue;  // keep taking the named barriers with the other epilogue warps
+      ptx::tc_fence_after_sync();
       // two register buffers: the tensor-memory load of the next 32 columns runs under the bias add, the
       // packing and the stores of the current ones
       const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
       uint32_t ra[32], rb[32];
+      uint4 qa[4], qb[4];  // the residual of the same chunks, loaded together with the accumulator
+      const bool has_res = rrow != nullptr, res_live = has_res && row < M;
       const int c_begin = ((warp - 2) >> 2) * (kBN / 2), c_end = c_begin + kBN / 2;  // this warp's 128 columns
-      if (n0 + c_begin < N) ptx::tmem_ld_32x32b_x32(tacc + c_begin, ra);
+      if (n0 + c_begin < N) {
+        ptx::tmem_ld_32x32b_x32(tacc + c_begin, ra);
+        if (has_res) load_res32(rrow + c_begin, N - (n0 + c_begin), res_live, qa);
+      }
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += 64) {
         if (n0 + c >= N) break;
         ptx::tmem_ld_wait();
         const bool second = n0 + c + 32 < N;
-        if (second) ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
-        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide, act, rrow != nullptr ? rrow + c : nullptr);
+        if (second) {
+          ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
+          if (has_res) load_res32(rrow + c + 32, N - (n0 + c + 32), res_live, qb);
+        }
+        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide, act, qa, has_res);
         if (!second) break;
         ptx::tmem_ld_wait();
-        if (c + 64 < c_end && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
-        if (row < M)
-          store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide, act, rrow != nullptr ? rrow + c + 32 : nullptr);
+        if (c + 64 < c_end && n0 + c + 64 < N) {
+          ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
+          if (has_res) load_res32(rrow + c + 64, N - (n0 + c + 64), res_live, qa);
+        }
+        if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide, act, qb, has_res);
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -461,30 +484,41 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
         s_bias[i] = (bias != nullptr && n < N) ? OutPack<FMT>::load(bias, n) : 0.0f;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
-      if (!ok) continue;
-      ptx::tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
       const uint16_t* rrow = residual != nullptr ? reinterpret_cast<const uint16_t*>(residual) + (size_t)row * N + n0 : nullptr;
+      prefetch_res_l2(rrow, row < M, ((warp - 2) >> 2) * (kBN / 2), N - n0);  // while the main loop of this tile still runs
+      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
+      if (!ok) continue;
+      ptx::tc_fence_after_sync();
       // two register buffers: the tensor-memory load of the next 32 columns runs under the bias add, the
       // packing and the stores of the current ones
       const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
       uint32_t ra[32], rb[32];
+      uint4 qa[4], qb[4];  // the residual of the same chunks, loaded together with the accumulator
+      const bool has_res = rrow != nullptr, res_live = has_res && row < M;
       const int c_begin = ((warp - 2) >> 2) * (kBN / 2), c_end = c_begin + kBN / 2;  // this warp's 128 columns
-      if (n0 + c_begin < N) ptx::tmem_ld_32x32b_x32(tacc + c_begin, ra);
+      if (n0 + c_begin < N) {
+        ptx::tmem_ld_32x32b_x32(tacc + c_begin, ra);
+        if (has_res) load_res32(rrow + c_begin, N - (n0 + c_begin), res_live, qa);
+      }
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += 64) {
         if (n0 + c >= N) break;
         ptx::tmem_ld_wait();
         const bool second = n0 + c + 32 < N;
-        if (second) ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
-        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide, act, rrow != nullptr ? rrow + c : nullptr);
+        if (second) {
+          ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
+          if (has_res) load_res32(rrow + c + 32, N - (n0 + c + 32), res_live, qb);
+        }
+        if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide, act, qa, has_res);
         if (!second) break;
         ptx::tmem_ld_wait();
-        if (c + 64 < c_end && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
-        if (row < M)
-          store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide, act, rrow != nullptr ? rrow + c + 32 : nullptr);
+        if (c + 64 < c_end && n0 + c + 64 < N) {
+          ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
+          if (has_res) load_res32(rrow + c + 64, N - (n0 + c + 64), res_live, qa);
+        }
+        if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide, act, qb, has_res);
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
