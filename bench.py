@@ -663,6 +663,19 @@ def run_kernels(args, local):
         T = int(Ls.sum())
         bi = lambda: ops.token_index(meta[:wl.batch + 1] // E, T)
         add("token_index", name, timed(bi, n), None)
+    # cross-attention of a DETR-style decoder: 100 object queries per image over a ragged memory of 400-1200 tokens
+    g = torch.Generator().manual_seed(20247)
+    lk = torch.randint(400, 1201, (32,), generator=g)
+    for E, H, dtype in ((256, 8, torch.float16), (512, 8, torch.bfloat16)):
+        qn = nt.NestedTensor(torch.randn(32 * 100 * E, device=device).to(dtype), torch.tensor([[100, E]] * 32))
+        kn = nt.NestedTensor(torch.randn(int(lk.sum()) * E, device=device).to(dtype), torch.stack([lk, torch.full_like(lk, E)], 1))
+        mha = torch.nn.MultiheadAttention(E, H).eval().to(dtype).to(device)
+        with torch.no_grad():
+            fn = lambda: mha(qn, kn, kn, need_weights=False)
+            ms = timed(fn, n)
+        fl = 4.0 * E * 100 * float(lk.sum()) + 2.0 * E * E * (2 * 3200 + 2 * float(lk.sum()))
+        add("MultiheadAttention(query != key)", "DETR-like 32 x (100 queries, 400-1200 keys), E=%d, %d heads x %d" % (E, H, E // H),
+            ms, None, fl)
     from nestedtensor_b200 import _cabi
     return {"metric": "per-operator timings", "unit": "ms", "n_gpus": 1, "steps": n, "data": "synthetic",
             "peaks": peaks, "rows": rows, "device_error_flags": _cabi.load().ntb200_device_error_flags()}

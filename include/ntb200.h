@@ -263,6 +263,23 @@ int ntb200_pack_pointers(const void* const* srcs, const int64_t* offsets, int64_
 int ntb200_embedding(const void* weight, const void* index, int index_bytes, void* out, int64_t tokens,
                      int64_t vocab, int64_t embed_dim, int elem_size, void* stream);
 
+/* Attention of the queries of sequence b over the keys / values of sequence b of ANOTHER nested tensor
+ * (cross-attention, or self-attention with separately stored q / k / v):
+ *   out[tq, h*d:(h+1)*d] = softmax(scaling * q_b,h k_b,h^T) v_b,h
+ * q / k / v point at head 0 of token 0 of their matrices, ldq / ldk / ldv are the row strides in elements
+ * (>= H*d; k and v may be the two halves of one [Tk, 2*H*d] projection output); offsets_q / offsets_k are the
+ * B+1 ELEMENT offsets of the sequences in the [tokens, H*d] query and key inputs; out is [q_tokens, H*d].
+ * A query whose key sequence is empty gets zeros.  path: 0 = mma.sync flash kernel for head_dim 64 in
+ * fp16/bf16 with 16-byte aligned rows, else SIMT;  1 = SIMT;  2 = flash kernel (error if unsupported).
+ * Replaces the generic per-sequence attention of min_mha (nestedtensor/csrc/mha.cpp:18-69) for query != key,
+ * which the reference's CUDA path does not accelerate (nestedtensor/nn/mha.py:57).
+ */
+int ntb200_varlen_cross_attention(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                                  int64_t ldv, void* out, const int64_t* offsets_q,
+                                  const int64_t* offsets_k, int64_t batch, int64_t q_tokens, int num_heads,
+                                  int head_dim, int64_t max_len_q, float scaling, int dtype, int path,
+                                  void* stream);
+
 /* ------------------------------------------------------------------ reference-shaped helpers
  * q/k/v_buf[b, h, l, :] = qkv[tok(b,l), {0,E,2E} + h*d + :] + bias  for valid tokens (padded
  * positions are left untouched): bias add fused with packed -> padded head-major scatter.

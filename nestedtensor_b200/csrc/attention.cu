@@ -56,9 +56,13 @@ constexpr int kSimtWarps = 8;
 constexpr int kMaxHeadDim = 256;
 
 template <typename T>
-__global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
-                                                                    const int64_t* __restrict__ offsets, int64_t batch,
-                                                                    int64_t total_tokens, int H, int d, float scale) {
+__global__ void __launch_bounds__(kSimtWarps * 32)
+attn_simt_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, int64_t ldk, const T* __restrict__ v, int64_t ldv,
+                 T* __restrict__ out, const int64_t* __restrict__ offsets_q, const int64_t* __restrict__ offsets_k,
+                 int64_t batch, int64_t total_tokens, int H, int d, float scale) {
+  // q / k / v: first element of head 0 of token 0, row strides ldq / ldk / ldv (self-attention on a packed
+  // [T, 3E] buffer: the three thirds of one row, all strides 3E, offsets_k == offsets_q); offsets in elements
+  // of the [tokens, E] matrices of the query and of the key / value nested tensors
   __shared__ float s_q[kSimtWarps][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t wg = (int64_t)blockIdx.x * kSimtWarps + warp;
@@ -66,14 +70,14 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(const T* __r
   const int64_t t = wg / H;
   const int h = (int)(wg % H);
   const int64_t E = (int64_t)H * d;
-  const int64_t b = find_entry(offsets, batch, t * E);
-  const int64_t tok0 = offsets[b] / E;
-  const int L = (int)((offsets[b + 1] - offsets[b]) / E);
-  const T* qrow = qkv + t * 3 * E + (int64_t)h * d;
+  const int64_t b = find_entry(offsets_q, batch, t * E);
+  const int64_t tok0 = offsets_k[b] / E;
+  const int L = (int)((offsets_k[b + 1] - offsets_k[b]) / E);
+  const T* qrow = q + t * ldq + (int64_t)h * d;
   for (int i = lane; i < d; i += 32) s_q[warp][i] = Cvt<T>::to_f(qrow[i]) * scale;
   __syncwarp();
-  const T* kbase = qkv + tok0 * 3 * E + E + (int64_t)h * d;
-  const T* vbase = kbase + E;
+  const T* kbase = k + tok0 * ldk + (int64_t)h * d;
+  const T* vbase = v + tok0 * ldv + (int64_t)h * d;
   constexpr int DPL = kMaxHeadDim / 32;
   float acc[DPL];
 #pragma unroll
@@ -83,7 +87,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(const T* __r
     const int j = c0 + lane;
     float s = -INFINITY;
     if (j < L) {
-      const T* krow = kbase + (int64_t)j * 3 * E;
+      const T* krow = kbase + (int64_t)j * ldk;
       float dot = 0.0f;
       for (int i = 0; i < d; ++i) dot = fmaf(s_q[warp][i], Cvt<T>::to_f(krow[i]), dot);
       s = dot;
@@ -103,7 +107,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(const T* __r
     const int nj = (L - c0) < 32 ? (L - c0) : 32;
     for (int jj = 0; jj < nj; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const T* vrow = vbase + (int64_t)(c0 + jj) * 3 * E;
+      const T* vrow = vbase + (int64_t)(c0 + jj) * ldv;
 #pragma unroll
       for (int i = 0; i < DPL; ++i) {
         const int dim = lane + 32 * i;
@@ -112,7 +116,7 @@ __global__ void __launch_bounds__(kSimtWarps * 32) attn_simt_kernel(const T* __r
     }
     m = m_new;
   }
-  const float inv = 1.0f / l;
+  const float inv = L > 0 ? 1.0f / l : 0.0f;  // a query whose key sequence is empty gets zeros
   T* orow = out + t * E + (int64_t)h * d;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
@@ -184,24 +188,26 @@ __device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const T* __r
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kFaThreads) attn_fa_d64_kernel(const T* __restrict__ qkv, T* __restrict__ out,
-                                                                  const int64_t* __restrict__ offsets, int H,
-                                                                  float scale_log2e) {
+__global__ void __launch_bounds__(kFaThreads)
+attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, int64_t ldk, const T* __restrict__ v,
+                   int64_t ldv, T* __restrict__ out, const int64_t* __restrict__ offsets_q, const int64_t* __restrict__ offsets_k,
+                   int H, float scale_log2e) {  // arguments as in attn_simt_kernel
   __shared__ __align__(128) uint8_t s_q[kBQ * kD * 2];
   __shared__ __align__(128) uint8_t s_k[2][kBKV * kD * 2];
   __shared__ __align__(128) uint8_t s_v[2][kBKV * kD * 2];
 
   const int b = blockIdx.z, h = blockIdx.y;
   const int64_t E = (int64_t)H * kD;
-  const int64_t off_b = offsets[b];
-  const int L = (int)((offsets[b + 1] - off_b) / E);
+  const int64_t off_b = offsets_q[b];
+  const int Lq = (int)((offsets_q[b + 1] - off_b) / E);
   const int q0 = blockIdx.x * kBQ;
-  if (q0 >= L) return;
-  const int64_t tok0 = off_b / E;
-  const int64_t ld = 3 * E;
-  const T* qbase = qkv + tok0 * ld + (int64_t)h * kD;
-  const T* kbase = qbase + E;
-  const T* vbase = kbase + E;
+  if (q0 >= Lq) return;
+  const int64_t tok0 = off_b / E;  // first query token (also the first output row)
+  const int64_t tokk0 = offsets_k[b] / E;
+  const int L = (int)((offsets_k[b + 1] - offsets_k[b]) / E);  // keys
+  const T* qbase = q + tok0 * ldq + (int64_t)h * kD;
+  const T* kbase = k + tokk0 * ldk + (int64_t)h * kD;
+  const T* vbase = v + tokk0 * ldv + (int64_t)h * kD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t sq = (uint32_t)__cvta_generic_to_shared(s_q);
   const uint32_t sk = (uint32_t)__cvta_generic_to_shared(s_k);
@@ -209,9 +215,16 @@ __global__ void __launch_bounds__(kFaThreads) attn_fa_d64_kernel(const T* __rest
   constexpr uint32_t kTileBytes = kBKV * kD * 2;
 
   const int n_kv = (L + kBKV - 1) / kBKV;
-  load_tile_async<T>(sq, qbase, ld, q0, L - 1);
-  load_tile_async<T>(sk, kbase, ld, 0, L - 1);
-  load_tile_async<T>(sv, vbase, ld, 0, L - 1);
+  if (L <= 0) {  // no keys: the output rows of this tile are zeros
+    for (int i = threadIdx.x; i < kBQ * (kD / 2); i += kFaThreads) {
+      const int r = q0 + i / (kD / 2);
+      if (r < Lq) reinterpret_cast<uint32_t*>(out + (tok0 + r) * E + (int64_t)h * kD)[i % (kD / 2)] = 0u;
+    }
+    return;
+  }
+  load_tile_async<T>(sq, qbase, ldq, q0, Lq - 1);
+  load_tile_async<T>(sk, kbase, ldk, 0, L - 1);
+  load_tile_async<T>(sv, vbase, ldv, 0, L - 1);
   cp_async_commit();
 
   uint32_t qf[4][4];  // Q fragments: 4 k-steps of 16 head dims
@@ -225,8 +238,8 @@ __global__ void __launch_bounds__(kFaThreads) attn_fa_d64_kernel(const T* __rest
   for (int it = 0; it < n_kv; ++it) {
     const int buf = it & 1;
     if (it + 1 < n_kv) {
-      load_tile_async<T>(sk + (buf ^ 1) * kTileBytes, kbase, ld, (it + 1) * kBKV, L - 1);
-      load_tile_async<T>(sv + (buf ^ 1) * kTileBytes, vbase, ld, (it + 1) * kBKV, L - 1);
+      load_tile_async<T>(sk + (buf ^ 1) * kTileBytes, kbase, ldk, (it + 1) * kBKV, L - 1);
+      load_tile_async<T>(sv + (buf ^ 1) * kTileBytes, vbase, ldv, (it + 1) * kBKV, L - 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -328,8 +341,8 @@ __global__ void __launch_bounds__(kFaThreads) attn_fa_d64_kernel(const T* __rest
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt) {
     const int col2 = nt * 4 + (lane & 3);  // index in 32-bit pairs
-    if (r0 < L) obase[col2] = MmaOp<T>::pack(o[nt][0] * i0, o[nt][1] * i0);
-    if (r1 < L) obase1[col2] = MmaOp<T>::pack(o[nt][2] * i1, o[nt][3] * i1);
+    if (r0 < Lq) obase[col2] = MmaOp<T>::pack(o[nt][0] * i0, o[nt][1] * i0);
+    if (r1 < Lq) obase1[col2] = MmaOp<T>::pack(o[nt][2] * i1, o[nt][3] * i1);
   }
 }
 
@@ -416,23 +429,51 @@ __global__ void __launch_bounds__(256) softmax_masked_kernel(T* __restrict__ sco
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Separate query / key / value sources (self-attention passes the thirds of one packed row)
+struct QkvSrc {
+  const void *q, *k, *v;
+  int64_t ldq, ldk, ldv;
+  const int64_t *offsets_q, *offsets_k;
+};
+
 template <typename T>
-int launch_attn_simt(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t T_tokens, int H, int d,
-                     float scale, cudaStream_t st) {
-  const int64_t blocks = ceil_div(T_tokens * H, kSimtWarps);
+int launch_attn_simt(const QkvSrc& s, void* out, int64_t batch, int64_t q_tokens, int H, int d, float scale, cudaStream_t st) {
+  const int64_t blocks = ceil_div(q_tokens * H, kSimtWarps);
   if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
-  attn_simt_kernel<T><<<(unsigned)blocks, kSimtWarps * 32, 0, st>>>(static_cast<const T*>(qkv), static_cast<T*>(out), offsets,
-                                                                    batch, T_tokens, H, d, scale);
+  attn_simt_kernel<T><<<(unsigned)blocks, kSimtWarps * 32, 0, st>>>(static_cast<const T*>(s.q), s.ldq, static_cast<const T*>(s.k),
+                                                                    s.ldk, static_cast<const T*>(s.v), s.ldv, static_cast<T*>(out),
+                                                                    s.offsets_q, s.offsets_k, batch, q_tokens, H, d, scale);
   return status_from_cuda(cudaGetLastError());
 }
 
 template <typename T>
-int launch_attn_fa(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int H, int64_t max_len, float scale,
-                   cudaStream_t st) {
-  dim3 grid((unsigned)ceil_div(max_len, kBQ), (unsigned)H, (unsigned)batch);
-  attn_fa_d64_kernel<T><<<grid, kFaThreads, 0, st>>>(static_cast<const T*>(qkv), static_cast<T*>(out), offsets, H,
-                                                     scale * 1.4426950408889634f);
+int launch_attn_fa(const QkvSrc& s, void* out, int64_t batch, int H, int64_t max_len_q, float scale, cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div(max_len_q, kBQ), (unsigned)H, (unsigned)batch);
+  attn_fa_d64_kernel<T><<<grid, kFaThreads, 0, st>>>(static_cast<const T*>(s.q), s.ldq, static_cast<const T*>(s.k), s.ldk,
+                                                     static_cast<const T*>(s.v), s.ldv, static_cast<T*>(out), s.offsets_q,
+                                                     s.offsets_k, H, scale * 1.4426950408889634f);
   return status_from_cuda(cudaGetLastError());
+}
+
+// The non-tcgen05 kernels behind both entry points: mma.sync flash kernel for head_dim 64 in fp16 / bf16 with
+// 16-byte aligned rows, SIMT otherwise.  path: 0 best of the two, 1 SIMT, 2 flash (error if unsupported).
+int launch_attn_generic(const QkvSrc& s, void* out, int64_t batch, int64_t q_tokens, int H, int d, int64_t max_len_q,
+                        float scaling, int dtype, int path, cudaStream_t st) {
+  const size_t es = dtype == NTB200_F32 ? 4 : 2;
+  auto rows16 = [&](const void* p, int64_t ld) { return aligned16(p) && (ld * (int64_t)es) % 16 == 0; };
+  const bool fa = path != 1 && dtype != NTB200_F32 && d == kD && rows16(s.q, s.ldq) && rows16(s.k, s.ldk) && rows16(s.v, s.ldv) &&
+                  aligned16(out) && batch <= 65535 && H <= 65535 && max_len_q > 0;
+  if (path == 2 && !fa) return NTB200_UNSUPPORTED_SHAPE;
+  if (fa) {
+    if (dtype == NTB200_F16) return launch_attn_fa<__half>(s, out, batch, H, max_len_q, scaling, st);
+    return launch_attn_fa<__nv_bfloat16>(s, out, batch, H, max_len_q, scaling, st);
+  }
+  switch (dtype) {
+    case NTB200_F32: return launch_attn_simt<float>(s, out, batch, q_tokens, H, d, scaling, st);
+    case NTB200_F16: return launch_attn_simt<__half>(s, out, batch, q_tokens, H, d, scaling, st);
+    case NTB200_BF16: return launch_attn_simt<__nv_bfloat16>(s, out, batch, q_tokens, H, d, scaling, st);
+  }
+  return NTB200_UNSUPPORTED_DTYPE;
 }
 
 }  // namespace
@@ -469,20 +510,28 @@ int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, 
     if (!aligned16(workspace)) return NTB200_MISALIGNED;
     return attn_tcgen05_launch(qkv, out, offsets, batch, total_tokens, num_heads, scaling, dtype, workspace, st);
   }
-  const bool fa = !force_simt && dtype != NTB200_F32 && head_dim == kD && aligned16(qkv) && aligned16(out) && batch <= 65535 &&
-                  num_heads <= 65535 && max_len > 0;
-  if (path == 2 && !fa) return NTB200_UNSUPPORTED_SHAPE;
-  if (fa) {
-    if (dtype == NTB200_F16) return launch_attn_fa<__half>(qkv, out, offsets, batch, num_heads, max_len, scaling, st);
-    return launch_attn_fa<__nv_bfloat16>(qkv, out, offsets, batch, num_heads, max_len, scaling, st);
-  }
-  switch (dtype) {
-    case NTB200_F32: return launch_attn_simt<float>(qkv, out, offsets, batch, total_tokens, num_heads, head_dim, scaling, st);
-    case NTB200_F16: return launch_attn_simt<__half>(qkv, out, offsets, batch, total_tokens, num_heads, head_dim, scaling, st);
-    case NTB200_BF16:
-      return launch_attn_simt<__nv_bfloat16>(qkv, out, offsets, batch, total_tokens, num_heads, head_dim, scaling, st);
-  }
-  return NTB200_UNSUPPORTED_DTYPE;
+  const int64_t E = (int64_t)num_heads * head_dim;
+  const size_t es = dtype == NTB200_F32 ? 4 : 2;
+  const char* base = static_cast<const char*>(qkv);
+  const QkvSrc src = {base, base + E * es, base + 2 * E * es, 3 * E, 3 * E, 3 * E, offsets, offsets};
+  return launch_attn_generic(src, out, batch, total_tokens, num_heads, head_dim, max_len, scaling, dtype, force_simt ? 1 : path, st);
+}
+
+int ntb200_varlen_cross_attention(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, void* out,
+                                  const int64_t* offsets_q, const int64_t* offsets_k, int64_t batch, int64_t q_tokens,
+                                  int num_heads, int head_dim, int64_t max_len_q, float scaling, int dtype, int path,
+                                  void* stream) {
+  if (batch < 0 || q_tokens < 0 || num_heads < 1 || head_dim < 1 || max_len_q < 0 || path < 0 || path > 2) return NTB200_INVALID_ARG;
+  if (dtype != NTB200_F32 && dtype != NTB200_F16 && dtype != NTB200_BF16) return NTB200_UNSUPPORTED_DTYPE;
+  if (head_dim > kMaxHeadDim) return NTB200_UNSUPPORTED_SHAPE;
+  const int64_t E = (int64_t)num_heads * head_dim;
+  if (ldq < E || ldk < E || ldv < E) return NTB200_INVALID_ARG;
+  if (batch == 0 || q_tokens == 0) return NTB200_OK;
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || offsets_q == nullptr || offsets_k == nullptr)
+    return NTB200_INVALID_ARG;
+  const QkvSrc src = {q, k, v, ldq, ldk, ldv, offsets_q, offsets_k};
+  return launch_attn_generic(src, out, batch, q_tokens, num_heads, head_dim, max_len_q, scaling, dtype, path,
+                             static_cast<cudaStream_t>(stream));
 }
 
 #define NTB200_DISPATCH_DTYPE(dtype, CALL)                 \

@@ -515,6 +515,84 @@ Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, boo
   return out;
 }
 
+// min_mha (nestedtensor/csrc/mha.cpp:18-69) for query != key: q, k and v are projected from three nested
+// tensors with the three thirds of in_proj (k and v in one GEMM when key and value are the same tensor), the
+// queries of sequence b attend over the keys of sequence b, then the output projection.
+Tensor min_mha_cross(int64_t num_heads, int64_t head_dim, const Tensor& q_buffer, const Tensor& q_sizes, const Tensor& q_meta,
+                     const Tensor& k_buffer, const Tensor& k_sizes, const Tensor& k_meta, const Tensor& v_buffer,
+                     const Tensor& attr_kernel, const Tensor& attr_bias, double scaling, const Tensor& out_proj_weight,
+                     const c10::optional<Tensor>& out_proj_bias) {
+  Record rq = make_record(q_sizes, q_meta), rk = make_record(k_sizes, k_meta);
+  TORCH_CHECK(rq.tdim == 2, "query needs to be 3 dim.");
+  TORCH_CHECK(rk.tdim == 2, "key needs to be 3 dim.");
+  TORCH_CHECK(rq.B == rk.B, "nestedtensor_b200: query and key must hold the same number of sequences");
+  check_buffer(q_buffer, rq, "min_mha");
+  check_buffer(k_buffer, rk, "min_mha");
+  check_buffer(v_buffer, rk, "min_mha");
+  const int64_t E = num_heads * head_dim;
+  TORCH_CHECK(rq.B == 0 || (rq.regular[1] && rq.max_sizes[1] == E), "query's third dimension must be regular.");
+  TORCH_CHECK(rk.B == 0 || (rk.regular[1] && rk.max_sizes[1] == E), "key's third dimension must be regular.");
+  TORCH_CHECK(num_heads >= 1 && head_dim >= 1 && head_dim <= 256, "nestedtensor_b200: head_dim must be in [1, 256]");
+  const int dt = dtype_code(q_buffer.scalar_type());
+  auto same = [&](const Tensor& w, const char* name) {
+    TORCH_CHECK(w.is_cuda() && w.device() == q_buffer.device() && w.scalar_type() == q_buffer.scalar_type(),
+                "nestedtensor_b200: ", name, " must be on the query's device and of its dtype");
+  };
+  same(k_buffer, "key");
+  same(v_buffer, "value");
+  same(attr_kernel, "in_proj_weight");
+  same(attr_bias, "in_proj_bias");
+  same(out_proj_weight, "out_proj_weight");
+  TORCH_CHECK(attr_kernel.dim() == 2 && attr_kernel.size(0) == 3 * E && attr_kernel.size(1) == E, "in_proj_weight must be [3E, E]");
+  TORCH_CHECK(attr_bias.numel() == 3 * E, "in_proj_bias must have 3E entries");
+  TORCH_CHECK(out_proj_weight.dim() == 2 && out_proj_weight.size(0) == E && out_proj_weight.size(1) == E, "out_proj_weight must be [E, E]");
+  c10::cuda::CUDAGuard guard(q_buffer.device());
+  const int64_t Tq = rq.numel / (E > 0 ? E : 1), Tk = rk.numel / (E > 0 ? E : 1);
+  Tensor out = at::empty({Tq * E}, q_buffer.options());
+  if (Tq == 0) return out;
+  Tensor w = attr_kernel.contiguous(), b = attr_bias.contiguous().view({3 * E}), w_out = out_proj_weight.contiguous();
+  const int64_t es = q_buffer.element_size();
+  const char* wp = static_cast<const char*>(w.data_ptr());
+  const char* bp = static_cast<const char*>(b.data_ptr());
+  void* st = cur_stream();
+  Tensor q = at::empty({Tq, E}, q_buffer.options());
+  check_rc(ntb200_gemm_bias(q_buffer.data_ptr(), wp, bp, q.data_ptr(), Tq, E, E, dt, 0, st), "ntb200_gemm_bias");
+  Tensor kv;
+  const void *kptr, *vptr;
+  int64_t ldkv;
+  if (v_buffer.data_ptr() == k_buffer.data_ptr()) {  // key is value: one [Tk, 2E] projection
+    kv = at::empty({std::max<int64_t>(Tk, 1), 2 * E}, q_buffer.options());
+    check_rc(ntb200_gemm_bias(k_buffer.data_ptr(), wp + E * E * es, bp + E * es, kv.data_ptr(), Tk, 2 * E, E, dt, 0, st),
+             "ntb200_gemm_bias");
+    kptr = kv.data_ptr();
+    vptr = static_cast<const char*>(kv.data_ptr()) + E * es;
+    ldkv = 2 * E;
+  } else {
+    kv = at::empty({2, std::max<int64_t>(Tk, 1), E}, q_buffer.options());
+    check_rc(ntb200_gemm_bias(k_buffer.data_ptr(), wp + E * E * es, bp + E * es, kv[0].data_ptr(), Tk, E, E, dt, 0, st),
+             "ntb200_gemm_bias");
+    check_rc(ntb200_gemm_bias(v_buffer.data_ptr(), wp + 2 * E * E * es, bp + 2 * E * es, kv[1].data_ptr(), Tk, E, E, dt, 0, st),
+             "ntb200_gemm_bias");
+    kptr = kv[0].data_ptr();
+    vptr = kv[1].data_ptr();
+    ldkv = E;
+  }
+  Tensor attn = at::empty({Tq, E}, q_buffer.options());
+  check_rc(ntb200_varlen_cross_attention(q.data_ptr(), E, kptr, ldkv, vptr, ldkv, attn.data_ptr(), rq.d_offsets, rk.d_offsets, rq.B,
+                                         Tq, (int)num_heads, (int)head_dim, rq.max_sizes[0], (float)scaling, dt, 0, st),
+           "ntb200_varlen_cross_attention");
+  const void* b_out = nullptr;
+  Tensor b_out_t;
+  if (out_proj_bias && out_proj_bias->defined()) {
+    same(*out_proj_bias, "out_proj_bias");
+    TORCH_CHECK(out_proj_bias->numel() == E, "out_proj_bias must have E entries");
+    b_out_t = out_proj_bias->contiguous();
+    b_out = b_out_t.data_ptr();
+  }
+  check_rc(ntb200_gemm_bias(attn.data_ptr(), w_out.data_ptr(), b_out, out.data_ptr(), Tq, E, E, dt, 0, st), "ntb200_gemm_bias");
+  return out;
+}
+
 // ------------------------------------------------------------------ packed row operators and projections
 // Dense CUDA [T, cols] views of a packed buffer go straight to the C ABI.
 void check_rows(const Tensor& x, const char* op) {
@@ -687,6 +765,11 @@ TORCH_LIBRARY(nestedtensor, m) {
       "bt_min_mha_core(int num_heads, int head_dim, Tensor buffer, Tensor sizes, Tensor meta, Tensor attr_kernel, "
       "Tensor attr_bias, float scaling) -> Tensor",
       &bt_min_mha_core);
+  m.def(
+      "min_mha_cross(int num_heads, int head_dim, Tensor q_buffer, Tensor q_sizes, Tensor q_meta, Tensor k_buffer, "
+      "Tensor k_sizes, Tensor k_meta, Tensor v_buffer, Tensor attr_kernel, Tensor attr_bias, float scaling, "
+      "Tensor out_proj_weight, Tensor? out_proj_bias) -> Tensor",
+      &min_mha_cross);
   m.def("layer_norm(Tensor buffer, Tensor sizes, Tensor meta, int[] normalized_shape, Tensor? weight, Tensor? bias, float eps) -> Tensor",
         &layer_norm);
   m.def("add_bias_residual_layer_norm(Tensor x, Tensor? residual, Tensor? bias, Tensor? weight, Tensor? beta, float eps) -> Tensor",

@@ -10,12 +10,24 @@ from ..nested import NestedTensor
 
 def bt_min_mha(num_heads, head_dim, dropout_p, training, query, key, value, attr_kernel, attr_bias, scaling,
                out_proj_weight, out_proj_bias):
-    """``torch.ops.nestedtensor.bt_min_mha`` with the reference's argument list.  query, key and value
-    must be the same NestedTensor (self-attention); returns a NestedTensor of the same nested size."""
-    if not (query is key and key is value):
-        raise NotImplementedError("nestedtensor_b200: bt_min_mha implements self-attention (query is key is value)")
+    """``torch.ops.nestedtensor.bt_min_mha`` with the reference's argument list; returns a NestedTensor with the
+    query's nested size.  query is key is value: the packed self-attention path; otherwise the general form of
+    ``min_mha`` (queries of sequence b over the keys / values of sequence b)."""
     if query.dim() != 3:
         raise RuntimeError("query needs to be 3 dim.")
+    if not (query is key and key is value):
+        # the general form (nestedtensor/csrc/mha.cpp:18-69): queries of sequence b over the keys / values of
+        # sequence b of other nested tensors, e.g. a decoder's cross-attention
+        if key.dim() != 3 or value.dim() != 3:
+            raise RuntimeError("key and value need to be 3 dim.")
+        if not torch.equal(key._sizes, value._sizes):
+            raise RuntimeError("nestedtensor_b200: key and value must have the same nested size")
+        qb, qs, qm = query._record()
+        kb, ks, km = key._record()
+        vb = kb if value is key else value._record()[0]
+        out = _ops.ops().min_mha_cross(num_heads, head_dim, qb, qs, qm, kb, ks, km, vb, attr_kernel, attr_bias, float(scaling),
+                                       out_proj_weight, out_proj_bias)
+        return NestedTensor(out, qs, qm)
     buf, sizes, meta = query._record()
     out = _ops.ops().bt_min_mha(num_heads, head_dim, float(dropout_p), bool(training), buf, sizes, meta, attr_kernel,
                                 attr_bias, float(scaling), out_proj_weight, out_proj_bias)
@@ -73,14 +85,12 @@ def multi_head_attention_forward(query,
     assert head_dim * num_heads == embed_dim, "embed_dim must be divisible by num_heads"
     scaling = float(head_dim) ** -0.5
 
-    if query is key and key is value:
-        if not in_proj_weight.is_cuda:
-            raise RuntimeError("nestedtensor_b200: attention needs CUDA weights (this build has no CPU implementation)")
-        return bt_min_mha(num_heads, head_dim, dropout_p, False, query, query, query, in_proj_weight, in_proj_bias,
-                          scaling, out_proj_weight, out_proj_bias), None
-    raise NotImplementedError(
-        "nestedtensor_b200: only self-attention (query is key is value) is implemented; cross-attention is outside "
-        "the accelerated path")
+    if not in_proj_weight.is_cuda:
+        raise RuntimeError("nestedtensor_b200: attention needs CUDA weights (this build has no CPU implementation)")
+    # self-attention runs on the tcgen05 kernels; query != key (a decoder's cross-attention, which the reference
+    # leaves to its per-sequence loop, nestedtensor/nn/mha.py:57-83) on the general kernels
+    return bt_min_mha(num_heads, head_dim, dropout_p, False, query, key, value, in_proj_weight, in_proj_bias,
+                      scaling, out_proj_weight, out_proj_bias), None
 
 
 class MultiheadAttention(torch.nn.MultiheadAttention):

@@ -221,12 +221,62 @@ def test_stock_module_matches_dense_attention(native_libs, cuda_device):
     assert torch.allclose(got.to_padded_tensor(padding=0), dense, atol=5e-4, rtol=1e-8)
 
 
-def test_cross_attention_is_rejected(native_libs, cuda_device):
-    a = nt.nested_tensor([torch.randn(3, 8)], device=cuda_device)
-    b = nt.nested_tensor([torch.randn(4, 8)], device=cuda_device)
-    mha = torch.nn.MultiheadAttention(8, 2).to(cuda_device)
-    with pytest.raises(NotImplementedError):
-        mha(a, b, b)
+@pytest.mark.parametrize("dtype,E,H", [(torch.float32, 8, 2), (torch.float32, 96, 3), (torch.bfloat16, 128, 2), (torch.float16, 256, 4)],
+                         ids=str)
+@pytest.mark.parametrize("separate_value", [False, True])
+def test_cross_attention_matches_oracle(native_libs, cuda_device, dtype, E, H, separate_value):
+    """query != key (a DETR-style decoder: a fixed number of object queries per image over a ragged memory,
+    test/test_nested_tensor_functional.py:960-1032), with key == value and with a separate value tensor,
+    against min_mha (nestedtensor/csrc/mha.cpp:18-69) in fp32."""
+    g = torch.Generator().manual_seed(E + int(separate_value))
+    lk = [int(v) for v in torch.randint(1, 150, (9,), generator=g)]
+    lq = [10, 10, 10, 10, 1, 70, 10, 129, 10]
+    qs = [torch.randn(l, E, generator=g).to(dtype) for l in lq]
+    ks = [torch.randn(l, E, generator=g).to(dtype) for l in lk]
+    vs = [torch.randn(l, E, generator=g).to(dtype) for l in lk] if separate_value else ks
+    torch.manual_seed(1)
+    mha = torch.nn.MultiheadAttention(E, H).eval().to(dtype).to(cuda_device)
+    q = nt.nested_tensor(qs, device=cuda_device, dtype=dtype)
+    k = nt.nested_tensor(ks, device=cuda_device, dtype=dtype)
+    v = nt.nested_tensor(vs, device=cuda_device, dtype=dtype) if separate_value else k
+    with torch.no_grad():
+        got, _ = mha(q, k, v, need_weights=False)
+    assert got.nested_size() == q.nested_size()
+    want = ntref.min_mha(H, E // H, qs, ks, vs, mha.in_proj_weight.cpu(), mha.in_proj_bias.cpu(), float(E // H) ** -0.5,
+                         mha.out_proj.weight.cpu(), mha.out_proj.bias.cpu())
+    err = max((a.float().cpu() - b).abs().max().item() for a, b in zip(got.unbind(), want))
+    assert err <= TOL[dtype], err
+
+
+def test_cabi_cross_attention_paths_and_empty_key_sequence(native_libs, cuda_device):
+    """SIMT and mma.sync kernels agree with plain torch; a query whose key sequence is empty gets zeros."""
+    lib = _cabi.load()
+    H, d = 2, 64
+    E = H * d
+    g = torch.Generator().manual_seed(9)
+    lq, lk = [5, 70, 3], [33, 0, 129]
+    q = torch.randn(sum(lq), E, generator=g).to(torch.bfloat16).to(cuda_device)
+    kv = torch.randn(sum(lk), 2 * E, generator=g).to(torch.bfloat16).to(cuda_device)
+    mq = build_meta(torch.tensor([[l, E] for l in lq]), cuda_device)
+    mk = build_meta(torch.tensor([[l, E] for l in lk]), cuda_device)
+    want, oq, ok = [], 0, 0
+    for a, b in zip(lq, lk):
+        qq = q[oq:oq + a].float().reshape(a, H, d).transpose(0, 1) * d ** -0.5
+        kk = kv[ok:ok + b, :E].float().reshape(b, H, d).transpose(0, 1)
+        vv = kv[ok:ok + b, E:].float().reshape(b, H, d).transpose(0, 1)
+        o = torch.softmax(qq @ kk.transpose(1, 2), -1) @ vv if b > 0 else torch.zeros(H, a, d, device=cuda_device)
+        want.append(o.transpose(0, 1).reshape(a, E))
+        oq += a
+        ok += b
+    want = torch.cat(want)
+    for path in (1, 2, 0):
+        out = torch.full((sum(lq), E), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+        rc = lib.ntb200_varlen_cross_attention(q.data_ptr(), E, kv.data_ptr(), 2 * E, kv.data_ptr() + 2 * E, 2 * E, out.data_ptr(),
+                                               mq.data_ptr(), mk.data_ptr(), 3, sum(lq), H, d, max(lq), d ** -0.5, 2, path,
+                                               stream_ptr())
+        _cabi.check("ntb200_varlen_cross_attention", rc)
+        torch.cuda.synchronize()
+        assert (out.float() - want).abs().max().item() <= 2e-2, path
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=str)
