@@ -210,8 +210,8 @@ int ntb200_device_error_flags(void);
  * [total_tokens, H*d] input (B+1 entries, multiples of H*d), max_len the longest sequence.
  * Padded tokens are never materialised.
  *   path       0 = best available: head_dim 64 in fp16/bf16 runs on tcgen05/TMEM fed by TMA when a
- *              workspace is supplied, on an mma.sync flash kernel when it is not, everything else on
- *              a SIMT kernel;  1 = SIMT;  2 = mma.sync kernel;  3 = tcgen05 kernel (for cross-checks)
+ *              workspace is supplied, on an mma.sync flash kernel when it is not (as do head_dim 32
+ *              and 128), everything else on a SIMT kernel;  1 = SIMT;  2 = mma.sync kernel;  3 = tcgen05 kernel (for cross-checks)
  *   workspace  device scratch of ntb200_varlen_attention_workspace_bytes(...) bytes, 16-byte aligned
  *              (holds the device-built list of (sequence, query tile) work items); may be NULL
  * Replaces steps 2-8 of bt_min_mha (nestedtensor/csrc/cuda/mha.cpp:59-105) including
@@ -269,8 +269,8 @@ int ntb200_embedding(const void* weight, const void* index, int index_bytes, voi
  * q / k / v point at head 0 of token 0 of their matrices, ldq / ldk / ldv are the row strides in elements
  * (>= H*d; k and v may be the two halves of one [Tk, 2*H*d] projection output); offsets_q / offsets_k are the
  * B+1 ELEMENT offsets of the sequences in the [tokens, H*d] query and key inputs; out is [q_tokens, H*d].
- * A query whose key sequence is empty gets zeros.  path: 0 = mma.sync flash kernel for head_dim 64 in
- * fp16/bf16 with 16-byte aligned rows, else SIMT;  1 = SIMT;  2 = flash kernel (error if unsupported).
+ * A query whose key sequence is empty gets zeros.  path: 0 = mma.sync flash kernel for head_dim 32 / 64 / 128
+ * in fp16/bf16 with 16-byte aligned rows, else SIMT;  1 = SIMT;  2 = flash kernel (error if unsupported).
  * Replaces the generic per-sequence attention of min_mha (nestedtensor/csrc/mha.cpp:18-69) for query != key,
  * which the reference's CUDA path does not accelerate (nestedtensor/nn/mha.py:57).
  */

@@ -125,8 +125,8 @@ attn_simt_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, 
   }
 }
 
-// ------------------------------------------------------- tensor-core flash kernel, head_dim 64
-constexpr int kBQ = 64, kBKV = 64, kD = 64, kFaThreads = 128;
+// ------------------------------------------------------- tensor-core flash kernel, head_dim 32 / 64 / 128
+constexpr int kBQ = 64, kBKV = 64, kFaThreads = 128;
 
 template <typename T>
 struct MmaOp;
@@ -170,31 +170,40 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// byte offset of 16-byte chunk `c` of row `r` in a [rows][64] two-byte tile (128-byte rows, XOR swizzle)
-__device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+// byte offset of 16-byte chunk `c` of row `r` in a [rows][D] two-byte tile; the chunk index is XOR-swizzled with
+// the row so that the eight rows one ldmatrix phase reads fall into eight different 16-byte bank groups
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  if (D == 32) return (uint32_t)(r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+  if (D == 64) return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
+  return (uint32_t)(r * 256 + ((((c & 7) ^ (r & 7)) | (c & 8)) << 4));
+}
 
-// copy rows [row0, row0+64) (clamped to last_row) x 64 columns of one head from global into a swizzled tile
-template <typename T>
+// copy rows [row0, row0+64) (clamped to last_row) x D columns of one head from global into a swizzled tile
+template <typename T, int D>
 __device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const T* __restrict__ gbase, int64_t ld, int row0,
                                                 int last_row) {
+  constexpr int kChunks = D / 8;  // 16-byte chunks per row
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int idx = threadIdx.x + i * kFaThreads;  // 512 chunks
-    const int r = idx >> 3, c = idx & 7;
+  for (int i = 0; i < (64 * kChunks) / kFaThreads; ++i) {
+    const int idx = threadIdx.x + i * kFaThreads;
+    const int r = idx / kChunks, c = idx % kChunks;
     int gr = row0 + r;
     gr = gr > last_row ? last_row : gr;
-    cp_async_16(smem_tile + tile_off(r, c), gbase + (int64_t)gr * ld + c * 8);
+    cp_async_16(smem_tile + tile_off<D>(r, c), gbase + (int64_t)gr * ld + c * 8);
   }
 }
 
-template <typename T>
+template <typename T, int kD>
 __global__ void __launch_bounds__(kFaThreads)
-attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, int64_t ldk, const T* __restrict__ v,
+attn_fa_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, int64_t ldk, const T* __restrict__ v,
                    int64_t ldv, T* __restrict__ out, const int64_t* __restrict__ offsets_q, const int64_t* __restrict__ offsets_k,
                    int H, float scale_log2e) {  // arguments as in attn_simt_kernel
-  __shared__ __align__(128) uint8_t s_q[kBQ * kD * 2];
-  __shared__ __align__(128) uint8_t s_k[2][kBKV * kD * 2];
-  __shared__ __align__(128) uint8_t s_v[2][kBKV * kD * 2];
+  extern __shared__ __align__(128) uint8_t fa_smem[];  // Q tile, two K tiles, two V tiles of 64 x kD each
+  constexpr uint32_t kTileBytes = kBKV * kD * 2;
+  uint8_t* s_q = fa_smem;
+  uint8_t* s_k = fa_smem + kTileBytes;
+  uint8_t* s_v = fa_smem + 3 * kTileBytes;
 
   const int b = blockIdx.z, h = blockIdx.y;
   const int64_t E = (int64_t)H * kD;
@@ -212,7 +221,6 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
   const uint32_t sq = (uint32_t)__cvta_generic_to_shared(s_q);
   const uint32_t sk = (uint32_t)__cvta_generic_to_shared(s_k);
   const uint32_t sv = (uint32_t)__cvta_generic_to_shared(s_v);
-  constexpr uint32_t kTileBytes = kBKV * kD * 2;
 
   const int n_kv = (L + kBKV - 1) / kBKV;
   if (L <= 0) {  // no keys: the output rows of this tile are zeros
@@ -222,15 +230,16 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
     }
     return;
   }
-  load_tile_async<T>(sq, qbase, ldq, q0, Lq - 1);
-  load_tile_async<T>(sk, kbase, ldk, 0, L - 1);
-  load_tile_async<T>(sv, vbase, ldv, 0, L - 1);
+  load_tile_async<T, kD>(sq, qbase, ldq, q0, Lq - 1);
+  load_tile_async<T, kD>(sk, kbase, ldk, 0, L - 1);
+  load_tile_async<T, kD>(sv, vbase, ldv, 0, L - 1);
   cp_async_commit();
 
-  uint32_t qf[4][4];  // Q fragments: 4 k-steps of 16 head dims
-  float o[8][4];      // O accumulator: 8 n-tiles of 8 head dims
+  constexpr int KS = kD / 16, NO = kD / 8;
+  uint32_t qf[KS][4];  // Q fragments: k-steps of 16 head dims
+  float o[NO][4];      // O accumulator: n-tiles of 8 head dims
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < NO; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // rows g and g+8 of this warp's 16
@@ -238,8 +247,8 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
   for (int it = 0; it < n_kv; ++it) {
     const int buf = it & 1;
     if (it + 1 < n_kv) {
-      load_tile_async<T>(sk + (buf ^ 1) * kTileBytes, kbase, ldk, (it + 1) * kBKV, L - 1);
-      load_tile_async<T>(sv + (buf ^ 1) * kTileBytes, vbase, ldv, (it + 1) * kBKV, L - 1);
+      load_tile_async<T, kD>(sk + (buf ^ 1) * kTileBytes, kbase, ldk, (it + 1) * kBKV, L - 1);
+      load_tile_async<T, kD>(sv + (buf ^ 1) * kTileBytes, vbase, ldv, (it + 1) * kBKV, L - 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -248,8 +257,8 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
     __syncthreads();
     if (it == 0) {
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        ldmatrix_x4(qf[ks], sq + tile_off(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+      for (int ks = 0; ks < KS; ++ks)
+        ldmatrix_x4(qf[ks], sq + tile_off<kD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
     }
     // S = Q K^T for this warp's 16 rows x 64 keys
     float s[8][4];
@@ -259,11 +268,11 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
       for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
     const uint32_t kt = sk + buf * kTileBytes, vt = sv + buf * kTileBytes;
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
+    for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
       for (int np = 0; np < 4; ++np) {  // pairs of key n-tiles
         uint32_t kf[4];
-        ldmatrix_x4(kf, kt + tile_off(np * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
+        ldmatrix_x4(kf, kt + tile_off<kD>(np * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)));
         MmaOp<T>::mma(s[np * 2], qf[ks], kf[0], kf[1]);
         MmaOp<T>::mma(s[np * 2 + 1], qf[ks], kf[2], kf[3]);
       }
@@ -309,7 +318,7 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
     m0 = mn0;
     m1 = mn1;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < NO; ++nt) {
       o[nt][0] *= c0;
       o[nt][1] *= c0;
       o[nt][2] *= c1;
@@ -319,9 +328,9 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {  // pairs of head-dim n-tiles
+      for (int np = 0; np < NO / 2; ++np) {  // pairs of head-dim n-tiles
         uint32_t vf[4];
-        ldmatrix_x4_trans(vf, vt + tile_off(ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
+        ldmatrix_x4_trans(vf, vt + tile_off<kD>(ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), np * 2 + (lane >> 4)));
         MmaOp<T>::mma(o[np * 2], pf[ks], vf[0], vf[1]);
         MmaOp<T>::mma(o[np * 2 + 1], pf[ks], vf[2], vf[3]);
       }
@@ -339,7 +348,7 @@ attn_fa_d64_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k
   uint32_t* obase = reinterpret_cast<uint32_t*>(out + (tok0 + r0) * E + (int64_t)h * kD);
   uint32_t* obase1 = reinterpret_cast<uint32_t*>(out + (tok0 + r1) * E + (int64_t)h * kD);
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt) {
+  for (int nt = 0; nt < NO; ++nt) {
     const int col2 = nt * 4 + (lane & 3);  // index in 32-bit pairs
     if (r0 < Lq) obase[col2] = MmaOp<T>::pack(o[nt][0] * i0, o[nt][1] * i0);
     if (r1 < Lq) obase1[col2] = MmaOp<T>::pack(o[nt][2] * i1, o[nt][3] * i1);
@@ -446,27 +455,46 @@ int launch_attn_simt(const QkvSrc& s, void* out, int64_t batch, int64_t q_tokens
   return status_from_cuda(cudaGetLastError());
 }
 
-template <typename T>
+template <typename T, int D>
 int launch_attn_fa(const QkvSrc& s, void* out, int64_t batch, int H, int64_t max_len_q, float scale, cudaStream_t st) {
+  constexpr int kSmem = 5 * kBKV * D * 2;  // 20 / 40 / 80 KB
+  if (kSmem > 48 * 1024) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return NTB200_LAUNCH_FAILED;
+    if (!configured[dev]) {
+      if (cudaFuncSetAttribute(attn_fa_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+        return NTB200_LAUNCH_FAILED;
+      configured[dev] = true;
+    }
+  }
   dim3 grid((unsigned)ceil_div(max_len_q, kBQ), (unsigned)H, (unsigned)batch);
-  attn_fa_d64_kernel<T><<<grid, kFaThreads, 0, st>>>(static_cast<const T*>(s.q), s.ldq, static_cast<const T*>(s.k), s.ldk,
-                                                     static_cast<const T*>(s.v), s.ldv, static_cast<T*>(out), s.offsets_q,
-                                                     s.offsets_k, H, scale * 1.4426950408889634f);
+  attn_fa_kernel<T, D><<<grid, kFaThreads, kSmem, st>>>(static_cast<const T*>(s.q), s.ldq, static_cast<const T*>(s.k), s.ldk,
+                                                        static_cast<const T*>(s.v), s.ldv, static_cast<T*>(out), s.offsets_q,
+                                                        s.offsets_k, H, scale * 1.4426950408889634f);
   return status_from_cuda(cudaGetLastError());
 }
 
-// The non-tcgen05 kernels behind both entry points: mma.sync flash kernel for head_dim 64 in fp16 / bf16 with
+template <typename T>
+int launch_attn_fa_any(const QkvSrc& s, void* out, int64_t batch, int H, int d, int64_t max_len_q, float scale, cudaStream_t st) {
+  if (d == 32) return launch_attn_fa<T, 32>(s, out, batch, H, max_len_q, scale, st);
+  if (d == 64) return launch_attn_fa<T, 64>(s, out, batch, H, max_len_q, scale, st);
+  return launch_attn_fa<T, 128>(s, out, batch, H, max_len_q, scale, st);
+}
+
+// The non-tcgen05 kernels behind both entry points: mma.sync flash kernel for head_dim 32 / 64 / 128 in fp16 / bf16 with
 // 16-byte aligned rows, SIMT otherwise.  path: 0 best of the two, 1 SIMT, 2 flash (error if unsupported).
 int launch_attn_generic(const QkvSrc& s, void* out, int64_t batch, int64_t q_tokens, int H, int d, int64_t max_len_q,
                         float scaling, int dtype, int path, cudaStream_t st) {
   const size_t es = dtype == NTB200_F32 ? 4 : 2;
   auto rows16 = [&](const void* p, int64_t ld) { return aligned16(p) && (ld * (int64_t)es) % 16 == 0; };
-  const bool fa = path != 1 && dtype != NTB200_F32 && d == kD && rows16(s.q, s.ldq) && rows16(s.k, s.ldk) && rows16(s.v, s.ldv) &&
+  const bool fa = path != 1 && dtype != NTB200_F32 && (d == 32 || d == 64 || d == 128) && rows16(s.q, s.ldq) && rows16(s.k, s.ldk) && rows16(s.v, s.ldv) &&
                   aligned16(out) && batch <= 65535 && H <= 65535 && max_len_q > 0;
   if (path == 2 && !fa) return NTB200_UNSUPPORTED_SHAPE;
   if (fa) {
-    if (dtype == NTB200_F16) return launch_attn_fa<__half>(s, out, batch, H, max_len_q, scaling, st);
-    return launch_attn_fa<__nv_bfloat16>(s, out, batch, H, max_len_q, scaling, st);
+    if (dtype == NTB200_F16) return launch_attn_fa_any<__half>(s, out, batch, H, d, max_len_q, scaling, st);
+    return launch_attn_fa_any<__nv_bfloat16>(s, out, batch, H, d, max_len_q, scaling, st);
   }
   switch (dtype) {
     case NTB200_F32: return launch_attn_simt<float>(s, out, batch, q_tokens, H, d, scaling, st);

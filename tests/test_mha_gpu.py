@@ -106,6 +106,21 @@ def test_varlen_attention_d64(native_libs, cuda_device, dtype):
         assert err <= 2e-2, "%s attention max-abs %g" % (name, err)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+@pytest.mark.parametrize("H,d", [(8, 32), (3, 128), (1, 32)])
+def test_varlen_attention_flash_other_head_dims(native_libs, cuda_device, dtype, H, d):
+    """The mma.sync flash kernel at head_dim 32 and 128 (the default for these sizes), against the SIMT kernel's
+    oracle."""
+    lengths = [1, 63, 64, 65, 130, 200, 7, 16]
+    g = torch.Generator().manual_seed(H * d)
+    qkv = torch.randn(sum(lengths), 3 * H * d, generator=g).to(dtype).to(cuda_device)
+    want = _attention_oracle(qkv, lengths, H, d)
+    for path, name in ((2, "mma.sync"), (1, "SIMT"), (0, "default")):
+        got = _attention(qkv, lengths, H, d, path=path)
+        err = (got.float().cpu() - want).abs().max().item()
+        assert err <= 2e-2, "%s attention max-abs %g" % (name, err)
+
+
 @pytest.mark.parametrize("lengths", [[1], [128], [129], [256, 1, 255], [300, 512, 700, 1024, 33], [16] * 40 + [1000]],
                          ids=lambda l: "L" + "_".join(map(str, l[:5])))
 def test_varlen_attention_tcgen05_lengths(native_libs, cuda_device, lengths):
@@ -221,8 +236,8 @@ def test_stock_module_matches_dense_attention(native_libs, cuda_device):
     assert torch.allclose(got.to_padded_tensor(padding=0), dense, atol=5e-4, rtol=1e-8)
 
 
-@pytest.mark.parametrize("dtype,E,H", [(torch.float32, 8, 2), (torch.float32, 96, 3), (torch.bfloat16, 128, 2), (torch.float16, 256, 4)],
-                         ids=str)
+@pytest.mark.parametrize("dtype,E,H", [(torch.float32, 8, 2), (torch.float32, 96, 3), (torch.bfloat16, 128, 2), (torch.float16, 256, 4),
+                                       (torch.float16, 256, 8), (torch.bfloat16, 256, 2)], ids=str)
 @pytest.mark.parametrize("separate_value", [False, True])
 def test_cross_attention_matches_oracle(native_libs, cuda_device, dtype, E, H, separate_value):
     """query != key (a DETR-style decoder: a fixed number of object queries per image over a ragged memory,
