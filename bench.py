@@ -676,6 +676,18 @@ def run_kernels(args, local):
         fl = 4.0 * E * 100 * float(lk.sum()) + 2.0 * E * E * (2 * 3200 + 2 * float(lk.sum()))
         add("MultiheadAttention(query != key)", "DETR-like 32 x (100 queries, 400-1200 keys), E=%d, %d heads x %d" % (E, H, E // H),
             ms, None, fl)
+    # image-shaped path: 32 fp16 feature maps (256, H_i, W_i), H_i, W_i in [100, 168] (a stride-8 backbone level)
+    hw = torch.randint(100, 169, (32, 2), generator=g)
+    isz = torch.cat([torch.full((32, 1), 256), hw], 1).contiguous()
+    nimg = int((isz[:, 0] * isz[:, 1] * isz[:, 2]).sum())
+    img = nt.NestedTensor(torch.randn(nimg, device=device).to(torch.float16), isz)
+    add("transpose_nchw_nhwc", "32 x (256, 100-168, 100-168) fp16", timed(lambda: nt.nn.transpose_nchw_nhwc(img), n), 4 * nimg)
+    nhwc = nt.nn.transpose_nchw_nhwc(img)
+    add("transpose_nhwc_nchw", "same batch", timed(lambda: nt.nn.transpose_nhwc_nchw(nhwc), n), 4 * nimg)
+    w11 = (torch.randn(256, 256, 1, 1, device=device) * 0.05).to(torch.float16)
+    add("conv2d 1x1 (transpose + packed GEMM + transpose)", "same batch, 256 -> 256 channels",
+        timed(lambda: nt.nn.conv2d(img, w11), n), None, 2.0 * (nimg // 256) * 256 * 256)
+    del img, nhwc
     from nestedtensor_b200 import _cabi
     return {"metric": "per-operator timings", "unit": "ms", "n_gpus": 1, "steps": n, "data": "synthetic",
             "peaks": peaks, "rows": rows, "device_error_flags": _cabi.load().ntb200_device_error_flags()}

@@ -280,6 +280,18 @@ int ntb200_varlen_cross_attention(const void* q, int64_t ldq, const void* k, int
                                   int head_dim, int64_t max_len_q, float scaling, int dtype, int path,
                                   void* stream);
 
+/* ------------------------------------------------------------------ ragged NCHW <-> NHWC
+ * Constituent b (at element offset offsets[b]) is a row-major matrix with one regular extent `regular`
+ * (channels) and one ragged extent n_b = (offsets[b+1] - offsets[b]) / regular (pixels); `out` receives its
+ * transpose at the same offset.  regular_is_rows = 1: [regular x n_b] -> [n_b x regular] (NCHW -> NHWC);
+ * 0: [n_b x regular] -> [regular x n_b] (NHWC -> NCHW).  max_ragged = max n_b (sizes the grid).  in != out.
+ * Replaces transpose_nchw_nhwc_kernelLauncher / transpose_nhwc_nchw_kernelLauncher
+ * (nestedtensor/csrc/cuda/transpose.cu:10-238) and their host-built block tables
+ * (nestedtensor/csrc/transpose.cpp:16-85).
+ */
+int ntb200_transpose_ragged(const void* in, void* out, const int64_t* offsets, int64_t batch, int64_t regular,
+                            int regular_is_rows, int64_t max_ragged, int elem_size, void* stream);
+
 /* ------------------------------------------------------------------ reference-shaped helpers
  * q/k/v_buf[b, h, l, :] = qkv[tok(b,l), {0,E,2E} + h*d + :] + bias  for valid tokens (padded
  * positions are left untouched): bias add fused with packed -> padded head-major scatter.

@@ -44,6 +44,7 @@ SIGNATURES = {
     "ntb200_add_bias_gelu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "ntb200_pack_pointers": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p]),
     "ntb200_embedding": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "ntb200_transpose_ragged": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int, c_void_p]),
     "ntb200_device_error_flags": (c_int, []),
     "ntb200_varlen_attention_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int, c_int]),
     "ntb200_varlen_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int64,

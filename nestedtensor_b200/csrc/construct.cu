@@ -165,3 +165,84 @@ int ntb200_embedding(const void* weight, const void* index, int index_bytes, voi
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------- ragged 2-D transposes (NCHW <-> NHWC)
+// Constituent b is a row-major [rows_b x cols_b] matrix with one regular extent R and one ragged extent n_b
+// (channels x pixels or pixels x channels); the output holds its transpose at the same element offset.
+// Replaces transpose_nchw_nhwc / transpose_nhwc_nchw (nestedtensor/csrc/cuda/transpose.cu:10-238,
+// nestedtensor/csrc/transpose.cpp:87-202) without their host-built block-offset tables: the grid is
+// (tiles of the largest constituent, batch) and blocks past a constituent's last tile exit.
+namespace ntb200 {
+namespace {
+
+constexpr int kTrTile = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+transpose_ragged_kernel(const T* __restrict__ in, T* __restrict__ out, const int64_t* __restrict__ offsets, int64_t regular,
+                        int regular_is_rows) {
+  __shared__ T tile[kTrTile][kTrTile + 1];
+  const int64_t b = blockIdx.y;
+  const int64_t off = offsets[b];
+  const int64_t n = (offsets[b + 1] - off) / regular;  // ragged extent
+  const int64_t rows = regular_is_rows ? regular : n, cols = regular_is_rows ? n : regular;
+  const int64_t tiles_reg = (regular + kTrTile - 1) / kTrTile;
+  const int64_t t_rag = blockIdx.x / tiles_reg, t_reg = blockIdx.x % tiles_reg;
+  if (t_rag * kTrTile >= n) return;
+  const int64_t r0 = (regular_is_rows ? t_reg : t_rag) * kTrTile, c0 = (regular_is_rows ? t_rag : t_reg) * kTrTile;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const T* src = in + off;
+  T* dst = out + off;
+#pragma unroll
+  for (int i = 0; i < kTrTile; i += 8) {
+    const int64_t r = r0 + ty + i;
+#pragma unroll
+    for (int j = 0; j < kTrTile; j += 32) {
+      const int64_t c = c0 + tx + j;
+      if (r < rows && c < cols) tile[ty + i][tx + j] = src[r * cols + c];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kTrTile; i += 8) {
+    const int64_t c = c0 + ty + i;  // output row
+#pragma unroll
+    for (int j = 0; j < kTrTile; j += 32) {
+      const int64_t r = r0 + tx + j;  // output column
+      if (r < rows && c < cols) dst[c * rows + r] = tile[tx + j][ty + i];
+    }
+  }
+}
+
+template <typename T>
+int launch_transpose_ragged(const void* in, void* out, const int64_t* offsets, int64_t batch, int64_t regular,
+                            int regular_is_rows, int64_t max_ragged, cudaStream_t st) {
+  const int64_t tiles = ((regular + kTrTile - 1) / kTrTile) * ((max_ragged + kTrTile - 1) / kTrTile);
+  if (tiles > 0x7fffffff) return NTB200_UNSUPPORTED_SHAPE;
+  for (int64_t b0 = 0; b0 < batch; b0 += 65535) {  // gridDim.y limit
+    const int64_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
+    dim3 grid((unsigned)tiles, (unsigned)nb);
+    transpose_ragged_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular,
+                                                     regular_is_rows);
+  }
+  return status_from_cuda(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace ntb200
+
+extern "C" int ntb200_transpose_ragged(const void* in, void* out, const int64_t* offsets, int64_t batch, int64_t regular,
+                                       int regular_is_rows, int64_t max_ragged, int elem_size, void* stream) {
+  using namespace ntb200;
+  if (batch < 0 || regular < 0 || max_ragged < 0) return NTB200_INVALID_ARG;
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return NTB200_UNSUPPORTED_DTYPE;
+  if (batch == 0 || regular == 0 || max_ragged == 0) return NTB200_OK;
+  if (in == nullptr || out == nullptr || offsets == nullptr || in == out) return NTB200_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (elem_size) {
+    case 1: return launch_transpose_ragged<uint8_t>(in, out, offsets, batch, regular, regular_is_rows, max_ragged, st);
+    case 2: return launch_transpose_ragged<uint16_t>(in, out, offsets, batch, regular, regular_is_rows, max_ragged, st);
+    case 4: return launch_transpose_ragged<uint32_t>(in, out, offsets, batch, regular, regular_is_rows, max_ragged, st);
+    default: return launch_transpose_ragged<uint64_t>(in, out, offsets, batch, regular, regular_is_rows, max_ragged, st);
+  }
+}

@@ -14,6 +14,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <algorithm>
 #include <cstring>
 #include <tuple>
 #include <vector>
@@ -741,6 +742,37 @@ Tensor embedding(const Tensor& weight, const Tensor& index_buffer, const Tensor&
   return out;
 }
 
+// ------------------------------------------------------------------ ragged NCHW <-> NHWC
+// nestedtensor/csrc/transpose.cpp:124-150 and :186-202 on the record: (C, H_i, W_i) -> (H_i, W_i, C) and back.
+Tensor transpose_images(const Tensor& buffer, const Tensor& sizes, const Tensor& meta, bool to_nhwc) {
+  Record r = make_record(sizes, meta);
+  const char* name = to_nhwc ? "transpose_nchw_nhwc" : "transpose_nhwc_nchw";
+  TORCH_CHECK(r.tdim == 3, name, " needs 4d input.");
+  const int64_t cdim = to_nhwc ? 0 : 2;
+  TORCH_CHECK(r.B == 0 || r.regular[cdim], to_nhwc ? "Expected first dimension to be regular." : "Expected last dimension to be regular.");
+  check_buffer(buffer, r, name);
+  Tensor out = at::empty_like(buffer);
+  if (buffer.numel() == 0) return out;
+  const int64_t C = r.max_sizes[cdim];
+  int64_t max_pixels = 0;
+  for (int64_t b = 0; b < r.B; ++b) {
+    const int64_t* s = r.sz + b * 3;
+    const int64_t px = to_nhwc ? s[1] * s[2] : s[0] * s[1];
+    max_pixels = std::max(max_pixels, px);
+  }
+  c10::cuda::CUDAGuard guard(buffer.device());
+  check_rc(ntb200_transpose_ragged(buffer.data_ptr(), out.data_ptr(), r.d_offsets, r.B, C, to_nhwc ? 1 : 0, max_pixels,
+                                   (int)buffer.element_size(), cur_stream()),
+           "ntb200_transpose_ragged");
+  return out;
+}
+Tensor transpose_nchw_nhwc(const Tensor& buffer, const Tensor& sizes, const Tensor& meta) {
+  return transpose_images(buffer, sizes, meta, true);
+}
+Tensor transpose_nhwc_nchw(const Tensor& buffer, const Tensor& sizes, const Tensor& meta) {
+  return transpose_images(buffer, sizes, meta, false);
+}
+
 }  // namespace
 
 // The operator names follow the reference's `nestedtensor` namespace
@@ -776,6 +808,8 @@ TORCH_LIBRARY(nestedtensor, m) {
         &add_bias_residual_layer_norm);
   m.def("packed_linear(Tensor x, Tensor weight, Tensor? bias, int act, Tensor? residual) -> Tensor", &packed_linear);
   m.def("add_bias_gelu(Tensor x, Tensor? bias) -> Tensor", &add_bias_gelu);
+  m.def("transpose_nchw_nhwc(Tensor buffer, Tensor sizes, Tensor meta) -> Tensor", &transpose_nchw_nhwc);
+  m.def("transpose_nhwc_nchw(Tensor buffer, Tensor sizes, Tensor meta) -> Tensor", &transpose_nhwc_nchw);
   m.def("pack_list(Tensor[] tensors) -> (Tensor, Tensor, Tensor)", &pack_list);
   m.def("embedding(Tensor weight, Tensor index_buffer, Tensor sizes, Tensor meta) -> Tensor", &embedding);
 }

@@ -214,6 +214,12 @@ class NestedTensor(object):
         if func is torch.nn.functional.multi_head_attention_forward:
             from .nn import multi_head_attention_forward
             return multi_head_attention_forward(*args, **kwargs)
+        if func is torch.nn.functional.conv2d or func is torch.conv2d:
+            from .nn import conv2d
+            return conv2d(*args, **kwargs)
+        if func is torch.nn.functional.max_pool2d or func is torch.max_pool2d:
+            from .nn import max_pool2d
+            return max_pool2d(*args, **kwargs)
         if func is torch.nn.functional.embedding:
             from .nn import embedding
             return embedding(*args, **kwargs)
@@ -272,7 +278,19 @@ def _op_bt_min_mha(num_heads, head_dim, dropout_p, training, query, key, value, 
                           scaling, out_proj_weight, out_proj_bias)
 
 
+def _op_transpose_nchw_nhwc(nt):
+    from .nn import transpose_nchw_nhwc
+    return transpose_nchw_nhwc(nt)
+
+
+def _op_transpose_nhwc_nchw(nt):
+    from .nn import transpose_nhwc_nchw
+    return transpose_nhwc_nchw(nt)
+
+
 _RECORD_OPS = {
+    "transpose_nchw_nhwc": _op_transpose_nchw_nhwc,
+    "transpose_nhwc_nchw": _op_transpose_nhwc_nchw,
     "to_padded_tensor": _op_to_padded_tensor,
     "to_tensor_mask": _op_to_tensor_mask,
     "to_mask": _op_to_mask,

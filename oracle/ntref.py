@@ -400,3 +400,25 @@ def embedding(indices: NTList, weight: torch.Tensor) -> NTList:
     """nestedtensor/csrc/functions.cpp:57-63 (``at::embedding`` mapped over the constituents; the packed fast
     path :29-56 is the same gather on the concatenated indices)."""
     return [F.embedding(i.long(), weight) for i in indices]
+
+
+# ---------------------------------------------------------------- image-shaped nested tensors
+def transpose_nchw_nhwc(tensors: NTList) -> NTList:
+    """nestedtensor/csrc/transpose.cpp:124-150: each (C, H, W) constituent as (H, W, C)."""
+    return [t.permute(1, 2, 0).contiguous() for t in tensors]
+
+
+def transpose_nhwc_nchw(tensors: NTList) -> NTList:
+    """nestedtensor/csrc/transpose.cpp:186-202: each (H, W, C) constituent as (C, H, W)."""
+    return [t.permute(2, 0, 1).contiguous() for t in tensors]
+
+
+def conv2d(tensors: NTList, weight, bias=None, stride=1, padding=0, dilation=1, groups=1) -> NTList:
+    """nestedtensor/csrc/conv2d.cpp:91-105: ``at::conv2d`` on each constituent, in fp32."""
+    b = None if bias is None else bias.float()
+    return [F.conv2d(t.float().unsqueeze(0), weight.float(), b, stride, padding, dilation, groups).squeeze(0) for t in tensors]
+
+
+def max_pool2d(tensors: NTList, kernel_size, stride=None, padding=0, dilation=1) -> NTList:
+    """nestedtensor/csrc/pooling.cpp:58-70: ``at::max_pool2d`` on each constituent."""
+    return [F.max_pool2d(t.unsqueeze(0), kernel_size, stride, padding, dilation, False).squeeze(0) for t in tensors]
