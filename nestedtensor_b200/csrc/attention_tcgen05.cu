@@ -389,26 +389,25 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       if (pend.warp_active) {
         const uint32_t stage = s_v + pend.vstage * kTile;
         {
-          uint32_t r0[32], r1[32];
-          ptx::tmem_ld_32x32b_x32(t_o, r0);
-          ptx::tmem_ld_32x32b_x32(t_o + 32, r1);
-          ptx::tmem_ld_wait();
           const float inv = pend.inv;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint32_t a0 = stage + row * 128 + ((c ^ (row & 7)) << 4);
-            const uint32_t a1 = stage + row * 128 + (((c + 4) ^ (row & 7)) << 4);
+          for (int c = 0; c < 4; ++c) {  // 16 columns at a time: few registers, so this can run while an S row is live
+            uint32_t r0[16];
+            ptx::tmem_ld_32x32b_x16(t_o + c * 16, r0);
+            ptx::tmem_ld_wait();
+            const uint32_t a0 = stage + row * 128 + (((2 * c) ^ (row & 7)) << 4);
+            const uint32_t a1 = stage + row * 128 + (((2 * c + 1) ^ (row & 7)) << 4);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a0),
-                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 0]) * inv, __uint_as_float(r0[c * 8 + 1]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 2]) * inv, __uint_as_float(r0[c * 8 + 3]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 4]) * inv, __uint_as_float(r0[c * 8 + 5]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[c * 8 + 6]) * inv, __uint_as_float(r0[c * 8 + 7]) * inv))
+                         "r"(pack2<FMT>(__uint_as_float(r0[0]) * inv, __uint_as_float(r0[1]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[2]) * inv, __uint_as_float(r0[3]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[4]) * inv, __uint_as_float(r0[5]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[6]) * inv, __uint_as_float(r0[7]) * inv))
                          : "memory");
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a1),
-                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 0]) * inv, __uint_as_float(r1[c * 8 + 1]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 2]) * inv, __uint_as_float(r1[c * 8 + 3]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 4]) * inv, __uint_as_float(r1[c * 8 + 5]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r1[c * 8 + 6]) * inv, __uint_as_float(r1[c * 8 + 7]) * inv))
+                         "r"(pack2<FMT>(__uint_as_float(r0[8]) * inv, __uint_as_float(r0[9]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[10]) * inv, __uint_as_float(r0[11]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[12]) * inv, __uint_as_float(r0[13]) * inv)),
+                         "r"(pack2<FMT>(__uint_as_float(r0[14]) * inv, __uint_as_float(r0[15]) * inv))
                          : "memory");
           }
         }
@@ -493,6 +492,14 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         if (threadIdx.x == 0) NTB200_TRACE(g, 9);
         // PV of the previous block must have retired before P is overwritten / O is rescaled
         if (ok && g > 0 && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
+        if (ok && j == 0 && pend.any) {
+          // Output of the previous item, written while this item's first block is already in flight: its last
+          // PV retired during the work above, and this item's first PV (which overwrites O) cannot be issued
+          // before these warps arrive at p_ready below.
+          ptx::tc_fence_after_sync();
+          pend.vstage = (g - 1) % kStages;
+          write_pending();
+        }
         if (ok && warp_active) {
           ptx::tc_fence_after_sync();
           if (j > 0 && any_up) {
@@ -558,16 +565,18 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           if (j + 1 < it.n_blk) ptx::mbar_arrive(ptx::smem_u32(&ctrl->empty_v[g % kStages]));
         }
       }
-      // output of this item: wait for its last PV, then write through the staging buffer
+      // the output of this item is written during the next item's first block (or after the loop)
       pend.any = true;
       pend.warp_active = warp_active;
       pend.inv = 1.0f / l;
       pend.rows = it.L - it.q0 < kQT ? it.L - it.q0 : kQT;
       pend.out_row0 = ((int64_t)it.tok0 + it.q0) * E + (int64_t)it.h * kHD;
-      pend.vstage = (g - 1) % kStages;
-      if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
+    }
+    if (ok && pend.any) {  // the last item of this CTA
+      if (!wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
       if (ok) {
         ptx::tc_fence_after_sync();
+        pend.vstage = (g - 1) % kStages;
         write_pending();
       }
     }
