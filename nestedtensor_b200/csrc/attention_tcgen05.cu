@@ -148,6 +148,11 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
 // (s_free), before PV of block g: the tensor pipe works under the softmax of the same CTA.
 // Two 256-thread CTAs per SM at 128 registers per thread; the control warpgroup then drops to 48 and the
 // softmax warpgroup rises to 208.
+// The output of an item is written during the FIRST block of the next item (after that block's row maximum,
+// 16 columns at a time so that it fits beside the live S row): its last PV retires while the next S is loaded
+// and reduced, instead of being waited for.  The softmax warps sit at their register budget; this only pays
+// because the write needs about 30 registers (it spilled, and lost 20 %, before the row sums were cut to two
+// packed accumulators).
 template <int FMT>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restrict__ out, const int64_t* __restrict__ offsets,
