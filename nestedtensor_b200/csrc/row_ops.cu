@@ -15,6 +15,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace ntb200 {
 namespace {
@@ -85,6 +86,24 @@ struct Vec16<NTB200_BF16> {
   }
 };
 
+// The same 16 bytes as kElems / 2 packed fp32 pairs (sm_100 adds, subtracts and multiplies two fp32 values
+// held in a 64-bit register pair with one instruction: the LayerNorm kernel is otherwise bound by its issue
+// slots, not by memory).
+template <int DT>
+__device__ __forceinline__ void unpack_pairs(const uint4& r, uint64_t* p) {
+  float f[Vec16<DT>::kElems];
+  Vec16<DT>::unpack(r, f);
+#pragma unroll
+  for (int k = 0; k < Vec16<DT>::kElems / 2; ++k) p[k] = ptx::f32x2_pack(f[2 * k], f[2 * k + 1]);
+}
+template <int DT>
+__device__ __forceinline__ uint4 pack_pairs(const uint64_t* p) {
+  float f[Vec16<DT>::kElems];
+#pragma unroll
+  for (int k = 0; k < Vec16<DT>::kElems / 2; ++k) ptx::f32x2_unpack(p[k], f[2 * k], f[2 * k + 1]);
+  return Vec16<DT>::pack(f);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -124,62 +143,69 @@ layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* 
   const int nv = cols / EPV;
   const uint4* xr = reinterpret_cast<const uint4*>(x) + row * nv;
   const uint4* rr = reinterpret_cast<const uint4*>(residual) + row * nv;
-  float v[VPL][EPV];
-  float sum = 0.0f;
+  constexpr int PPV = EPV / 2;  // packed pairs per vector
+  uint64_t v[VPL][PPV];
+  uint64_t sum2 = 0;
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     const int vec = t + j * GROUP;
     if (vec < nv) {
-      Vec16<DT>::unpack(xr[vec], v[j]);
+      unpack_pairs<DT>(xr[vec], v[j]);
       if (FUSED) {
-        float a[EPV];
+        uint64_t a[PPV];
         if (residual != nullptr) {
-          Vec16<DT>::unpack(rr[vec], a);
+          unpack_pairs<DT>(rr[vec], a);
 #pragma unroll
-          for (int k = 0; k < EPV; ++k) v[j][k] += a[k];
+          for (int k = 0; k < PPV; ++k) v[j][k] = ptx::f32x2_add(v[j][k], a[k]);
         }
         if (bias != nullptr) {
-          Vec16<DT>::unpack(reinterpret_cast<const uint4*>(bias)[vec], a);
+          unpack_pairs<DT>(reinterpret_cast<const uint4*>(bias)[vec], a);
 #pragma unroll
-          for (int k = 0; k < EPV; ++k) v[j][k] += a[k];
+          for (int k = 0; k < PPV; ++k) v[j][k] = ptx::f32x2_add(v[j][k], a[k]);
         }
       }
 #pragma unroll
-      for (int k = 0; k < EPV; ++k) sum += v[j][k];
+      for (int k = 0; k < PPV; ++k) sum2 = ptx::f32x2_add(sum2, v[j][k]);
     } else {
 #pragma unroll
-      for (int k = 0; k < EPV; ++k) v[j][k] = 0.0f;
+      for (int k = 0; k < PPV; ++k) v[j][k] = 0;
     }
   }
-  const float mean = group_sum<GROUP>(sum, scratch) / (float)cols;
-  float sq = 0.0f;
+  float s_lo, s_hi;
+  ptx::f32x2_unpack(sum2, s_lo, s_hi);
+  const float mean = group_sum<GROUP>(s_lo + s_hi, scratch) / (float)cols;
+  const uint64_t mean2 = ptx::f32x2_pack(mean, mean);
+  uint64_t sq2 = 0;
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     if (t + j * GROUP < nv) {
 #pragma unroll
-      for (int k = 0; k < EPV; ++k) {
-        const float d = v[j][k] - mean;
-        sq += d * d;
+      for (int k = 0; k < PPV; ++k) {
+        v[j][k] = ptx::f32x2_sub(v[j][k], mean2);  // deviations replace the values
+        sq2 = ptx::f32x2_fma(v[j][k], v[j][k], sq2);
       }
     }
   }
-  const float rstd = rsqrtf(group_sum<GROUP>(sq, scratch) / (float)cols + eps);
+  ptx::f32x2_unpack(sq2, s_lo, s_hi);
+  const float rstd = rsqrtf(group_sum<GROUP>(s_lo + s_hi, scratch) / (float)cols + eps);
+  const uint64_t rstd2 = ptx::f32x2_pack(rstd, rstd);
   uint4* orow = reinterpret_cast<uint4*>(out) + row * nv;
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     const int vec = t + j * GROUP;
     if (vec < nv) {
-      float g[EPV], b[EPV], o[EPV];
+      uint64_t o[PPV];
       if (gamma != nullptr) {
-        Vec16<DT>::unpack(reinterpret_cast<const uint4*>(gamma)[vec], g);
-        Vec16<DT>::unpack(reinterpret_cast<const uint4*>(beta)[vec], b);
+        uint64_t g[PPV], b[PPV];
+        unpack_pairs<DT>(reinterpret_cast<const uint4*>(gamma)[vec], g);
+        unpack_pairs<DT>(reinterpret_cast<const uint4*>(beta)[vec], b);
 #pragma unroll
-        for (int k = 0; k < EPV; ++k) o[k] = (v[j][k] - mean) * rstd * g[k] + b[k];
+        for (int k = 0; k < PPV; ++k) o[k] = ptx::f32x2_fma(ptx::f32x2_fma(v[j][k], rstd2, 0ull), g[k], b[k]);
       } else {
 #pragma unroll
-        for (int k = 0; k < EPV; ++k) o[k] = (v[j][k] - mean) * rstd;
+        for (int k = 0; k < PPV; ++k) o[k] = ptx::f32x2_fma(v[j][k], rstd2, 0ull);
       }
-      orow[vec] = Vec16<DT>::pack(o);
+      orow[vec] = pack_pairs<DT>(o);
     }
   }
 }
