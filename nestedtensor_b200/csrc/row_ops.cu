@@ -129,7 +129,7 @@ constexpr int kLnThreads = 256;
 // write per element).  VPL = 16-byte vectors per thread; vector v of the row belongs to thread v % GROUP.
 // Mean and variance are the two-pass forms of the reference kernel (sum, then sum of squared deviations).
 template <int DT, int VPL, int GROUP, bool FUSED>
-__global__ void __launch_bounds__(kLnThreads, VPL <= 2 ? 6 : (VPL == 4 ? 5 : 2))  // caps registers so that 6 / 5 / 2 CTAs fit an SM
+__global__ void __launch_bounds__(kLnThreads)
 layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* __restrict__ bias,
                   const void* __restrict__ gamma, const void* __restrict__ beta, float eps, void* out, int64_t rows,
                   int cols) {  // out may alias x: a thread has read all it needs of the row before it writes
