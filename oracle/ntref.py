@@ -16,7 +16,12 @@ input/output tensors of the reference's own tests
 (test/test_nested_tensor_masking.py) against these functions, and checks
 ``min_mha`` against stock ``torch.nn.functional.multi_head_attention_forward``
 with ``key_padding_mask`` exactly as test/test_nested_tensor_functional.py:648-667
-and :1040-1161 do.
+and :1040-1161 do.  The functions added for the rows around the core path are
+pinned the same way: ``layer_norm`` against ``torch.nn.LayerNorm`` applied to each
+constituent (the reference's own check, test/test_nested_tensor_functional.py:895-957),
+``encoder_layer`` against stock ``torch.nn.TransformerEncoderLayer`` evaluated per
+sequence, ``embedding`` / ``conv2d`` / ``max_pool2d`` / the NCHW<->NHWC transposes are
+the per-constituent ATen calls of the reference's generic branches themselves.
 
 Deliberate differences from the reference (its defects are not reproduced):
   * a scalar constituent is appended twice by the reference's CPU
