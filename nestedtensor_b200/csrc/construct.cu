@@ -218,12 +218,14 @@ transpose_ragged_kernel(const T* __restrict__ in, T* __restrict__ out, const int
 // a multiple of 16, always so for fp16 / bf16 feature maps with C % 8 == 0): the side on which the regular
 // extent is contiguous moves 16 bytes per thread, the ragged side (rows of n_b elements at any phase) stays
 // element-wise but coalesced.
+constexpr int kTrRag = 128;  // ragged-extent tile of the vector kernel (more bytes in flight per CTA)
+
 template <typename T, bool REG_IS_ROWS>
 __global__ void __launch_bounds__(256)
 transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const int64_t* __restrict__ offsets, int64_t regular) {
   constexpr int VE = 16 / (int)sizeof(T);        // elements per vector
   constexpr int kVecPerRow = kTrTile / VE;       // vectors covering the tile's regular extent
-  __shared__ T tile[kTrTile][kTrTile + 1];       // [regular][ragged]
+  __shared__ T tile[kTrTile][kTrRag + 2];        // [regular][ragged]
   union Vec {
     uint4 v;
     T e[VE];
@@ -233,20 +235,20 @@ transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const
   const int64_t n = (offsets[b + 1] - off) / regular;
   const int64_t tiles_reg = (regular + kTrTile - 1) / kTrTile;
   const int64_t t_rag = blockIdx.x / tiles_reg, t_reg = blockIdx.x % tiles_reg;
-  if (t_rag * kTrTile >= n) return;
-  const int64_t p0 = t_rag * kTrTile, c0 = t_reg * kTrTile;
+  if (t_rag * kTrRag >= n) return;
+  const int64_t p0 = t_rag * kTrRag, c0 = t_reg * kTrTile;
   const T* src = in + off;
   T* dst = out + off;
-  const int px_l = threadIdx.x & 63, cy = threadIdx.x >> 6;  // element-wise side: 64 ragged positions x 4 regular
+  const int px_l = threadIdx.x & (kTrRag - 1), cy = threadIdx.x / kTrRag;  // element-wise side: 128 ragged x 2 regular
   if (REG_IS_ROWS) {  // in [regular][n] -> out [n][regular]
 #pragma unroll
-    for (int i = 0; i < kTrTile; i += 4) {
+    for (int i = 0; i < kTrTile; i += 256 / kTrRag) {
       const int64_t c = c0 + cy + i, px = p0 + px_l;
       if (c < regular && px < n) tile[cy + i][px_l] = src[c * n + px];
     }
   } else {  // in [n][regular] -> out [regular][n]
 #pragma unroll
-    for (int k = 0; k < (kTrTile * kVecPerRow) / 256; ++k) {
+    for (int k = 0; k < (kTrRag * kVecPerRow) / 256; ++k) {
       const int idx = k * 256 + threadIdx.x;
       const int pl = idx / kVecPerRow, cl = (idx % kVecPerRow) * VE;
       const int64_t px = p0 + pl, c = c0 + cl;
@@ -261,7 +263,7 @@ transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const
   __syncthreads();
   if (REG_IS_ROWS) {
 #pragma unroll
-    for (int k = 0; k < (kTrTile * kVecPerRow) / 256; ++k) {
+    for (int k = 0; k < (kTrRag * kVecPerRow) / 256; ++k) {
       const int idx = k * 256 + threadIdx.x;
       const int pl = idx / kVecPerRow, cl = (idx % kVecPerRow) * VE;
       const int64_t px = p0 + pl, c = c0 + cl;
@@ -274,7 +276,7 @@ transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < kTrTile; i += 4) {
+    for (int i = 0; i < kTrTile; i += 256 / kTrRag) {
       const int64_t c = c0 + cy + i, px = p0 + px_l;
       if (c < regular && px < n) dst[c * n + px] = tile[cy + i][px_l];
     }
@@ -284,19 +286,26 @@ transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const
 template <typename T>
 int launch_transpose_ragged(const void* in, void* out, const int64_t* offsets, int64_t batch, int64_t regular,
                             int regular_is_rows, int64_t max_ragged, cudaStream_t st) {
-  const int64_t tiles = ((regular + kTrTile - 1) / kTrTile) * ((max_ragged + kTrTile - 1) / kTrTile);
+  const bool vec = sizeof(T) < 8 && (regular * (int64_t)sizeof(T)) % 16 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const int64_t rag_tile = vec ? kTrRag : kTrTile;
+  const int64_t tiles = ((regular + kTrTile - 1) / kTrTile) * ((max_ragged + rag_tile - 1) / rag_tile);
   if (tiles > 0x7fffffff) return NTB200_UNSUPPORTED_SHAPE;
   for (int64_t b0 = 0; b0 < batch; b0 += 65535) {  // gridDim.y limit
     const int64_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
     dim3 grid((unsigned)tiles, (unsigned)nb);
-    const bool vec = sizeof(T) < 8 && (regular * (int64_t)sizeof(T)) % 16 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-    if (vec && regular_is_rows)
-      transpose_ragged_vec_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular);
-    else if (vec)
-      transpose_ragged_vec_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular);
-    else
-      transpose_ragged_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular,
-                                                       regular_is_rows);
+    if constexpr (sizeof(T) < 8) {
+      if (vec && regular_is_rows) {
+        transpose_ragged_vec_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular);
+        continue;
+      }
+      if (vec) {
+        transpose_ragged_vec_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular);
+        continue;
+      }
+    }
+    transpose_ragged_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular,
+                                                     regular_is_rows);
   }
   return status_from_cuda(cudaGetLastError());
 }
