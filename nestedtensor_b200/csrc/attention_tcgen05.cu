@@ -59,7 +59,7 @@ struct Ctrl {
   uint64_t full_k[kStages];   // K tile (plus Q with the first block of an item) landed
   uint64_t empty_k[kStages];  // QK^T of that stage retired: K (and the Q buffer two items back) reusable
   uint64_t full_v[kStages];
-  uint64_t empty_v[kStages];  // PV of that stage retired and the softmax warps are done with it (output staging)
+  uint64_t empty_v[kStages];  // PV of that stage retired (and the softmax warps have stored its P)
   uint64_t s_ready;
   uint64_t s_free;
   uint64_t p_ready;
@@ -379,59 +379,39 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
     bool ok = true;
     uint32_t g = 0;
 
-    // The output rows of an item go through the V stage that its last PV just released (128 rows x 128
-    // bytes, XOR-swizzled) so that every global store instruction writes four full 128-byte rows instead of
-    // 32 scattered 16-byte pieces; the stage is handed back to the producer afterwards.
+    // State of the item whose output is still to be written (by write_pending, during the next item).
     struct Pending {
       bool any;          // an item is waiting for its output
       bool warp_active;  // this warp owns valid rows of it
       float inv;         // 1 / softmax denominator of this thread's row
       int rows;          // valid rows in the tile
       int64_t out_row0;  // element offset of (first token of the tile, head) in the output
-      uint32_t vstage;   // V stage to hand back to the producer afterwards
-    } pend = {false, false, 0.0f, 0, 0, 0};
+    } pend = {false, false, 0.0f, 0, 0};
     auto write_pending = [&]() {
+      // each thread normalises its own row and stores it 32 bytes (one full sector) at a time, 16 accumulator
+      // columns per step so that it fits beside a live S row
       if (pend.warp_active) {
-        const uint32_t stage = s_v + pend.vstage * kTile;
-        {
-          const float inv = pend.inv;
+        const bool live = row < pend.rows;  // (the tensor-memory loads are warp-wide: only the store is per row)
+        const float inv = pend.inv;
+        uint16_t* orow = reinterpret_cast<uint16_t*>(out) + pend.out_row0 + (int64_t)row * E;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {  // 16 columns at a time: few registers, so this can run while an S row is live
-            uint32_t r0[16];
-            ptx::tmem_ld_32x32b_x16(t_o + c * 16, r0);
-            ptx::tmem_ld_wait();
-            const uint32_t a0 = stage + row * 128 + (((2 * c) ^ (row & 7)) << 4);
-            const uint32_t a1 = stage + row * 128 + (((2 * c + 1) ^ (row & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a0),
-                         "r"(pack2<FMT>(__uint_as_float(r0[0]) * inv, __uint_as_float(r0[1]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[2]) * inv, __uint_as_float(r0[3]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[4]) * inv, __uint_as_float(r0[5]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[6]) * inv, __uint_as_float(r0[7]) * inv))
-                         : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a1),
-                         "r"(pack2<FMT>(__uint_as_float(r0[8]) * inv, __uint_as_float(r0[9]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[10]) * inv, __uint_as_float(r0[11]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[12]) * inv, __uint_as_float(r0[13]) * inv)),
-                         "r"(pack2<FMT>(__uint_as_float(r0[14]) * inv, __uint_as_float(r0[15]) * inv))
-                         : "memory");
-          }
-        }
-        __syncwarp();  // a warp reads back only the 32 rows it wrote itself
-        uint16_t* obase = reinterpret_cast<uint16_t*>(out) + pend.out_row0;
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const int rr = q * 32 + 4 * jj + (lane >> 3), cc = lane & 7;
-          uint4 v;
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                       : "r"(stage + rr * 128 + ((cc ^ (rr & 7)) << 4))
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r0[16];
+          ptx::tmem_ld_32x32b_x16(t_o + c * 16, r0);
+          ptx::tmem_ld_wait();
+          if (live)
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + c * 16),
+                       "r"(pack2<FMT>(__uint_as_float(r0[0]) * inv, __uint_as_float(r0[1]) * inv)),
+                       "r"(pack2<FMT>(__uint_as_float(r0[2]) * inv, __uint_as_float(r0[3]) * inv)),
+                       "r"(pack2<FMT>(__uint_as_float(r0[4]) * inv, __uint_as_float(r0[5]) * inv)),
+                       "r"(pack2<FMT>(__uint_as_float(r0[6]) * inv, __uint_as_float(r0[7]) * inv)),
+                       "r"(pack2<FMT>(__uint_as_float(r0[8]) * inv, __uint_as_float(r0[9]) * inv)),
+                       "r"(pack2<FMT>(__uint_as_float(r0[10]) * inv, __uint_as_float(r0[11]) * inv)),
+                       "r"(pack2<FMT>(__uint_as_float(r0[12]) * inv, __uint_as_float(r0[13]) * inv)),
+                       "r"(pack2<FMT>(__uint_as_float(r0[14]) * inv, __uint_as_float(r0[15]) * inv))
                        : "memory");
-          if (rr < pend.rows) *reinterpret_cast<uint4*>(obase + (int64_t)rr * E + cc * 8) = v;
         }
-        ptx::fence_proxy_async();  // the stage is refilled by TMA (async proxy) after this
       }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->empty_v[pend.vstage]));
       pend.any = false;
     };
     int4 rec = fetch(first);
@@ -502,7 +482,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           // PV retired during the work above, and this item's first PV (which overwrites O) cannot be issued
           // before these warps arrive at p_ready below.
           ptx::tc_fence_after_sync();
-          pend.vstage = (g - 1) % kStages;
           write_pending();
         }
         if (ok && warp_active) {
@@ -566,8 +545,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         __syncwarp();
         if (lane == 0) {
           ptx::mbar_arrive(ptx::smem_u32(&ctrl->p_ready));
-          // the V stage of the item's last block doubles as the output staging buffer and is released later
-          if (j + 1 < it.n_blk) ptx::mbar_arrive(ptx::smem_u32(&ctrl->empty_v[g % kStages]));
+          ptx::mbar_arrive(ptx::smem_u32(&ctrl->empty_v[g % kStages]));
         }
       }
       // the output of this item is written during the next item's first block (or after the loop)
@@ -581,7 +559,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       if (!wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
       if (ok) {
         ptx::tc_fence_after_sync();
-        pend.vstage = (g - 1) % kStages;
         write_pending();
       }
     }
