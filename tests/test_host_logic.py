@@ -45,6 +45,28 @@ def test_cabi_rejects_bad_arguments_without_launching(native_libs):
     assert lib.ntb200_offsets_workspace_bytes(5000) == 8 * 5
 
 
+def test_cabi_rejects_bad_arguments_of_the_surrounding_operators(native_libs):
+    """The entry points around the core path validate on the host too (no device is touched here)."""
+    lib = _cabi.load()
+    assert lib.ntb200_layer_norm(None, None, None, 1e-5, None, -1, 8, 0, None) == -1            # negative rows
+    assert lib.ntb200_layer_norm(16, 16, None, 1e-5, 16, 1, 8, 0, None) == -1                   # gamma without beta
+    assert lib.ntb200_layer_norm(16, None, None, 1e-5, 16, 1, 8, 7, None) == -2                 # dtype
+    assert lib.ntb200_layer_norm(None, None, None, 1e-5, None, 0, 8, 0, None) == 0              # no rows: no-op
+    assert lib.ntb200_add_bias_gelu(None, None, None, 3, 8, 0, None) == -1                      # null pointers
+    assert lib.ntb200_gemm_bias_act(16, 16, None, None, 16, 4, 4, 4, 0, 3, 0, None) == -1       # activation code
+    assert lib.ntb200_gemm_bias_act(16, 16, None, None, 16, 4, 4, 4, 9, 0, 0, None) == -2       # dtype
+    assert lib.ntb200_pack_pointers(16, 16, 2, 8, 10, 4, None) == -3                            # misaligned output
+    assert lib.ntb200_pack_pointers(16, 16, 2, 16, 10, 3, None) == -2                           # element size
+    assert lib.ntb200_pack_pointers(None, None, 0, None, 0, 4, None) == 0                       # empty batch
+    assert lib.ntb200_embedding(16, 16, 2, 16, 4, 10, 8, 4, None) == -1                         # index width
+    assert lib.ntb200_embedding(16, 16, 8, 16, 4, 0, 8, 4, None) == -1                          # empty vocabulary
+    assert lib.ntb200_transpose_ragged(16, 16, 16, 2, 8, 1, 10, 4, None) == -1                  # in place
+    assert lib.ntb200_transpose_ragged(16, 32, 16, 2, 8, 1, 10, 3, None) == -2                  # element size
+    assert lib.ntb200_varlen_cross_attention(16, 4, 16, 64, 16, 64, 16, 16, 16, 1, 4, 1, 64, 4, 1.0, 2, 0, None) == -1  # ldq < E
+    assert lib.ntb200_varlen_cross_attention(16, 64, 16, 64, 16, 64, 16, 16, 16, 1, 4, 1, 64, 4, 1.0, 2, 5, None) == -1  # path
+    assert lib.ntb200_varlen_cross_attention(16, 64, 16, 64, 16, 64, 16, 16, 16, 0, 0, 1, 64, 0, 1.0, 2, 0, None) == 0  # empty
+
+
 def test_no_cpu_fallback(native_libs):
     a = nt.nested_tensor([torch.randn(3, 4), torch.randn(5, 4)])
     with pytest.raises(RuntimeError, match="no CPU implementation"):
