@@ -119,8 +119,22 @@ __device__ __forceinline__ void store_chunk32(uint16_t* dst, const uint32_t (&r)
 #pragma unroll
   for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]) + bias32[k];
   if (act == 1) {
+    // tanh GELU on packed fp32 pairs: 0.5 x (1 + tanh(k x (1 + c x^2))), six packed FMA-pipe instructions and two
+    // MUFU tanh per pair
+    const uint64_t c2 = ptx::f32x2_pack(0.044715f, 0.044715f), one2 = ptx::f32x2_pack(1.0f, 1.0f);
+    const uint64_t k2 = ptx::f32x2_pack(0.7978845608028654f, 0.7978845608028654f), half2 = ptx::f32x2_pack(0.5f, 0.5f);
 #pragma unroll
-    for (int k = 0; k < 32; ++k) v[k] = gelu_tanh_fast(v[k]);
+    for (int k = 0; k < 16; ++k) {
+      const uint64_t x = ptx::f32x2_pack(v[2 * k], v[2 * k + 1]);
+      const uint64_t x2 = ptx::f32x2_fma(x, x, 0ull);
+      const uint64_t arg = ptx::f32x2_fma(ptx::f32x2_fma(x, ptx::f32x2_fma(x2, c2, one2), 0ull), k2, 0ull);
+      float a0, a1, t0, t1;
+      ptx::f32x2_unpack(arg, a0, a1);
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(a0));
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(a1));
+      const uint64_t hx = ptx::f32x2_fma(x, half2, 0ull);
+      ptx::f32x2_unpack(ptx::f32x2_fma(hx, ptx::f32x2_pack(t0, t1), hx), v[2 * k], v[2 * k + 1]);
+    }
   } else if (act == 2) {
 #pragma unroll
     for (int k = 0; k < 32; ++k) v[k] = fmaxf(v[k], 0.0f);
