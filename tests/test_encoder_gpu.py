@@ -78,6 +78,29 @@ def test_cabi_add_bias_residual_layer_norm(native_libs, cuda_device, dtype, cols
     assert (got.float().cpu() - want).abs().max().item() <= TOL[dtype] * (4 if dtype == torch.float32 else 1)
 
 
+@pytest.mark.parametrize("cols", [1024, 512, 256, 64, 200])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16], ids=str)
+@pytest.mark.parametrize("fused", [False, True])
+def test_cabi_layer_norm_many_rows(native_libs, cuda_device, dtype, cols, fused):
+    """Thousands of rows (more than one wave of CTAs), plain and with residual + bias, out of place and in place."""
+    g = torch.Generator().manual_seed(cols + int(fused))
+    rows = 9001
+    x = (torch.randn(rows, cols, generator=g) + 0.3).to(dtype)
+    res = torch.randn(rows, cols, generator=g).to(dtype) if fused else None
+    bias = (0.2 * torch.randn(cols, generator=g)).to(dtype) if fused else None
+    gamma = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+    beta = (0.1 * torch.randn(cols, generator=g)).to(dtype)
+    d = lambda t: None if t is None else t.to(cuda_device)
+    ref_in = x.float() + (res.float() if fused else 0) + (bias.float() if fused else 0)
+    want = torch.nn.functional.layer_norm(ref_in, (cols,), gamma.float(), beta.float(), 1e-5)
+    tol = TOL[dtype] * (4 if dtype == torch.float32 else 1)
+    got = _layer_norm(d(x), d(res), d(bias), d(gamma), d(beta), 1e-5)
+    assert (got.float().cpu() - want).abs().max().item() <= tol
+    xin = d(x).clone()
+    got = _layer_norm(xin, d(res), d(bias), d(gamma), d(beta), 1e-5, inplace=True)
+    assert (got.float().cpu() - want).abs().max().item() <= tol
+
+
 @pytest.mark.parametrize("cols", [4096, 24, 7])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=str)
 def test_cabi_add_bias_gelu(native_libs, cuda_device, dtype, cols):
