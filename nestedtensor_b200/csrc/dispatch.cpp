@@ -253,6 +253,48 @@ std::tuple<Tensor, Tensor> to_tensor_mask(const Tensor& buffer, const Tensor& si
   return std::make_tuple(out, mask);
 }
 
+// ------------------------------------------------------------------ get_max_size / pad_nt
+// nestedtensor/csrc/masking.cpp:83-108: per-dimension maximum of the constituent sizes
+std::vector<int64_t> get_max_size(const Tensor& sizes) {
+  TORCH_CHECK(sizes.device().is_cpu() && sizes.scalar_type() == at::kLong && sizes.dim() == 2 && sizes.is_contiguous(),
+              "nestedtensor_b200: sizes must be a contiguous CPU int64 [B, tensor_dim] tensor");
+  std::vector<int64_t> mx(sizes.size(1), 0);
+  const int64_t* p = sizes.data_ptr<int64_t>();
+  for (int64_t b = 0; b < sizes.size(0); ++b)
+    for (int64_t j = 0; j < sizes.size(1); ++j) mx[j] = std::max(mx[j], p[b * sizes.size(1) + j]);
+  return mx;
+}
+
+// nestedtensor/csrc/masking.cpp:138-179: every constituent zero-padded to `shape` and stacked, with the uint8
+// mask of the same shape (1 inside a constituent).  One fused launch instead of a pad + stack per constituent.
+std::tuple<Tensor, Tensor> pad_nt(const Tensor& buffer, const Tensor& sizes, const Tensor& meta, at::IntArrayRef shape) {
+  Record r = make_record(sizes, meta);
+  if (r.B == 0)  // masking.cpp:164-166
+    return std::make_tuple(at::zeros({1}, at::TensorOptions().dtype(at::kLong)), at::zeros({1}, at::TensorOptions().dtype(at::kByte)));
+  check_buffer(buffer, r, "pad_nt");
+  TORCH_CHECK(!r.any_empty, "Empty tensors are not yet supported.");
+  TORCH_CHECK((int64_t)shape.size() == r.tdim, "nestedtensor_b200: pad_nt needs one extent per tensor dimension");
+  TORCH_CHECK(r.tdim >= 1 && r.tdim <= 3, "nestedtensor_b200: pad_nt supports 1 to 3 tensor dimensions");
+  std::vector<int64_t> dense(shape.begin(), shape.end()), full{r.B};
+  for (int64_t d = 0; d < r.tdim; ++d) {
+    TORCH_CHECK(dense[d] >= r.max_sizes[d], "nestedtensor_b200: pad_nt shape ", dense[d], " of dim ", d,
+                " is smaller than the largest constituent (", r.max_sizes[d], ")");
+    full.push_back(dense[d]);
+  }
+  c10::cuda::CUDAGuard guard(buffer.device());
+  Tensor out = at::empty(full, buffer.options());
+  Tensor mask = at::empty(full, buffer.options().dtype(at::kByte));
+  if (out.numel() == 0) return std::make_tuple(out, mask);
+  int nd;
+  int64_t inner;
+  fold_dims(r, dense.data(), &nd, &inner);
+  check_rc(ntb200_pad_with_mask(buffer.data_ptr(), out.data_ptr(), static_cast<uint8_t*>(mask.data_ptr()), r.d_offsets,
+                                r.d_sizes, r.tdim, nd, inner, r.B, dense.data(), (int)buffer.element_size(), r.d_sizes,
+                                r.tdim, (int)r.tdim, dense.data(), cur_stream()),
+           "ntb200_pad_with_mask");
+  return std::make_tuple(out, mask);
+}
+
 // ------------------------------------------------------------------ to_mask
 // nestedtensor/csrc/masking.cpp:408-457.  The reference builds this mask on the host; here it is
 // written on the device that holds the nested tensor.
@@ -784,6 +826,8 @@ TORCH_LIBRARY(nestedtensor, m) {
         &to_padded_tensor_out);
   m.def("to_tensor_mask(Tensor buffer, Tensor sizes, Tensor meta, int? mask_dim) -> (Tensor, Tensor)", &to_tensor_mask);
   m.def("to_mask(Tensor sizes, Tensor meta, int? mask_dim) -> Tensor", &to_mask);
+  m.def("get_max_size(Tensor sizes) -> int[]", &get_max_size);
+  m.def("pad_nt(Tensor buffer, Tensor sizes, Tensor meta, int[] shape) -> (Tensor, Tensor)", &pad_nt);
   m.def("from_padded_tensor(Tensor padded, Tensor sizes, Tensor meta) -> Tensor", &from_padded_tensor);
   m.def("sizes_from_padded(Tensor tensor, Scalar padding) -> (Tensor, Tensor)", &sizes_from_padded);
   m.def("sizes_from_mask(Tensor mask) -> (Tensor, Tensor)", &sizes_from_mask);
@@ -791,6 +835,10 @@ TORCH_LIBRARY(nestedtensor, m) {
   m.def("token_index(Tensor token_offsets, int total_tokens) -> (Tensor, Tensor)", &token_index);
   m.def(
       "bt_min_mha(int num_heads, int head_dim, float dropout_p, bool training, Tensor buffer, Tensor sizes, Tensor meta, "
+      "Tensor attr_kernel, Tensor attr_bias, float scaling, Tensor out_proj_weight, Tensor? out_proj_bias) -> Tensor",
+      &bt_min_mha);
+  m.def(
+      "min_mha(int num_heads, int head_dim, float dropout_p, bool training, Tensor buffer, Tensor sizes, Tensor meta, "
       "Tensor attr_kernel, Tensor attr_bias, float scaling, Tensor out_proj_weight, Tensor? out_proj_bias) -> Tensor",
       &bt_min_mha);
   m.def(

@@ -288,7 +288,21 @@ def _op_transpose_nhwc_nchw(nt):
     return transpose_nhwc_nchw(nt)
 
 
+def _op_get_max_size(nt):
+    """``torch.ops.nestedtensor.get_max_size`` (nestedtensor/csrc/masking.cpp:105-108)."""
+    return list(_ops.ops().get_max_size(nt._sizes))
+
+
+def _op_pad_nt(nt, shape):
+    """``torch.ops.nestedtensor.pad_nt`` (nestedtensor/csrc/masking.cpp:138-179)."""
+    buf, sizes, meta = nt._record()
+    return _ops.ops().pad_nt(buf, sizes, meta, list(shape))
+
+
 _RECORD_OPS = {
+    "get_max_size": _op_get_max_size,
+    "pad_nt": _op_pad_nt,
+    "min_mha": _op_bt_min_mha,
     "transpose_nchw_nhwc": _op_transpose_nchw_nhwc,
     "transpose_nhwc_nchw": _op_transpose_nhwc_nchw,
     "to_padded_tensor": _op_to_padded_tensor,

@@ -95,3 +95,37 @@ def test_conv2d_rejects_images_smaller_than_the_kernel(native_libs, cuda_device)
     w = torch.randn(4, 3, 5, 5, device=cuda_device)
     with pytest.raises(RuntimeError):
         torch.nn.functional.conv2d(x, w)
+
+
+def test_remaining_operator_names_of_the_reference_surface(native_libs, cuda_device):
+    """get_max_size, pad_nt and min_mha under torch.ops.nestedtensor (nestedtensor/csrc/masking.cpp:652-675,
+    nestedtensor/csrc/mha.cpp:71-74), called with the wrapper like the reference's own tests do."""
+    g = torch.Generator().manual_seed(8)
+    ts = [torch.randn(3, 5, generator=g), torch.randn(6, 2, generator=g), torch.randn(1, 7, generator=g)]
+    x = nt.nested_tensor(ts, device=cuda_device)
+    assert torch.ops.nestedtensor.get_max_size(x) == [6, 7]
+    data, mask = torch.ops.nestedtensor.pad_nt(x, [8, 9])
+    assert mask.dtype == torch.uint8 and tuple(data.shape) == (3, 8, 9) and tuple(mask.shape) == (3, 8, 9)
+    want = torch.stack([torch.nn.functional.pad(t, (0, 9 - t.size(1), 0, 8 - t.size(0))) for t in ts])
+    wmask = torch.stack([torch.nn.functional.pad(torch.ones_like(t, dtype=torch.uint8), (0, 9 - t.size(1), 0, 8 - t.size(0)))
+                         for t in ts])
+    assert_bit_equal(data, want, "pad_nt data")
+    assert torch.equal(mask.cpu(), wmask)
+    with pytest.raises(RuntimeError, match="smaller than the largest constituent"):
+        torch.ops.nestedtensor.pad_nt(x, [5, 9])
+    with pytest.raises(RuntimeError, match="Empty tensors are not yet supported."):
+        torch.ops.nestedtensor.pad_nt(nt.nested_tensor([torch.randn(0, 3), torch.randn(2, 3)], device=cuda_device), [4, 4])
+
+    E, H = 32, 2
+    xs = [torch.randn(l, E, generator=g) for l in (4, 9)]
+    ks = [torch.randn(l, E, generator=g) for l in (7, 2)]
+    torch.manual_seed(5)
+    mha = torch.nn.MultiheadAttention(E, H).eval().to(cuda_device)
+    q, k = nt.nested_tensor(xs, device=cuda_device), nt.nested_tensor(ks, device=cuda_device)
+    args = (mha.in_proj_weight, mha.in_proj_bias, float(E // H) ** -0.5, mha.out_proj.weight, mha.out_proj.bias)
+    cpu = [a.detach().cpu() if torch.is_tensor(a) else a for a in args]
+    for key in (q, k):
+        got = torch.ops.nestedtensor.min_mha(H, E // H, 0.0, False, q, key, key, *args)
+        kk = xs if key is q else ks
+        want = ntref.min_mha(H, E // H, xs, kk, kk, *cpu)
+        assert max((a.cpu() - b).abs().max().item() for a, b in zip(got.unbind(), want)) <= 1e-5
