@@ -134,6 +134,19 @@ def test_varlen_attention_tcgen05_lengths(native_libs, cuda_device, lengths):
     assert err <= 2e-2, "tcgen05 attention max-abs %g" % err
 
 
+@pytest.mark.parametrize("H", [1, 3, 7, 40, 300])
+def test_varlen_attention_tcgen05_head_counts(native_libs, cuda_device, H):
+    """The persistent kernel steps through the flattened (item, head) list by its grid size: head counts that do not
+    divide it, exceed it, or equal 1."""
+    d = 64
+    lengths = [5, 130, 64, 1, 257] if H < 100 else [5, 70]
+    g = torch.Generator().manual_seed(H)
+    qkv = torch.randn(sum(lengths), 3 * H * d, generator=g).to(torch.bfloat16).to(cuda_device)
+    want = _attention_oracle(qkv, lengths, H, d)
+    got = _attention(qkv, lengths, H, d, path=3)
+    assert (got.float().cpu() - want).abs().max().item() <= 2e-2
+
+
 @pytest.mark.parametrize("H,d", [(2, 1), (1, 4), (2, 2), (8, 16), (4, 256), (3, 40), (16, 64)])
 def test_varlen_attention_fp32(native_libs, cuda_device, H, d):
     lengths = [5, 1, 33, 50, 2, 64, 100]
