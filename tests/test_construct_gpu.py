@@ -116,3 +116,45 @@ def test_embedding_out_of_range_index_is_reported_not_trapped(native_libs, cuda_
     assert torch.equal(out[0], w[0]) and torch.equal(out[1], w[9]) and torch.equal(out[4], w[3])
     assert bool((out[2] == 0).all()) and bool((out[3] == 0).all())
     assert lib.ntb200_device_error_flags() == 0
+
+
+def test_full_size_construction_embedding_and_transposes(native_libs, cuda_device):
+    """Size-independent properties at the benchmark sizes: packing 4096 separately allocated (L_i, 1024) bf16
+    tensors reproduces their concatenation, the packed embedding equals an index-select, and the ragged transposes
+    are inverse to each other."""
+    from nestedtensor_b200 import workloads
+    L = workloads.lengths_c2(workloads._gen(2), 4096)
+    g = torch.Generator(device=cuda_device).manual_seed(1)
+    parts = [torch.randn(int(l), 1024, device=cuda_device, generator=g).to(torch.bfloat16) for l in L[:4096]]
+    x = nt.nested_tensor(parts, device=cuda_device, dtype=torch.bfloat16)
+    for i in (0, 1, 77, 2048, 4095):
+        start = int(L[:i].sum()) * 1024
+        assert torch.equal(x._buffer[start:start + parts[i].numel()].view(torch.int16), parts[i].reshape(-1).view(torch.int16))
+    assert x._buffer.numel() == int(L.sum()) * 1024
+    checksum = sum(int(p.view(torch.int16).to(torch.int64).sum()) for p in parts[::64])
+    got = 0
+    for i in range(0, 4096, 64):
+        start = int(L[:i].sum()) * 1024
+        got += int(x._buffer[start:start + parts[i].numel()].view(torch.int16).to(torch.int64).sum())
+    assert got == checksum
+    del parts, x
+    torch.cuda.empty_cache()
+
+    c5 = workloads.config5()
+    T = int(c5.sizes[:, 0].sum())
+    table = torch.randn(30522, 1024, device=cuda_device, generator=g).to(torch.bfloat16)
+    idx = torch.randint(0, 30522, (T,), device=cuda_device, generator=g)
+    ids = nt.NestedTensor(idx, c5.sizes[:, :1].contiguous())
+    emb = torch.nn.functional.embedding(ids, table)
+    assert torch.equal(emb._buffer.view(T, 1024).view(torch.int16), table.index_select(0, idx).view(torch.int16))
+    assert _cabi.load().ntb200_device_error_flags() == 0
+
+    hw = torch.randint(100, 169, (32, 2), generator=torch.Generator().manual_seed(2))
+    isz = torch.cat([torch.full((32, 1), 256), hw], 1).contiguous()
+    n = int((isz[:, 0] * isz[:, 1] * isz[:, 2]).sum())
+    img = nt.NestedTensor(torch.randn(n, device=cuda_device, generator=g).to(torch.float16), isz)
+    nhwc = nt.nn.transpose_nchw_nhwc(img)
+    back = nt.nn.transpose_nhwc_nchw(nhwc)
+    assert torch.equal(back._buffer.view(torch.int16), img._buffer.view(torch.int16))
+    first = img.unbind()[0]
+    assert torch.equal(nhwc.unbind()[0], first.permute(1, 2, 0))
