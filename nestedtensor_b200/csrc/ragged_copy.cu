@@ -699,7 +699,9 @@ __global__ void __launch_bounds__(kThreads) sizes_scan_kernel(const ScanParams p
 
   // accumulators for the tile's first entry (reduced over the block at the end);
   // elements of later entries inside the tile go to global atomics directly
-  unsigned long long cnt0 = 0, mx0[3] = {0, 0, 0};
+  // (32-bit while a padded entry has fewer than 2^30 elements: half the instructions of the bookkeeping)
+  using A = typename IP::T;
+  A cnt0 = 0, mx0[3] = {0, 0, 0};
 
   // all loads of the tile first (read-only kernel: memory-level parallelism is everything), then the
   // bookkeeping
@@ -740,17 +742,20 @@ __global__ void __launch_bounds__(kThreads) sizes_scan_kernel(const ScanParams p
     decompose<ND, BIG>(p, (uint64_t)r, idx);
     const uint64_t row_len = (ND == 1) ? p.P : p.m[ND - 1];
     if (idx[ND - 1] + VE <= row_len) {
-      unsigned long long mx[3];
+      A mx[3];
 #pragma unroll
-      for (int j = 0; j < ND - 1; ++j) mx[j] = idx[j] + 1;
-      mx[ND - 1] = idx[ND - 1] + (32 - __clz(bits));
-      const unsigned long long c = __popc(bits);
+      for (int j = 0; j < ND - 1; ++j) mx[j] = (A)idx[j] + 1;
+      mx[ND - 1] = (A)idx[ND - 1] + (A)(32 - __clz(bits));
+      const A c = (A)__popc(bits);
       if (qb == 0) {
         cnt0 += c;
 #pragma unroll
         for (int j = 0; j < ND; ++j) mx0[j] = mx0[j] > mx[j] ? mx0[j] : mx[j];
       } else {
-        scan_flush<ND>(p, b, c, mx);
+        unsigned long long mx64[3] = {0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < ND; ++j) mx64[j] = mx[j];
+        scan_flush<ND>(p, b, (unsigned long long)c, mx64);
       }
     } else {
 #pragma unroll
@@ -780,7 +785,7 @@ __global__ void __launch_bounds__(kThreads) sizes_scan_kernel(const ScanParams p
     cnt0 += __shfl_xor_sync(full, cnt0, o);
 #pragma unroll
     for (int j = 0; j < ND; ++j) {
-      const unsigned long long other = __shfl_xor_sync(full, mx0[j], o);
+      const A other = __shfl_xor_sync(full, mx0[j], o);
       mx0[j] = mx0[j] > other ? mx0[j] : other;
     }
   }
