@@ -88,6 +88,17 @@ def transformer_encoder_layer(layer: torch.nn.TransformerEncoderLayer, src: Nest
     return NestedTensor(out.reshape(-1), sizes, meta)
 
 
+def transformer_encoder(encoder: torch.nn.TransformerEncoder, src: NestedTensor, activation: Optional[str] = None) -> NestedTensor:
+    """Forward of a stock ``torch.nn.TransformerEncoder`` (its layers in turn, then its final norm if it has one) on
+    a NestedTensor; the tokens stay packed from the first layer to the last."""
+    out = src
+    for layer in encoder.layers:
+        out = transformer_encoder_layer(layer, out, activation)
+    if encoder.norm is not None:
+        out = layer_norm(out, encoder.norm.normalized_shape, encoder.norm.weight, encoder.norm.bias, encoder.norm.eps)
+    return out
+
+
 def embedding(input: NestedTensor, weight: torch.Tensor, padding_idx=None, max_norm=None, norm_type=2.0,
               scale_grad_by_freq=False, sparse=False) -> NestedTensor:
     """``torch.nn.functional.embedding`` on a NestedTensor of 1-D index sequences

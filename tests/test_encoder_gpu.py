@@ -251,3 +251,23 @@ def test_encoder_layer_bert_large_sampled(native_libs, cuda_device):
     err = max((outs[i].float().cpu() - w).abs().max().item() for i, w in zip(idx, want))
     assert rel <= 2e-2 and err <= 8e-2, (rel, err)
     assert not torch.isnan(got._buffer.float()).any()
+
+
+def test_transformer_encoder_stack_from_token_ids(native_libs, cuda_device):
+    """Embedding lookup on packed token ids, three encoder layers and a final LayerNorm, never padded; against the
+    per-sequence fp32 oracle."""
+    torch.manual_seed(21)
+    V, E, H, F = 97, 64, 4, 128
+    emb = torch.nn.Embedding(V, E)
+    layer = torch.nn.TransformerEncoderLayer(E, H, dim_feedforward=F, dropout=0.0, activation=torch.nn.functional.relu)
+    enc = torch.nn.TransformerEncoder(layer, num_layers=3, norm=torch.nn.LayerNorm(E), enable_nested_tensor=False).eval()
+    g = torch.Generator().manual_seed(4)
+    ids = [torch.randint(0, V, (int(l),), generator=g) for l in torch.randint(1, 90, (11,), generator=g)]
+    want = ntref.embedding(ids, emb.weight.detach())
+    for lyr in enc.layers:
+        want = ntref.encoder_layer(want, H, _params(lyr), "relu", False, lyr.norm1.eps)
+    want = ntref.layer_norm(want, (E,), enc.norm.weight.detach(), enc.norm.bias.detach(), enc.norm.eps)
+    x = nt.nested_tensor(ids, device=cuda_device, dtype=torch.int64)
+    got = nt.nn.transformer_encoder(enc.to(cuda_device), emb.to(cuda_device)(x))
+    err = max((a.cpu() - b).abs().max().item() for a, b in zip(got.unbind(), want))
+    assert err <= 3e-4, err
