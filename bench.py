@@ -356,7 +356,8 @@ def run_copy(args, kind, rank, world, local):
 # L2 at kernel end, which does not grow with the batch, so the full-size figure is algorithmic - residue:
 #   pad   1.950 + 8.590 - 0.055 GB      unpad 1.950 + 1.950 - 0.051 GB
 #   QKV projection (A 310.9 MB + W 6.3 MB read, C 932.6 MB written) - 0.052 GB
-NCU_TRAFFIC = {"pad": 10.48e9, "unpad": 3.85e9, "mha": 1.20e9}
+#   feed-forward up-projection (A 310.9 MB + W 8.4 MB read, C 1243.5 MB written) - 0.05 GB
+NCU_TRAFFIC = {"pad": 10.48e9, "unpad": 3.85e9, "mha": 1.20e9, "encoder": 1.51e9}
 
 
 # ---------------------------------------------------------------------- reference arm
@@ -798,7 +799,8 @@ def run_encoder(args, rank, world, local):
         "roofline": {"bound": "tensor", "kernel": "gemm_bias_tcgen05_pair_kernel (feed-forward up-projection + bias + GELU, "
                                                   "M=%d N=4096 K=1024)" % T,
                      "achieved": f1tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": f1tf / peaks["bf16_tflops"],
-                     "frac_of_sustained": f1tf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"], "traffic": None},
+                     "frac_of_sustained": f1tf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
+                     "traffic": NCU_TRAFFIC.get("encoder")},
         "e2e": e2e, "gpu_launches": 8 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
     }
     if not KERNEL_ONLY:
