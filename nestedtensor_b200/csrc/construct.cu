@@ -217,19 +217,22 @@ transpose_ragged_kernel(const T* __restrict__ in, T* __restrict__ out, const int
 // The same transpose when a row of `regular` elements is a whole number of 16-byte vectors (C * element size
 // a multiple of 16, always so for fp16 / bf16 feature maps with C % 8 == 0): the side on which the regular
 // extent is contiguous moves 16 bytes per thread, the ragged side (rows of n_b elements at any phase) stays
-// element-wise but coalesced.
+// element-wise but coalesced.  The tile lives in shared memory as [ragged][regular] 32-bit words with an odd
+// word stride: the vector side touches it with four 32-bit accesses per vector and the element side with one
+// element per thread over 32 consecutive ragged positions, both free of bank conflicts for 2-byte elements
+// (at most two-way for 1- and 4-byte ones).
 constexpr int kTrRag = 128;  // ragged-extent tile of the vector kernel (more bytes in flight per CTA)
 
 template <typename T, bool REG_IS_ROWS>
 __global__ void __launch_bounds__(256)
 transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const int64_t* __restrict__ offsets, int64_t regular) {
-  constexpr int VE = 16 / (int)sizeof(T);        // elements per vector
-  constexpr int kVecPerRow = kTrTile / VE;       // vectors covering the tile's regular extent
-  __shared__ T tile[kTrTile][kTrRag + 2];        // [regular][ragged]
-  union Vec {
-    uint4 v;
-    T e[VE];
-  };
+  constexpr int VE = 16 / (int)sizeof(T);               // elements per vector
+  constexpr int kVecPerRow = kTrTile / VE;              // vectors covering the tile's regular extent
+  constexpr int kWords = kTrTile * (int)sizeof(T) / 4;  // 32-bit words of one ragged position's slice
+  constexpr int kStride = (kWords + 1) * 4 / (int)sizeof(T);  // elements per tile row: an odd number of words
+  constexpr int kPerThread = kTrTile / (256 / kTrRag);        // element-side accesses per thread
+  constexpr int kVecPerThread = (kTrRag * kVecPerRow) / 256;  // vector-side accesses per thread
+  __shared__ __align__(16) T tile[kTrRag][kStride];           // [ragged][regular]
   const int64_t b = blockIdx.y;
   const int64_t off = offsets[b];
   const int64_t n = (offsets[b + 1] - off) / regular;
@@ -240,45 +243,67 @@ transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const
   const T* src = in + off;
   T* dst = out + off;
   const int px_l = threadIdx.x & (kTrRag - 1), cy = threadIdx.x / kTrRag;  // element-wise side: 128 ragged x 2 regular
+  // The element-wise side costs one compare, one pointer step, one global and one shared access per element:
+  // thread (px_l, cy) owns regular positions cy, cy + kRegStep, ... of ragged position p0 + px_l, walks them with
+  // a pointer that advances kRegStep rows of n elements, and tests i * kRegStep against `lim`, the count of
+  // valid regular positions from cy on (0 when its ragged position lies past the constituent's end).
+  constexpr int kRegStep = 256 / kTrRag;
+  const int64_t step = (int64_t)kRegStep * n;
+  const int64_t reg_left = regular - c0 - cy;
+  const int lim = (p0 + px_l < n && reg_left > 0) ? (int)(reg_left < kTrTile ? reg_left : kTrTile) : 0;
+  // every global load of a phase is issued before the first shared-memory store that depends on one
   if (REG_IS_ROWS) {  // in [regular][n] -> out [n][regular]
+    constexpr int kBatch = kPerThread / 2;  // loads in flight per thread (two batches keep the register count down)
+    const T* p = src + (c0 + cy) * n + p0 + px_l;
 #pragma unroll
-    for (int i = 0; i < kTrTile; i += 256 / kTrRag) {
-      const int64_t c = c0 + cy + i, px = p0 + px_l;
-      if (c < regular && px < n) tile[cy + i][px_l] = src[c * n + px];
+    for (int h = 0; h < kPerThread; h += kBatch) {
+      T vals[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        vals[i] = ((h + i) * kRegStep < lim) ? *p : T(0);
+        p += step;
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) tile[px_l][cy + (h + i) * kRegStep] = vals[i];
     }
   } else {  // in [n][regular] -> out [regular][n]
+    uint4 x[kVecPerThread];
 #pragma unroll
-    for (int k = 0; k < (kTrRag * kVecPerRow) / 256; ++k) {
+    for (int k = 0; k < kVecPerThread; ++k) {
       const int idx = k * 256 + threadIdx.x;
-      const int pl = idx / kVecPerRow, cl = (idx % kVecPerRow) * VE;
-      const int64_t px = p0 + pl, c = c0 + cl;
-      if (px < n && c < regular) {
-        Vec x;
-        x.v = *reinterpret_cast<const uint4*>(src + px * regular + c);
+      const int pl = idx / kVecPerRow, v = idx % kVecPerRow;
+      const int64_t px = p0 + pl, c = c0 + v * VE;
+      x[k] = (px < n && c < regular) ? *reinterpret_cast<const uint4*>(src + px * regular + c) : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-        for (int e = 0; e < VE; ++e) tile[cl + e][pl] = x.e[e];
-      }
+    for (int k = 0; k < kVecPerThread; ++k) {
+      const int idx = k * 256 + threadIdx.x;
+      const int pl = idx / kVecPerRow, v = idx % kVecPerRow;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&tile[pl][v * VE]);
+      w[0] = x[k].x;
+      w[1] = x[k].y;
+      w[2] = x[k].z;
+      w[3] = x[k].w;
     }
   }
   __syncthreads();
   if (REG_IS_ROWS) {
 #pragma unroll
-    for (int k = 0; k < (kTrRag * kVecPerRow) / 256; ++k) {
+    for (int k = 0; k < kVecPerThread; ++k) {
       const int idx = k * 256 + threadIdx.x;
-      const int pl = idx / kVecPerRow, cl = (idx % kVecPerRow) * VE;
-      const int64_t px = p0 + pl, c = c0 + cl;
+      const int pl = idx / kVecPerRow, v = idx % kVecPerRow;
+      const int64_t px = p0 + pl, c = c0 + v * VE;
       if (px < n && c < regular) {
-        Vec x;
-#pragma unroll
-        for (int e = 0; e < VE; ++e) x.e[e] = tile[cl + e][pl];
-        *reinterpret_cast<uint4*>(dst + px * regular + c) = x.v;
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&tile[pl][v * VE]);
+        *reinterpret_cast<uint4*>(dst + px * regular + c) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   } else {
+    T* q = dst + (c0 + cy) * n + p0 + px_l;
 #pragma unroll
-    for (int i = 0; i < kTrTile; i += 256 / kTrRag) {
-      const int64_t c = c0 + cy + i, px = p0 + px_l;
-      if (c < regular && px < n) dst[c * n + px] = tile[cy + i][px_l];
+    for (int i = 0; i < kPerThread; ++i) {
+      if (i * kRegStep < lim) *q = tile[px_l][cy + i * kRegStep];
+      q += step;
     }
   }
 }
