@@ -262,6 +262,11 @@ def run_copy(args, kind, rank, world, local):
     out_elems = n_pad if kind == "pad" else n_valid
     in_elems = n_valid if kind == "pad" else n_pad
     need = es * (out_elems + in_elems)
+    if world > 1:  # every rank takes the same branch: the smallest figure any rank saw decides
+        import torch.distributed as dist
+        t_av = torch.tensor([float(avail)], dtype=torch.float64, device=device)
+        dist.all_reduce(t_av, op=dist.ReduceOp.MIN)
+        avail = float(t_av.item())
     if KERNEL_ONLY:
         e2e = {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "sample": "skipped: --kernel-only"}
     elif avail > 3 * need * max(world, 1):
