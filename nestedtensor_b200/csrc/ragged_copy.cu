@@ -451,6 +451,71 @@ __device__ __forceinline__ void unpad_locate(const UnpadParams& p, int64_t b, ui
   }
 }
 
+// The divisors of unpad_locate are per entry (its own row and plane lengths), so they cannot be turned into
+// multiply-shift pairs on the host the way the padded extents are.  A tile touches few entries: the block
+// builds the pairs for the first kUnpadEnt of them in shared memory once, and a vector whose entry is in the
+// table (and small enough for 32-bit arithmetic) locates itself without a division.
+constexpr int kUnpadEnt = 8;
+struct UnpadEnt {
+  FastDiv f_plane, f_row;  // divide by s12 (3 ragged dims only) and by s2
+  uint32_t s12, s2;        // elements of one valid plane / of one valid innermost row
+  uint32_t ok;
+};
+
+__device__ __forceinline__ FastDiv make_fastdiv_device(uint32_t d) {
+  FastDiv f;
+  if (d == 0) d = 1;
+  const uint32_t shift = d <= 1 ? 0 : 32 - __clz(d - 1);  // smallest shift with 2^shift >= d
+  f.d = d;
+  f.mul = (uint32_t)(((1ull << 32) * ((1ull << shift) - d)) / d + 1);
+  f.shift = shift;
+  return f;
+}
+
+template <int ND>
+__device__ __forceinline__ UnpadEnt unpad_entry_divisors(const UnpadParams& p, int64_t b) {
+  UnpadEnt en;
+  en.ok = 0;
+  en.s12 = en.s2 = 1;
+  en.f_plane = en.f_row = FastDiv{1, 1, 0};
+  const int64_t* s = p.sizes + b * p.size_stride;
+  const uint64_t s2 = (uint64_t)(s[ND - 1] * p.inner);
+  const uint64_t s12 = (ND == 3 ? (uint64_t)s[1] : 1ull) * s2;
+  const uint64_t count = (uint64_t)(p.offsets[b + 1] - p.offsets[b]);
+  if (s12 > 0 && s12 < (1ull << 30) && count < (1ull << 30)) {
+    en.ok = 1;
+    en.s12 = (uint32_t)s12;
+    en.s2 = (uint32_t)s2;
+    en.f_plane = make_fastdiv_device((uint32_t)s12);
+    en.f_row = make_fastdiv_device((uint32_t)s2);
+  }
+  return en;
+}
+
+// unpad_locate for an entry of the table: r < 2^30 and both divisors < 2^30
+template <int ND>
+__device__ __forceinline__ void unpad_locate_fast(const UnpadParams& p, const UnpadEnt& en, int64_t b, uint32_t r,
+                                                  int64_t& src_idx, int64_t& run, uint64_t& w0, uint64_t& w1) {
+  const int64_t base = b * (int64_t)p.P;
+  if (ND == 2) {
+    const uint32_t i0 = fastdiv(r, en.f_row);
+    const uint32_t c = r - i0 * en.s2;
+    w0 = i0;
+    w1 = 0;
+    src_idx = base + (int64_t)((uint64_t)i0 * p.m[1] + c);
+    run = (int64_t)(en.s2 - c);
+  } else {
+    const uint32_t i0 = fastdiv(r, en.f_plane);
+    const uint32_t rem = r - i0 * en.s12;
+    const uint32_t i1 = fastdiv(rem, en.f_row);
+    const uint32_t c = rem - i1 * en.s2;
+    w0 = i0;
+    w1 = i1;
+    src_idx = base + (int64_t)(((uint64_t)i0 * p.m[1] + i1) * p.m[2] + c);
+    run = (int64_t)(en.s2 - c);
+  }
+}
+
 // Same two-pass structure as pad_kernel: pass 1 copies every output vector whose 16 bytes come from one
 // source row, pass 2 walks the flagged ones (end of a source row or entry, ragged tail).
 template <int ES, int ND>
@@ -459,6 +524,7 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
   constexpr int VE = 16 / ES;
   constexpr uint32_t kTileElems = kThreads * kVecPerThread * VE;
   __shared__ int64_t s_range[2];
+  __shared__ UnpadEnt s_ent[ND >= 2 ? kUnpadEnt : 1];
 
   const int64_t tile_e0 = (int64_t)blockIdx.x * kTileElems;
   if (threadIdx.x == 0) {
@@ -470,6 +536,10 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
   }
   __syncthreads();
   const int64_t blo = s_range[0], bhi = s_range[1];
+  if (ND >= 2) {
+    if (threadIdx.x < kUnpadEnt && blo + threadIdx.x <= bhi) s_ent[threadIdx.x] = unpad_entry_divisors<ND>(p, blo + threadIdx.x);
+    __syncthreads();
+  }
   E* __restrict__ dst = reinterpret_cast<E*>(p.dst);
   const E* __restrict__ src = reinterpret_cast<const E*>(p.src);
   union Vec {
@@ -487,7 +557,12 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
     const int64_t b = find_entry(p.offsets, blo, bhi, e);
     int64_t src_idx, run;
     uint64_t w0, w1;
-    unpad_locate<ND>(p, b, (uint64_t)(e - p.offsets[b]), src_idx, run, w0, w1);
+    const int64_t ei = b - blo;
+    if (ND >= 2 && ei < kUnpadEnt && s_ent[ei].ok) {
+      unpad_locate_fast<ND>(p, s_ent[ei], b, (uint32_t)(e - p.offsets[b]), src_idx, run, w0, w1);
+    } else {
+      unpad_locate<ND>(p, b, (uint64_t)(e - p.offsets[b]), src_idx, run, w0, w1);
+    }
     if (run < VE) {  // also covers the ragged tail: run >= VE implies e + VE <= total
       boundary |= 1u << u;
       continue;
