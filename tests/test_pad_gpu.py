@@ -116,6 +116,21 @@ def test_config1_roundtrip(native_libs, cuda_device):
     # default padding of the API is -1
     assert_bit_equal(a.to_padded_tensor(), ntref.to_padded_tensor(tensors, -1), "padding=-1")
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.uint8, torch.float64], ids=str)
+@pytest.mark.parametrize("tdim", [2, 3])
+def test_unpad_many_entries_per_tile(native_libs, cuda_device, dtype, tdim):
+    """2 and 3 ragged dims with large and tiny constituents interleaved: tiles that start in the middle of a
+    large constituent, tiles that span dozens of tiny ones (more than the kernel's per-tile table of
+    per-constituent divisors holds), and extents of 1."""
+    g = torch.Generator().manual_seed(4242 + tdim)
+    big = random_list(g, 4, tdim, 40, 90 if tdim == 2 else 60, dtype)
+    tiny = random_list(g, 60, tdim, 1, 5, dtype)
+    tensors = tiny[:25] + big[:2] + tiny[25:40] + big[2:] + tiny[40:]
+    want = _oracle_pad(tensors, 0)
+    got = cabi_pad(tensors, 0, cuda_device)
+    assert_bit_equal(got, want, "pad")
+    assert_bit_equal(cabi_unpad(got, sizes_of(tensors)), torch.cat([t.reshape(-1) for t in tensors]), "unpad")
+
 
 def test_config3_images(native_libs, cuda_device):
     """Configuration 3: 32 fp32 images (3, H_i, W_i): 4-D pad, the un-collapsible 4-D mask, and the
