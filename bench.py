@@ -15,6 +15,12 @@ synthetic input:
 N > 1 (launched by torch.distributed.run, one rank per GPU): the global job is N batches of the
 configuration drawn as one sequence list and cut into N contiguous token-balanced shards; no
 collective on the data path (weak scaling).  `value` is whole-job throughput over the slowest rank.
+The same line carries a `strong` record: the FIXED configuration lists (4096 / 1024 / 128 sequences) cut
+into N token-balanced shards, with the shard outputs all-gathered over NCCL outside the timed region and
+compared on rank 0 with the one-GPU result of the whole list.
+
+Every device-timed figure is the MEDIAN of five timed regions of K steps each (the best region is kept
+beside it as `best_ms`).
 
 `--impl reference` times the CPU restatement of the reference's own implementation
 (oracle/ntref.py; the reference extension cannot be built against this torch) on the host cores.
@@ -138,6 +144,12 @@ def timed_region(fn, steps, world, device):
     return ms
 
 
+def timed_regions(fn, steps, world, device, regions=5):
+    """`regions` timed regions of `steps` steps; returns (median ms per step, best ms per step)."""
+    ms = sorted(timed_region(fn, steps, world, device) / steps for _ in range(regions))
+    return ms[len(ms) // 2], ms[0]
+
+
 def all_sum(x, world, device):
     if world == 1:
         return x
@@ -152,10 +164,24 @@ SEQUENCE_LIMIT = 0   # --sequences: keep only the first N sequences of each shar
 KERNEL_ONLY = False  # --kernel-only: skip the end-to-end pass, the CPU baseline and the parity spot check
 
 
+def _pure_module(name):
+    """`nestedtensor_b200.workloads` / `.sharding` loaded by file path: they are plain Python, and importing the
+    package instead would load the native libraries, which the reference arm must not touch."""
+    import importlib.util
+    key = "_ntb200_pure_" + name
+    if key in sys.modules:
+        return sys.modules[key]
+    spec = importlib.util.spec_from_file_location(key, os.path.join(ROOT, "nestedtensor_b200", name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[key] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def shard_lengths(kind, world, rank):
     """Lengths of this rank's shard: N batches of the configuration drawn as ONE list (generator of the
     configuration, batch = N * config batch) and cut token-balanced into N contiguous slices."""
-    from nestedtensor_b200 import workloads, sharding
+    workloads, sharding = _pure_module("workloads"), _pure_module("sharding")
     if kind in ("pad", "unpad"):
         L = workloads.lengths_c2(workloads._gen(2), 4096 * world)
     else:
@@ -211,6 +237,27 @@ def time_cpu(fn, warmup, iters):
 
 
 # ------------------------------------------------------------------------- pad / unpad
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per ALGORITHMIC byte of the dominant kernel, from the ncu
+# captures summarised under profiles/ (taken on the first 512 sequences of configuration 2 and the first 256 of
+# configuration 5, where traffic grows in proportion to the batch: reads equalled the algorithmic bytes, writes fell
+# short of them by the lines still dirty in L2 when the kernel ended).  The bench line scales the ratio by the
+# algorithmic bytes of the launch it timed, and prints null for a sub-batch run.
+NCU_TRAFFIC_PER_ALG_BYTE = {"pad": 10.48 / 10.54, "unpad": 3.85 / 3.90}
+NCU_TRAFFIC_GEMM_BYTES_PER_TOKEN = {"mha": 1.20e9 / 151792, "encoder": 1.51e9 / 151792}
+NCU_TRAFFIC_SOURCE = "ncu capture summarised in profiles/ (sub-batch, scaled by the units of this launch)"
+
+
+def copy_values(L, hidden, dtype, world, rank):
+    """Values of this rank's shard.  One GPU: the whole configuration-2 buffer from the configuration's own generator
+    (lengths first, then all values in one draw).  N > 1: the global list is N batches and only the lengths are drawn
+    from that generator on every rank; each rank draws its shard's values from a generator seeded by its rank."""
+    if world == 1 and not SEQUENCE_LIMIT:
+        w = _pure_module("workloads").config2()
+        assert torch.equal(w.sizes[:, 0], L)
+        return w.buffer, "workloads.config2 (seed 20242: lengths, then values)"
+    return host_values(int(L.sum()) * hidden, dtype, 20242 + 1000 * (rank + 1)), "per-rank generator (seed 20242 + 1000*(rank+1))"
+
+
 def run_copy(args, kind, rank, world, local):
     import nestedtensor_b200 as nt
     from nestedtensor_b200 import _ops
@@ -225,7 +272,7 @@ def run_copy(args, kind, rank, world, local):
     alg_bytes = es * (n_valid + n_pad) if kind == "pad" else 2 * es * n_valid
 
     # resident inputs (generated on the host, copied once, outside the timed region)
-    host = host_values(n_valid, dtype, 20242 + rank)
+    host, values_from = copy_values(L, hidden, dtype, world, rank)
     ragged = host.to(device)
     a = nt.NestedTensor(ragged, sizes)
     ops = _ops.ops()
@@ -238,12 +285,9 @@ def run_copy(args, kind, rank, world, local):
     for _ in range(max(args.warmup, 3)):
         step()
     with ClockSampler(local) as clocks:
-        ms = timed_region(step, args.steps, world, device)
-        ms2 = timed_region(step, args.steps, world, device)  # second pass keeps the sampler busy longer
-    ms = min(ms, ms2)
+        kernel_ms, best_ms = timed_regions(step, args.steps, world, device)
     total_bytes = all_sum(alg_bytes, world, device)
-    value = total_bytes / (ms / args.steps * 1e-3) / 1e9
-    kernel_ms = ms / args.steps
+    value = total_bytes / (kernel_ms * 1e-3) / 1e9
 
     # parity spot check in the same run (size-independent property): round trip is the identity
     parity_ok = None
@@ -251,6 +295,23 @@ def run_copy(args, kind, rank, world, local):
         chk = ops.from_padded_tensor(ops.to_padded_tensor(buf, sz, meta, 0.0), sz, meta)
         parity_ok = bool(torch.equal(chk.view(torch.int16), ragged.view(torch.int16)))
         del chk
+
+    # the inverse on the same shard, device-timed (sub-record of the pad line)
+    inverse = None
+    if kind == "pad" and not KERNEL_ONLY:
+        padded = ops.to_padded_tensor(buf, sz, meta, 0.0)
+        inv = lambda: ops.from_padded_tensor(padded, sz, meta)
+        for _ in range(3):
+            inv()
+        ims, ibest = timed_regions(inv, args.steps, world, device)
+        ib = 2 * es * n_valid
+        inverse = {"metric": "from_padded_tensor HBM GB/s", "value": all_sum(ib, world, device) / (ims * 1e-3) / 1e9, "unit": "GB/s",
+                   "ms_per_step": ims, "best_ms": ibest, "algorithmic_bytes_per_gpu": ib,
+                   "roofline": {"bound": "hbm", "achieved": ib / (ims * 1e-3) / 1e9, "peak": measured_peaks()["hbm_gbs"], "unit": "GB/s",
+                                "frac": ib / (ims * 1e-3) / 1e9 / measured_peaks()["hbm_gbs"],
+                                "traffic": None if SEQUENCE_LIMIT else ib * NCU_TRAFFIC_PER_ALG_BYTE["unpad"],
+                                "traffic_source": NCU_TRAFFIC_SOURCE}}
+        del padded
 
     # end to end: pinned host input -> device -> kernel -> pinned host output, every step
     e2e = None
@@ -273,6 +334,7 @@ def run_copy(args, kind, rank, world, local):
         if kind == "unpad":
             del padded
         torch.cuda.empty_cache()
+        bind_note = bind_to_gpu_numa_node(local) if world > 1 else "not bound (single rank)"
         h_in = torch.empty(in_elems, dtype=dtype).pin_memory()
         if kind == "pad":
             h_in.copy_(host)
@@ -302,12 +364,21 @@ def run_copy(args, kind, rank, world, local):
             e2e_step()
         with ClockSampler(local) as clocks2:
             ems = timed_region(e2e_step, e2e_steps, world, device)
+        # copy-only legs of the same buffers (what the host side allows with no kernel at all)
+        h2d_ms = timed_region(lambda: d_in.copy_(h_in, non_blocking=True), 2, world, device) / 2
+        d_out = torch.empty(min(out_elems, 1 << 30), dtype=dtype, device=device)
+        d2h_ms = timed_region(lambda: h_out[:d_out.numel()].copy_(d_out, non_blocking=True), 2, world, device) / 2
         e2e = {"value": total_bytes / (ems / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": es * in_elems, "d2h_bytes_per_step": es * out_elems,
                "ms_per_step": ems / e2e_steps, "steps": e2e_steps, "sample": "full shard",
                "api": "%s_host (pinned host in/out, 8 ranges pipelined on 3 streams)" %
                       ("to_padded_tensor" if kind == "pad" else "from_padded_tensor"),
-               "single_stream_value": total_bytes / (sms / e2e_steps * 1e-3) / 1e9}
+               "single_stream_value": total_bytes / (sms / e2e_steps * 1e-3) / 1e9,
+               "copy_only": {"h2d_GBps_per_rank": es * in_elems / (h2d_ms * 1e-3) / 1e9,
+                             "d2h_GBps_per_rank": es * d_out.numel() / (d2h_ms * 1e-3) / 1e9,
+                             "note": "all ranks copy at the same time; max over ranks of the time"},
+               "host_binding": bind_note}
+        del d_out
         clocks.samples += clocks2.samples
         clocks.reasons |= clocks2.reasons
     else:
@@ -317,9 +388,9 @@ def run_copy(args, kind, rank, world, local):
     peaks = measured_peaks()
     line = None
     if rank == 0:
-        cpu = None
-        if world == 1 and not KERNEL_ONLY:  # a single-GPU-run figure; other ranks would compete for the cores
-            seqs = 256
+        cpu = {"skipped": "measured at N=1 only (the other ranks would compete for the host cores)"}
+        if world == 1 and not KERNEL_ONLY:
+            seqs = 512
             if kind == "pad":
                 _, nbytes, fn = cpu_pad_sample(L, hidden, dtype, seqs)
             else:
@@ -330,72 +401,107 @@ def run_copy(args, kind, rank, world, local):
                    "sample": "first %d sequences of the shard, median of 3, torch CPU ops of the reference's "
                              "CPU branch (constant_pad_nd + stack)" % seqs if kind == "pad" else
                              "first %d sequences of the shard, median of 3, reference CPU branch (mask + masked_select)" % seqs}
+        elif KERNEL_ONLY:
+            cpu = {"skipped": "--kernel-only"}
         line = {
             "metric": "to_padded_tensor HBM GB/s" if kind == "pad" else "from_padded_tensor HBM GB/s",
             "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": kernel_ms, "best_ms": best_ms, "timing": "median of 5 timed regions of `steps` steps",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 (bit copy, u16)", "data": "synthetic",
             "config": {"workload": ("FIRST %d SEQUENCES ONLY of " % SEQUENCE_LIMIT if SEQUENCE_LIMIT else "") +
                                    "config2: %d bf16 sequences (L_i,1024), L_i=clip(round(lognormal(ln200,0.6)),1,1024) "
                                    "per GPU; %s" % (4096, "to_padded_tensor(padding=0)" if kind == "pad" else
                                                     "from_padded_tensor with known sizes"),
                        "batch_per_gpu": B, "tokens_per_gpu": T, "max_len": maxL, "hidden": hidden,
-                       "algorithmic_bytes_per_gpu": alg_bytes, "token_imbalance": imb,
+                       "algorithmic_bytes_per_gpu": alg_bytes, "token_imbalance": imb, "values": values_from,
                        "l2": "inputs+outputs (%.1f GB) far larger than the 126 MB L2" % (alg_bytes / 1e9)},
             "roofline": {"bound": "hbm", "achieved": alg_bytes / (kernel_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": alg_bytes / (kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                          "frac_of_nominal_8000": alg_bytes / (kernel_ms * 1e-3) / 1e9 / 8000.0,
-                         "peak_source": peaks["source"], "traffic": NCU_TRAFFIC.get(kind)},
+                         "peak_source": peaks["source"],
+                         "traffic": None if SEQUENCE_LIMIT else alg_bytes * NCU_TRAFFIC_PER_ALG_BYTE[kind],
+                         "traffic_source": NCU_TRAFFIC_SOURCE},
             "cpu_baseline": cpu,
             "e2e": e2e,
-            "gpu_launches": args.steps,
+            "gpu_launches": 5 * args.steps,
             "clocks": clocks.summary(),
             "parity_roundtrip_bit_exact": parity_ok,
         }
+        if inverse is not None:
+            line["unpad"] = inverse
     return line
 
 
-# Per-launch DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the ncu
-# captures summarised under profiles/.  The captures ran on the first 512 (copies) / 256 (MHA) sequences;
-# reads equalled the algorithmic bytes and writes fell short of them only by the 50-55 MB still dirty in
-# L2 at kernel end, which does not grow with the batch, so the full-size figure is algorithmic - residue:
-#   pad   1.950 + 8.590 - 0.055 GB      unpad 1.950 + 1.950 - 0.051 GB
-#   QKV projection (A 310.9 MB + W 6.3 MB read, C 932.6 MB written) - 0.052 GB
-#   feed-forward up-projection (A 310.9 MB + W 8.4 MB read, C 1243.5 MB written) - 0.05 GB
-NCU_TRAFFIC = {"pad": 10.48e9, "unpad": 3.85e9, "mha": 1.20e9, "encoder": 1.51e9}
+def bind_to_gpu_numa_node(local):
+    """Pin this process's threads (and, through first touch, the pinned buffers it allocates next) to the CPUs NVML
+    reports as local to the GPU.  Returns a note for the bench line.  Reading the affinity changes no GPU setting."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        n_words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, n_words)
+        cpus = [w * 64 + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if not allowed:
+            return "no CPU of the GPU's affinity mask is available to this process"
+        os.sched_setaffinity(0, allowed)
+        torch.set_num_threads(max(1, min(len(allowed), 8)))
+        return "threads bound to %d CPUs local to GPU %d (%d..%d)" % (len(allowed), local, allowed[0], allowed[-1])
+    except Exception as e:  # NVML absent or affinity not permitted: measure unbound and say so
+        return "unbound (%s)" % type(e).__name__
 
 
 # ---------------------------------------------------------------------- reference arm
+def _reference_budget_sequences(est_full_s, steps, warmup, full, fallback):
+    """The whole configuration when `steps + warmup` passes of it fit in about three minutes of host time, else the
+    stated sub-batch."""
+    return full if est_full_s * (steps + warmup) <= 180.0 else fallback
+
+
 def run_reference(args, kind, rank, world):
-    """The reference's own CPU implementation of the path (oracle port) on the host cores; rank 0 only."""
+    """The reference's own CPU implementation of the path (oracle port) on the host cores; rank 0 only.  Imports
+    nothing of the package but its pure-Python length generators, so no native library is loaded."""
     if rank != 0:
         return None
     torch.set_num_threads(os.cpu_count() or 1)
-    L, _ = shard_lengths("pad" if kind in ("pad", "unpad") else "mha", 1, 0)
-    hidden, dtype = 1024, torch.bfloat16
-    seqs = 256
-    if kind == "pad":
-        _, nbytes, fn = cpu_pad_sample(L, hidden, dtype, seqs)
-        metric = "to_padded_tensor HBM GB/s"
-    elif kind == "unpad":
-        _, nbytes, fn = cpu_unpad_sample(L, hidden, dtype, seqs)
-        metric = "from_padded_tensor HBM GB/s"
-    else:
+    if kind in ("mha", "encoder"):
         return run_reference_mha(args, world, encoder=(kind == "encoder"))
-    for _ in range(max(1, min(args.warmup, 2))):
+    L, _ = shard_lengths("pad", 1, 0)
+    hidden, dtype = 1024, torch.bfloat16
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = 0
+    # calibrate on 128 sequences, then take the whole configuration if time and host memory allow
+    make = cpu_pad_sample if kind == "pad" else cpu_unpad_sample
+    _, nb0, fn0 = make(L, hidden, dtype, 128)
+    t0 = time_cpu(fn0, 1, 1)
+    full_bytes = 2 * (int(L.sum()) * hidden + (int(L.numel()) * int(L.max()) * hidden if kind == "pad" else int(L.sum()) * hidden))
+    est_full = t0 * full_bytes / nb0
+    seqs = _reference_budget_sequences(est_full, steps, warmup, int(L.numel()), 512)
+    if seqs == int(L.numel()) and avail < 4 * 2 * int(L.numel()) * int(L.max()) * hidden:
+        seqs = 512  # the dense result, its per-sequence pieces and the stack do not fit in host memory
+    _, nbytes, fn = make(L, hidden, dtype, seqs)
+    metric = "to_padded_tensor HBM GB/s" if kind == "pad" else "from_padded_tensor HBM GB/s"
+    for _ in range(warmup):
         fn()
-    steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(steps):
         fn()
     dt = (time.perf_counter() - t0) / steps
     v = nbytes / dt / 1e9
     cores = torch.get_num_threads()
-    sample = "each step = the first %d sequences of configuration 2 (%.2f GB algorithmic)" % (seqs, nbytes / 1e9)
+    whole = seqs == int(L.numel())
+    sample = ("each step = the whole configuration 2 (%d sequences, %.2f GB algorithmic)" if whole else
+              "each step = the first %d sequences of configuration 2 (%.2f GB algorithmic)") % (seqs, nbytes / 1e9)
     return {"impl": "reference", "metric": metric, "value": v, "unit": "GB/s", "n_gpus": world, "steps": steps,
-            "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 (bit copy, u16)", "data": "synthetic",
-            "config": {"workload": "config2 (CPU sample): " + sample},
+            "config": {"workload": "config2 on the host cores: " + sample, "whole_configuration": whole},
             "cpu_baseline": {"value": v, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
@@ -403,7 +509,7 @@ def run_reference(args, kind, rank, world):
 def cpu_mha_sample(L, E, H, dtype, seqs):
     """The reference's generic (CPU-capable) MHA, nestedtensor/csrc/mha.cpp:18-69, on the first `seqs` sequences."""
     from oracle import ntref
-    from nestedtensor_b200 import workloads
+    workloads = _pure_module("workloads")
     Ls = L[:seqs].tolist()
     g = torch.Generator().manual_seed(13)
     tensors = [torch.randn(l, E, generator=g).to(dtype) for l in Ls]
@@ -416,38 +522,47 @@ def cpu_mha_sample(L, E, H, dtype, seqs):
 
 def run_reference_mha(args, world, encoder=False):
     L, _ = shard_lengths("mha", 1, 0)
-    E, H, dtype, seqs = 1024, 16, torch.bfloat16, 64
-    if encoder:
-        from oracle import ntref
-        seqs = 32
-        Ls = L[:seqs].tolist()
-        g = torch.Generator().manual_seed(13)
-        tensors = [torch.randn(l, E, generator=g).to(dtype) for l in Ls]
-        params = _layer_params(_bert_large_layer(torch.float32, "cpu"))
-        tokens, fn = sum(Ls), (lambda: ntref.encoder_layer(tensors, H, params, "gelu_tanh", False, 1e-5))
-    else:
-        tokens, fn = cpu_mha_sample(L, E, H, dtype, seqs)
-    for _ in range(max(1, min(args.warmup, 2))):
+    E, H, dtype = 1024, 16, torch.bfloat16
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+
+    def make(seqs):
+        if encoder:
+            from oracle import ntref
+            Ls = L[:seqs].tolist()
+            g = torch.Generator().manual_seed(13)
+            tensors = [torch.randn(l, E, generator=g).to(dtype) for l in Ls]
+            params = _layer_params(_bert_large_layer(torch.float32, "cpu"))
+            return sum(Ls), (lambda: ntref.encoder_layer(tensors, H, params, "gelu_tanh", False, 1e-5))
+        return cpu_mha_sample(L, E, H, dtype, seqs)
+
+    tok0, fn0 = make(16)
+    t0 = time_cpu(fn0, 1, 1)
+    est_full = t0 * float(L.sum()) / tok0
+    seqs = _reference_budget_sequences(est_full, steps, warmup, int(L.numel()), 64)
+    tokens, fn = make(seqs)
+    for _ in range(warmup):
         fn()
-    steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(steps):
         fn()
     dt = (time.perf_counter() - t0) / steps
     v = tokens / dt
-    sample = "each step = the first %d sequences of configuration 5 (%d tokens), per-sequence fp32 loop" % (seqs, tokens)
+    whole = seqs == int(L.numel())
+    sample = ("each step = the whole configuration 5 (%d sequences, %d tokens), per-sequence fp32 loop" if whole else
+              "each step = the first %d sequences of configuration 5 (%d tokens), per-sequence fp32 loop") % (seqs, tokens)
     return {"impl": "reference", "metric": "varlen encoder layer valid tokens/s" if encoder else "varlen MHA valid tokens/s",
             "value": v, "unit": "tokens/s", "n_gpus": world,
-            "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 inputs, fp32 math", "data": "synthetic",
-            "config": {"workload": "config5 (CPU sample): " + sample},
+            "config": {"workload": "config5 on the host cores: " + sample, "whole_configuration": whole},
             "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                              "sample": sample},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
 def run_mha(args, rank, world, local, brief=False):
-    """Configuration 5: BERT-large varlen self-attention forward (bf16, E=1024, 16 heads x 64)."""
+    """Configuration 5: BERT-large varlen self-attention forward (bf16, E=1024, 16 heads x 64).  `brief` (or
+    --kernel-only) leaves out the end-to-end pass, the sustained loop and the CPU baseline."""
     import ctypes
     import nestedtensor_b200 as nt
     from nestedtensor_b200 import _ops, _cabi, workloads
@@ -458,9 +573,14 @@ def run_mha(args, rank, world, local, brief=False):
     B, T, maxL = int(L.numel()), int(L.sum()), int(L.max())
     sizes = torch.stack([L, torch.full_like(L, E)], 1).contiguous()
     flops = workloads.mha_flops(L, E)
-    gemm_flops = 2.0 * T * 3 * E * E
-    host = host_values(T * E, dtype, 20245 + rank)
-    w = workloads._mha_weights(workloads._gen(5), E, dtype)
+    attn_flops = 4.0 * E * float((L.double() ** 2).sum())
+    if world == 1 and not SEQUENCE_LIMIT:
+        w5 = workloads.config5()
+        assert torch.equal(w5.sizes[:, 0], L)
+        host, w = w5.buffer, w5.weights
+    else:
+        host = host_values(T * E, dtype, 20245 + 1000 * (rank + 1))
+        w = workloads._mha_weights(workloads._gen(5), E, dtype)
     wd = {k: v.to(device) for k, v in w.items()}
     x = nt.NestedTensor(host.to(device), sizes)
     ops = _ops.ops()
@@ -468,37 +588,72 @@ def run_mha(args, rank, world, local, brief=False):
     scaling = float(d) ** -0.5
     step = lambda: ops.bt_min_mha(H, d, 0.0, False, buf, sz, meta, wd["in_proj_weight"], wd["in_proj_bias"], scaling,
                                   wd["out_proj_weight"], wd["out_proj_bias"])
-    steps = args.steps if not brief else min(args.steps, 20)
+    steps = args.steps
     for _ in range(max(args.warmup, 3)):
         step()
+    lib = _cabi.load()
     with ClockSampler(local) as clocks:
-        ms = timed_region(step, steps, world, device)
-        ms = min(ms, timed_region(step, steps, world, device))
-        # the dominant kernel alone: QKV projection through the C ABI, same stream, same events
-        lib = _cabi.load()
+        step_ms, best_ms = timed_regions(step, steps, world, device)
+        # The same three kernels through the C ABI with an event between them, inside a loop of whole steps: per-kernel
+        # times that add up to the step (kernels timed alone, after the loop, run at other clocks and overstate it).
         qkv = torch.empty(T, 3 * E, dtype=dtype, device=device)
-        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        gemm = lambda: lib.ntb200_gemm_bias(buf.data_ptr(), wd["in_proj_weight"].data_ptr(), wd["in_proj_bias"].data_ptr(),
-                                            qkv.data_ptr(), T, 3 * E, E, 2, 0, stream)
-        for _ in range(3):
-            gemm()
-        gms = timed_region(gemm, steps, world, device) / steps
         attn_out = torch.empty(T, E, dtype=dtype, device=device)
+        y = torch.empty(T, E, dtype=dtype, device=device)
         ws_bytes = lib.ntb200_varlen_attention_workspace_bytes(B, T, H, d, 2)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
-        attn = lambda: lib.ntb200_varlen_attention(qkv.data_ptr(), attn_out.data_ptr(), meta.data_ptr(), B, T, H, d, maxL,
-                                                   scaling, 2, 0, ws.data_ptr() if ws_bytes else None, ws_bytes, stream)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def cabi_step(events=None):
+            if events is not None:
+                events[0].record()
+            lib.ntb200_gemm_bias(buf.data_ptr(), wd["in_proj_weight"].data_ptr(), wd["in_proj_bias"].data_ptr(),
+                                 qkv.data_ptr(), T, 3 * E, E, 2, 0, stream)
+            if events is not None:
+                events[1].record()
+            lib.ntb200_varlen_attention(qkv.data_ptr(), attn_out.data_ptr(), meta.data_ptr(), B, T, H, d, maxL, scaling, 2, 0,
+                                        ws.data_ptr() if ws_bytes else None, ws_bytes, stream)
+            if events is not None:
+                events[2].record()
+            lib.ntb200_gemm_bias(attn_out.data_ptr(), wd["out_proj_weight"].data_ptr(), wd["out_proj_bias"].data_ptr(),
+                                 y.data_ptr(), T, E, E, 2, 0, stream)
+            if events is not None:
+                events[3].record()
+
         for _ in range(3):
-            attn()
-        ams = timed_region(attn, steps, world, device) / steps
-    step_ms = ms / steps
+            cabi_step()
+        n_inst = max(steps, 10)
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_inst)]
+        torch.cuda.synchronize(device)
+        for e in evs:
+            cabi_step(e)
+        torch.cuda.synchronize(device)
+        seg = [sorted(e[k].elapsed_time(e[k + 1]) for e in evs) for k in range(3)]
+        whole = sorted(e[0].elapsed_time(e[3]) for e in evs)
+        med = lambda v: v[len(v) // 2]
+        kernels_ms = {"qkv_gemm": med(seg[0]), "attention": med(seg[1]), "out_proj_gemm": med(seg[2]),
+                      "sum": med(seg[0]) + med(seg[1]) + med(seg[2]), "instrumented_step": med(whole), "step": step_ms,
+                      "how": "CUDA events between the three launches of %d back-to-back steps through the C ABI, median per segment; "
+                             "attention includes its work-list kernel" % n_inst}
     total_tokens = all_sum(T, world, device)
     value = total_tokens / (step_ms * 1e-3)
     flags = lib.ntb200_device_error_flags()
 
     brief = brief or KERNEL_ONLY
+    peaks = measured_peaks()
+    sustained = None
     e2e = None
     if not brief:
+        # sustained: the step in a loop for >= 2 s, clocks sampled meanwhile (the 20-step regions above are bursts)
+        n_sus = max(steps, int(2000.0 / step_ms) + 1)
+        with ClockSampler(local) as sclk:
+            sus_ms = timed_region(step, n_sus, world, device) / n_sus
+        stf = flops / (sus_ms * 1e-3) / 1e12
+        sustained = {"value": total_tokens / (sus_ms * 1e-3), "unit": "tokens/s", "ms_per_step": sus_ms, "steps": n_sus,
+                     "seconds": sus_ms * n_sus * 1e-3, "step_tflops": stf, "frac_of_bf16_sustained": stf / peaks["bf16_tflops_sustained"],
+                     "frac_of_bf16_burst": stf / peaks["bf16_tflops"], "clocks": sclk.summary()}
+        clocks.reasons |= sclk.reasons
+
+        bind_note = bind_to_gpu_numa_node(local) if world > 1 else "not bound (single rank)"
         h_in = torch.empty(T * E, dtype=dtype).pin_memory()
         h_in.copy_(host)
         h_out = torch.empty(T * E, dtype=dtype).pin_memory()
@@ -526,17 +681,18 @@ def run_mha(args, rank, world, local, brief=False):
         e2e = {"value": total_tokens / (ems * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * T * E,
                "d2h_bytes_per_step": 2 * T * E, "ms_per_step": ems, "steps": e2e_steps,
                "api": "multi_head_attention_host (pinned host in/out, 8 ranges pipelined on 3 streams)",
-               "single_stream_value": total_tokens / (sms * 1e-3)}
+               "single_stream_value": total_tokens / (sms * 1e-3), "host_binding": bind_note}
 
     if rank != 0:
         return None
-    peaks = measured_peaks()
     tf = flops / (step_ms * 1e-3) / 1e12
-    gtf = gemm_flops / (gms * 1e-3) / 1e12
-    atf = 4.0 * E * float((L.double() ** 2).sum()) / (ams * 1e-3) / 1e12
+    gemm_flops = 2.0 * T * 3 * E * E
+    gtf = gemm_flops / (kernels_ms["qkv_gemm"] * 1e-3) / 1e12
+    atf = attn_flops / (kernels_ms["attention"] * 1e-3) / 1e12
     line = {
         "metric": "varlen MHA valid tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "best_ms": best_ms,
+        "timing": "median of 5 timed regions of `steps` steps", "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": ("FIRST %d SEQUENCES ONLY of " % SEQUENCE_LIMIT if SEQUENCE_LIMIT else "") +
                                "config5: BERT-large varlen self-attention forward, batch 1024 per GPU, 70% L~U[16,128] / "
@@ -546,22 +702,169 @@ def run_mha(args, rank, world, local, brief=False):
                    "l2": "activations per step (x, qkv, attn, out = %.2f GB) exceed the 126 MB L2" % (12 * T * E / 1e9)},
         "step_tflops": tf, "step_frac_of_bf16_peak": tf / peaks["bf16_tflops"],
         "step_frac_of_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
-        "kernels_ms": {"qkv_gemm": gms, "attention": ams, "step": step_ms},
-        "attention_tflops_valid": atf,
-        "roofline": {"bound": "tensor", "kernel": "gemm_bias_tcgen05_pair_kernel (QKV projection, M=%d N=3072 K=1024)" % T,
+        "kernels_ms": kernels_ms,
+        "attention_tflops_valid": atf, "attention_frac_of_bf16_peak": atf / peaks["bf16_tflops"],
+        "roofline": {"bound": "tensor", "kernel": "gemm_bias_tcgen05_pair_kernel (QKV projection, M=%d N=3072 K=1024), timed inside the step" % T,
                      "achieved": gtf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": gtf / peaks["bf16_tflops"],
                      "frac_of_sustained": gtf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
-                     "traffic": NCU_TRAFFIC.get("mha")},
-        "e2e": e2e, "gpu_launches": 4 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
+                     "traffic": None if SEQUENCE_LIMIT else T * NCU_TRAFFIC_GEMM_BYTES_PER_TOKEN["mha"],
+                     "traffic_source": NCU_TRAFFIC_SOURCE},
+        "sustained": sustained,
+        "e2e": e2e, "gpu_launches": 4 * 5 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
     }
-    if not brief:
+    if brief:
+        line["cpu_baseline"] = {"skipped": "--kernel-only"}
+    elif world > 1:
+        line["cpu_baseline"] = {"skipped": "measured at N=1 only (the other ranks would compete for the host cores)"}
+    else:
         torch.set_num_threads(os.cpu_count() or 1)
-        tokens, fn = cpu_mha_sample(L, E, H, dtype, 32)
+        tokens, fn = cpu_mha_sample(L, E, H, dtype, 64)
         t = time_cpu(fn, 1, 3)
         line["cpu_baseline"] = {"value": tokens / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                                "sample": "first 32 sequences (%d tokens), median of 3, per-sequence fp32 loop of the "
-                                          "reference's generic MHA" % tokens}
+                                "sample": "first 64 sequences (%d tokens), median of 3, per-sequence fp32 loop of the "
+                                          "reference's generic MHA (nestedtensor/csrc/mha.cpp:18-69)" % tokens}
     return line
+
+
+def run_small_configs(args, local):
+    """Configurations 3 and 4, device-timed on one GPU (sub-records of the default line): 4-D to_padded_tensor /
+    to_tensor_mask / from_padded_tensor on 32 fp32 images, and the BERT-base fp16 MHA step."""
+    import nestedtensor_b200 as nt
+    from nestedtensor_b200 import _ops, workloads
+    device = torch.device("cuda", local)
+    ops = _ops.ops()
+    peaks = measured_peaks()
+    n = max(args.steps, 10)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        return timed_regions(fn, n, 1, device)
+
+    def hbm(ms, nbytes):
+        g = nbytes / ms / 1e6
+        return {"ms": ms, "GB/s": g, "frac_hbm_measured": g / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+
+    w = workloads.config3()
+    a = nt.NestedTensor(w.buffer.to(device), w.sizes)
+    b, sz, meta = a._record()
+    nv = w.buffer.numel()
+    padded = ops.to_padded_tensor(b, sz, meta, 0.0)
+    npad = padded.numel()
+    c3 = {"workload": "config3: 32 fp32 images (3, H_i, W_i), H_i, W_i ~ U[400,1024]",
+          "note": "0.6 GB per call; about 1 GB moved in and out: above the 126 MB L2, but part of a call's data is served from it",
+          "to_padded_tensor": hbm(timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0))[0], 4 * (nv + npad)),
+          "to_tensor_mask": hbm(timed(lambda: ops.to_tensor_mask(b, sz, meta, None))[0], 4 * (nv + npad) + npad),
+          "from_padded_tensor": hbm(timed(lambda: ops.from_padded_tensor(padded, sz, meta))[0], 8 * nv),
+          "sizes_from_padded": hbm(timed(lambda: ops.sizes_from_padded(padded, 0.0))[0], 4 * npad)}
+    del padded, a, b
+    w = workloads.config4()
+    a = nt.NestedTensor(w.buffer.to(device), w.sizes)
+    b, sz, meta = a._record()
+    wd = {k: v.to(device) for k, v in w.weights.items()}
+    E, H = 768, 12
+    d = E // H
+    fn = lambda: ops.bt_min_mha(H, d, 0.0, False, b, sz, meta, wd["in_proj_weight"], wd["in_proj_bias"], float(d) ** -0.5,
+                                wd["out_proj_weight"], wd["out_proj_bias"])
+    ms, best = timed(fn)
+    Ls = w.sizes[:, 0]
+    fl = workloads.mha_flops(Ls, E)
+    c4 = {"workload": "config4: BERT-base varlen self-attention forward, 128 sequences L~U[32,512], E=768, 12 heads x 64, fp16",
+          "ms_per_step": ms, "best_ms": best, "tokens": int(Ls.sum()), "tokens_per_s": float(Ls.sum()) / (ms * 1e-3),
+          "step_tflops": fl / ms / 1e9, "step_frac_of_bf16_peak": fl / ms / 1e9 / peaks["bf16_tflops"],
+          "note": "0.198 TFLOP per step: a step lasts about 0.3 ms, short of filling the GPU for long"}
+    return {"config3": c3, "config4": c4}
+
+
+def run_strong(args, rank, world, local):
+    """Strong scaling of the FIXED configuration lists: configuration 2 (4096 sequences, to_padded_tensor), 5 (1024
+    sequences, MHA) and 4 (128 sequences, MHA) cut into `world` contiguous token-balanced shards, no collective on the
+    data path.  Rank 0 also runs the whole list alone (the other ranks wait), which gives the one-GPU time and the
+    result the shard outputs are compared with after an NCCL all-gather outside the timed region."""
+    import torch.distributed as dist
+    import nestedtensor_b200 as nt
+    from nestedtensor_b200 import _ops, workloads, sharding
+    device = torch.device("cuda", local)
+    ops = _ops.ops()
+    n = max(3, min(args.steps, 20))
+    out = {}
+
+    def one(name, wl, kind):
+        Ls = wl.sizes[:, 0].tolist()
+        parts = sharding.token_balanced_partition(Ls, world)
+        a, b = parts[rank]
+        sub = wl.slice(a, b)
+        E = int(wl.sizes[0, 1])
+        if kind == "mha":
+            H = wl.num_heads
+            d = E // H
+            wd = {k: v.to(device) for k, v in wl.weights.items()}
+            run = lambda x: ops.bt_min_mha(H, d, 0.0, False, *x._record(), wd["in_proj_weight"], wd["in_proj_bias"], float(d) ** -0.5,
+                                           wd["out_proj_weight"], wd["out_proj_bias"])
+            work = lambda lens: sum(8.0 * E * E * l + 4.0 * E * l * l for l in lens)
+        else:
+            run = lambda x: ops.to_padded_tensor(*x._record(), 0.0)
+            work = lambda lens: float(sum(lens)) if lens else 0.0
+        have = b > a
+        xs = nt.NestedTensor(sub.buffer.to(device), sub.sizes) if have else None
+        shard_fn = (lambda: run(xs)) if have else (lambda: None)
+        for _ in range(3):
+            shard_fn()
+        t_n = timed_region(shard_fn, n, world, device) / n  # max over ranks
+        res = run(xs) if have else torch.empty(0, dtype=wl.dtype, device=device)
+        # one GPU, whole list (rank 0 alone; the others wait at the barrier inside the next collective)
+        t_1 = torch.zeros(1, dtype=torch.float64, device=device)
+        full = None
+        if rank == 0:
+            xf = nt.NestedTensor(wl.buffer.to(device), wl.sizes)
+            for _ in range(3):
+                run(xf)
+            t_1[0] = timed_region(lambda: run(xf), n, 1, device) / n
+            full = run(xf)
+        dist.broadcast(t_1, 0)
+        # verification, outside every timed region: all-gather the shard outputs over NCCL, compare on rank 0
+        if kind == "mha":
+            gathered, gsz = sharding.gather_ragged(res.reshape(-1), sub.sizes if have else torch.zeros((0, 2), dtype=torch.int64))
+            ok, err = None, None
+            if rank == 0:
+                err = float((gathered.float() - full.reshape(-1).float()).abs().max())
+                ok = bool(torch.equal(gsz, wl.sizes)) and err <= 2e-2
+        else:
+            shape = torch.tensor([list(res.shape)], dtype=torch.int64) if have else torch.zeros((0, 3), dtype=torch.int64)
+            gathered, gsz = sharding.gather_ragged(res.reshape(-1), shape)
+            ok, err = None, None
+            if rank == 0:
+                ok, off, row = True, 0, 0
+                for r_b, r_l, r_e in gsz.tolist():
+                    piece = gathered[off:off + r_b * r_l * r_e].view(r_b, r_l, r_e)
+                    ref = full[row:row + r_b]
+                    ok = ok and bool(torch.equal(piece.view(torch.int16), ref[:, :r_l].view(torch.int16)))
+                    ok = ok and int(ref[:, r_l:].view(torch.int16).count_nonzero()) == 0
+                    off += r_b * r_l * r_e
+                    row += r_b
+                ok = ok and row == wl.batch
+                err = 0.0 if ok else None
+        del gathered
+        toks = [sum(Ls[x:y]) for x, y in parts]
+        wk = [work(Ls[x:y]) for x, y in parts]
+        t1 = float(t_1.item())
+        out[name] = {"sequences": wl.batch, "tokens": int(sum(Ls)), "ms_1gpu": t1, "ms_%dgpu" % world: t_n,
+                     "tokens_per_s": float(sum(Ls)) / (t_n * 1e-3), "speedup": t1 / t_n, "efficiency": t1 / (t_n * world),
+                     "token_imbalance": max(toks) / (sum(toks) / world), "work_imbalance": max(wk) / (sum(wk) / world),
+                     "sequences_per_rank": [y - x for x, y in parts], "verified": ok, "max_abs_vs_1gpu": err,
+                     "verification": "shard outputs all-gathered over NCCL (sharding.gather_ragged), compared on rank 0 with "
+                                     "the one-GPU result of the whole list" + (" (max-abs <= 2e-2)" if kind == "mha" else " (bit-exact)")}
+        torch.cuda.empty_cache()
+
+    one("config2_pad", workloads.config2(), "pad")
+    one("config5_mha", workloads.config5(), "mha")
+    one("config4_mha", workloads.config4(), "mha")
+    eff = [v["efficiency"] for v in out.values()]
+    out["efficiency"] = out["config5_mha"]["efficiency"]
+    out["verified"] = all(v["verified"] for k, v in out.items() if isinstance(v, dict)) if rank == 0 else None
+    out["note"] = ("fixed lists, contiguous token-balanced shards, no collective on the data path; efficiency = "
+                   "t(1 GPU) / (N * t(N GPUs, slowest rank)); `efficiency` at the top is configuration 5's")
+    return out
 
 
 def run_kernels(args, local):
@@ -581,6 +884,8 @@ def run_kernels(args, local):
         ms = timed_region(fn, n, 1, device) / n
         return ms
 
+    only = args.only
+
     def add(name, config, ms, nbytes=None, flops=None):
         r = {"op": name, "config": config, "ms": ms}
         if nbytes is not None:
@@ -592,6 +897,27 @@ def run_kernels(args, local):
         rows.append(r)
 
     n = max(args.steps, 5)
+
+    def image_path():
+        # image-shaped path: 32 fp16 feature maps (256, H_i, W_i), H_i, W_i in [100, 168] (a stride-8 backbone level)
+        gi = torch.Generator().manual_seed(20248)
+        hw = torch.randint(100, 169, (32, 2), generator=gi)
+        isz = torch.cat([torch.full((32, 1), 256), hw], 1).contiguous()
+        nimg = int((isz[:, 0] * isz[:, 1] * isz[:, 2]).sum())
+        img = nt.NestedTensor(torch.randn(nimg, device=device).to(torch.float16), isz)
+        add("transpose_nchw_nhwc", "32 x (256, 100-168, 100-168) fp16", timed(lambda: nt.nn.transpose_nchw_nhwc(img), n), 4 * nimg)
+        nhwc = nt.nn.transpose_nchw_nhwc(img)
+        add("transpose_nhwc_nchw", "same batch", timed(lambda: nt.nn.transpose_nhwc_nchw(nhwc), n), 4 * nimg)
+        w11 = (torch.randn(256, 256, 1, 1, device=device) * 0.05).to(torch.float16)
+        add("conv2d 1x1 (transpose + packed GEMM + transpose)", "same batch, 256 -> 256 channels",
+            timed(lambda: nt.nn.conv2d(img, w11), n), None, 2.0 * (nimg // 256) * 256 * 256)
+        del img, nhwc
+
+    if only == "transpose":
+        image_path()
+        from nestedtensor_b200 import _cabi
+        return {"metric": "per-operator timings (--only transpose)", "unit": "ms", "n_gpus": 1, "steps": n, "data": "synthetic",
+                "peaks": peaks, "rows": rows, "device_error_flags": _cabi.load().ntb200_device_error_flags()}
     # configuration 1: 64 fp32 (L_i, 256)
     w = workloads.config1()
     a = nt.NestedTensor(w.buffer.to(device), w.sizes)
@@ -682,18 +1008,7 @@ def run_kernels(args, local):
         fl = 4.0 * E * 100 * float(lk.sum()) + 2.0 * E * E * (2 * 3200 + 2 * float(lk.sum()))
         add("MultiheadAttention(query != key)", "DETR-like 32 x (100 queries, 400-1200 keys), E=%d, %d heads x %d" % (E, H, E // H),
             ms, None, fl)
-    # image-shaped path: 32 fp16 feature maps (256, H_i, W_i), H_i, W_i in [100, 168] (a stride-8 backbone level)
-    hw = torch.randint(100, 169, (32, 2), generator=g)
-    isz = torch.cat([torch.full((32, 1), 256), hw], 1).contiguous()
-    nimg = int((isz[:, 0] * isz[:, 1] * isz[:, 2]).sum())
-    img = nt.NestedTensor(torch.randn(nimg, device=device).to(torch.float16), isz)
-    add("transpose_nchw_nhwc", "32 x (256, 100-168, 100-168) fp16", timed(lambda: nt.nn.transpose_nchw_nhwc(img), n), 4 * nimg)
-    nhwc = nt.nn.transpose_nchw_nhwc(img)
-    add("transpose_nhwc_nchw", "same batch", timed(lambda: nt.nn.transpose_nhwc_nchw(nhwc), n), 4 * nimg)
-    w11 = (torch.randn(256, 256, 1, 1, device=device) * 0.05).to(torch.float16)
-    add("conv2d 1x1 (transpose + packed GEMM + transpose)", "same batch, 256 -> 256 channels",
-        timed(lambda: nt.nn.conv2d(img, w11), n), None, 2.0 * (nimg // 256) * 256 * 256)
-    del img, nhwc
+    image_path()
     from nestedtensor_b200 import _cabi
     return {"metric": "per-operator timings", "unit": "ms", "n_gpus": 1, "steps": n, "data": "synthetic",
             "peaks": peaks, "rows": rows, "device_error_flags": _cabi.load().ntb200_device_error_flags()}
@@ -741,8 +1056,7 @@ def run_encoder(args, rank, world, local):
         step()
     lib = _cabi.load()
     with ClockSampler(local) as clocks:
-        ms = timed_region(step, steps, world, device)
-        ms = min(ms, timed_region(step, steps, world, device))
+        step_ms, best_ms = timed_regions(step, steps, world, device)
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         # the dominant kernel alone: feed-forward up-projection with the fused bias + GELU epilogue
         a = torch.randn(T, E, device=device).to(dtype)
@@ -760,7 +1074,6 @@ def run_encoder(args, rank, world, local):
             ln()
         lnms = timed_region(ln, steps, world, device) / steps
         del h
-    step_ms = ms / steps
     total_tokens = all_sum(T, world, device)
     value = total_tokens / (step_ms * 1e-3)
     flags = lib.ntb200_device_error_flags()
@@ -789,7 +1102,8 @@ def run_encoder(args, rank, world, local):
     ln_gbs = 4.0 * T * E / (lnms * 1e-3) / 1e9
     line = {
         "metric": "varlen encoder layer valid tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "best_ms": best_ms,
+        "timing": "median of 5 timed regions of `steps` steps", "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": ("FIRST %d SEQUENCES ONLY of " % SEQUENCE_LIMIT if SEQUENCE_LIMIT else "") +
                                "config5 batch (1024 sequences per GPU, 70% L~U[16,128] / 30% L~U[128,512]) through one BERT-large "
@@ -805,8 +1119,9 @@ def run_encoder(args, rank, world, local):
                                                   "M=%d N=4096 K=1024)" % T,
                      "achieved": f1tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": f1tf / peaks["bf16_tflops"],
                      "frac_of_sustained": f1tf / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
-                     "traffic": NCU_TRAFFIC.get("encoder")},
-        "e2e": e2e, "gpu_launches": 8 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
+                     "traffic": None if SEQUENCE_LIMIT else T * NCU_TRAFFIC_GEMM_BYTES_PER_TOKEN["encoder"],
+                     "traffic_source": NCU_TRAFFIC_SOURCE},
+        "e2e": e2e, "gpu_launches": 8 * 5 * steps, "clocks": clocks.summary(), "device_error_flags": flags,
     }
     if not KERNEL_ONLY:
         from oracle import ntref
@@ -836,6 +1151,8 @@ def main():
     ap.add_argument("--sequences", type=int, default=0,
                     help="use only the first N sequences of each GPU's batch (small cases for profiler captures; "
                          "the line then does not describe the named configuration)")
+    ap.add_argument("--only", default="", help="kernels workload: run only this group (transpose) so that a profiler capture "
+                                               "holds no more than the group's own data on the device")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end pass, the CPU baseline and the parity spot check")
     args = ap.parse_args()
@@ -867,16 +1184,34 @@ def main():
         elif args.workload in ("pad", "unpad"):
             line = run_copy(args, args.workload, rank, world, local)
             if args.workload == "pad" and not args.no_mha:
-                # the metric has two halves; attach a short MHA (configuration 5) measurement to the same line
+                # the metric has two halves: the same line carries the full MHA (configuration 5) record, the
+                # device-timed figures of configurations 3 and 4, and (N > 1) the strong-scaling record
                 torch.cuda.empty_cache()
-                mha = run_mha(args, rank, world, local, brief=True)
+                mha = run_mha(args, rank, world, local)
                 if line is not None and mha is not None:
-                    line["mha"] = {k: mha[k] for k in ("metric", "value", "unit", "ms_per_step", "step_tflops",
-                                                        "step_frac_of_bf16_peak", "kernels_ms", "roofline", "config")}
+                    line["mha"] = {k: mha[k] for k in ("metric", "value", "unit", "ms_per_step", "best_ms", "step_tflops",
+                                                        "step_frac_of_bf16_peak", "step_frac_of_bf16_sustained", "kernels_ms",
+                                                        "attention_tflops_valid", "roofline", "sustained", "e2e", "cpu_baseline",
+                                                        "config", "device_error_flags")}
+                    line["gpu_launches"] += mha["gpu_launches"]
+                torch.cuda.empty_cache()
+                if rank == 0 and not KERNEL_ONLY and not SEQUENCE_LIMIT:
+                    small = run_small_configs(args, local)
+                    if line is not None:
+                        line.update(small)
+                if world > 1 and not KERNEL_ONLY and not SEQUENCE_LIMIT:
+                    torch.cuda.empty_cache()
+                    strong = run_strong(args, rank, world, local)
+                    if line is not None:
+                        line["strong"] = strong
         elif args.workload == "encoder":
             line = run_encoder(args, rank, world, local)
         else:
             line = run_mha(args, rank, world, local)
+            if world > 1 and not KERNEL_ONLY and not SEQUENCE_LIMIT:
+                strong = run_strong(args, rank, world, local)
+                if line is not None:
+                    line["strong"] = strong
         if rank == 0 and line is not None:
             print(json.dumps(line), flush=True)
     finally:

@@ -459,15 +459,11 @@ template <typename T, int D>
 int launch_attn_fa(const QkvSrc& s, void* out, int64_t batch, int H, int64_t max_len_q, float scale, cudaStream_t st) {
   constexpr int kSmem = 5 * kBKV * D * 2;  // 20 / 40 / 80 KB
   if (kSmem > 48 * 1024) {
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return NTB200_LAUNCH_FAILED;
-    if (!configured[dev]) {
-      if (cudaFuncSetAttribute(attn_fa_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
-        return NTB200_LAUNCH_FAILED;
-      configured[dev] = true;
-    }
+    static std::atomic<int> configured[kMaxDevices];
+    if (!once_per_device(configured, [] {
+          return cudaFuncSetAttribute(attn_fa_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) == cudaSuccess;
+        }))
+      return NTB200_LAUNCH_FAILED;
   }
   dim3 grid((unsigned)ceil_div(max_len_q, kBQ), (unsigned)H, (unsigned)batch);
   attn_fa_kernel<T, D><<<grid, kFaThreads, kSmem, st>>>(static_cast<const T*>(s.q), s.ldq, static_cast<const T*>(s.k), s.ldk,

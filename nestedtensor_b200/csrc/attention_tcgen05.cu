@@ -26,29 +26,18 @@ namespace {
 
 __device__ int g_attn_error = 0;  // bit 0 producer, 1 MMA issuer, 2 softmax
 
-#ifdef NTB200_ATTN_TRACE
-// Timing probe (development builds only): SM clock at the phase boundaries of CTA 0's first blocks.
-constexpr int kTraceBlocks = 96, kTraceSlots = 16;
-__device__ long long g_trace[kTraceBlocks * kTraceSlots];
-__device__ long long g_cta_info[1024 * 3];  // per CTA: SM id, start and end time (ns)
-__device__ long long g_pv_issue[32 * 12];   // SM clock before each PV MMA of CTA 0's first blocks
-#define NTB200_TRACE(g, slot) \
-  do { if (blockIdx.x == 0 && (g) < (uint32_t)kTraceBlocks) g_trace[(g) * kTraceSlots + (slot)] = clock64(); } while (0)
-#else
-#define NTB200_TRACE(g, slot) do { } while (0)
-#endif
-
 constexpr int kQT = 128;   // query rows per CTA (TMEM lanes)
 constexpr int kKV = 128;   // keys per block
 constexpr int kHD = 64;    // head dim
 constexpr int kTile = kQT * kHD * 2;  // 16 KB: one 128 x 64 two-byte tile
 constexpr int kStages = 2;
-#ifndef NTB200_ATTN_POLY_PAIRS
-#define NTB200_ATTN_POLY_PAIRS 0xaa
-#endif
 // Of the 16 key pairs of a 32-key chunk, pair 2k+1 is exponentiated by the polynomial when bit k is set
-// (0xff: half of all exponentials, 0xaa: a quarter, 0: none), the others on the MUFU unit.
-constexpr unsigned kPolyPairs = NTB200_ATTN_POLY_PAIRS;
+// (0xff: half of all exponentials, 0xaa: a quarter, 0: none), the others on the MUFU unit.  A quarter measured
+// best on B200 at the BERT-large batch (none: +1 %, half: +6 %).
+constexpr unsigned kPolyPairs = 0xaa;
+// A row's reference maximum is raised (and its running output rescaled) only when a block's maximum exceeds it
+// by more than this many powers of two.
+constexpr float kLazyRescale = 8.0f;
 constexpr int kTmemCols = 256;        // S: columns [0,128), P: [128,192), O: [192,256)
 constexpr int kPCol = 128;
 constexpr int kOCol = 192;
@@ -159,14 +148,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
                     const int4* __restrict__ items, const int* __restrict__ count, int H, float scale_log2e) {
   const int n_items = *count;
   if ((int64_t)blockIdx.x >= (int64_t)n_items * H) return;
-#ifdef NTB200_ATTN_TRACE
-  if (threadIdx.x == 0 && blockIdx.x < 1024) {
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    g_cta_info[blockIdx.x * 3 + 0] = smid;
-    g_cta_info[blockIdx.x * 3 + 1] = (long long)ptx::globaltimer_ns();
-  }
-#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kTile * (2 + 2 * kStages));
@@ -293,9 +274,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       int4 rec_a = fetch(next(ia));
       auto issue_qk = [&]() -> bool {
         const uint32_t s = ga % kStages, ph = (ga / kStages) & 1;
-        NTB200_TRACE(ga, 0);
         if (!wait_or_abort(ptx::smem_u32(&ctrl->full_k[s]), ph, &ctrl->abort)) return false;
-        NTB200_TRACE(ga, 1);
         ptx::tc_fence_after_sync();
         int nvalid = a.L - ja * kKV;
         nvalid = nvalid > kKV ? kKV : nvalid;
@@ -306,7 +285,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         for (int k = 0; k < kHD / 16; ++k) ptx::umma_f16(t_s, dq + 2 * k, dk + 2 * k, idesc_qk, k != 0 ? 1u : 0u);
         ptx::umma_commit(ptx::smem_u32(&ctrl->empty_k[s]));
         ptx::umma_commit(ptx::smem_u32(&ctrl->s_ready));
-        NTB200_TRACE(ga, 2);
         ++ga;
         if (++ja == a.n_blk) {
           ja = 0;
@@ -329,9 +307,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
             if (!wait_or_abort(ptx::smem_u32(&ctrl->s_free), gb & 1, &ctrl->abort)) { ok = false; break; }
             if (!issue_qk()) { ok = false; break; }
           }
-          NTB200_TRACE(gb, 3);
           if (!wait_or_abort(ptx::smem_u32(&ctrl->p_ready), gb & 1, &ctrl->abort)) { ok = false; break; }
-          NTB200_TRACE(gb, 4);
           const uint32_t s = gb % kStages;
           if (!wait_or_abort(ptx::smem_u32(&ctrl->full_v[s]), (gb / kStages) & 1, &ctrl->abort)) { ok = false; break; }
           ptx::tc_fence_after_sync();
@@ -341,24 +317,11 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           const uint64_t dv = desc_v0 + (uint64_t)(s * (kTile >> 4));
 #pragma unroll
           for (int ks = 0; ks < kKV / 16; ++ks) {
-#ifdef NTB200_ATTN_TRACE
-            if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + ks] = clock64();
-#endif
             if (ks < ksteps)
               ptx::umma_f16_ts(t_o, t_p + ks * 8, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (jb | ks) != 0 ? 1u : 0u);
           }
-#ifdef NTB200_ATTN_TRACE
-          if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 8] = clock64();
-#endif
           ptx::umma_commit(ptx::smem_u32(&ctrl->empty_v[s]));
-#ifdef NTB200_ATTN_TRACE
-          if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 9] = clock64();
-#endif
           ptx::umma_commit(ptx::smem_u32(&ctrl->o_ready));
-#ifdef NTB200_ATTN_TRACE
-          if (blockIdx.x == 0 && gb < 32) g_pv_issue[gb * 12 + 10] = clock64();
-#endif
-          NTB200_TRACE(gb, 5);
         }
       }
       if (!ok) {
@@ -421,9 +384,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       const bool warp_active = it.q0 + q * 32 < it.L;  // warp-uniform
       float m = -INFINITY, l = 0.0f;
       for (int j = 0; j < it.n_blk; ++j, ++g) {
-        if (threadIdx.x == 0) NTB200_TRACE(g, 6);
         if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->s_ready), g & 1, &ctrl->abort)) ok = false;
-        if (threadIdx.x == 0) NTB200_TRACE(g, 7);
         int nvalid = it.L - j * kKV;
         nvalid = nvalid > kKV ? kKV : nvalid;
         const int nchunks = (nvalid + 31) >> 5;
@@ -440,19 +401,23 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->s_free));
-        if (threadIdx.x == 0) NTB200_TRACE(g, 8);
         float m_new = m, corr = 1.0f;
         bool any_up = false;
         if (ok && warp_active) {
           // Keys past the end of the sequence become -inf once, here, so that the maximum and the exponentials
           // below need no per-element predicate (only the last 32-key chunk of a block can be ragged).
+          // (Written as a loop of zero or one trips: as a plain `if` the compiler predicates the 128 selects and
+          // issues them for every block, ragged or not - about 230 cycles per block on the measured build.)
+#pragma unroll 1
+          for (int ragged = (nvalid & 31) != 0 ? 1 : 0; ragged > 0; --ragged) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            // (a range test, not "c == nchunks - 1": the latter is turned into a run-time index and sends the
-            // row to local memory)
-            if (nvalid > c * 32 && nvalid < (c + 1) * 32) {
+            for (int c = 0; c < 4; ++c) {
+              // (a range test, not "c == nchunks - 1": the latter is turned into a run-time index and sends the
+              // row to local memory)
+              if (nvalid > c * 32 && nvalid < (c + 1) * 32) {
 #pragma unroll
-              for (int k = 0; k < 32; ++k) sv[c][k] = (c * 32 + k >= nvalid) ? 0xff800000u : sv[c][k];
+                for (int k = 0; k < 32; ++k) sv[c][k] = (c * 32 + k >= nvalid) ? 0xff800000u : sv[c][k];
+              }
             }
           }
           // row maximum, four independent chains of three-input maxima
@@ -469,12 +434,20 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
               }
             }
           }
-          const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-          m_new = fmaxf(m, mx * scale_log2e);
-          corr = ptx::ex2_approx(m - m_new);  // 0 for the first block
-          any_up = __any_sync(0xffffffffu, m_new > m);
+          const float mxs = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2e;
+          if (j == 0) {
+            m_new = mxs;  // the first block of an item: O is overwritten and the row sum starts at zero
+          } else {
+            // Lazy rescaling: while no row of the warp exceeds its reference maximum by more than kLazyRescale, the
+            // reference stays and P simply grows up to 2^kLazyRescale, which fp32 sums and 16-bit P hold without
+            // loss; the final division by the row sum cancels the offset.
+            any_up = __any_sync(0xffffffffu, mxs > m + kLazyRescale);
+            if (any_up) {
+              m_new = fmaxf(m, mxs);
+              corr = ptx::ex2_approx(m - m_new);
+            }
+          }
         }
-        if (threadIdx.x == 0) NTB200_TRACE(g, 9);
         // PV of the previous block must have retired before P is overwritten / O is rescaled
         if (ok && g > 0 && !wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
         if (ok && j == 0 && pend.any) {
@@ -486,8 +459,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
         }
         if (ok && warp_active) {
           ptx::tc_fence_after_sync();
-          if (j > 0 && any_up) {
-            // rescale the running output (skipped when no row of the warp raised its maximum)
+          if (any_up) {
+            // rescale the running output (only when some row of the warp raised its reference maximum)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {  // 16 columns at a time: the S row stays live in registers
               uint32_t r0[16];
@@ -498,7 +471,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
               ptx::tmem_st_32x32b_x16(t_o + c * 16, r0);
             }
           }
-          if (threadIdx.x == 0) NTB200_TRACE(g, 10);
           // P = exp2(S*scale*log2e - m_new), packed two per column.  A quarter of the exponentials go through
           // a polynomial on the FMA pipe instead of the MUFU unit (16 results per clock per SM); measured at
           // the BERT-large workload a quarter beats none, three eighths and a half, because the polynomial
@@ -539,7 +511,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           l = l * corr + rs;
           m = m_new;
           ptx::tmem_st_wait();
-          if (threadIdx.x == 0) NTB200_TRACE(g, 11);
         }
         ptx::tc_fence_before_sync();
         __syncwarp();
@@ -570,9 +541,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-#ifdef NTB200_ATTN_TRACE
-  if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta_info[blockIdx.x * 3 + 2] = (long long)ptx::globaltimer_ns();
-#endif
   if (warp == 5) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
@@ -610,12 +578,11 @@ int launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, in
   if (fn(&map, dt, 2, const_cast<void*>(qkv), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return NTB200_LAUNCH_FAILED;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_tcgen05_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess)
-      return NTB200_LAUNCH_FAILED;
-    attr_set = true;
-  }
+  static std::atomic<int> attr_set[kMaxDevices];
+  if (!once_per_device(attr_set, [] {
+        return cudaFuncSetAttribute(attn_tcgen05_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) == cudaSuccess;
+      }))
+    return NTB200_LAUNCH_FAILED;
   const int64_t capacity = attn_tcgen05_item_capacity(batch, total_tokens);
   int* count = static_cast<int*>(workspace);
   int4* items = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + 16);
@@ -649,32 +616,6 @@ int attn_tcgen05_launch(const void* qkv, void* out, const int64_t* offsets, int6
   return launch<1>(qkv, out, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
 }
 
-#ifdef NTB200_ATTN_TRACE
-extern "C" int ntb200_attn_occupancy2(int threads, int smem) {
-  int nb = -1;
-  cudaFuncSetAttribute(attn_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, attn_tcgen05_kernel<1>, threads, smem);
-  return nb;
-}
-extern "C" int ntb200_attn_occupancy(void) {
-  int nb = -1;
-  cudaFuncSetAttribute(attn_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, attn_tcgen05_kernel<1>, kAttnThreads, kAttnSmem);
-  cudaFuncAttributes fa;
-  cudaFuncGetAttributes(&fa, attn_tcgen05_kernel<1>);
-  return nb * 1000 + fa.numRegs;
-}
-extern "C" int ntb200_attn_pv_issue_read(long long* h_out, int n) {
-  return cudaMemcpyFromSymbol(h_out, g_pv_issue, sizeof(long long) * (n < 384 ? n : 384)) == cudaSuccess ? 0 : -1;
-}
-extern "C" int ntb200_attn_cta_info_read(long long* h_out, int n) {
-  return cudaMemcpyFromSymbol(h_out, g_cta_info, sizeof(long long) * (n < 3072 ? n : 3072)) == cudaSuccess ? 0 : -1;
-}
-extern "C" int ntb200_attn_trace_read(long long* h_out, int n) {
-  const int total = kTraceBlocks * kTraceSlots;
-  return cudaMemcpyFromSymbol(h_out, g_trace, sizeof(long long) * (n < total ? n : total)) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int attn_tcgen05_error_flags_read_and_clear() {
   int v = 0;

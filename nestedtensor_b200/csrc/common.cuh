@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "ntb200.h"
 
 namespace ntb200 {
@@ -81,22 +83,24 @@ struct ElemBits<4> { using T = uint32_t; };
 template <>
 struct ElemBits<8> { using T = uint64_t; };
 
-// 16-byte global accesses.  Measured on B200 at the 4096 x (L_i, 1024) bf16 workload: default-cached
-// loads and stores beat the streaming (.cs) variants (pad 6.62 vs 6.22 TB/s, unpad 6.31 vs 5.72 TB/s), so
-// the plain forms are the default; NTB200_COPY_STREAM_LD / _ST select the streaming forms for experiments.
-__device__ __forceinline__ uint4 ld_global_16_stream(const void* p) {
-#ifdef NTB200_COPY_STREAM_LD
-  return __ldcs(reinterpret_cast<const uint4*>(p));
-#else
-  return *reinterpret_cast<const uint4*>(p);
-#endif
-}
-__device__ __forceinline__ void st_global_16_stream(void* p, const uint4& v) {
-#ifdef NTB200_COPY_STREAM_ST
-  __stcs(reinterpret_cast<uint4*>(p), v);
-#else
-  *reinterpret_cast<uint4*>(p) = v;
-#endif
+// 16-byte global accesses of the copy kernels.  Measured on B200 at the 4096 x (L_i, 1024) bf16 workload: default-cached
+// loads and stores beat the streaming (.cs) forms (pad 6.62 vs 6.22 TB/s, unpad 6.31 vs 5.72 TB/s).
+__device__ __forceinline__ uint4 ld_global_16_stream(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st_global_16_stream(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// One-time, per-device host set-up (cudaFuncSetAttribute and occupancy queries apply to the current device only, so
+// a process that drives several GPUs must repeat them on each).  `done` is an array of kMaxDevices flags; `setup`
+// runs with the calling thread's current device and returns false on failure.  Two threads racing on the same
+// device may both run `setup`, which is idempotent.
+constexpr int kMaxDevices = 64;
+template <typename F>
+inline bool once_per_device(std::atomic<int>* done, F&& setup) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+  if (done[dev].load(std::memory_order_acquire) != 0) return true;
+  if (!setup()) return false;
+  done[dev].store(1, std::memory_order_release);
+  return true;
 }
 
 inline int status_from_cuda(cudaError_t e) { return e == cudaSuccess ? NTB200_OK : NTB200_LAUNCH_FAILED; }

@@ -591,12 +591,12 @@ int launch_tcgen05(const void* A, const void* W, const void* bias, const void* r
   CUtensorMap map_a, map_w;
   if (!make_map_2d(&map_a, A, dtype, (uint64_t)M, (uint64_t)K, kBM)) return NTB200_LAUNCH_FAILED;
   if (!make_map_2d(&map_w, W, dtype, (uint64_t)N, (uint64_t)K, kBN)) return NTB200_LAUNCH_FAILED;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bias_tcgen05_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
-      return NTB200_LAUNCH_FAILED;
-    attr_set = true;
-  }
+  static std::atomic<int> attr_set[kMaxDevices];
+  if (!once_per_device(attr_set, [] {
+        return cudaFuncSetAttribute(gemm_bias_tcgen05_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) ==
+               cudaSuccess;
+      }))
+    return NTB200_LAUNCH_FAILED;
   const int num_tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
   int dev = 0, sms = kNumSMs;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -611,12 +611,12 @@ int launch_tcgen05_pair(const void* A, const void* W, const void* bias, const vo
   CUtensorMap map_a, map_w;
   if (!make_map_2d(&map_a, A, dtype, (uint64_t)M, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
   if (!make_map_2d(&map_w, W, dtype, (uint64_t)N, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bias_tcgen05_pair_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, k2Smem) != cudaSuccess)
-      return NTB200_LAUNCH_FAILED;
-    attr_set = true;
-  }
+  static std::atomic<int> attr_set[kMaxDevices];
+  if (!once_per_device(attr_set, [] {
+        return cudaFuncSetAttribute(gemm_bias_tcgen05_pair_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, k2Smem) ==
+               cudaSuccess;
+      }))
+    return NTB200_LAUNCH_FAILED;
   const int num_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   int dev = 0, sms = kNumSMs;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -632,13 +632,16 @@ int launch_tcgen05_pair(const void* A, const void* W, const void* bias, const vo
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   // how many CTA pairs can be resident at once (GPCs with an odd SM count leave one SM without a partner)
-  static int max_pairs = 0;
+  static std::atomic<int> max_pairs_of[kMaxDevices];
+  if (dev < 0 || dev >= kMaxDevices) return NTB200_LAUNCH_FAILED;
+  int max_pairs = max_pairs_of[dev].load(std::memory_order_relaxed);
   if (max_pairs == 0) {
     cfg.gridDim = dim3(2 * (sms / 2));
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, gemm_bias_tcgen05_pair_kernel<FMT>, &cfg) == cudaSuccess && n > 0) max_pairs = n;
     else max_pairs = sms / 2;
     (void)cudaGetLastError();
+    max_pairs_of[dev].store(max_pairs, std::memory_order_relaxed);
   }
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
   cfg.gridDim = dim3(2 * pairs);

@@ -16,20 +16,10 @@
 namespace ntb200 {
 namespace {
 
-#ifndef NTB200_COPY_THREADS
-#define NTB200_COPY_THREADS 256
-#endif
-#ifndef NTB200_COPY_VECS
-#define NTB200_COPY_VECS 8
-#endif
-#ifndef NTB200_PAD_PHASED
-#define NTB200_PAD_PHASED 1   // two-pass kernel: 1 = all loads of a tile, then all stores; 0 = store each vector at once
-#endif
-#ifndef NTB200_PAD_MINBLOCKS
-#define NTB200_PAD_MINBLOCKS 1
-#endif
-constexpr int kThreads = NTB200_COPY_THREADS;
-constexpr int kVecPerThread = NTB200_COPY_VECS;  // 16-byte vectors per thread per tile (32 KB tiles measured best)
+// Tile shape of the copy kernels, fixed after a sweep on B200 at the 4096 x (L_i, 1024) bf16 batch: 256 threads x 8
+// 16-byte vectors = 32 KB per tile, all loads of a tile issued before its stores.
+constexpr int kThreads = 256;
+constexpr int kVecPerThread = 8;
 
 // ------------------------------------------------------------------------------ pad
 struct PadParams {
@@ -256,7 +246,7 @@ __device__ __forceinline__ PadPos<ND, MASK, BIG> pad_locate(const PadParams& p, 
 // while carrying the indices over the boundary.  Keeping the boundary code out of the unrolled body keeps
 // the kernels small: a warp takes the boundary path whenever one of its 32 vectors needs it.
 template <int ES, int ND, bool MASK, bool BIG>
-__global__ void __launch_bounds__(kThreads, NTB200_PAD_MINBLOCKS) pad_kernel(const PadParams p) {
+__global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
   using E = typename ElemBits<ES>::T;
   using IP = IdxPolicy<BIG>;
   using I = typename IP::T;
@@ -319,17 +309,12 @@ __global__ void __launch_bounds__(kThreads, NTB200_PAD_MINBLOCKS) pad_kernel(con
         else out.e[k] = MASK ? (E)0 : padv;
       }
     }
-#if !NTB200_PAD_PHASED
-    st_global_16_stream(dst + e, out.v);
-#endif
   }
-#if NTB200_PAD_PHASED
   // pass 1b: the stores
 #pragma unroll
   for (int u = 0; u < kVecPerThread; ++u) {
     if (ready & (1u << u)) st_global_16_stream(dst + tile_e0 + (uint32_t)(u * kThreads + threadIdx.x) * VE, val[u].v);
   }
-#endif
 
   // pass 2: the flagged vectors
 #pragma unroll 1
@@ -967,7 +952,6 @@ static __device__ __align__(256) int64_t g_static_block_sums[kStaticScanBlocks];
 
 // In host code `g_static_block_sums` is only a handle for the runtime, not a device address, so the
 // address the kernels receive is looked up once per device with cudaGetSymbolAddress.
-constexpr int kMaxDevices = 64;
 int64_t* g_static_block_sums_addr[kMaxDevices] = {};
 
 int static_block_sums_for_current_device(int64_t** out) {
