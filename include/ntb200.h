@@ -5,12 +5,15 @@
  * Conventions for every entry point
  *   - plain pointers and sizes only; all data pointers are DEVICE pointers unless the
  *     parameter name starts with `h_` (host);
- *   - returns NTB200_OK (0) or a negative ntb200_status; never throws, never
- *     synchronises, never allocates (scratch memory, where a kernel needs it, is passed
- *     in by the caller and sized by the matching *_workspace_bytes function);
+ *   - returns NTB200_OK (0) or a negative ntb200_status; never throws, never allocates
+ *     (scratch memory, where a kernel needs it, is passed in by the caller and sized by the
+ *     matching *_workspace_bytes function), and never synchronises - with two exceptions
+ *     stated at their declarations: ntb200_device_error_flags() waits for the device, and
+ *     ntb200_offsets_from_sizes_static keeps its scratch inside the library;
  *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = default stream);
- *   - re-entrant and thread-safe; arguments are validated on the host before any launch,
- *     so an invalid call launches nothing;
+ *   - re-entrant and thread-safe, except ntb200_offsets_from_sizes_static, whose calls share
+ *     one scratch array per GPU (see its comment); arguments are validated on the host
+ *     before any launch, so an invalid call launches nothing;
  *   - "ragged buffer" = the constituents of a nested tensor concatenated row-major in
  *     one 1-D buffer; `offsets[b]` = element offset of constituent b in that buffer
  *     (B+1 entries, int64, offsets[0] = 0); `sizes[b*size_stride + j]` = extent of
@@ -157,6 +160,9 @@ int ntb200_offsets_from_sizes(const int64_t* sizes, int64_t size_stride, int nd,
  *                on the GPU (different streams, no dependency between them) race and may both
  *                return wrong offsets; calls on one stream are safe.  Nothing needs clearing
  *                between calls: each call overwrites every entry it later reads.
+ *   reset        the looked-up address belongs to the device's primary context: a host that destroys
+ *                that context (cudaDeviceReset) and goes on using the library in the same process
+ *                must not call this entry point again on that device.
  * This entry point has no counterpart in the reference.
  */
 int64_t ntb200_offsets_static_max_batch(void);

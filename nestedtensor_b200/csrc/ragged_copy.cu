@@ -38,7 +38,21 @@ struct PadParams {
   uint64_t pad_bits;
   int64_t inner;    // contiguous elements per innermost index (folded regular trailing dims);
                     // m[ND-1] is already multiplied by it, sizes[.][ND-1] is not
+  uint8_t* mask;    // FUSE kernels: one byte per output element (1 inside a constituent), same shape as dst
 };
+
+// Validity bytes of one output vector: the n low bytes of the result are 0x01 (n in [0, 8]).
+__device__ __forceinline__ uint64_t ones_bytes(int n) {
+  return n >= 8 ? 0x0101010101010101ull : (0x0101010101010101ull & ((1ull << (8 * n)) - 1ull));
+}
+// Store the VE validity bytes of a vector (VE = 2, 4, 8 or 16) with one aligned store.
+template <int VE>
+__device__ __forceinline__ void store_mask_vec(uint8_t* p, uint64_t lo, uint64_t hi) {
+  if (VE == 2) *reinterpret_cast<uint16_t*>(p) = (uint16_t)lo;
+  else if (VE == 4) *reinterpret_cast<uint32_t*>(p) = (uint32_t)lo;
+  else if (VE == 8) *reinterpret_cast<uint64_t*>(p) = lo;
+  else *reinterpret_cast<uint4*>(p) = make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
+}
 
 // ---- one ragged dimension (sequences (L_i, D), the common case): everything inline.  For ND = 1 the
 // boundary path needs no division, the whole kernel stays small and needs only 32 registers (full
@@ -76,7 +90,8 @@ __device__ __forceinline__ typename ElemBits<ES>::T pad1_elem(const PadParams& p
   return reinterpret_cast<const E*>(p.src)[p.offsets[b] + lin];
 }
 
-template <int ES, bool MASK, bool BIG>
+// FUSE: besides the data, write the validity mask of the same shape (one byte per output element) in the same pass.
+template <int ES, bool MASK, bool BIG, bool FUSE = false>
 __global__ void __launch_bounds__(kThreads) pad1_kernel(const PadParams p) {
   constexpr int ND = 1;
   using E = typename ElemBits<ES>::T;
@@ -139,10 +154,15 @@ __global__ void __launch_bounds__(kThreads) pad1_kernel(const PadParams p) {
       src_row = MASK ? 0 : p.offsets[b] + ((int64_t)i0 * s1 + (int64_t)i1) * s_last;
     }
 
+    uint64_t mlo = 0, mhi = 0;  // FUSE: validity bytes of this vector
     if ((uint64_t)c + VE <= row_len) {
       // the whole vector lies in one innermost row
       int64_t nvalid = outer_valid ? (s_last - (int64_t)c) : 0;
       nvalid = nvalid < 0 ? 0 : (nvalid > VE ? VE : nvalid);
+      if (FUSE) {
+        mlo = ones_bytes((int)nvalid);
+        if (VE == 16) mhi = ones_bytes((int)nvalid - 8 > 0 ? (int)nvalid - 8 : 0);
+      }
       if (nvalid == VE) {
         if (MASK) {
 #pragma unroll
@@ -178,15 +198,23 @@ __global__ void __launch_bounds__(kThreads) pad1_kernel(const PadParams p) {
           ++bk;
         }
         out.e[k] = (e + k < p.total) ? pad1_elem<ES, 1, MASK, BIG>(p, bk, rk) : (E)0;
+        if (FUSE && e + k < p.total && (int64_t)rk < p.sizes[bk * p.size_stride] * p.inner) {
+          if (k < 8) mlo |= 1ull << (8 * (k & 7));
+          else mhi |= 1ull << (8 * (k & 7));
+        }
       }
     }
 
     if (e + VE <= p.total) {
       st_global_16_stream(dst + e, out.v);
+      if (FUSE) store_mask_vec<VE>(p.mask + e, mlo, mhi);
     } else {
 #pragma unroll
       for (int k = 0; k < VE; ++k)
-        if (e + k < p.total) dst[e + k] = out.e[k];
+        if (e + k < p.total) {
+          dst[e + k] = out.e[k];
+          if (FUSE) p.mask[e + k] = (uint8_t)(((k < 8 ? mlo : mhi) >> (8 * (k & 7))) & 1);
+        }
     }
   }
 }
@@ -245,7 +273,7 @@ __device__ __forceinline__ PadPos<ND, MASK, BIG> pad_locate(const PadParams& p, 
 // the flagged vectors (row / entry boundaries, the ragged tail of the output) that walks element by element
 // while carrying the indices over the boundary.  Keeping the boundary code out of the unrolled body keeps
 // the kernels small: a warp takes the boundary path whenever one of its 32 vectors needs it.
-template <int ES, int ND, bool MASK, bool BIG>
+template <int ES, int ND, bool MASK, bool BIG, bool FUSE = false>
 __global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
   using E = typename ElemBits<ES>::T;
   using IP = IdxPolicy<BIG>;
@@ -265,6 +293,7 @@ __global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
   };
   uint32_t boundary = 0, ready = 0;
   Vec val[kVecPerThread];
+  uint8_t nval[FUSE ? kVecPerThread : 1];  // FUSE: valid elements of each located vector (they form a prefix)
 
   // pass 1a: locate every vector of the tile and issue all its loads back to back
 #pragma unroll
@@ -285,6 +314,7 @@ __global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
     Vec& out = val[u];
     int64_t nvalid = q.outer_valid ? (q.s_last - (int64_t)q.c) : 0;
     nvalid = nvalid < 0 ? 0 : (nvalid > VE ? VE : nvalid);
+    if (FUSE) nval[u] = (uint8_t)nvalid;
     if (nvalid == VE) {
       if (MASK) {
 #pragma unroll
@@ -315,6 +345,16 @@ __global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
   for (int u = 0; u < kVecPerThread; ++u) {
     if (ready & (1u << u)) st_global_16_stream(dst + tile_e0 + (uint32_t)(u * kThreads + threadIdx.x) * VE, val[u].v);
   }
+  if (FUSE) {
+#pragma unroll
+    for (int u = 0; u < kVecPerThread; ++u) {
+      if (ready & (1u << u)) {
+        const int nv = nval[u];
+        store_mask_vec<VE>(p.mask + tile_e0 + (uint32_t)(u * kThreads + threadIdx.x) * VE, ones_bytes(nv),
+                           VE == 16 ? ones_bytes(nv - 8 > 0 ? nv - 8 : 0) : 0ull);
+      }
+    }
+  }
 
   // pass 2: the flagged vectors
 #pragma unroll 1
@@ -330,11 +370,16 @@ __global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
     PadPos<ND, MASK, BIG> q = pad_locate<ND, MASK, BIG>(p, bb, r);
     uint64_t cc = (uint64_t)q.c;
     Vec out;
+    uint64_t mlo = 0, mhi = 0;
 #pragma unroll
     for (int k = 0; k < VE; ++k) {
       const bool in_range = e + k < p.total;
       const bool v = in_range && q.outer_valid && (int64_t)cc < q.s_last;
       out.e[k] = v ? (MASK ? (E)1 : src[q.src_row + (int64_t)cc]) : (MASK || !in_range ? (E)0 : padv);
+      if (FUSE && v) {
+        if (k < 8) mlo |= 1ull << (8 * (k & 7));
+        else mhi |= 1ull << (8 * (k & 7));
+      }
       if (++cc == q.row_len) {
         cc = 0;
         bool next_entry = false;
@@ -377,10 +422,14 @@ __global__ void __launch_bounds__(kThreads) pad_kernel(const PadParams p) {
     }
     if (e + VE <= p.total) {
       st_global_16_stream(dst + e, out.v);
+      if (FUSE) store_mask_vec<VE>(p.mask + e, mlo, mhi);
     } else {
 #pragma unroll
       for (int k = 0; k < VE; ++k)
-        if (e + k < p.total) dst[e + k] = out.e[k];
+        if (e + k < p.total) {
+          dst[e + k] = out.e[k];
+          if (FUSE) p.mask[e + k] = (uint8_t)(((k < 8 ? mlo : mhi) >> (8 * (k & 7))) & 1);
+        }
     }
   }
 }
@@ -1007,28 +1056,28 @@ int make_geometry(int nd, const int64_t* h_max_sizes, int64_t inner, Geometry* g
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-template <int ES, int ND, bool MASK>
+template <int ES, int ND, bool MASK, bool FUSE>
 int launch_pad_es_nd(const PadParams& p, bool big, cudaStream_t st) {
   constexpr int VE = 16 / ES;
   const int64_t tile = (int64_t)kThreads * kVecPerThread * VE;
   const int64_t blocks = ceil_div(p.total, tile);
   if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
   if (ND == 1) {
-    if (big) pad1_kernel<ES, MASK, true><<<(unsigned)blocks, kThreads, 0, st>>>(p);
-    else pad1_kernel<ES, MASK, false><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+    if (big) pad1_kernel<ES, MASK, true, FUSE><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+    else pad1_kernel<ES, MASK, false, FUSE><<<(unsigned)blocks, kThreads, 0, st>>>(p);
   } else {
-    if (big) pad_kernel<ES, ND, MASK, true><<<(unsigned)blocks, kThreads, 0, st>>>(p);
-    else pad_kernel<ES, ND, MASK, false><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+    if (big) pad_kernel<ES, ND, MASK, true, FUSE><<<(unsigned)blocks, kThreads, 0, st>>>(p);
+    else pad_kernel<ES, ND, MASK, false, FUSE><<<(unsigned)blocks, kThreads, 0, st>>>(p);
   }
   return status_from_cuda(cudaGetLastError());
 }
 
-template <int ES, bool MASK>
+template <int ES, bool MASK, bool FUSE = false>
 int launch_pad_es(const PadParams& p, int nd, bool big, cudaStream_t st) {
   switch (nd) {
-    case 1: return launch_pad_es_nd<ES, 1, MASK>(p, big, st);
-    case 2: return launch_pad_es_nd<ES, 2, MASK>(p, big, st);
-    case 3: return launch_pad_es_nd<ES, 3, MASK>(p, big, st);
+    case 1: return launch_pad_es_nd<ES, 1, MASK, FUSE>(p, big, st);
+    case 2: return launch_pad_es_nd<ES, 2, MASK, FUSE>(p, big, st);
+    case 3: return launch_pad_es_nd<ES, 3, MASK, FUSE>(p, big, st);
   }
   return NTB200_INVALID_ARG;
 }
@@ -1113,9 +1162,10 @@ const char* ntb200_status_string(int status) {
 
 int ntb200_version(void) { return 1000; }
 
-int ntb200_pad_nd(const void* ragged, void* padded, const int64_t* offsets, const int64_t* sizes,
-                  int64_t size_stride, int nd, int64_t inner, int64_t batch, const int64_t* h_max_sizes,
-                  int elem_size, uint64_t pad_bits, void* stream) {
+// to_padded_tensor, optionally with the validity mask of the same shape written in the same pass (fused_mask != NULL)
+static int pad_common(const void* ragged, void* padded, uint8_t* fused_mask, const int64_t* offsets, const int64_t* sizes,
+                      int64_t size_stride, int nd, int64_t inner, int64_t batch, const int64_t* h_max_sizes,
+                      int elem_size, uint64_t pad_bits, void* stream) {
   Geometry g;
   int rc = make_geometry(nd, h_max_sizes, inner, &g);
   if (rc != NTB200_OK) return rc;
@@ -1140,7 +1190,18 @@ int ntb200_pad_nd(const void* ragged, void* padded, const int64_t* offsets, cons
   fill_divs(nd, g, &p.divP, &p.div1, &p.div2);
   p.pad_bits = pad_bits;
   p.inner = inner;
+  p.mask = fused_mask;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (fused_mask != nullptr) {
+    if (!aligned_to(fused_mask, 16)) return NTB200_MISALIGNED;
+    switch (elem_size) {
+      case 1: return launch_pad_es<1, false, true>(p, nd, g.big, st);
+      case 2: return launch_pad_es<2, false, true>(p, nd, g.big, st);
+      case 4: return launch_pad_es<4, false, true>(p, nd, g.big, st);
+      case 8: return launch_pad_es<8, false, true>(p, nd, g.big, st);
+    }
+    return NTB200_UNSUPPORTED_DTYPE;
+  }
   switch (elem_size) {
     case 1: return launch_pad_es<1, false>(p, nd, g.big, st);
     case 2: return launch_pad_es<2, false>(p, nd, g.big, st);
@@ -1148,6 +1209,13 @@ int ntb200_pad_nd(const void* ragged, void* padded, const int64_t* offsets, cons
     case 8: return launch_pad_es<8, false>(p, nd, g.big, st);
   }
   return NTB200_UNSUPPORTED_DTYPE;
+}
+
+int ntb200_pad_nd(const void* ragged, void* padded, const int64_t* offsets, const int64_t* sizes,
+                  int64_t size_stride, int nd, int64_t inner, int64_t batch, const int64_t* h_max_sizes,
+                  int elem_size, uint64_t pad_bits, void* stream) {
+  return pad_common(ragged, padded, nullptr, offsets, sizes, size_stride, nd, inner, batch, h_max_sizes, elem_size, pad_bits,
+                    stream);
 }
 
 int ntb200_mask_from_sizes(uint8_t* mask, const int64_t* sizes, int64_t size_stride, int nd, int64_t batch,
@@ -1173,6 +1241,7 @@ int ntb200_mask_from_sizes(uint8_t* mask, const int64_t* sizes, int64_t size_str
   fill_divs(nd, g, &p.divP, &p.div1, &p.div2);
   p.pad_bits = 0;
   p.inner = 1;
+  p.mask = nullptr;
   return launch_pad_es<1, true>(p, nd, g.big, static_cast<cudaStream_t>(stream));
 }
 
@@ -1180,6 +1249,23 @@ int ntb200_pad_with_mask(const void* ragged, void* padded, uint8_t* mask, const 
                          const int64_t* sizes, int64_t size_stride, int nd, int64_t inner, int64_t batch,
                          const int64_t* h_max_sizes, int elem_size, const int64_t* mask_sizes,
                          int64_t mask_size_stride, int mask_nd, const int64_t* mask_h_max_sizes, void* stream) {
+  // When the mask has the shape of the dense tensor (one byte per output element: images, pad_nt) both are written
+  // by ONE kernel in one walk over the output.  A coarser mask (one byte per row of `inner` elements, e.g.
+  // (B, max L) beside (B, max L, D) data) is `inner` times smaller than the data and is written by its own launch.
+  if (mask == nullptr || mask_nd < 1 || mask_nd > 3 || mask_h_max_sizes == nullptr || h_max_sizes == nullptr || nd < 1 || nd > 3)
+    return NTB200_INVALID_ARG;
+  bool same_shape = mask_sizes == sizes && mask_size_stride == size_stride;
+  if (same_shape) {
+    // the mask's dims are the leading tensor dims; it is element-wise when they cover all of them, i.e. when the two
+    // padded entry sizes agree and the leading extents coincide
+    uint64_t pd = (uint64_t)(inner > 0 ? inner : 0), pm = 1;
+    for (int j = 0; j < nd; ++j) pd *= (uint64_t)(h_max_sizes[j] > 0 ? h_max_sizes[j] : 0);
+    for (int j = 0; j < mask_nd; ++j) pm *= (uint64_t)(mask_h_max_sizes[j] > 0 ? mask_h_max_sizes[j] : 0);
+    same_shape = pd == pm && (inner == 1 ? mask_nd == nd : mask_nd > nd);
+    for (int j = 0; same_shape && j < nd && j < mask_nd; ++j) same_shape = mask_h_max_sizes[j] == h_max_sizes[j];
+  }
+  if (same_shape)
+    return pad_common(ragged, padded, mask, offsets, sizes, size_stride, nd, inner, batch, h_max_sizes, elem_size, 0, stream);
   int rc = ntb200_pad_nd(ragged, padded, offsets, sizes, size_stride, nd, inner, batch, h_max_sizes, elem_size, 0,
                          stream);
   if (rc != NTB200_OK) return rc;

@@ -5,8 +5,7 @@ reserved one fixed arena at start-up, or a binding from a language runtime that 
 to offer - so they cannot supply the workspace ntb200_offsets_from_sizes asks for.  The static variant
 keeps that scratch inside the library.  This test calls it through the C ABI twice in a row (the second
 call reuses the scratch the first one left dirty) and requires bit-identical offsets to the regular
-entry point.  It lives in a file that sorts last so that a run stopping at the first failure has
-already executed every other test.
+entry point.
 """
 import ctypes
 
