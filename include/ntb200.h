@@ -98,8 +98,11 @@ int ntb200_mask_from_sizes(uint8_t* mask, const int64_t* sizes, int64_t size_str
                            int64_t batch, const int64_t* h_max_sizes, void* stream);
 
 /* ------------------------------------------------------------------ data + mask in one call
- * ntb200_pad_nd with padding 0 followed by ntb200_mask_from_sizes over the first
- * mask_nd (<= nd) dimensions (mask_h_max_sizes), enqueued back to back on `stream`.
+ * Zero-padded data and the validity mask over the leading mask_nd tensor dimensions
+ * (mask_h_max_sizes), on `stream`.  When the mask has the shape of the dense tensor (one byte
+ * per output element: mask_sizes == sizes, the same stride and the same padded extents) ONE
+ * kernel writes both in a single walk over the output; a coarser mask (one byte per row of
+ * `inner` elements) is written by a second, `inner` times smaller launch.
  * Replaces add_padding_mask_kernelLauncher<T> (nestedtensor/csrc/cuda/padding.cu:217-284,
  * padding.h:24-34) called from to_tensor_mask (nestedtensor/csrc/masking.cpp:254-296),
  * without its pre-zeroing passes and int32 -> bool cast.

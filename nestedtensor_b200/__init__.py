@@ -14,7 +14,7 @@ All compute runs in hand-written CUDA kernels reached through the C ABI of
 from .nested import NestedTensor
 from .creation import nested_tensor, as_nested_tensor
 from .masking import (nested_tensor_from_tensor_mask, nested_tensor_from_padded_tensor, nt_from_tensor_mask,
-                      TensorMask)
+                      merge_tensor_mask, TensorMask)
 from . import nn
 from .sharding import token_balanced_partition
 from .host_pipeline import (to_padded_tensor_host, from_padded_tensor_host, multi_head_attention_host,
@@ -29,6 +29,15 @@ from . import _build as _b, _ops as _o
 if _os.path.exists(_b.CABI_LIB) and _os.path.exists(_b.DISPATCH_LIB):
     _o.load()
 del _os, _b, _o
+
+
+def device_error_flags():
+    """Bit mask of device-side conditions recorded since the last call (0 = none): a bounded wait of a tcgen05
+    kernel that ran out (projection: bits 0-2, attention: bits 8-10; the affected output tiles were left unwritten)
+    or an embedding index out of range (bit 16).  Synchronises the device.  The torch operators do not read it on
+    every call; a caller that wants the check after each of them sets ``NTB200_CHECK_DEVICE_ERRORS=1``."""
+    from . import _cabi
+    return int(_cabi.load().ntb200_device_error_flags())
 
 
 def is_nested_tensor(obj):

@@ -512,6 +512,23 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           m = m_new;
           ptx::tmem_st_wait();
         }
+        if (q == 0 && (nvalid & 15) != 0) {
+          // The last 16-key step of a ragged block multiplies P (exactly zero there) with V rows that belong to the
+          // NEXT sequence: 0 x NaN or 0 x Inf in such a row would reach this sequence's output.  Warp 0 clears those
+          // rows of the V tile once it has landed, before P is handed over, so that a non-finite value stays inside
+          // the sequence that holds it (the reference pads every sequence with zeros).
+          const uint32_t sv_stage = g % kStages;
+          if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->full_v[sv_stage]), (g / kStages) & 1, &ctrl->abort)) ok = false;
+          if (ok) {
+            const int nz = ((nvalid + 15) & ~15) - nvalid;  // 1..15 rows of 128 bytes
+            for (int i = lane; i < nz * 8; i += 32) {
+              const int r = nvalid + (i >> 3);
+              const uint32_t addr = s_v + sv_stage * kTile + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + (i & 7) * 16);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+            }
+            ptx::fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+          }
+        }
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {

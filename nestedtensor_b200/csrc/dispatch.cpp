@@ -15,6 +15,7 @@
 #include <torch/library.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <tuple>
 #include <vector>
@@ -27,6 +28,20 @@ using at::Tensor;
 
 void check_rc(int rc, const char* fn) {
   TORCH_CHECK(rc == NTB200_OK, "nestedtensor_b200: ", fn, " failed: ", ntb200_status_string(rc), " (", rc, ")");
+}
+
+// NTB200_CHECK_DEVICE_ERRORS=1: after every operator that runs a tcgen05 kernel, wait for the device and raise if one of
+// its bounded waits ran out (the affected output tiles would otherwise be returned unwritten).  Off by default: the
+// check synchronises.  Callers that leave it off poll nestedtensor_b200.device_error_flags() where it suits them.
+void maybe_check_device_errors(const char* op) {
+  static const bool enabled = [] {
+    const char* v = std::getenv("NTB200_CHECK_DEVICE_ERRORS");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  if (!enabled) return;
+  const int flags = ntb200_device_error_flags();
+  TORCH_CHECK(flags == 0, "nestedtensor_b200: ", op, ": device error flags 0x", std::hex, flags,
+              " (bits 0-2 projection, 8-10 attention: a bounded device-side wait ran out; bit 16: embedding index out of range)");
 }
 
 void* cur_stream() { return static_cast<void*>(at::cuda::getCurrentCUDAStream().stream()); }
@@ -266,7 +281,8 @@ std::vector<int64_t> get_max_size(const Tensor& sizes) {
 }
 
 // nestedtensor/csrc/masking.cpp:138-179: every constituent zero-padded to `shape` and stacked, with the uint8
-// mask of the same shape (1 inside a constituent).  One fused launch instead of a pad + stack per constituent.
+// mask of the same shape (1 inside a constituent).  One kernel writes data and mask in a single pass over the output
+// (ntb200_pad_with_mask, same-shape case) instead of a pad + stack per constituent.
 std::tuple<Tensor, Tensor> pad_nt(const Tensor& buffer, const Tensor& sizes, const Tensor& meta, at::IntArrayRef shape) {
   Record r = make_record(sizes, meta);
   if (r.B == 0)  // masking.cpp:164-166
@@ -446,6 +462,112 @@ std::tuple<Tensor, Tensor> sizes_from_mask(const Tensor& mask_) {
   return std::make_tuple(out_sizes, out_counts);
 }
 
+// ------------------------------------------------------------------ merge_tensor_mask
+// nestedtensor/csrc/masking.cpp:12-43: trailing mask dimensions whose slices are all-0 or all-1 are dropped until
+// `mask_dim` is reached (or, with no `mask_dim`, as far as possible).  A plain-tensor operator on either device; one
+// host read per level instead of the reference's two.
+std::tuple<Tensor, Tensor> merge_tensor_mask(const Tensor& tensor, const Tensor& mask_, c10::optional<int64_t> mask_dim) {
+  Tensor mask = mask_;
+  while (true) {
+    if (mask_dim && mask.dim() == *mask_dim) return std::make_tuple(tensor, mask);
+    if (mask.dim() == 0) return std::make_tuple(tensor, mask);
+    const int64_t last = mask.size(-1);
+    Tensor collapsed = mask.sum(-1);
+    const bool uniform = at::logical_or(collapsed == last, collapsed == 0).all().item<bool>();
+    if (!uniform) break;
+    mask = collapsed.to(at::kBool);
+  }
+  TORCH_CHECK(!(mask_dim && *mask_dim != mask.dim()), "Mask dimension is too small to represent data tensor.");
+  return std::make_tuple(tensor.contiguous(), mask.contiguous());
+}
+
+// ------------------------------------------------------------------ nt_from_tensor_mask
+// nestedtensor/csrc/masking.cpp:181-249 for nested_dim 1.  The reference walks the mask on the host with one .item()
+// per element and returns a NestedTensor; here one kernel recovers every entry's extents from the mask, the host checks
+// that they describe a padding mask (every entry keeps a leading box), the unpad kernel gathers the data, and the
+// result is the record (buffer, sizes, meta) that the Python class wraps.
+std::tuple<Tensor, Tensor, Tensor> record_from_extents(const Tensor& tensor, const Tensor& sizes_dev, const Tensor& counts_dev,
+                                                       int64_t lead_dims);
+
+std::tuple<Tensor, Tensor, Tensor> whole_entries(const Tensor& src) {
+  const int64_t B = src.size(0), tdim = src.dim() - 1;
+  Tensor sizes = at::empty({B, tdim}, at::TensorOptions().dtype(at::kLong));
+  int64_t* p = sizes.data_ptr<int64_t>();
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t j = 0; j < tdim; ++j) p[b * tdim + j] = src.size(j + 1);
+  int64_t per = 1;
+  for (int64_t j = 0; j < tdim; ++j) per *= src.size(j + 1);
+  Tensor meta_h = at::empty({(B + 1) + B * tdim}, at::TensorOptions().dtype(at::kLong));
+  int64_t* m = meta_h.data_ptr<int64_t>();
+  for (int64_t b = 0; b <= B; ++b) m[b] = b * per;
+  for (int64_t i = 0; i < B * tdim; ++i) m[B + 1 + i] = p[i];
+  return std::make_tuple(src.reshape({-1}).clone(), sizes, meta_h.to(src.device()));
+}
+
+std::tuple<Tensor, Tensor, Tensor> nt_from_tensor_mask(const Tensor& tensor, const Tensor& mask_, int64_t nested_dim) {
+  TORCH_CHECK(nested_dim == 1, "Only nested_dim of 1 is currently supported.");
+  TORCH_CHECK(tensor.dim() >= 1, "Can't construct nested tensor from a scalar.");
+  if (tensor.numel() == 0) {
+    if (tensor.dim() > 1) return whole_entries(tensor);
+    return std::make_tuple(tensor.reshape({-1}).clone(), at::zeros({0, 0}, at::TensorOptions().dtype(at::kLong)),
+                           at::zeros({1}, at::TensorOptions().dtype(at::kLong).device(tensor.device())));
+  }
+  TORCH_CHECK(tensor.is_cuda(), "nestedtensor_b200: nested_tensor_from_tensor_mask needs a CUDA tensor (this build has no CPU implementation)");
+  c10::cuda::CUDAGuard guard(tensor.device());
+  if (mask_.numel() == 1) {
+    if (mask_.reshape({-1}).to(at::kBool).item<bool>()) return whole_entries(tensor);
+    return std::make_tuple(at::empty({0}, tensor.options()), at::zeros({0, 0}, at::TensorOptions().dtype(at::kLong)),
+                           at::zeros({1}, at::TensorOptions().dtype(at::kLong).device(tensor.device())));
+  }
+  bool prefix = mask_.dim() <= tensor.dim();
+  for (int64_t j = 0; prefix && j < mask_.dim(); ++j) prefix = mask_.size(j) == tensor.size(j);
+  TORCH_CHECK(prefix, "nestedtensor_b200: mask shape ", mask_.sizes(), " must equal the leading dimensions of the tensor shape ",
+              tensor.sizes());
+  Tensor mask = mask_.to(tensor.device());
+  if (mask.scalar_type() != at::kBool && mask.scalar_type() != at::kByte) mask = mask != 0;
+  if (mask.dim() == 1)  // one flag per entry: entries are kept or dropped whole (masking.cpp:185-201)
+    return whole_entries(tensor.index({mask.to(at::kBool)}));
+  auto ext = sizes_from_mask(mask);
+  return record_from_extents(tensor, std::get<0>(ext), std::get<1>(ext), mask.dim() - 1);
+}
+
+// Host validation of device-computed extents, then the gather: an entry must keep exactly its leading box.
+std::tuple<Tensor, Tensor, Tensor> record_from_extents(const Tensor& tensor, const Tensor& sizes_dev, const Tensor& counts_dev,
+                                                       int64_t lead_dims) {
+  const int64_t B = tensor.size(0);
+  Tensor both = at::cat({sizes_dev, counts_dev.unsqueeze(1)}, 1).cpu();  // the one synchronising copy
+  const int64_t* q = both.data_ptr<int64_t>();
+  const int64_t trail = tensor.dim() - 1 - lead_dims, tdim = lead_dims + trail;
+  Tensor sizes = at::empty({B, tdim}, at::TensorOptions().dtype(at::kLong));
+  int64_t* p = sizes.data_ptr<int64_t>();
+  for (int64_t b = 0; b < B; ++b) {
+    int64_t box = 1;
+    for (int64_t j = 0; j < lead_dims; ++j) box *= q[b * (lead_dims + 1) + j];
+    const int64_t count = q[b * (lead_dims + 1) + lead_dims];
+    TORCH_CHECK(count == box, "nestedtensor_b200: entry ", b, " of the mask is not a padding mask (", count,
+                " valid elements do not fill its leading box); only masks that keep a leading box of every entry are supported");
+    for (int64_t j = 0; j < lead_dims; ++j) p[b * tdim + j] = q[b * (lead_dims + 1) + j];
+    for (int64_t j = 0; j < trail; ++j) p[b * tdim + lead_dims + j] = tensor.size(1 + lead_dims + j);
+    if (count == 0) {
+      // an all-false entry keeps its outer extents and gets an empty innermost one (masking.cpp:203-216)
+      for (int64_t j = 0; j + 1 < lead_dims; ++j) p[b * tdim + j] = tensor.size(1 + j);
+      p[b * tdim + lead_dims - 1] = 0;
+    }
+  }
+  Tensor meta_h = at::empty({(B + 1) + B * tdim}, at::TensorOptions().dtype(at::kLong).pinned_memory(true));
+  int64_t* m = meta_h.data_ptr<int64_t>();
+  m[0] = 0;
+  for (int64_t b = 0; b < B; ++b) {
+    int64_t n = 1;
+    for (int64_t j = 0; j < tdim; ++j) n *= p[b * tdim + j];
+    m[b + 1] = m[b] + n;
+  }
+  for (int64_t i = 0; i < B * tdim; ++i) m[B + 1 + i] = p[i];
+  Tensor meta = meta_h.to(tensor.device(), /*non_blocking=*/true);
+  Tensor buffer = from_padded_tensor(tensor, sizes, meta);
+  return std::make_tuple(buffer, sizes, meta);
+}
+
 // ------------------------------------------------------------------ metadata on the device
 // meta = [offsets (B+1) | sizes (B*tdim)] from device-resident sizes
 // (device-side batch_offsets_from_efficient_size, nestedtensor/csrc/masking.cpp:110-125).
@@ -555,6 +677,7 @@ Tensor bt_min_mha(int64_t num_heads, int64_t head_dim, double /*dropout_p*/, boo
   check_rc(ntb200_gemm_bias(attn.data_ptr(), w_out.data_ptr(), b_out, out.data_ptr(), T, E, E, dtype_code(buffer.scalar_type()), 0,
                             cur_stream()),
            "ntb200_gemm_bias");
+  maybe_check_device_errors("bt_min_mha");
   return out;
 }
 
@@ -633,6 +756,7 @@ Tensor min_mha_cross(int64_t num_heads, int64_t head_dim, const Tensor& q_buffer
     b_out = b_out_t.data_ptr();
   }
   check_rc(ntb200_gemm_bias(attn.data_ptr(), w_out.data_ptr(), b_out, out.data_ptr(), Tq, E, E, dt, 0, st), "ntb200_gemm_bias");
+  maybe_check_device_errors("min_mha");
   return out;
 }
 
@@ -707,6 +831,7 @@ Tensor packed_linear(const Tensor& x, const Tensor& weight, const c10::optional<
   check_rc(ntb200_gemm_bias_act(x.data_ptr(), w.data_ptr(), b, r, out.data_ptr(), T, N, K, dtype_code(x.scalar_type()), (int)act,
                                 0, cur_stream()),
            "ntb200_gemm_bias_act");
+  maybe_check_device_errors("packed_linear");
   return out;
 }
 
@@ -828,6 +953,8 @@ TORCH_LIBRARY(nestedtensor, m) {
   m.def("to_mask(Tensor sizes, Tensor meta, int? mask_dim) -> Tensor", &to_mask);
   m.def("get_max_size(Tensor sizes) -> int[]", &get_max_size);
   m.def("pad_nt(Tensor buffer, Tensor sizes, Tensor meta, int[] shape) -> (Tensor, Tensor)", &pad_nt);
+  m.def("merge_tensor_mask(Tensor tensor, Tensor mask, int? mask_dim=None) -> (Tensor, Tensor)", &merge_tensor_mask);
+  m.def("nt_from_tensor_mask(Tensor tensor, Tensor mask, int nested_dim) -> (Tensor, Tensor, Tensor)", &nt_from_tensor_mask);
   m.def("from_padded_tensor(Tensor padded, Tensor sizes, Tensor meta) -> Tensor", &from_padded_tensor);
   m.def("sizes_from_padded(Tensor tensor, Scalar padding) -> (Tensor, Tensor)", &sizes_from_padded);
   m.def("sizes_from_mask(Tensor mask) -> (Tensor, Tensor)", &sizes_from_mask);

@@ -92,35 +92,16 @@ def nested_tensor_from_tensor_mask(tensor, mask, nested_dim=1):
     return nt_from_tensor_mask(tensor, mask, nested_dim)
 
 
-def _whole_entries(tensor, keep=None):
-    """Every (kept) ``tensor[i]`` is a constituent as it stands."""
-    src = tensor if keep is None else tensor[keep]
-    B = src.size(0)
-    sizes = torch.tensor(list(src.shape[1:]), dtype=torch.int64).expand(B, src.dim() - 1).contiguous()
-    return NestedTensor(src.reshape(-1).clone(), sizes)
-
-
 def nt_from_tensor_mask(tensor, mask, nested_dim):
-    """nestedtensor/csrc/masking.cpp:223-249 (nested_dim 1)."""
+    """``torch.ops.nestedtensor.nt_from_tensor_mask`` (nestedtensor/csrc/masking.cpp:223-249, nested_dim 1) with its
+    record wrapped in a NestedTensor."""
     if nested_dim != 1:
         raise RuntimeError("Only nested_dim of 1 is currently supported.")
-    if tensor.numel() == 0:
-        B = tensor.size(0) if tensor.dim() > 1 else 0
-        sizes = torch.tensor(list(tensor.shape[1:]), dtype=torch.int64).expand(B, max(tensor.dim() - 1, 0)).contiguous()
-        return NestedTensor(tensor.reshape(-1).clone(), sizes)
-    _require_cuda(tensor, "nested_tensor_from_tensor_mask")
-    if mask.numel() == 1:
-        if bool(mask.reshape(-1)[0].item()):
-            return _whole_entries(tensor)
-        return NestedTensor(tensor.new_empty(0), torch.zeros((0, 0), dtype=torch.int64))
-    if mask.dim() > tensor.dim() or tuple(mask.shape) != tuple(tensor.shape[:mask.dim()]):
-        raise RuntimeError("nestedtensor_b200: mask shape {} must equal the leading dimensions of the tensor shape {}"
-                           .format(tuple(mask.shape), tuple(tensor.shape)))
-    mask = mask.to(device=tensor.device)
-    if mask.dtype not in (torch.bool, torch.uint8):
-        mask = mask != 0
-    if mask.dim() == 1:
-        # one flag per entry: entries are kept or dropped whole (masking.cpp:185-201)
-        return _whole_entries(tensor, mask.to(torch.bool))
-    sizes_dev, counts_dev = _ops.ops().sizes_from_mask(mask)
-    return _from_sizes(tensor, sizes_dev, counts_dev, mask.dim() - 1)
+    buffer, sizes, meta = _ops.ops().nt_from_tensor_mask(tensor, mask, nested_dim)
+    return NestedTensor(buffer, sizes, meta if meta.numel() == (sizes.size(0) + 1) + sizes.numel() and meta.device == buffer.device else None)
+
+
+def merge_tensor_mask(tensor, mask, mask_dim=None):
+    """``torch.ops.nestedtensor.merge_tensor_mask`` (nestedtensor/csrc/masking.cpp:12-43): drop trailing mask
+    dimensions whose slices are all-0 or all-1."""
+    return _ops.ops().merge_tensor_mask(tensor, mask, mask_dim)

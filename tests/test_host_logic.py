@@ -174,3 +174,31 @@ def test_host_pipeline_rejects_pageable_memory_before_touching_the_gpu():
         nt.to_padded_tensor_host(torch.zeros(20), sizes, 0)
     with pytest.raises(ValueError, match="pinned"):
         nt.from_padded_tensor_host(torch.zeros(2, 3, 4), sizes)
+
+
+def test_merge_tensor_mask_operator_matches_the_oracle(native_libs):
+    """torch.ops.nestedtensor.merge_tensor_mask (nestedtensor/csrc/masking.cpp:12-43) is a plain-tensor operator: the
+    reference's own cases (test/test_nested_tensor_masking.py: all-true, all-false, mixed and ragged masks, with and
+    without a target mask_dim) against the CPU restatement."""
+    from oracle import ntref
+    op = torch.ops.nestedtensor.merge_tensor_mask
+    t = torch.arange(24.0).reshape(2, 3, 4)
+    ragged = torch.tensor([[[1, 1, 0, 0], [1, 1, 0, 0], [0, 0, 0, 0]], [[1, 1, 1, 1], [1, 1, 1, 1], [1, 1, 1, 1]]], dtype=torch.uint8)
+    rows = torch.tensor([[[1, 1, 1, 1], [1, 1, 1, 1], [0, 0, 0, 0]], [[1, 1, 1, 1], [0, 0, 0, 0], [0, 0, 0, 0]]], dtype=torch.uint8)
+    for mask in (torch.ones(2, 3, 4, dtype=torch.uint8), torch.zeros(2, 3, 4, dtype=torch.uint8), ragged, rows):
+        for md in (None, 1, 2, 3):
+            try:
+                want = ntref.merge_tensor_mask(t, mask, md)
+            except RuntimeError as e:
+                with pytest.raises(RuntimeError, match="Mask dimension is too small"):
+                    op(t, mask, md)
+                assert "too small" in str(e)
+                continue
+            got = op(t, mask, md)
+            assert torch.equal(got[0], want[0])
+            assert got[1].dtype == want[1].dtype and torch.equal(got[1], want[1]), (md, got[1], want[1])
+    assert nt.merge_tensor_mask(t, rows)[1].shape == (2, 3)
+
+
+def test_device_error_flags_wrapper_needs_a_device(native_libs):
+    assert callable(nt.device_error_flags)
