@@ -289,6 +289,21 @@ int ntb200_varlen_cross_attention(const void* q, int64_t ldq, const void* k, int
                                   int head_dim, int64_t max_len_q, float scaling, int dtype, int path,
                                   void* stream);
 
+/* The attention probabilities themselves (torch.nn.MultiheadAttention(need_weights=True)):
+ *   average != 0   weights[weight_offsets[b] + i*Lk_b + j]            = mean over heads of softmax_j(scaling q_b,h,i . k_b,h,j)
+ *   average == 0   weights[weight_offsets[b] + (h*Lq_b + i)*Lk_b + j] = softmax_j(scaling q_b,h,i . k_b,h,j)
+ * q / k, ldq / ldk, offsets_q / offsets_k as in ntb200_varlen_cross_attention; weight_offsets holds the B element
+ * offsets of the per-sequence matrices; max_len_k sizes the shared-memory row (about 25 000 keys at most).  Rows of
+ * sequences without keys are left untouched.  A separate, slower kernel: the attention kernels above never
+ * materialise the probabilities.  The reference returns None for the weights on both of its paths
+ * (nestedtensor/nn/mha.py:57-83); this entry point has no counterpart there.
+ */
+int ntb200_varlen_attention_weights(const void* q, int64_t ldq, const void* k, int64_t ldk, void* weights,
+                                    const int64_t* offsets_q, const int64_t* offsets_k,
+                                    const int64_t* weight_offsets, int64_t batch, int64_t q_tokens, int num_heads,
+                                    int head_dim, int64_t max_len_k, float scaling, int dtype, int average,
+                                    void* stream);
+
 /* ------------------------------------------------------------------ ragged NCHW <-> NHWC
  * Constituent b (at element offset offsets[b]) is a row-major matrix with one regular extent `regular`
  * (channels) and one ragged extent n_b = (offsets[b+1] - offsets[b]) / regular (pixels); `out` receives its

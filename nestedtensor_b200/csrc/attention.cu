@@ -438,6 +438,88 @@ __global__ void __launch_bounds__(256) softmax_masked_kernel(T* __restrict__ sco
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// ------------------------------------------------------------------ attention weights (need_weights=True)
+// softmax(scale * q_b,h k_b,h^T) itself, for callers that ask for it: one block per query token walks the heads;
+// the scores of a row live in shared memory (fp32), the row is written once.  average != 0: mean over heads into a
+// (Lq_b x Lk_b) matrix per sequence; average == 0: (H x Lq_b x Lk_b) per sequence.  `weight_offsets[b]` is the element
+// offset of sequence b's matrix in `weights`.  Not on the hot path: the attention kernels never materialise this.
+constexpr int kWeightsThreads = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(kWeightsThreads)
+attn_weights_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, int64_t ldk, T* __restrict__ weights,
+                    const int64_t* __restrict__ offsets_q, const int64_t* __restrict__ offsets_k,
+                    const int64_t* __restrict__ weight_offsets, int64_t batch, int H, int d, float scale, int average) {
+  extern __shared__ float w_smem[];  // [d] query, [Lk] scores of the current head, [Lk] running mean (average mode)
+  __shared__ float s_red[kWeightsThreads / 32];
+  __shared__ float s_bcast;
+  const int64_t t = blockIdx.x;
+  const int64_t E = (int64_t)H * d;
+  const int64_t b = find_entry(offsets_q, batch, t * E);
+  const int64_t iq = t - offsets_q[b] / E;
+  const int Lq = (int)((offsets_q[b + 1] - offsets_q[b]) / E);
+  const int64_t tokk0 = offsets_k[b] / E;
+  const int Lk = (int)((offsets_k[b + 1] - offsets_k[b]) / E);
+  if (Lk <= 0) return;
+  float* s_qv = w_smem;
+  float* s_sc = w_smem + d;
+  float* s_acc = s_sc + Lk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto block_reduce = [&](float v, bool is_max) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, other) : v + other;
+    }
+    __syncthreads();  // s_red / s_bcast of the previous reduction have been read
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float r = s_red[0];
+      for (int w = 1; w < kWeightsThreads / 32; ++w) r = is_max ? fmaxf(r, s_red[w]) : r + s_red[w];
+      s_bcast = r;
+    }
+    __syncthreads();
+    return s_bcast;
+  };
+  if (average)
+    for (int j = threadIdx.x; j < Lk; j += kWeightsThreads) s_acc[j] = 0.0f;
+  for (int h = 0; h < H; ++h) {
+    __syncthreads();
+    const T* qrow = q + t * ldq + (int64_t)h * d;
+    for (int i = threadIdx.x; i < d; i += kWeightsThreads) s_qv[i] = Cvt<T>::to_f(qrow[i]) * scale;
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int j = threadIdx.x; j < Lk; j += kWeightsThreads) {
+      const T* krow = k + (tokk0 + j) * ldk + (int64_t)h * d;
+      float dot = 0.0f;
+      for (int i = 0; i < d; ++i) dot = fmaf(s_qv[i], Cvt<T>::to_f(krow[i]), dot);
+      s_sc[j] = dot;
+      mx = fmaxf(mx, dot);
+    }
+    mx = block_reduce(mx, true);
+    float sum = 0.0f;
+    for (int j = threadIdx.x; j < Lk; j += kWeightsThreads) {
+      const float e = __expf(s_sc[j] - mx);
+      s_sc[j] = e;
+      sum += e;
+    }
+    sum = block_reduce(sum, false);
+    const float inv = 1.0f / sum;
+    if (average) {
+      for (int j = threadIdx.x; j < Lk; j += kWeightsThreads) s_acc[j] += s_sc[j] * inv;
+    } else {
+      T* wrow = weights + weight_offsets[b] + ((int64_t)h * Lq + iq) * Lk;
+      for (int j = threadIdx.x; j < Lk; j += kWeightsThreads) wrow[j] = Cvt<T>::from_f(s_sc[j] * inv);
+    }
+  }
+  if (average) {
+    const float invh = 1.0f / (float)H;
+    T* wrow = weights + weight_offsets[b] + iq * Lk;
+    for (int j = threadIdx.x; j < Lk; j += kWeightsThreads) wrow[j] = Cvt<T>::from_f(s_acc[j] * invh);
+  }
+}
+
 // Separate query / key / value sources (self-attention passes the thirds of one packed row)
 struct QkvSrc {
   const void *q, *k, *v;
@@ -556,6 +638,45 @@ int ntb200_varlen_cross_attention(const void* q, int64_t ldq, const void* k, int
   const QkvSrc src = {q, k, v, ldq, ldk, ldv, offsets_q, offsets_k};
   return launch_attn_generic(src, out, batch, q_tokens, num_heads, head_dim, max_len_q, scaling, dtype, path,
                              static_cast<cudaStream_t>(stream));
+}
+
+int ntb200_varlen_attention_weights(const void* q, int64_t ldq, const void* k, int64_t ldk, void* weights,
+                                    const int64_t* offsets_q, const int64_t* offsets_k, const int64_t* weight_offsets,
+                                    int64_t batch, int64_t q_tokens, int num_heads, int head_dim, int64_t max_len_k,
+                                    float scaling, int dtype, int average, void* stream) {
+  if (batch < 0 || q_tokens < 0 || num_heads < 1 || head_dim < 1 || max_len_k < 0) return NTB200_INVALID_ARG;
+  if (dtype != NTB200_F32 && dtype != NTB200_F16 && dtype != NTB200_BF16) return NTB200_UNSUPPORTED_DTYPE;
+  if (head_dim > kMaxHeadDim) return NTB200_UNSUPPORTED_SHAPE;
+  const int64_t E = (int64_t)num_heads * head_dim;
+  if (ldq < E || ldk < E) return NTB200_INVALID_ARG;
+  if (batch == 0 || q_tokens == 0 || max_len_k == 0) return NTB200_OK;
+  if (q == nullptr || k == nullptr || weights == nullptr || offsets_q == nullptr || offsets_k == nullptr || weight_offsets == nullptr)
+    return NTB200_INVALID_ARG;
+  if (q_tokens > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  const size_t smem = sizeof(float) * ((size_t)head_dim + 2 * (size_t)max_len_k);
+  if (smem > 200 * 1024) return NTB200_UNSUPPORTED_SHAPE;  // key sequences beyond about 25 000 tokens
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define NTB200_LAUNCH_WEIGHTS(T)                                                                                          \
+  do {                                                                                                                    \
+    if (smem > 48 * 1024) {                                                                                               \
+      static std::atomic<int> configured[kMaxDevices];                                                                    \
+      if (!once_per_device(configured, [] {                                                                               \
+            return cudaFuncSetAttribute(attn_weights_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == \
+                   cudaSuccess;                                                                                           \
+          }))                                                                                                             \
+        return NTB200_LAUNCH_FAILED;                                                                                      \
+    }                                                                                                                     \
+    attn_weights_kernel<T><<<(unsigned)q_tokens, kWeightsThreads, smem, st>>>(                                            \
+        static_cast<const T*>(q), ldq, static_cast<const T*>(k), ldk, static_cast<T*>(weights), offsets_q, offsets_k,     \
+        weight_offsets, batch, num_heads, head_dim, scaling, average);                                                    \
+  } while (0)
+  switch (dtype) {
+    case NTB200_F32: NTB200_LAUNCH_WEIGHTS(float); break;
+    case NTB200_F16: NTB200_LAUNCH_WEIGHTS(__half); break;
+    case NTB200_BF16: NTB200_LAUNCH_WEIGHTS(__nv_bfloat16); break;
+  }
+#undef NTB200_LAUNCH_WEIGHTS
+  return status_from_cuda(cudaGetLastError());
 }
 
 #define NTB200_DISPATCH_DTYPE(dtype, CALL)                 \

@@ -760,6 +760,68 @@ Tensor min_mha_cross(int64_t num_heads, int64_t head_dim, const Tensor& q_buffer
   return out;
 }
 
+// Attention probabilities for need_weights=True: q and k are projected (two GEMMs with the first two thirds of in_proj), a
+// separate kernel writes softmax(scaling q k^T) per sequence.  Returns (weights buffer, sizes [B, 2 or 3]): one
+// (Lq_b x Lk_b) matrix per sequence averaged over the heads, or (H x Lq_b x Lk_b) with average = false.  The
+// reference returns None for the weights (nestedtensor/nn/mha.py:57-83).
+std::tuple<Tensor, Tensor> attention_weights(int64_t num_heads, int64_t head_dim, const Tensor& q_buffer, const Tensor& q_sizes,
+                                             const Tensor& q_meta, const Tensor& k_buffer, const Tensor& k_sizes, const Tensor& k_meta,
+                                             const Tensor& attr_kernel, const Tensor& attr_bias, double scaling, bool average) {
+  Record rq = make_record(q_sizes, q_meta), rk = make_record(k_sizes, k_meta);
+  TORCH_CHECK(rq.tdim == 2, "query needs to be 3 dim.");
+  TORCH_CHECK(rk.tdim == 2, "key needs to be 3 dim.");
+  TORCH_CHECK(rq.B == rk.B, "nestedtensor_b200: query and key must hold the same number of sequences");
+  check_buffer(q_buffer, rq, "attention_weights");
+  check_buffer(k_buffer, rk, "attention_weights");
+  const int64_t E = num_heads * head_dim;
+  TORCH_CHECK(rq.B == 0 || (rq.regular[1] && rq.max_sizes[1] == E), "query's third dimension must be regular.");
+  TORCH_CHECK(rk.B == 0 || (rk.regular[1] && rk.max_sizes[1] == E), "key's third dimension must be regular.");
+  TORCH_CHECK(num_heads >= 1 && head_dim >= 1 && head_dim <= 256, "nestedtensor_b200: head_dim must be in [1, 256]");
+  const int dt = dtype_code(q_buffer.scalar_type());
+  TORCH_CHECK(k_buffer.is_cuda() && k_buffer.device() == q_buffer.device() && k_buffer.scalar_type() == q_buffer.scalar_type() &&
+                  attr_kernel.is_cuda() && attr_kernel.device() == q_buffer.device() && attr_kernel.scalar_type() == q_buffer.scalar_type() &&
+                  attr_bias.is_cuda() && attr_bias.device() == q_buffer.device() && attr_bias.scalar_type() == q_buffer.scalar_type(),
+              "nestedtensor_b200: key and the projection parameters must be on the query's device and of its dtype");
+  TORCH_CHECK(attr_kernel.dim() == 2 && attr_kernel.size(0) == 3 * E && attr_kernel.size(1) == E, "in_proj_weight must be [3E, E]");
+  TORCH_CHECK(attr_bias.numel() == 3 * E, "in_proj_bias must have 3E entries");
+  c10::cuda::CUDAGuard guard(q_buffer.device());
+  const int64_t B = rq.B, Tq = rq.numel / (E > 0 ? E : 1), Tk = rk.numel / (E > 0 ? E : 1);
+  const int64_t wd = average ? 2 : 3;
+  Tensor w_sizes = at::empty({B, wd}, at::TensorOptions().dtype(at::kLong));
+  Tensor w_off_h = at::empty({B + 1}, at::TensorOptions().dtype(at::kLong).pinned_memory(B > 0));
+  int64_t* ws = w_sizes.data_ptr<int64_t>();
+  int64_t* wo = w_off_h.data_ptr<int64_t>();
+  wo[0] = 0;
+  for (int64_t b = 0; b < B; ++b) {
+    const int64_t lq = rq.sz[b * 2], lk = rk.sz[b * 2];
+    if (average) {
+      ws[b * 2] = lq;
+      ws[b * 2 + 1] = lk;
+    } else {
+      ws[b * 3] = num_heads;
+      ws[b * 3 + 1] = lq;
+      ws[b * 3 + 2] = lk;
+    }
+    wo[b + 1] = wo[b] + (average ? 1 : num_heads) * lq * lk;
+  }
+  Tensor weights = at::zeros({wo[B]}, q_buffer.options());
+  if (wo[B] == 0) return std::make_tuple(weights, w_sizes);
+  Tensor w_off = w_off_h.to(q_buffer.device(), /*non_blocking=*/true);
+  Tensor w = attr_kernel.contiguous(), bias = attr_bias.contiguous().view({3 * E});
+  const int64_t es = q_buffer.element_size();
+  const char* wp = static_cast<const char*>(w.data_ptr());
+  const char* bp = static_cast<const char*>(bias.data_ptr());
+  void* st = cur_stream();
+  Tensor q = at::empty({Tq, E}, q_buffer.options()), k = at::empty({Tk, E}, q_buffer.options());
+  check_rc(ntb200_gemm_bias(q_buffer.data_ptr(), wp, bp, q.data_ptr(), Tq, E, E, dt, 0, st), "ntb200_gemm_bias");
+  check_rc(ntb200_gemm_bias(k_buffer.data_ptr(), wp + E * E * es, bp + E * es, k.data_ptr(), Tk, E, E, dt, 0, st), "ntb200_gemm_bias");
+  check_rc(ntb200_varlen_attention_weights(q.data_ptr(), E, k.data_ptr(), E, weights.data_ptr(), rq.d_offsets, rk.d_offsets,
+                                           w_off.data_ptr<int64_t>(), B, Tq, (int)num_heads, (int)head_dim, rk.max_sizes[0],
+                                           (float)scaling, dt, average ? 1 : 0, st),
+           "ntb200_varlen_attention_weights");
+  return std::make_tuple(weights, w_sizes);
+}
+
 // ------------------------------------------------------------------ packed row operators and projections
 // Dense CUDA [T, cols] views of a packed buffer go straight to the C ABI.
 void check_rows(const Tensor& x, const char* op) {
@@ -977,6 +1039,10 @@ TORCH_LIBRARY(nestedtensor, m) {
       "Tensor k_sizes, Tensor k_meta, Tensor v_buffer, Tensor attr_kernel, Tensor attr_bias, float scaling, "
       "Tensor out_proj_weight, Tensor? out_proj_bias) -> Tensor",
       &min_mha_cross);
+  m.def(
+      "attention_weights(int num_heads, int head_dim, Tensor q_buffer, Tensor q_sizes, Tensor q_meta, Tensor k_buffer, Tensor k_sizes, "
+      "Tensor k_meta, Tensor attr_kernel, Tensor attr_bias, float scaling, bool average) -> (Tensor, Tensor)",
+      &attention_weights);
   m.def("layer_norm(Tensor buffer, Tensor sizes, Tensor meta, int[] normalized_shape, Tensor? weight, Tensor? bias, float eps) -> Tensor",
         &layer_norm);
   m.def("add_bias_residual_layer_norm(Tensor x, Tensor? residual, Tensor? bias, Tensor? weight, Tensor? beta, float eps) -> Tensor",

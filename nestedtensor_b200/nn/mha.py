@@ -60,8 +60,11 @@ def multi_head_attention_forward(query,
                                  average_attn_weights=True,
                                  is_causal=False):
     """Stock signature; the unsupported options are rejected exactly as the reference does
-    (nestedtensor/nn/mha.py:37-45).  Returns ``(output, None)``.  The output projection bias is applied
-    (the reference's CUDA path drops it, nestedtensor/csrc/cuda/mha.cpp:106 and nn/mha.py:69; its generic
+    (nestedtensor/nn/mha.py:37-45).  Returns ``(output, weights)``: with ``need_weights`` the attention
+    probabilities as a nested tensor of one ``(L_q,i, L_k,i)`` matrix per sequence (averaged over the heads, or
+    ``(H, L_q,i, L_k,i)`` with ``average_attn_weights=False``), computed by a separate kernel; without it ``None``,
+    which is what the reference returns in every case (nestedtensor/nn/mha.py:57-83).  The output projection bias is
+    applied (the reference's CUDA path drops it, nestedtensor/csrc/cuda/mha.cpp:106 and nn/mha.py:69; its generic
     path adds it, nestedtensor/csrc/mha.cpp:66-67)."""
     assert isinstance(query, NestedTensor)
     assert isinstance(key, NestedTensor)
@@ -89,8 +92,20 @@ def multi_head_attention_forward(query,
         raise RuntimeError("nestedtensor_b200: attention needs CUDA weights (this build has no CPU implementation)")
     # self-attention runs on the tcgen05 kernels; query != key (a decoder's cross-attention, which the reference
     # leaves to its per-sequence loop, nestedtensor/nn/mha.py:57-83) on the general kernels
-    return bt_min_mha(num_heads, head_dim, dropout_p, False, query, key, value, in_proj_weight, in_proj_bias,
-                      scaling, out_proj_weight, out_proj_bias), None
+    out = bt_min_mha(num_heads, head_dim, dropout_p, False, query, key, value, in_proj_weight, in_proj_bias,
+                     scaling, out_proj_weight, out_proj_bias)
+    return out, (attention_weights(num_heads, head_dim, query, key, in_proj_weight, in_proj_bias, scaling,
+                                   average_attn_weights) if need_weights else None)
+
+
+def attention_weights(num_heads, head_dim, query, key, in_proj_weight, in_proj_bias, scaling, average=True):
+    """softmax(scaling * q k^T) of every sequence as a nested tensor: ``(L_q,i, L_k,i)`` per sequence averaged over the
+    heads, or ``(H, L_q,i, L_k,i)``.  What ``torch.nn.MultiheadAttention(need_weights=True)`` returns per sequence."""
+    qb, qs, qm = query._record()
+    kb, ks, km = key._record()
+    w, wsizes = _ops.ops().attention_weights(num_heads, head_dim, qb, qs, qm, kb, ks, km, in_proj_weight, in_proj_bias,
+                                             float(scaling), bool(average))
+    return NestedTensor(w, wsizes)
 
 
 class MultiheadAttention(torch.nn.MultiheadAttention):
@@ -105,6 +120,6 @@ class MultiheadAttention(torch.nn.MultiheadAttention):
                 query, key, value, self.embed_dim, self.num_heads, self.in_proj_weight, self.in_proj_bias, self.bias_k,
                 self.bias_v, self.add_zero_attn, self.dropout, self.out_proj.weight, self.out_proj.bias,
                 training=self.training, key_padding_mask=key_padding_mask, need_weights=need_weights,
-                attn_mask=attn_mask, is_causal=is_causal)
+                attn_mask=attn_mask, average_attn_weights=average_attn_weights, is_causal=is_causal)
         return super().forward(query, key, value, key_padding_mask=key_padding_mask, need_weights=need_weights,
                                attn_mask=attn_mask, average_attn_weights=average_attn_weights, is_causal=is_causal)

@@ -332,6 +332,26 @@ def min_mha(num_heads: int, head_dim: int, query: NTList, key: NTList, value: NT
     return out
 
 
+def mha_weights(num_heads: int, head_dim: int, query: NTList, key: NTList, in_proj_weight: torch.Tensor,
+                in_proj_bias: torch.Tensor, scaling: float, average: bool = True) -> NTList:
+    """The attention probabilities inside min_mha (nestedtensor/csrc/mha.cpp:55-62: softmax of the scaled q k^T of
+    every constituent), which the reference computes and discards - its Python layer returns None for the weights
+    (nestedtensor/nn/mha.py:57-83).  One (L_q, L_k) matrix per constituent averaged over the heads, as
+    torch.nn.MultiheadAttention(need_weights=True) does, or (H, L_q, L_k)."""
+    E = num_heads * head_dim
+    W = in_proj_weight.float()
+    bias = in_proj_bias.float()
+    Wq, Wk = W[:E].t().contiguous(), W[E:2 * E].t().contiguous()
+    bq, bk = bias[:E], bias[E:2 * E]
+    out = []
+    for xq, xk in zip(query, key):
+        q = ((xq.float() @ Wq + bq) * scaling).reshape(-1, num_heads, head_dim).transpose(0, 1)
+        k = (xk.float() @ Wk + bk).reshape(-1, num_heads, head_dim).transpose(0, 1)
+        w = torch.softmax(q @ k.transpose(1, 2), -1)
+        out.append(w.mean(0) if average else w)
+    return out
+
+
 def masked_softmax(scores: torch.Tensor, mask: torch.Tensor, scaling: float) -> torch.Tensor:
     """The live softmax of the reference's CUDA MHA
     (nestedtensor/csrc/cuda/attention.cu:182-225): ``softmax(S*scaling + (1-mask)*-10000)``

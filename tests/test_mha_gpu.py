@@ -276,6 +276,42 @@ def test_cross_attention_matches_oracle(native_libs, cuda_device, dtype, E, H, s
     assert err <= TOL[dtype], err
 
 
+@pytest.mark.parametrize("dtype,E,H", [(torch.float32, 96, 3), (torch.bfloat16, 128, 2), (torch.float16, 256, 8)], ids=str)
+@pytest.mark.parametrize("cross", [False, True])
+@pytest.mark.parametrize("average", [True, False])
+def test_need_weights_returns_the_attention_probabilities(native_libs, cuda_device, dtype, E, H, cross, average):
+    """need_weights=True: one (L_q, L_k) matrix per sequence (averaged over the heads) or (H, L_q, L_k), against the
+    oracle; the oracle itself is pinned to stock torch.nn.MultiheadAttention(need_weights=True) run per sequence."""
+    g = torch.Generator().manual_seed(E + 2 * int(cross))
+    lq = [7, 1, 130, 33, 64]
+    lk = [int(v) for v in torch.randint(1, 200, (5,), generator=g)] if cross else lq
+    qs = [torch.randn(l, E, generator=g).to(dtype) for l in lq]
+    ks = [torch.randn(l, E, generator=g).to(dtype) for l in lk] if cross else qs
+    torch.manual_seed(2)
+    mha = torch.nn.MultiheadAttention(E, H).eval().to(dtype).to(cuda_device)
+    with torch.no_grad():
+        mha.in_proj_bias.normal_(0, 0.05)
+    q = nt.nested_tensor(qs, device=cuda_device, dtype=dtype)
+    k = nt.nested_tensor(ks, device=cuda_device, dtype=dtype) if cross else q
+    with torch.no_grad():
+        out, w = mha(q, k, k, need_weights=True, average_attn_weights=average)
+    assert out.nested_size() == q.nested_size()
+    want = ntref.mha_weights(H, E // H, qs, ks, mha.in_proj_weight.cpu(), mha.in_proj_bias.cpu(), float(E // H) ** -0.5, average)
+    got = w.unbind()
+    assert len(got) == len(want)
+    for a, b in zip(got, want):
+        assert tuple(a.shape) == tuple(b.shape)
+        assert (a.float().cpu() - b).abs().max().item() <= (1e-5 if dtype == torch.float32 else 4e-3)
+        assert abs(float(a.float().sum(-1).mean()) - 1.0) <= (1e-4 if dtype == torch.float32 else 1e-2)
+    if dtype == torch.float32:  # pin the oracle to the stock module, one sequence at a time
+        cpu = torch.nn.MultiheadAttention(E, H).eval()
+        cpu.load_state_dict({n: p.cpu() for n, p in mha.state_dict().items()})
+        with torch.no_grad():
+            for xq, xk, b in zip(qs, ks, want):
+                _, ws = cpu(xq.unsqueeze(1), xk.unsqueeze(1), xk.unsqueeze(1), need_weights=True, average_attn_weights=average)
+                assert torch.allclose(ws[0], b, atol=2e-6)
+
+
 def test_cabi_cross_attention_paths_and_empty_key_sequence(native_libs, cuda_device):
     """SIMT and mma.sync kernels agree with plain torch; a query whose key sequence is empty gets zeros."""
     lib = _cabi.load()

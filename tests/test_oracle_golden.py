@@ -198,3 +198,23 @@ def test_oracle_encoder_layer_matches_stock_module(act, norm_first):
     want = [layer(x.unsqueeze(0)).squeeze(0).detach() for x in xs]
     for a, b in zip(got, want):
         assert (a - b).abs().max().item() <= 2e-6
+
+
+def test_oracle_attention_weights_pinned_to_stock_module():
+    """ntref.mha_weights against torch.nn.MultiheadAttention(need_weights=True) run on one sequence at a time
+    (self- and cross-attention, averaged over heads and per head)."""
+    E, H = 96, 3
+    g = torch.Generator().manual_seed(1)
+    qs = [torch.randn(l, E, generator=g) for l in (7, 1, 30)]
+    ks = [torch.randn(l, E, generator=g) for l in (9, 4, 50)]
+    torch.manual_seed(3)
+    mha = torch.nn.MultiheadAttention(E, H).eval()
+    with torch.no_grad():
+        mha.in_proj_bias.normal_(0, 0.05)
+    for keys in (qs, ks):
+        for average in (True, False):
+            want = ntref.mha_weights(H, E // H, qs, keys, mha.in_proj_weight, mha.in_proj_bias, float(E // H) ** -0.5, average)
+            with torch.no_grad():
+                for xq, xk, b in zip(qs, keys, want):
+                    _, ws = mha(xq.unsqueeze(1), xk.unsqueeze(1), xk.unsqueeze(1), need_weights=True, average_attn_weights=average)
+                    assert torch.allclose(ws[0], b, atol=2e-6)
