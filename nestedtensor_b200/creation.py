@@ -38,8 +38,6 @@ def nested_tensor(data, dtype=None, device=None, requires_grad=False, pin_memory
         raise RuntimeError(
             "This version of nestedtensor currently does not support autograd. Please open an issue on "
             "https://github.com/pytorch/nestedtensor if you need this.")
-    if channels_last:
-        raise NotImplementedError("nestedtensor_b200: channels_last nested tensors are outside the implemented path")
     if dtype is None:
         dtype = torch.get_default_dtype()
     if device is None:
@@ -87,7 +85,10 @@ def nested_tensor(data, dtype=None, device=None, requires_grad=False, pin_memory
         buffer = buffer.pin_memory()
     if meta is None and device.type == "cuda":
         meta = build_meta(sizes, device)
-    return NestedTensor(buffer, sizes, meta)
+    result = NestedTensor(buffer, sizes, meta)
+    if channels_last:  # nestedtensor/csrc/creation.cpp:217-220
+        result = result.contiguous(memory_format=torch.channels_last)
+    return result
 
 
 def as_nested_tensor(data, dtype=None, device=None, requires_grad=False, pin_memory=False):

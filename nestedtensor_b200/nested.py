@@ -43,20 +43,37 @@ def build_meta(sizes: torch.Tensor, device) -> torch.Tensor:
 
 
 class NestedTensor(object):
-    def __init__(self, buffer: torch.Tensor, sizes: torch.Tensor, meta: Optional[torch.Tensor] = None):
+    def __init__(self, buffer: torch.Tensor, sizes: torch.Tensor, meta: Optional[torch.Tensor] = None,
+                 channels_last: bool = False):
         if not torch.is_tensor(buffer) or buffer.dim() != 1:
             raise TypeError("Got unexpected type " + str(type(buffer)))
         if sizes.dtype != torch.int64 or sizes.dim() != 2 or sizes.device.type != "cpu":
             raise TypeError("sizes must be a CPU int64 [B, tensor_dim] tensor")
+        if channels_last and sizes.size(1) != 3:
+            raise RuntimeError("channels_last needs constituents of shape (C, H_i, W_i)")
         self._buffer = buffer
         self._sizes = sizes.contiguous()
         self._meta = meta
+        # channels_last (nestedtensor/csrc/nested_tensor_impl.cpp:46, storage_is_contiguous_channels_last): the sizes are
+        # the logical (C, H_i, W_i), every constituent is STORED as (H_i, W_i, C), i.e. with strides (1, W_i*C, C).
+        self._channels_last = bool(channels_last)
+        self._nchw = None  # cached contiguous copy of a channels_last tensor, made on first use by an operator
 
     # ---- record access -------------------------------------------------------------------
     def _record(self):
+        """(buffer, sizes, meta) in the contiguous layout every operator works on; a channels_last tensor is brought
+        there once (one transpose kernel) and the result is kept."""
+        if self._channels_last:
+            if self._nchw is None:
+                self._nchw = self.contiguous()
+            return self._nchw._record()
         if self._meta is None or self._meta.device != self._buffer.device:
             self._meta = build_meta(self._sizes, self._buffer.device)
         return self._buffer, self._sizes, self._meta
+
+    def _stored_sizes(self):
+        """Constituent shapes as they lie in the buffer."""
+        return self._sizes[:, [1, 2, 0]].contiguous() if self._channels_last else self._sizes
 
     # ---- attributes ----------------------------------------------------------------------
     @property
@@ -127,6 +144,10 @@ class NestedTensor(object):
     def nested_stride(self, dim=None):
         strides = []
         for row in self._sizes.tolist():
+            if self._channels_last:
+                c, _, w = row
+                strides.append((1, w * c, c))
+                continue
             st, acc = [], 1
             for s in reversed(row):
                 st.append(acc)
@@ -137,14 +158,34 @@ class NestedTensor(object):
         return tuple(s[dim - 1] for s in strides)
 
     def is_contiguous(self, memory_format=torch.contiguous_format):
+        """nestedtensor/csrc/nested_tensor_impl.h (get_is_contiguous): row-major or channels_last storage."""
         if memory_format == torch.contiguous_format:
-            return True
+            return not self._channels_last
         if memory_format == torch.channels_last:
-            return False
+            return self._channels_last
         raise RuntimeError("Given memory format " + str(memory_format) + " not supported.")
 
-    def contiguous(self):
-        return self
+    def contiguous(self, memory_format=torch.contiguous_format):
+        """NestedTensor_contiguous (nestedtensor/csrc/nested_tensor_impl.cpp, transpose.cpp:87-202): to and from
+        channels_last storage with one ragged transpose kernel over the whole batch."""
+        if memory_format not in (torch.contiguous_format, torch.channels_last):
+            raise RuntimeError("Given memory format " + str(memory_format) + " not supported.")
+        want_cl = memory_format == torch.channels_last
+        if want_cl == self._channels_last:
+            return self
+        if self.dim() != 4:
+            raise RuntimeError("transpose_nchw_nhwc needs 4d input.")
+        if len(self) > 0 and bool((self._sizes[:, 0] != self._sizes[0, 0]).any()):
+            raise RuntimeError("Expected first dimension to be regular.")
+        if not self._buffer.is_cuda:
+            raise RuntimeError("nestedtensor_b200: channels_last conversion needs a CUDA nested tensor (this build has no CPU implementation)")
+        ops = _ops.ops()
+        if want_cl:
+            buf, sizes, meta = self._record()
+            return NestedTensor(ops.transpose_nchw_nhwc(buf, sizes, meta), sizes, meta, channels_last=True)
+        stored = self._stored_sizes()
+        out = ops.transpose_nhwc_nchw(self._buffer, stored, build_meta(stored, self._buffer.device))
+        return NestedTensor(out, self._sizes)
 
     # ---- views of the constituents -------------------------------------------------------
     def unbind(self, dim=0):
@@ -155,7 +196,8 @@ class NestedTensor(object):
             n = 1
             for s in row:
                 n *= s
-            out.append(self._buffer[off:off + n].reshape(row))
+            piece = self._buffer[off:off + n]
+            out.append(piece.reshape(row[1], row[2], row[0]).permute(2, 0, 1) if self._channels_last else piece.reshape(row))
             off += n
         return tuple(out)
 
@@ -173,7 +215,7 @@ class NestedTensor(object):
     def to(self, *args, **kwargs):
         buf = self._buffer.to(*args, **kwargs)
         meta = self._meta if (self._meta is not None and self._meta.device == buf.device) else None
-        return NestedTensor(buf, self._sizes, meta)
+        return NestedTensor(buf, self._sizes, meta, channels_last=self._channels_last)
 
     def cuda(self, device=None):
         return self.to(torch.device("cuda") if device is None else device)

@@ -46,20 +46,27 @@ def conv2d(input: NestedTensor, weight, bias=None, stride=1, padding=0, dilation
     if isinstance(padding, str):
         raise NotImplementedError("nestedtensor_b200: string padding modes are not supported")
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
-    buf, sizes, meta = input._record()
+    sizes = input._sizes
     if bool((sizes[:, 0] != sizes[0, 0]).any()):
         raise RuntimeError("Expected first dimension to be regular.")
     ops = _ops.ops()
     cout, _, kh, kw = weight.shape
     if (bias is None and kh == 1 and kw == 1 and stride == (1, 1) and padding == (0, 0) and dilation == (1, 1) and groups == 1
-            and buf.dtype in (torch.float16, torch.bfloat16, torch.float32)):
-        # pointwise convolution: every pixel of every image is one row of a single packed GEMM
-        x = transpose_nchw_nhwc(input)
+            and input.dtype in (torch.float16, torch.bfloat16, torch.float32)):
+        # pointwise convolution: every pixel of every image is one row of a single packed GEMM.  A channels_last input is
+        # stored pixel-major already and the result stays channels_last: no transpose on either side.
+        cl = input._channels_last
+        pixels = input._buffer if cl else transpose_nchw_nhwc(input)._buffer
         cin = int(sizes[0, 0])
-        y = ops.packed_linear(x._buffer.view(-1, cin), weight.reshape(cout, cin), None, 0, None)
-        nhwc = x._sizes.clone()
+        y = ops.packed_linear(pixels.view(-1, cin), weight.reshape(cout, cin), None, 0, None)
+        if cl:
+            out_sizes = sizes.clone()
+            out_sizes[:, 0] = cout
+            return NestedTensor(y.reshape(-1), out_sizes, channels_last=True)
+        nhwc = sizes[:, [1, 2, 0]].contiguous()
         nhwc[:, 2] = cout
         return transpose_nhwc_nchw(NestedTensor(y.reshape(-1), nhwc))
+    buf, sizes, meta = input._record()
     dense = ops.to_padded_tensor(buf, sizes, meta, 0.0)
     res = torch.nn.functional.conv2d(dense, weight, bias, stride, padding, dilation, groups)
     new_sizes = sizes.clone()

@@ -98,3 +98,41 @@ def test_max_pool2d_matches_per_image_pooling(native_libs, cuda_device, dtype, k
     assert [tuple(s) for s in got._sizes.tolist()] == [tuple(t.shape) for t in want]
     for a, b in zip(got.unbind(), want):
         assert_bit_equal(a, b.to(dtype), "max_pool2d")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32], ids=str)
+def test_channels_last_nested_tensor(native_libs, cuda_device, dtype):
+    """nested_tensor(..., channels_last=True) (nestedtensor/csrc/creation.cpp:197,217-220): logical (C, H_i, W_i)
+    constituents stored pixel-major; unbind() gives channels_last-strided views with the same values, the operators see
+    the logical layout, contiguous() converts both ways, and a 1x1 convolution stays channels_last without a transpose."""
+    g = torch.Generator().manual_seed(21)
+    C = 24
+    imgs = [torch.randn(C, int(torch.randint(3, 40, (1,), generator=g)), int(torch.randint(3, 40, (1,), generator=g)), generator=g).to(dtype)
+            for _ in range(6)]
+    a = nt.nested_tensor(imgs, device=cuda_device, dtype=dtype, channels_last=True)
+    assert a.is_contiguous(memory_format=torch.channels_last) and not a.is_contiguous()
+    assert a.nested_size() == tuple(torch.Size(t.shape) for t in imgs)
+    for view, t in zip(a.unbind(), imgs):
+        assert view.stride() == (1, t.size(2) * C, C)
+        assert torch.equal(view.cpu(), t)
+    assert a.nested_stride()[0] == (1, imgs[0].size(2) * C, C)
+    # stored bytes are those of the NHWC transpose
+    want_buf = torch.cat([t.permute(1, 2, 0).reshape(-1) for t in imgs])
+    assert torch.equal(a._buffer.cpu(), want_buf)
+    # operators work on the logical layout
+    assert_equal = lambda x, y: torch.equal(x.cpu().view(torch.int16 if dtype == torch.float16 else torch.int32),
+                                            y.view(torch.int16 if dtype == torch.float16 else torch.int32))
+    assert_equal(a.to_padded_tensor(padding=0), ntref.to_padded_tensor(imgs, 0))
+    b = a.contiguous()
+    assert b.is_contiguous() and torch.equal(b._buffer.cpu(), torch.cat([t.reshape(-1) for t in imgs]))
+    assert b.contiguous(memory_format=torch.channels_last)._buffer.equal(a._buffer)
+    assert a.contiguous(memory_format=torch.channels_last) is a
+    # pointwise convolution keeps the storage format
+    w = (torch.randn(16, C, 1, 1, generator=g) * 0.2).to(dtype).to(cuda_device)
+    y = torch.nn.functional.conv2d(a, w)
+    assert y.is_contiguous(memory_format=torch.channels_last)
+    for got, t in zip(y.unbind(), imgs):
+        want = torch.nn.functional.conv2d(t.float().unsqueeze(0), w.float().cpu())[0]
+        assert (got.float().cpu() - want).abs().max().item() <= (2e-2 if dtype == torch.float16 else 1e-4)
+    with pytest.raises(RuntimeError, match="4d input"):
+        nt.nested_tensor([torch.randn(3, 4)], device=cuda_device, channels_last=True)
