@@ -289,6 +289,22 @@ int ntb200_varlen_cross_attention(const void* q, int64_t ldq, const void* k, int
                                   int head_dim, int64_t max_len_q, float scaling, int dtype, int path,
                                   void* stream);
 
+/* The same with a workspace, which opens the tcgen05 kernel to cross-attention (head_dim 64, fp16/bf16, q / k / v and out
+ * 16-byte aligned, row strides multiples of 8 elements): Q, K and V tiles are fetched through three tensor maps over
+ * the query, key and value projections (k_tokens = rows of the key / value matrices), the work list is built on the
+ * device from both offset arrays.  path: 0 = tcgen05 when the shape allows it and a workspace is given, else as
+ * ntb200_varlen_cross_attention;  1 = SIMT;  2 = mma.sync kernel;  3 = tcgen05 (error if unsupported).
+ * `workspace`: ntb200_varlen_cross_attention_workspace_bytes(...) bytes, 16-byte aligned, or NULL.
+ * Replaces the per-sequence attention of min_mha (nestedtensor/csrc/mha.cpp:18-69) for query != key.
+ */
+size_t ntb200_varlen_cross_attention_workspace_bytes(int64_t batch, int64_t q_tokens, int num_heads, int head_dim,
+                                                     int dtype);
+int ntb200_varlen_cross_attention_ws(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                                     int64_t ldv, void* out, const int64_t* offsets_q, const int64_t* offsets_k,
+                                     int64_t batch, int64_t q_tokens, int64_t k_tokens, int num_heads,
+                                     int head_dim, int64_t max_len_q, float scaling, int dtype, int path,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* The attention probabilities themselves (torch.nn.MultiheadAttention(need_weights=True)):
  *   average != 0   weights[weight_offsets[b] + i*Lk_b + j]            = mean over heads of softmax_j(scaling q_b,h,i . k_b,h,j)
  *   average == 0   weights[weight_offsets[b] + (h*Lq_b + i)*Lk_b + j] = softmax_j(scaling q_b,h,i . k_b,h,j)

@@ -51,6 +51,10 @@ SIGNATURES = {
                                         c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "ntb200_varlen_cross_attention": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
                                               c_void_p, c_int64, c_int64, c_int, c_int, c_int64, c_float, c_int, c_int, c_void_p]),
+    "ntb200_varlen_cross_attention_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int, c_int, c_int]),
+    "ntb200_varlen_cross_attention_ws": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                                                 c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int64, c_float, c_int, c_int,
+                                                 c_void_p, c_size_t, c_void_p]),
     "ntb200_varlen_attention_weights": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                                 c_int64, c_int, c_int, c_int64, c_float, c_int, c_int, c_void_p]),
     "ntb200_add_qkv_bias_pad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

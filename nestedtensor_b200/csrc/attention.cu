@@ -640,6 +640,42 @@ int ntb200_varlen_cross_attention(const void* q, int64_t ldq, const void* k, int
                              static_cast<cudaStream_t>(stream));
 }
 
+size_t ntb200_varlen_cross_attention_workspace_bytes(int64_t batch, int64_t q_tokens, int num_heads, int head_dim, int dtype) {
+  if (batch <= 0 || q_tokens <= 0) return 0;
+  if (!attn_tcgen05_supported(batch, q_tokens, num_heads, head_dim, dtype)) return 0;
+  return attn_tcgen05_workspace_bytes(batch, q_tokens);
+}
+
+int ntb200_varlen_cross_attention_ws(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, void* out,
+                                     const int64_t* offsets_q, const int64_t* offsets_k, int64_t batch, int64_t q_tokens,
+                                     int64_t k_tokens, int num_heads, int head_dim, int64_t max_len_q, float scaling, int dtype,
+                                     int path, void* workspace, size_t workspace_bytes, void* stream) {
+  if (batch < 0 || q_tokens < 0 || k_tokens < 0 || num_heads < 1 || head_dim < 1 || max_len_q < 0 || path < 0 || path > 3)
+    return NTB200_INVALID_ARG;
+  if (dtype != NTB200_F32 && dtype != NTB200_F16 && dtype != NTB200_BF16) return NTB200_UNSUPPORTED_DTYPE;
+  if (head_dim > kMaxHeadDim) return NTB200_UNSUPPORTED_SHAPE;
+  const int64_t E = (int64_t)num_heads * head_dim;
+  if (ldq < E || ldk < E || ldv < E) return NTB200_INVALID_ARG;
+  if (batch == 0 || q_tokens == 0) return NTB200_OK;
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || offsets_q == nullptr || offsets_k == nullptr)
+    return NTB200_INVALID_ARG;
+  // path 0: tcgen05 when the shape allows it and a workspace is given, else the mma.sync kernel, else SIMT; 3: tcgen05 or error
+  const bool tc_ok = dtype != NTB200_F32 && attn_tcgen05_supported(batch, q_tokens, num_heads, head_dim, dtype) && k_tokens > 0 &&
+                     k_tokens < (1ll << 31) - 128 && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
+                     ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0;
+  if (path == 3 || (path == 0 && tc_ok && workspace != nullptr)) {
+    if (!tc_ok) return NTB200_UNSUPPORTED_SHAPE;
+    const size_t need = attn_tcgen05_workspace_bytes(batch, q_tokens);
+    if (workspace == nullptr || workspace_bytes < need) return NTB200_WORKSPACE_TOO_SMALL;
+    if (!aligned16(workspace)) return NTB200_MISALIGNED;
+    return attn_tcgen05_cross_launch(q, ldq, k, ldk, v, ldv, out, offsets_q, offsets_k, batch, q_tokens, k_tokens, num_heads, scaling,
+                                     dtype, workspace, static_cast<cudaStream_t>(stream));
+  }
+  const QkvSrc src = {q, k, v, ldq, ldk, ldv, offsets_q, offsets_k};
+  return launch_attn_generic(src, out, batch, q_tokens, num_heads, head_dim, max_len_q, scaling, dtype, path,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int ntb200_varlen_attention_weights(const void* q, int64_t ldq, const void* k, int64_t ldk, void* weights,
                                     const int64_t* offsets_q, const int64_t* offsets_k, const int64_t* weight_offsets,
                                     int64_t batch, int64_t q_tokens, int num_heads, int head_dim, int64_t max_len_k,

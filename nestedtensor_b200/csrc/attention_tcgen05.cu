@@ -6,10 +6,12 @@
 //                                   cross-thread reduction); P is written back over S as packed 16-bit
 //     O[128 x 64] += P V            tcgen05.mma with A = P read from tensor memory, B = V tile as MN-major
 // S / P (128 columns) and O (64 columns) live in tensor memory (256 columns per CTA, two CTAs per SM so
-// one CTA's softmax overlaps the other's MMAs).  Q, K and V tiles come straight out of the packed
-// [T, 3E] projection output through ONE 2-D tensor map (row = token, column = which third + head), so
-// padded tokens are never materialised; rows past the end of a sequence belong to the next sequence
-// (or are zero-filled past the end of the buffer) and are masked / never stored.
+// one CTA's softmax overlaps the other's MMAs).  Q, K and V tiles come straight out of the packed token
+// matrices through 2-D tensor maps (row = token, column = head): for self-attention the three maps are one map over
+// the [T, 3E] projection output with column offsets 0 / E / 2E; for cross-attention (queries of sequence b over the
+// keys / values of sequence b of another nested tensor) they are maps over the [Tq, E] query projection and the
+// key / value projections.  Padded tokens are never materialised; rows past the end of a sequence belong to the next
+// sequence (or are zero-filled past the end of the buffer) and are masked / cleared / never stored.
 // The list of (sequence, query tile) work items is built on the device, longest sequences first.
 // Every wait is bounded; a wait that runs out sets an error flag, the CTA drains and frees its TMEM.
 // Replaces steps 2-8 of bt_min_mha (nestedtensor/csrc/cuda/mha.cpp:59-105).
@@ -58,6 +60,8 @@ struct Ctrl {
   volatile int abort;
 };
 
+static_assert(sizeof(Ctrl) <= 256, "control block exceeds its shared-memory slot");
+
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = ptx::globaltimer_ns();
@@ -82,24 +86,27 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // ------------------------------------------------------------------ work list
-// items[i] = (first token of the sequence, first query row, sequence length, sequence index) for every
-// 128-query tile, ordered by decreasing number of key blocks so that the longest items start first;
-// *count = number of items.  One block.
+// items[i] = (first query token of the tile, valid query rows in the tile, first key token of the sequence, number
+// of keys) for every 128-query tile, ordered by decreasing number of key blocks so that the longest items start
+// first; *count = number of items.  Sequences without queries or without keys produce no item; the output rows of a
+// sequence without keys are zeroed here (an empty softmax).  One block.
 constexpr int kListThreads = 1024;
 constexpr int kBuckets = 9;  // key blocks 1..8+, (0 unused)
 
-__global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t* __restrict__ offsets, int64_t batch,
+__global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t* __restrict__ offsets_q,
+                                                                   const int64_t* __restrict__ offsets_k, int64_t batch,
                                                                    int64_t row_elems, int4* __restrict__ items,
-                                                                   int* __restrict__ count, int64_t capacity) {
+                                                                   int* __restrict__ count, int64_t capacity,
+                                                                   uint16_t* __restrict__ out) {
   __shared__ int s_cnt[kBuckets];
   __shared__ int s_base[kBuckets];
   if (threadIdx.x < kBuckets) s_cnt[threadIdx.x] = 0;
   __syncthreads();
   for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
-    const int64_t L = (offsets[b + 1] - offsets[b]) / row_elems;
-    if (L <= 0) continue;
-    const int nq = (int)((L + kQT - 1) / kQT);
-    int nb = (int)((L + kKV - 1) / kKV);
+    const int64_t Lq = (offsets_q[b + 1] - offsets_q[b]) / row_elems, Lk = (offsets_k[b + 1] - offsets_k[b]) / row_elems;
+    if (Lq <= 0 || Lk <= 0) continue;
+    const int nq = (int)((Lq + kQT - 1) / kQT);
+    int nb = (int)((Lk + kKV - 1) / kKV);
     nb = nb >= kBuckets ? kBuckets - 1 : nb;
     atomicAdd(&s_cnt[nb], nq);
   }
@@ -114,15 +121,38 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
   }
   __syncthreads();
   for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
-    const int64_t L = (offsets[b + 1] - offsets[b]) / row_elems;
-    if (L <= 0) continue;
-    const int nq = (int)((L + kQT - 1) / kQT);
-    int nb = (int)((L + kKV - 1) / kKV);
+    const int64_t Lq = (offsets_q[b + 1] - offsets_q[b]) / row_elems, Lk = (offsets_k[b + 1] - offsets_k[b]) / row_elems;
+    if (Lq <= 0 || Lk <= 0) continue;
+    const int nq = (int)((Lq + kQT - 1) / kQT);
+    int nb = (int)((Lk + kKV - 1) / kKV);
     nb = nb >= kBuckets ? kBuckets - 1 : nb;
     const int pos = atomicAdd(&s_base[nb], nq);
-    const int tok0 = (int)(offsets[b] / row_elems);
-    for (int t = 0; t < nq; ++t)
-      if (pos + t < capacity) items[pos + t] = make_int4(tok0, t * kQT, (int)L, (int)b);
+    const int tq0 = (int)(offsets_q[b] / row_elems), tk0 = (int)(offsets_k[b] / row_elems);
+    for (int t = 0; t < nq; ++t) {
+      const int64_t rows = Lq - (int64_t)t * kQT < kQT ? Lq - (int64_t)t * kQT : kQT;
+      if (pos + t < capacity) items[pos + t] = make_int4(tq0 + t * kQT, (int)rows, tk0, (int)Lk);
+    }
+  }
+  // Queries whose key sequence is empty get zeros (self-attention never has any: Lq == Lk).  The sequences are found in
+  // parallel and listed in shared memory; the block then clears their rows together.
+  __shared__ int s_nempty;
+  __shared__ int s_empty[kListThreads];
+  if (threadIdx.x == 0) s_nempty = 0;
+  __syncthreads();
+  for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
+    if (offsets_k[b + 1] > offsets_k[b] || offsets_q[b + 1] == offsets_q[b]) continue;
+    const int pos = atomicAdd(&s_nempty, 1);
+    if (pos < kListThreads) {
+      s_empty[pos] = (int)b;
+    } else {  // more than the list holds: this thread clears the rows itself
+      for (int64_t e = offsets_q[b]; e < offsets_q[b + 1]; ++e) out[e] = 0;
+    }
+  }
+  __syncthreads();
+  const int n_listed = s_nempty < kListThreads ? s_nempty : kListThreads;
+  for (int i = 0; i < n_listed; ++i) {
+    const int64_t e0 = offsets_q[s_empty[i]], e1 = offsets_q[s_empty[i] + 1];
+    for (int64_t e = e0 + threadIdx.x; e < e1; e += kListThreads) out[e] = 0;
   }
 }
 
@@ -131,7 +161,7 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
 // barriers run on one global block counter g (one phase per 128-key block).
 //   warps 0-3  softmax warpgroup (one thread per query row; registers raised with setmaxnreg so a whole
 //              128-key row of S lives in registers: S is read from tensor memory ONCE per block)
-//   warp 4     TMA producer   warp 5  MMA issuer   warps 6-7  idle (they only give their registers away)
+//   warp 4     TMA producer   warp 5  MMA issuer (also clears V rows past a sequence's end)   warps 6-7  idle
 // Tensor memory (256 columns): S [0,128) fp32, P [128,192) packed 16-bit, O [192,256) fp32.  P has its own
 // columns, so QK^T of block g+1 is issued as soon as the softmax warps have read S of block g
 // (s_free), before PV of block g: the tensor pipe works under the softmax of the same CTA.
@@ -144,7 +174,8 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
 // packed accumulators).
 template <int FMT>
 __global__ void __launch_bounds__(kAttnThreads, 2)
-attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restrict__ out, const int64_t* __restrict__ offsets,
+attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, int col_q, int col_k, int col_v, void* __restrict__ out,
                     const int4* __restrict__ items, const int* __restrict__ count, int H, float scale_log2e) {
   const int n_items = *count;
   if ((int64_t)blockIdx.x >= (int64_t)n_items * H) return;
@@ -168,7 +199,9 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
     ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
     ctrl->abort = 0;
     ptx::fence_barrier_init();
-    ptx::prefetch_tensormap(&map_qkv);
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
   }
   if (warp == 5) {
     ptx::tmem_alloc(ptx::smem_u32(&ctrl->tmem_base), kTmemCols);
@@ -185,7 +218,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
   // One 16-byte record per work item; every role fetches the record of its NEXT item while it works on
   // the current one, so the load latency never sits on a critical path.
   struct Item {
-    int q0, h, L, tok0, n_blk;
+    int tq, rows, h, L, tok0, n_blk;  // first query token and valid rows of the tile; keys: first token and count
   };
   // Position in the flattened (work item, head) list; a CTA steps through it by gridDim.x without a
   // division per item.
@@ -203,14 +236,15 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
     }
     return p;
   };
-  auto fetch = [&](const Pos& p) { return p.item < n_items ? __ldg(items + p.item) : make_int4(0, 0, 1, 0); };
+  auto fetch = [&](const Pos& p) { return p.item < n_items ? __ldg(items + p.item) : make_int4(0, 1, 0, 1); };
   auto decode = [&](const Pos& p, const int4& w) {
     Item it;
     it.h = p.h;
-    it.tok0 = w.x;
-    it.q0 = w.y;
-    it.L = w.z;
-    it.n_blk = (w.z + kKV - 1) / kKV;
+    it.tq = w.x;
+    it.rows = w.y;
+    it.tok0 = w.z;
+    it.L = w.w;
+    it.n_blk = (w.w + kKV - 1) / kKV;
     return it;
   };
 
@@ -234,8 +268,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           const uint32_t fk = ptx::smem_u32(&ctrl->full_k[s]);
           ptx::mbar_arrive_expect_tx(fk, (j == 0 ? 2 : 1) * kTile);
           // Q buffer n&1 was last read by item n-2, all of whose QK^T precede the release of this stage
-          if (j == 0) ptx::tma_load_2d(s_q + (n & 1) * kTile, &map_qkv, fk, it.h * kHD, it.tok0 + it.q0);
-          ptx::tma_load_2d(s_k + s * kTile, &map_qkv, fk, (int)E + it.h * kHD, it.tok0 + j * kKV);
+          if (j == 0) ptx::tma_load_2d(s_q + (n & 1) * kTile, &map_q, fk, col_q + it.h * kHD, it.tq);
+          ptx::tma_load_2d(s_k + s * kTile, &map_k, fk, col_k + it.h * kHD, it.tok0 + j * kKV);
           // ... V only once the PV that last read its stage has retired
           if (!wait_or_abort(ptx::smem_u32(&ctrl->empty_v[s]), ph ^ 1, &ctrl->abort)) {
             ok = false;
@@ -244,7 +278,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           }
           const uint32_t fv = ptx::smem_u32(&ctrl->full_v[s]);
           ptx::mbar_arrive_expect_tx(fv, kTile);
-          ptx::tma_load_2d(s_v + s * kTile, &map_qkv, fv, 2 * (int)E + it.h * kHD, it.tok0 + j * kKV);
+          ptx::tma_load_2d(s_v + s * kTile, &map_v, fv, col_v + it.h * kHD, it.tok0 + j * kKV);
         }
       }
       if (!ok) {
@@ -307,12 +341,27 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
             if (!wait_or_abort(ptx::smem_u32(&ctrl->s_free), gb & 1, &ctrl->abort)) { ok = false; break; }
             if (!issue_qk()) { ok = false; break; }
           }
-          if (!wait_or_abort(ptx::smem_u32(&ctrl->p_ready), gb & 1, &ctrl->abort)) { ok = false; break; }
           const uint32_t s = gb % kStages;
-          if (!wait_or_abort(ptx::smem_u32(&ctrl->full_v[s]), (gb / kStages) & 1, &ctrl->abort)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
           int nvalid = b.L - jb * kKV;
           nvalid = nvalid > kKV ? kKV : nvalid;
+          if ((nvalid & 15) != 0) {
+            // The last 16-key step of a ragged block multiplies P (exactly zero there) with V rows that belong to the
+            // NEXT sequence: 0 x NaN or 0 x Inf in such a row would reach this sequence's output.  While the softmax
+            // warps are still busy with this block, this thread clears those rows of the landed V tile, so that a
+            // non-finite value stays inside the sequence that holds it (the reference pads every sequence with zeros).
+            if (!wait_or_abort(ptx::smem_u32(&ctrl->full_v[s]), (gb / kStages) & 1, &ctrl->abort)) { ok = false; break; }
+            const int r_end = (nvalid + 15) & ~15;
+            for (int r = nvalid; r < r_end; ++r) {
+              const uint32_t addr = s_v + s * kTile + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr + c * 16), "r"(0u) : "memory");
+            }
+            ptx::fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+          }
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->p_ready), gb & 1, &ctrl->abort)) { ok = false; break; }
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->full_v[s]), (gb / kStages) & 1, &ctrl->abort)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
           const int ksteps = (nvalid + 15) >> 4;
           const uint64_t dv = desc_v0 + (uint64_t)(s * (kTile >> 4));
 #pragma unroll
@@ -381,7 +430,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
     for (Pos i = first; i.item < n_items; i = next(i)) {
       const Item it = decode(i, rec);
       rec = fetch(next(i));
-      const bool warp_active = it.q0 + q * 32 < it.L;  // warp-uniform
+      const bool warp_active = q * 32 < it.rows;  // warp-uniform
       float m = -INFINITY, l = 0.0f;
       for (int j = 0; j < it.n_blk; ++j, ++g) {
         if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->s_ready), g & 1, &ctrl->abort)) ok = false;
@@ -512,23 +561,6 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
           m = m_new;
           ptx::tmem_st_wait();
         }
-        if (q == 0 && (nvalid & 15) != 0) {
-          // The last 16-key step of a ragged block multiplies P (exactly zero there) with V rows that belong to the
-          // NEXT sequence: 0 x NaN or 0 x Inf in such a row would reach this sequence's output.  Warp 0 clears those
-          // rows of the V tile once it has landed, before P is handed over, so that a non-finite value stays inside
-          // the sequence that holds it (the reference pads every sequence with zeros).
-          const uint32_t sv_stage = g % kStages;
-          if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->full_v[sv_stage]), (g / kStages) & 1, &ctrl->abort)) ok = false;
-          if (ok) {
-            const int nz = ((nvalid + 15) & ~15) - nvalid;  // 1..15 rows of 128 bytes
-            for (int i = lane; i < nz * 8; i += 32) {
-              const int r = nvalid + (i >> 3);
-              const uint32_t addr = s_v + sv_stage * kTile + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + (i & 7) * 16);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
-            }
-            ptx::fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
-          }
-        }
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -540,8 +572,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_qkv, void* __restric
       pend.any = true;
       pend.warp_active = warp_active;
       pend.inv = 1.0f / l;
-      pend.rows = it.L - it.q0 < kQT ? it.L - it.q0 : kQT;
-      pend.out_row0 = ((int64_t)it.tok0 + it.q0) * E + (int64_t)it.h * kHD;
+      pend.rows = it.rows;
+      pend.out_row0 = (int64_t)it.tq * E + (int64_t)it.h * kHD;
     }
     if (ok && pend.any) {  // the last item of this CTA
       if (!wait_or_abort(ptx::smem_u32(&ctrl->o_ready), (g - 1) & 1, &ctrl->abort)) ok = false;
@@ -580,35 +612,46 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int FMT>
-int launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens, int H, float scaling,
-           int dtype, void* workspace, cudaStream_t st) {
+// One source of 128-row x 64-column tiles: a row-major [rows, cols] two-byte matrix with row stride `ld` elements.
+struct TileSource {
+  const void* base;
+  int64_t rows, cols, ld;
+};
+
+bool make_tile_map(CUtensorMap* map, const TileSource& src, int dtype) {
   EncodeTiledFn fn = encode_tiled_fn();
-  if (fn == nullptr) return NTB200_LAUNCH_FAILED;
-  const int64_t E = (int64_t)H * kHD;
-  CUtensorMap map;
-  const cuuint64_t gdim[2] = {(cuuint64_t)(3 * E), (cuuint64_t)total_tokens};
-  const cuuint64_t gstride[1] = {(cuuint64_t)(3 * E * 2)};
+  if (fn == nullptr) return false;
+  const cuuint64_t gdim[2] = {(cuuint64_t)src.cols, (cuuint64_t)src.rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)(src.ld * 2)};
   const cuuint32_t box[2] = {(cuuint32_t)kHD, (cuuint32_t)kQT};
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = dtype == NTB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  if (fn(&map, dt, 2, const_cast<void*>(qkv), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+  return fn(map, dt, 2, const_cast<void*>(src.base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int FMT>
+int launch(const TileSource& q, int col_q, const TileSource& k, int col_k, const TileSource& v, int col_v, void* out,
+           const int64_t* offsets_q, const int64_t* offsets_k, int64_t batch, int64_t q_tokens, int H, float scaling, int dtype,
+           void* workspace, cudaStream_t st) {
+  const int64_t E = (int64_t)H * kHD;
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_tile_map(&map_q, q, dtype) || !make_tile_map(&map_k, k, dtype) || !make_tile_map(&map_v, v, dtype))
     return NTB200_LAUNCH_FAILED;
   static std::atomic<int> attr_set[kMaxDevices];
   if (!once_per_device(attr_set, [] {
         return cudaFuncSetAttribute(attn_tcgen05_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) == cudaSuccess;
       }))
     return NTB200_LAUNCH_FAILED;
-  const int64_t capacity = attn_tcgen05_item_capacity(batch, total_tokens);
+  const int64_t capacity = attn_tcgen05_item_capacity(batch, q_tokens);
   int* count = static_cast<int*>(workspace);
   int4* items = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + 16);
-  build_items_kernel<<<1, kListThreads, 0, st>>>(offsets, batch, E, items, count, capacity);
+  build_items_kernel<<<1, kListThreads, 0, st>>>(offsets_q, offsets_k, batch, E, items, count, capacity, static_cast<uint16_t*>(out));
   int dev = 0, sms = kNumSMs;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int64_t grid = 2ll * sms;  // two resident CTAs per SM, each loops over its share of the items
   if (grid > capacity * H) grid = capacity * H;
-  attn_tcgen05_kernel<FMT><<<(unsigned)grid, kAttnThreads, kAttnSmem, st>>>(map, out, offsets, items, count, H,
+  attn_tcgen05_kernel<FMT><<<(unsigned)grid, kAttnThreads, kAttnSmem, st>>>(map_q, map_k, map_v, col_q, col_k, col_v, out, items, count, H,
                                                                             scaling * 1.4426950408889634f);
   return status_from_cuda(cudaGetLastError());
 }
@@ -629,10 +672,22 @@ bool attn_tcgen05_supported(int64_t batch, int64_t total_tokens, int num_heads, 
 
 int attn_tcgen05_launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens, int H,
                         float scaling, int dtype, void* workspace, cudaStream_t st) {
-  if (dtype == NTB200_F16) return launch<0>(qkv, out, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
-  return launch<1>(qkv, out, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
+  const int64_t E = (int64_t)H * kHD;
+  const TileSource src = {qkv, total_tokens, 3 * E, 3 * E};  // one map, three column offsets
+  if (dtype == NTB200_F16)
+    return launch<0>(src, 0, src, (int)E, src, (int)(2 * E), out, offsets, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
+  return launch<1>(src, 0, src, (int)E, src, (int)(2 * E), out, offsets, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
 }
 
+int attn_tcgen05_cross_launch(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, void* out,
+                              const int64_t* offsets_q, const int64_t* offsets_k, int64_t batch, int64_t q_tokens, int64_t k_tokens,
+                              int H, float scaling, int dtype, void* workspace, cudaStream_t st) {
+  const int64_t E = (int64_t)H * kHD;
+  const TileSource sq = {q, q_tokens, E, ldq}, sk = {k, k_tokens, E, ldk}, sv = {v, k_tokens, E, ldv};
+  if (dtype == NTB200_F16)
+    return launch<0>(sq, 0, sk, 0, sv, 0, out, offsets_q, offsets_k, batch, q_tokens, H, scaling, dtype, workspace, st);
+  return launch<1>(sq, 0, sk, 0, sv, 0, out, offsets_q, offsets_k, batch, q_tokens, H, scaling, dtype, workspace, st);
+}
 
 int attn_tcgen05_error_flags_read_and_clear() {
   int v = 0;

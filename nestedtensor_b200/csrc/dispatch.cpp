@@ -744,9 +744,13 @@ Tensor min_mha_cross(int64_t num_heads, int64_t head_dim, const Tensor& q_buffer
     ldkv = E;
   }
   Tensor attn = at::empty({Tq, E}, q_buffer.options());
-  check_rc(ntb200_varlen_cross_attention(q.data_ptr(), E, kptr, ldkv, vptr, ldkv, attn.data_ptr(), rq.d_offsets, rk.d_offsets, rq.B,
-                                         Tq, (int)num_heads, (int)head_dim, rq.max_sizes[0], (float)scaling, dt, 0, st),
-           "ntb200_varlen_cross_attention");
+  // head_dim 64 in fp16 / bf16 runs on the tcgen05 kernel (three tensor maps, device-built work list in `ws`)
+  const size_t ws_bytes = ntb200_varlen_cross_attention_workspace_bytes(rq.B, Tq, (int)num_heads, (int)head_dim, dt);
+  Tensor ws = at::empty({(int64_t)std::max<size_t>(ws_bytes, 16)}, q_buffer.options().dtype(at::kByte));
+  check_rc(ntb200_varlen_cross_attention_ws(q.data_ptr(), E, kptr, ldkv, vptr, ldkv, attn.data_ptr(), rq.d_offsets, rk.d_offsets, rq.B,
+                                            Tq, Tk, (int)num_heads, (int)head_dim, rq.max_sizes[0], (float)scaling, dt, 0,
+                                            ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, st),
+           "ntb200_varlen_cross_attention_ws");
   const void* b_out = nullptr;
   Tensor b_out_t;
   if (out_proj_bias && out_proj_bias->defined()) {

@@ -312,6 +312,49 @@ def test_need_weights_returns_the_attention_probabilities(native_libs, cuda_devi
                 assert torch.allclose(ws[0], b, atol=2e-6)
 
 
+@pytest.mark.parametrize("dtype,code", [(torch.bfloat16, 2), (torch.float16, 1)], ids=["bf16", "f16"])
+@pytest.mark.parametrize("packed_kv", [True, False])
+def test_cabi_cross_attention_tcgen05_against_simt(native_libs, cuda_device, dtype, code, packed_kv):
+    """The tcgen05 kernel with separate query / key / value tensor maps (path 3) against the SIMT kernel (path 1):
+    query tiles of more than 128 rows, key sequences of one to several blocks, a sequence without keys (zeros), one
+    without queries, and k / v either as the halves of one [Tk, 2E] matrix or as two matrices."""
+    lib = _cabi.load()
+    H, d = 4, 64
+    E = H * d
+    g = torch.Generator().manual_seed(77 + int(packed_kv))
+    lq = [5, 300, 0, 129, 64, 100, 1]
+    lk = [700, 33, 50, 0, 128, 129, 1]
+    B, Tq, Tk = len(lq), sum(lq), sum(lk)
+    q = torch.randn(Tq, E, generator=g).to(dtype).to(cuda_device)
+    if packed_kv:
+        kv = torch.randn(Tk, 2 * E, generator=g).to(dtype).to(cuda_device)
+        kp, vp, ld = kv.data_ptr(), kv.data_ptr() + E * 2, 2 * E
+    else:
+        k = torch.randn(Tk, E, generator=g).to(dtype).to(cuda_device)
+        v = torch.randn(Tk, E, generator=g).to(dtype).to(cuda_device)
+        kp, vp, ld = k.data_ptr(), v.data_ptr(), E
+    mq = build_meta(torch.tensor([[l, E] for l in lq]), cuda_device)
+    mk = build_meta(torch.tensor([[l, E] for l in lk]), cuda_device)
+    nb = lib.ntb200_varlen_cross_attention_workspace_bytes(B, Tq, H, d, code)
+    assert nb > 0
+    ws = torch.empty(nb, dtype=torch.uint8, device=cuda_device)
+    outs = []
+    for path in (3, 1):
+        o = torch.full((Tq, E), 7.0, dtype=dtype, device=cuda_device)
+        rc = lib.ntb200_varlen_cross_attention_ws(q.data_ptr(), E, kp, ld, vp, ld, o.data_ptr(), mq.data_ptr(), mk.data_ptr(), B, Tq, Tk,
+                                                  H, d, max(lq), d ** -0.5, code, path, ws.data_ptr(), nb, stream_ptr())
+        _cabi.check("ntb200_varlen_cross_attention_ws", rc)
+        outs.append(o)
+    torch.cuda.synchronize()
+    assert lib.ntb200_device_error_flags() == 0
+    assert (outs[0].float() - outs[1].float()).abs().max().item() <= 2e-2
+    off = sum(lq[:3])
+    assert int(outs[0][off:off + lq[3]].count_nonzero()) == 0  # the sequence without keys
+    # too small a workspace is refused, nothing is launched
+    assert lib.ntb200_varlen_cross_attention_ws(q.data_ptr(), E, kp, ld, vp, ld, outs[0].data_ptr(), mq.data_ptr(), mk.data_ptr(), B, Tq, Tk,
+                                                H, d, max(lq), d ** -0.5, code, 3, ws.data_ptr(), 16, stream_ptr()) == -6
+
+
 def test_cabi_cross_attention_paths_and_empty_key_sequence(native_libs, cuda_device):
     """SIMT and mma.sync kernels agree with plain torch; a query whose key sequence is empty gets zeros."""
     lib = _cabi.load()
