@@ -913,10 +913,26 @@ def run_kernels(args, local):
             timed(lambda: nt.nn.conv2d(img, w11), n), None, 2.0 * (nimg // 256) * 256 * 256)
         del img, nhwc
 
-    if only == "transpose":
-        image_path()
+    def config3_group():
+        es = 4
+        # configuration 3: 32 fp32 images (3, H_i, W_i)
+        w = workloads.config3()
+        a = nt.NestedTensor(w.buffer.to(device), w.sizes)
+        b, sz, meta = a._record()
+        nv = w.buffer.numel()
+        padded = ops.to_padded_tensor(b, sz, meta, 0.0)
+        npad = padded.numel()
+        add("to_padded_tensor (4-D)", "c3", timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0), n), es * (nv + npad))
+        add("to_tensor_mask (4-D uint8 mask)", "c3", timed(lambda: ops.to_tensor_mask(b, sz, meta, None), n), es * (nv + npad) + npad)
+        add("to_mask(mask_dim=3)", "c3", timed(lambda: ops.to_mask(sz, meta, 3), n), None)
+        add("from_padded_tensor (4-D)", "c3", timed(lambda: ops.from_padded_tensor(padded, sz, meta), n), 2 * es * nv)
+        add("sizes_from_padded (scan)", "c3", timed(lambda: ops.sizes_from_padded(padded, 0.0), n), es * npad)
+        del padded
+
+    if only in ("transpose", "c3"):
+        image_path() if only == "transpose" else config3_group()
         from nestedtensor_b200 import _cabi
-        return {"metric": "per-operator timings (--only transpose)", "unit": "ms", "n_gpus": 1, "steps": n, "data": "synthetic",
+        return {"metric": "per-operator timings (--only %s)" % only, "unit": "ms", "n_gpus": 1, "steps": n, "data": "synthetic",
                 "peaks": peaks, "rows": rows, "device_error_flags": _cabi.load().ntb200_device_error_flags()}
     # configuration 1: 64 fp32 (L_i, 256)
     w = workloads.config1()
@@ -930,19 +946,7 @@ def run_kernels(args, local):
     add("from_padded_tensor", "c1", timed(lambda: ops.from_padded_tensor(padded, sz, meta), n), 2 * es * nv)
     add("nested_tensor_from_padded_tensor", "c1 (includes the one host sync of the API)",
         timed(lambda: nt.nested_tensor_from_padded_tensor(padded, padding=0), n), es * (npad + nv))
-    # configuration 3: 32 fp32 images (3, H_i, W_i)
-    w = workloads.config3()
-    a = nt.NestedTensor(w.buffer.to(device), w.sizes)
-    b, sz, meta = a._record()
-    nv = w.buffer.numel()
-    padded = ops.to_padded_tensor(b, sz, meta, 0.0)
-    npad = padded.numel()
-    add("to_padded_tensor (4-D)", "c3", timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0), n), es * (nv + npad))
-    add("to_tensor_mask (4-D uint8 mask)", "c3", timed(lambda: ops.to_tensor_mask(b, sz, meta, None), n), es * (nv + npad) + npad)
-    add("to_mask(mask_dim=3)", "c3", timed(lambda: ops.to_mask(sz, meta, 3), n), None)
-    add("from_padded_tensor (4-D)", "c3", timed(lambda: ops.from_padded_tensor(padded, sz, meta), n), 2 * es * nv)
-    add("sizes_from_padded (scan)", "c3", timed(lambda: ops.sizes_from_padded(padded, 0.0), n), es * npad)
-    del padded
+    config3_group()
     # configuration 2: 4096 bf16 (L_i, 1024)
     L, _ = shard_lengths("pad", 1, 0)
     sizes = torch.stack([L, torch.full_like(L, 1024)], 1).contiguous()
@@ -1151,7 +1155,7 @@ def main():
     ap.add_argument("--sequences", type=int, default=0,
                     help="use only the first N sequences of each GPU's batch (small cases for profiler captures; "
                          "the line then does not describe the named configuration)")
-    ap.add_argument("--only", default="", help="kernels workload: run only this group (transpose) so that a profiler capture "
+    ap.add_argument("--only", default="", help="kernels workload: run only this group (transpose | c3) so that a profiler capture "
                                                "holds no more than the group's own data on the device")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end pass, the CPU baseline and the parity spot check")
