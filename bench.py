@@ -726,6 +726,55 @@ def run_mha(args, rank, world, local, brief=False):
     return line
 
 
+def reference_kernel_times(w, device, n):
+    """The reference's own CUDA padding kernels (nestedtensor/csrc/cuda/padding.cu compiled unmodified for sm_100a into
+    oracle/_ref/ by oracle/build_ref.py) on a workload whose padded tensor has fewer than 2^31 elements (the
+    reference indexes with `int`): a secondary comparator beside the CPU baseline.  None when the library is absent."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libntref_cuda.so")
+    if not os.path.exists(path):
+        return None
+    sizes = w.sizes
+    B, dim = sizes.shape
+    mx = sizes.max(0).values.tolist()
+    npad = B
+    for v in mx:
+        npad *= v
+    if npad >= 2 ** 31 or w.dtype not in (torch.float32, torch.float16) or dim < 2 or dim > 3:
+        return None
+    lib = ctypes.CDLL(path)
+    lib.ntref_add_padding.restype = ctypes.c_int
+    lib.ntref_add_padding.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                      ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    lib.ntref_remove_padding.restype = ctypes.c_int
+    lib.ntref_remove_padding.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    numel = sizes.prod(1)
+    offsets = torch.zeros(B, dtype=torch.int64)
+    offsets[1:] = numel.cumsum(0)[:-1]
+    buf = w.buffer.to(device)
+    d_off = offsets.to(torch.int32).to(device)
+    d_sizes = sizes.to(torch.int32).contiguous().to(device)
+    out = torch.empty([B] + mx, dtype=buf.dtype, device=device)
+    back = torch.empty_like(buf)
+    out_sizes = (ctypes.c_int64 * (dim + 1))(*([B] + mx))
+    d_padded_sizes = torch.tensor([B] + mx, dtype=torch.int32, device=device)
+    code = 0 if buf.dtype == torch.float32 else 1
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    pad = lambda: lib.ntref_add_padding(buf.data_ptr(), out.data_ptr(), 0.0, d_off.data_ptr(), d_sizes.data_ptr(), dim, out_sizes, B, code, stream)
+    unpad = lambda: lib.ntref_remove_padding(out.data_ptr(), back.data_ptr(), d_off.data_ptr(), d_padded_sizes.data_ptr(), d_sizes.data_ptr(),
+                                             dim, B, code, stream)
+    es, nv = buf.element_size(), buf.numel()
+    res = {"what": "add_padding_3 / remove_padding of the reference, grid (B,16) x 256 threads, same inputs, CUDA events"}
+    for name, fn, nbytes in (("to_padded_tensor", pad, es * (nv + npad)), ("from_padded_tensor", unpad, 2 * es * nv)):
+        for _ in range(3):
+            assert fn() == 0
+        ms, _ = timed_regions(fn, n, 1, device)
+        res[name] = {"ms": ms, "GB/s": nbytes / ms / 1e6}
+    res["round_trip_bit_exact"] = bool(torch.equal(back.view(torch.int32 if es == 4 else torch.int16), buf.view(torch.int32 if es == 4 else torch.int16)))
+    return res
+
+
 def run_small_configs(args, local):
     """Configurations 3 and 4, device-timed on one GPU (sub-records of the default line): 4-D to_padded_tensor /
     to_tensor_mask / from_padded_tensor on 32 fp32 images, and the BERT-base fp16 MHA step."""
@@ -757,6 +806,9 @@ def run_small_configs(args, local):
           "to_tensor_mask": hbm(timed(lambda: ops.to_tensor_mask(b, sz, meta, None))[0], 4 * (nv + npad) + npad),
           "from_padded_tensor": hbm(timed(lambda: ops.from_padded_tensor(padded, sz, meta))[0], 8 * nv),
           "sizes_from_padded": hbm(timed(lambda: ops.sizes_from_padded(padded, 0.0))[0], 4 * npad)}
+    ref = reference_kernel_times(w, device, n)
+    if ref is not None:
+        c3["reference_kernels_sm100a"] = ref
     del padded, a, b
     w = workloads.config4()
     a = nt.NestedTensor(w.buffer.to(device), w.sizes)
