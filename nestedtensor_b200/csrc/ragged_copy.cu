@@ -669,6 +669,174 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
   }
 }
 
+// ------------------------------------------------------------------ row walks (2-3 ragged dims, long rows)
+// With two or three ragged dimensions the vector walks above locate every 16-byte vector on its own (three
+// multiply-shift divisions, the sizes of its entry, a validity test) and are bound by that arithmetic, not by DRAM,
+// when the innermost rows are long (images: 3-4 KB rows).  Here a WARP takes one innermost row of the padded tensor:
+// the row is located once (entry, plane, row index, valid length, source row) and its vectors then cost a compare, an
+// address step, a load and a store each.  The destination row is walked in 16-byte-aligned vectors with an
+// element-wise head and tail; the source row has one phase for the whole row, so its loads are either all aligned
+// 16-byte loads or all element-wise.  Used when a padded row holds at least 32 vectors.
+struct RowParams {
+  const void* src;
+  void* dst;
+  uint8_t* mask;            // pad FUSE: one byte per output element
+  const int64_t* offsets;
+  const int64_t* sizes;
+  int64_t size_stride;
+  int64_t batch;
+  uint64_t rows_per_entry;  // padded rows per entry: m0 (ND == 2) or m0 * m1 (ND == 3)
+  uint64_t m0, m1;          // padded outer extents
+  uint64_t m_last;          // padded row length in elements (innermost extent times inner)
+  int64_t inner;
+  uint64_t pad_bits;
+  uint64_t blocks_per_entry;  // unpad: CTAs of kRowWarps rows per entry
+};
+constexpr int kRowWarps = 8;
+
+template <int ES, int ND, bool FUSE>
+__global__ void __launch_bounds__(kRowWarps * 32) pad_rows_kernel(const RowParams p) {
+  using E = typename ElemBits<ES>::T;
+  constexpr int VE = 16 / ES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t row = (uint64_t)blockIdx.x * kRowWarps + warp;
+  if (row >= (uint64_t)p.batch * p.rows_per_entry) return;
+  uint64_t b, rr;
+  divmod_u64(row, p.rows_per_entry, b, rr);
+  const int64_t* s = p.sizes + (int64_t)b * p.size_stride;
+  int64_t nv, src_row;  // valid elements at the start of the row, source element index of the row
+  if (ND == 2) {
+    nv = (int64_t)rr < s[0] ? s[1] * p.inner : 0;
+    src_row = p.offsets[b] + (int64_t)rr * (s[1] * p.inner);
+  } else {
+    uint64_t i0, i1;
+    divmod_u64(rr, p.m1, i0, i1);
+    const int64_t s1 = s[1], s_last = s[2] * p.inner;
+    nv = ((int64_t)i0 < s[0] && (int64_t)i1 < s1) ? s_last : 0;
+    src_row = p.offsets[b] + ((int64_t)i0 * s1 + (int64_t)i1) * s_last;
+  }
+  const E padv = (E)p.pad_bits;
+  const int64_t m_last = (int64_t)p.m_last;
+  E* __restrict__ drow = reinterpret_cast<E*>(p.dst) + row * p.m_last;
+  const E* __restrict__ srow = reinterpret_cast<const E*>(p.src) + src_row;
+  uint8_t* mrow = FUSE ? p.mask + row * p.m_last : nullptr;
+  int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(drow) & 15)) & 15) / ES);
+  head = head < m_last ? head : m_last;
+  const int64_t nvec = (m_last - head) / VE;
+  const int64_t tail0 = head + nvec * VE;
+  if (lane < head) {
+    drow[lane] = lane < nv ? srow[lane] : padv;
+    if (FUSE) mrow[lane] = lane < nv ? 1 : 0;
+  }
+  if (tail0 + lane < m_last) {
+    const int64_t e = tail0 + lane;
+    drow[e] = e < nv ? srow[e] : padv;
+    if (FUSE) mrow[e] = e < nv ? 1 : 0;
+  }
+  const bool src_aligned = nv > 0 && ((reinterpret_cast<uintptr_t>(srow + head) & 15) == 0);
+  union Vec {
+    uint4 v;
+    E e[VE];
+  };
+  Vec padvec;
+#pragma unroll
+  for (int k = 0; k < VE; ++k) padvec.e[k] = padv;
+  constexpr int U = 4;  // vectors per lane in flight
+  for (int64_t j0 = lane; j0 < nvec; j0 += 32 * U) {
+    Vec val[U];
+    int n[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t j = j0 + 32 * u;
+      n[u] = -1;
+      if (j >= nvec) continue;
+      const int64_t e0 = head + j * VE;
+      int64_t nn = nv - e0;
+      nn = nn < 0 ? 0 : (nn > VE ? VE : nn);
+      n[u] = (int)nn;
+      if (nn == VE) {
+        if (src_aligned) {
+          val[u].v = ld_global_16_stream(srow + e0);
+        } else {
+#pragma unroll
+          for (int k = 0; k < VE; ++k) val[u].e[k] = srow[e0 + k];
+        }
+      } else if (nn == 0) {
+        val[u].v = padvec.v;
+      } else {
+#pragma unroll
+        for (int k = 0; k < VE; ++k) val[u].e[k] = k < nn ? srow[e0 + k] : padv;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (n[u] < 0) continue;
+      const int64_t e0 = head + (j0 + 32 * u) * VE;
+      st_global_16_stream(drow + e0, val[u].v);
+      if (FUSE) store_mask_vec<VE>(mrow + e0, ones_bytes(n[u]), VE == 16 ? ones_bytes(n[u] - 8 > 0 ? n[u] - 8 : 0) : 0ull);
+    }
+  }
+}
+
+// The inverse: a warp takes one innermost row of one constituent (source: the padded row, destination: the row in the
+// ragged buffer, which starts at any element phase).  CTA c of entry b = blockIdx.x / blocks_per_entry holds rows
+// c * kRowWarps ... of that entry; CTAs past the entry's last row exit.
+template <int ES, int ND>
+__global__ void __launch_bounds__(kRowWarps * 32) unpad_rows_kernel(const RowParams p) {
+  using E = typename ElemBits<ES>::T;
+  constexpr int VE = 16 / ES;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint64_t b, c;
+  divmod_u64((uint64_t)blockIdx.x, p.blocks_per_entry, b, c);
+  const int64_t* s = p.sizes + (int64_t)b * p.size_stride;
+  const int64_t rows_b = ND == 2 ? s[0] : s[0] * s[1];
+  const int64_t rr = (int64_t)c * kRowWarps + warp;
+  if (rr >= rows_b) return;
+  const int64_t s_last = s[ND - 1] * p.inner;
+  if (s_last <= 0) return;
+  int64_t src_row;  // row index in the padded tensor
+  if (ND == 2) {
+    src_row = (int64_t)b * (int64_t)p.m0 + rr;
+  } else {
+    const int64_t i0 = rr / s[1], i1 = rr - i0 * s[1];
+    src_row = ((int64_t)b * (int64_t)p.m0 + i0) * (int64_t)p.m1 + i1;
+  }
+  const E* __restrict__ srow = reinterpret_cast<const E*>(p.src) + src_row * (int64_t)p.m_last;
+  E* __restrict__ drow = reinterpret_cast<E*>(p.dst) + p.offsets[b] + rr * s_last;
+  int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(drow) & 15)) & 15) / ES);
+  head = head < s_last ? head : s_last;
+  const int64_t nvec = (s_last - head) / VE;
+  const int64_t tail0 = head + nvec * VE;
+  if (lane < head) drow[lane] = srow[lane];
+  if (tail0 + lane < s_last) drow[tail0 + lane] = srow[tail0 + lane];
+  const bool src_aligned = (reinterpret_cast<uintptr_t>(srow + head) & 15) == 0;
+  union Vec {
+    uint4 v;
+    E e[VE];
+  };
+  constexpr int U = 4;
+  for (int64_t j0 = lane; j0 < nvec; j0 += 32 * U) {
+    Vec val[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t j = j0 + 32 * u;
+      if (j >= nvec) continue;
+      const int64_t e0 = head + j * VE;
+      if (src_aligned) {
+        val[u].v = ld_global_16_stream(srow + e0);
+      } else {
+#pragma unroll
+        for (int k = 0; k < VE; ++k) val[u].e[k] = srow[e0 + k];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t j = j0 + 32 * u;
+      if (j < nvec) st_global_16_stream(drow + head + j * VE, val[u].v);
+    }
+  }
+}
+
 // ------------------------------------------------------------- sizes from padded / mask
 struct ScanParams {
   const void* src;
@@ -1082,6 +1250,34 @@ int launch_pad_es(const PadParams& p, int nd, bool big, cudaStream_t st) {
   return NTB200_INVALID_ARG;
 }
 
+// Rows long enough for the warp-per-row kernels: at least 32 sixteen-byte vectors.
+inline bool long_rows(int nd, const Geometry& g, int elem_size) { return nd >= 2 && g.m[nd - 1] * (uint64_t)elem_size >= 512; }
+
+template <int ES>
+int launch_pad_rows(const RowParams& p, int nd, bool fuse, cudaStream_t st) {
+  const uint64_t rows = (uint64_t)p.batch * p.rows_per_entry;
+  const uint64_t blocks = (rows + kRowWarps - 1) / kRowWarps;
+  if (blocks > 0x7fffffffull) return NTB200_UNSUPPORTED_SHAPE;
+  if (nd == 2) {
+    if (fuse) pad_rows_kernel<ES, 2, true><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(p);
+    else pad_rows_kernel<ES, 2, false><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(p);
+  } else {
+    if (fuse) pad_rows_kernel<ES, 3, true><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(p);
+    else pad_rows_kernel<ES, 3, false><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(p);
+  }
+  return status_from_cuda(cudaGetLastError());
+}
+
+template <int ES>
+int launch_unpad_rows(RowParams p, int nd, cudaStream_t st) {
+  p.blocks_per_entry = (p.rows_per_entry + kRowWarps - 1) / kRowWarps;
+  const uint64_t blocks = (uint64_t)p.batch * p.blocks_per_entry;
+  if (blocks > 0x7fffffffull) return NTB200_UNSUPPORTED_SHAPE;
+  if (nd == 2) unpad_rows_kernel<ES, 2><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(p);
+  else unpad_rows_kernel<ES, 3><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(p);
+  return status_from_cuda(cudaGetLastError());
+}
+
 void fill_divs(int nd, const Geometry& g, FastDiv* divP, FastDiv* div1, FastDiv* div2) {
   *divP = make_fastdiv(g.big ? 1 : g.P);
   *div1 = make_fastdiv(1);
@@ -1115,12 +1311,116 @@ int launch_unpad_es(const UnpadParams& p, int nd, cudaStream_t st) {
   return NTB200_INVALID_ARG;
 }
 
+// Row walk of the same scan (2-3 dims, rows of at least 32 vectors): a warp reads one innermost row, keeps the count
+// of non-padding elements and the end of the last one, and the CTA's eight rows are merged per entry before the
+// atomics.  No division per vector; the row's coordinates are computed once.
+template <int ES, int ND, int CMP>
+__global__ void __launch_bounds__(kRowWarps * 32) scan_rows_kernel(const ScanParams p) {
+  using E = typename ElemBits<ES>::T;
+  constexpr int VE = 16 / ES;
+  const NotPad<ES, CMP> notpad(p.pad_bits);
+  const VecAllPad<ES, CMP> all_pad(p.pad_bits);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t rows_per_entry = ND == 2 ? p.m[0] : p.m[0] * p.m[1];
+  const uint64_t n_rows = (uint64_t)p.batch * rows_per_entry;
+  const uint64_t row = (uint64_t)blockIdx.x * kRowWarps + warp;
+  const int64_t m_last = (int64_t)p.m[ND - 1];
+  __shared__ unsigned long long s_row[kRowWarps][3];  // entry, count, end of the last non-padding element
+  uint32_t cnt = 0, last = 0;
+  if (row < n_rows) {
+    const E* __restrict__ srow = reinterpret_cast<const E*>(p.src) + row * (uint64_t)m_last;
+    int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(srow) & 15)) & 15) / ES);
+    head = head < m_last ? head : m_last;
+    const int64_t nvec = (m_last - head) / VE;
+    const int64_t tail0 = head + nvec * VE;
+    if (lane < head && notpad(srow[lane])) {
+      cnt = 1;
+      last = (uint32_t)lane + 1;
+    }
+    union Vec {
+      uint4 v;
+      E e[VE];
+    };
+    constexpr int U = 4;
+    for (int64_t j0 = lane; j0 < nvec; j0 += 32 * U) {
+      Vec val[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (j0 + 32 * u < nvec) val[u].v = ld_global_16_stream(srow + head + (j0 + 32 * u) * VE);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (j0 + 32 * u >= nvec || all_pad(val[u].v)) continue;
+        uint32_t bits = 0;
+#pragma unroll
+        for (int k = 0; k < VE; ++k)
+          if (notpad(val[u].e[k])) bits |= 1u << k;
+        if (bits == 0) continue;
+        cnt += (uint32_t)__popc(bits);
+        last = (uint32_t)(head + (j0 + 32 * u) * VE) + (uint32_t)(32 - __clz(bits));  // j0 only grows
+      }
+    }
+    if (tail0 + lane < m_last && notpad(srow[tail0 + lane])) {
+      cnt += 1;
+      last = (uint32_t)(tail0 + lane) + 1;
+    }
+  }
+  const unsigned full = 0xffffffffu;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    cnt += __shfl_xor_sync(full, cnt, o);
+    const uint32_t other = __shfl_xor_sync(full, last, o);
+    last = last > other ? last : other;
+  }
+  if (lane == 0) {
+    s_row[warp][0] = row < n_rows ? row : ~0ull;
+    s_row[warp][1] = cnt;
+    s_row[warp][2] = last;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  // rows of one CTA are consecutive: merge runs of the same entry
+  long long cur_b = -1;
+  unsigned long long c = 0, mx[3] = {0, 0, 0};
+  for (int w = 0; w < kRowWarps; ++w) {
+    if (s_row[w][0] == ~0ull || s_row[w][1] == 0) continue;
+    uint64_t b, rr;
+    divmod_u64(s_row[w][0], rows_per_entry, b, rr);
+    if ((long long)b != cur_b) {
+      if (cur_b >= 0) scan_flush<ND>(p, cur_b, c, mx);
+      cur_b = (long long)b;
+      c = 0;
+      mx[0] = mx[1] = mx[2] = 0;
+    }
+    c += s_row[w][1];
+    unsigned long long e[3];
+    if (ND == 2) {
+      e[0] = rr + 1;
+    } else {
+      uint64_t i0, i1;
+      divmod_u64(rr, p.m[1], i0, i1);
+      e[0] = i0 + 1;
+      e[1] = i1 + 1;
+    }
+    e[ND - 1] = s_row[w][2];
+#pragma unroll
+    for (int j = 0; j < ND; ++j) mx[j] = mx[j] > e[j] ? mx[j] : e[j];
+  }
+  if (cur_b >= 0) scan_flush<ND>(p, cur_b, c, mx);
+}
+
 template <int ES, int ND, int CMP>
 int launch_scan_es_nd(const ScanParams& p, bool big, cudaStream_t st) {
   constexpr int VE = 16 / ES;
   const int64_t tile = (int64_t)kThreads * kVecPerThread * VE;
   const int64_t blocks = ceil_div(p.total, tile);
   if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  if (ND >= 2 && p.m[ND - 1] * (uint64_t)ES >= 512 && p.m[ND - 1] < (1ull << 31)) {
+    const uint64_t rows = (uint64_t)p.batch * (ND == 2 ? p.m[0] : p.m[0] * p.m[1]);
+    const uint64_t row_blocks = (rows + kRowWarps - 1) / kRowWarps;
+    if (row_blocks > 0x7fffffffull) return NTB200_UNSUPPORTED_SHAPE;
+    scan_rows_kernel<ES, (ND >= 2 ? ND : 2), CMP><<<(unsigned)row_blocks, kRowWarps * 32, 0, st>>>(p);
+    return status_from_cuda(cudaGetLastError());
+  }
   if (big) sizes_scan_kernel<ES, ND, CMP, true><<<(unsigned)blocks, kThreads, 0, st>>>(p);
   else sizes_scan_kernel<ES, ND, CMP, false><<<(unsigned)blocks, kThreads, 0, st>>>(p);
   return status_from_cuda(cudaGetLastError());
@@ -1192,8 +1492,32 @@ static int pad_common(const void* ragged, void* padded, uint8_t* fused_mask, con
   p.inner = inner;
   p.mask = fused_mask;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (fused_mask != nullptr && !aligned_to(fused_mask, 16)) return NTB200_MISALIGNED;
+  if (long_rows(nd, g, elem_size) && ragged != nullptr) {
+    RowParams rp;
+    rp.src = ragged;
+    rp.dst = padded;
+    rp.mask = fused_mask;
+    rp.offsets = offsets;
+    rp.sizes = sizes;
+    rp.size_stride = size_stride;
+    rp.batch = batch;
+    rp.m0 = g.m[0];
+    rp.m1 = nd == 3 ? g.m[1] : 1;
+    rp.rows_per_entry = nd == 3 ? g.m[0] * g.m[1] : g.m[0];
+    rp.m_last = g.m[nd - 1];
+    rp.inner = inner;
+    rp.pad_bits = pad_bits;
+    rp.blocks_per_entry = 0;
+    switch (elem_size) {
+      case 1: return launch_pad_rows<1>(rp, nd, fused_mask != nullptr, st);
+      case 2: return launch_pad_rows<2>(rp, nd, fused_mask != nullptr, st);
+      case 4: return launch_pad_rows<4>(rp, nd, fused_mask != nullptr, st);
+      case 8: return launch_pad_rows<8>(rp, nd, fused_mask != nullptr, st);
+    }
+    return NTB200_UNSUPPORTED_DTYPE;
+  }
   if (fused_mask != nullptr) {
-    if (!aligned_to(fused_mask, 16)) return NTB200_MISALIGNED;
     switch (elem_size) {
       case 1: return launch_pad_es<1, false, true>(p, nd, g.big, st);
       case 2: return launch_pad_es<2, false, true>(p, nd, g.big, st);
@@ -1298,6 +1622,30 @@ int ntb200_unpad_nd(const void* padded, void* ragged, const int64_t* offsets, co
   for (int j = 0; j < 3; ++j) p.m[j] = g.m[j];
   p.inner = inner;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (long_rows(nd, g, elem_size)) {
+    RowParams rp;
+    rp.src = padded;
+    rp.dst = ragged;
+    rp.mask = nullptr;
+    rp.offsets = offsets;
+    rp.sizes = sizes;
+    rp.size_stride = size_stride;
+    rp.batch = batch;
+    rp.m0 = g.m[0];
+    rp.m1 = nd == 3 ? g.m[1] : 1;
+    rp.rows_per_entry = nd == 3 ? g.m[0] * g.m[1] : g.m[0];
+    rp.m_last = g.m[nd - 1];
+    rp.inner = inner;
+    rp.pad_bits = 0;
+    rp.blocks_per_entry = 0;
+    switch (elem_size) {
+      case 1: return launch_unpad_rows<1>(rp, nd, st);
+      case 2: return launch_unpad_rows<2>(rp, nd, st);
+      case 4: return launch_unpad_rows<4>(rp, nd, st);
+      case 8: return launch_unpad_rows<8>(rp, nd, st);
+    }
+    return NTB200_UNSUPPORTED_DTYPE;
+  }
   switch (elem_size) {
     case 1: return launch_unpad_es<1>(p, nd, st);
     case 2: return launch_unpad_es<2>(p, nd, st);

@@ -132,6 +132,53 @@ def test_unpad_many_entries_per_tile(native_libs, cuda_device, dtype, tdim):
     assert_bit_equal(cabi_unpad(got, sizes_of(tensors)), torch.cat([t.reshape(-1) for t in tensors]), "unpad")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.uint8, torch.float64], ids=str)
+@pytest.mark.parametrize("tdim,regular_last", [(2, None), (3, None), (3, 3), (2, 5)])
+def test_long_rows(native_libs, cuda_device, dtype, tdim, regular_last):
+    """2 and 3 ragged dims whose innermost padded rows hold at least 32 sixteen-byte vectors (images): the
+    warp-per-row kernels.  Odd widths (every source row starts at another phase of a 16-byte vector), widths below
+    one vector, an empty constituent, one of a single element, a regular folded trailing dim; pad, data + mask in one
+    pass, unpad, and the size scan of the padded result."""
+    g = torch.Generator().manual_seed(977 + tdim)
+    es = torch.empty(0, dtype=dtype).element_size()
+    hi = 1100 // es + 37
+    tensors = random_list(g, 9, tdim, 3, 11, dtype, regular_last)
+    for i, t in enumerate(tensors):  # widen the innermost ragged dim
+        shape = list(t.shape)
+        j = tdim - 1 if regular_last is None else tdim - 2
+        shape[j] = [hi, 1, hi - 1, 3, hi // 2 + 1, 17, hi - 16, 2, hi - 5][i]
+        x = torch.randn(shape, generator=g)
+        tensors[i] = ((x * 40).abs() + 1).to(dtype) if dtype == torch.uint8 else x.to(dtype)
+    empty = list(tensors[0].shape)
+    empty[0] = 0
+    tensors.insert(4, torch.zeros(empty, dtype=dtype))
+    pad_value = 0 if dtype == torch.uint8 else 777.0  # a value the data cannot hold
+    full = tensors[:4] + tensors[5:]  # the operators (as the reference's) reject empty constituents; the C ABI takes them
+    a = nt.nested_tensor(full, device=cuda_device, dtype=dtype)
+    want = ntref.to_padded_tensor(full, pad_value)
+    padded = a.to_padded_tensor(padding=pad_value)
+    assert_bit_equal(padded, want, "to_padded_tensor")
+    want_e = torch.cat([want[:4], torch.full_like(want[:1], pad_value), want[4:]])
+    padded_e = cabi_pad(tensors, pad_value, cuda_device)
+    assert_bit_equal(padded_e, want_e, "ntb200_pad_nd")
+    data, mask = a.to_tensor_mask()
+    odata, omask = ntref.to_tensor_mask(full)
+    assert_bit_equal(data, odata, "to_tensor_mask data")
+    assert_bit_equal(mask, omask, "to_tensor_mask mask")
+    flat = torch.cat([t.reshape(-1) for t in tensors])
+    assert_bit_equal(cabi_unpad(padded_e, sizes_of(tensors)), flat, "ntb200_unpad_nd")
+    assert_bit_equal(nt.from_padded_tensor(padded, a)._buffer, flat, "from_padded_tensor")
+    # an unaligned view of the dense tensor as the source of the unpad (rows start at every phase)
+    shifted = torch.empty(padded_e.numel() + 1, dtype=dtype, device=cuda_device)[1:].view(padded_e.shape)
+    shifted.copy_(padded_e)
+    assert_bit_equal(cabi_unpad(shifted, sizes_of(tensors)), flat, "ntb200_unpad_nd, unaligned source")
+    back = nt.nested_tensor_from_padded_tensor(padded_e, padding=pad_value)
+    oback = ntref.from_padded_by_value_fast(want_e, pad_value)
+    for got_t, want_t in zip(back.unbind(), oback):
+        assert got_t.numel() == want_t.numel() and (want_t.numel() == 0 or tuple(got_t.shape) == tuple(want_t.shape))
+    assert_bit_equal(back._buffer, torch.cat([t.reshape(-1) for t in oback]), "nested_tensor_from_padded_tensor")
+
+
 def test_config3_images(native_libs, cuda_device):
     """Configuration 3: 32 fp32 images (3, H_i, W_i): 4-D pad, the un-collapsible 4-D mask, and the
     DETR (B, maxH, maxW) mask = channel 0 of it."""
