@@ -150,6 +150,40 @@ def timed_regions(fn, steps, world, device, regions=5):
     return ms[len(ms) // 2], ms[0]
 
 
+def graph_ms(fn, n, device):
+    """Device time per call with the host's launch cost taken out: `n` calls of `fn` captured into ONE CUDA graph,
+    replayed once between two events (after a warm-up replay).  For operators of 60-100 us the eager loop leaves a
+    few microseconds of idle device between launches; this is the figure to hold against the kernel's roofline.
+    Returns None if the call cannot be captured."""
+    try:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(n):
+                fn()
+        g.replay()
+        torch.cuda.synchronize(device)
+        best = None
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize(device)
+            ms = e0.elapsed_time(e1) / n
+            best = ms if best is None or ms < best else best
+        del g
+        return best
+    except Exception:
+        torch.cuda.synchronize(device)
+        return None
+
+
 def all_sum(x, world, device):
     if world == 1:
         return x
@@ -790,9 +824,14 @@ def run_small_configs(args, local):
             fn()
         return timed_regions(fn, n, 1, device)
 
-    def hbm(ms, nbytes):
+    def hbm(ms, nbytes, fn=None):
         g = nbytes / ms / 1e6
-        return {"ms": ms, "GB/s": g, "frac_hbm_measured": g / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+        r = {"ms": ms, "GB/s": g, "frac_hbm_measured": g / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+        gm = graph_ms(fn, n, device) if fn is not None else None
+        if gm is not None:  # the same launches replayed from one CUDA graph: no host launch cost between them
+            r["graph_ms"] = gm
+            r["graph_frac_hbm_measured"] = nbytes / gm / 1e6 / peaks["hbm_gbs"]
+        return r
 
     w = workloads.config3()
     a = nt.NestedTensor(w.buffer.to(device), w.sizes)
@@ -800,12 +839,16 @@ def run_small_configs(args, local):
     nv = w.buffer.numel()
     padded = ops.to_padded_tensor(b, sz, meta, 0.0)
     npad = padded.numel()
+    f_pad = lambda: ops.to_padded_tensor(b, sz, meta, 0.0)
+    f_mask = lambda: ops.to_tensor_mask(b, sz, meta, None)
+    f_unpad = lambda: ops.from_padded_tensor(padded, sz, meta)
+    f_scan = lambda: ops.sizes_from_padded(padded, 0.0)
     c3 = {"workload": "config3: 32 fp32 images (3, H_i, W_i), H_i, W_i ~ U[400,1024]",
           "note": "0.6 GB per call; about 1 GB moved in and out: above the 126 MB L2, but part of a call's data is served from it",
-          "to_padded_tensor": hbm(timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0))[0], 4 * (nv + npad)),
-          "to_tensor_mask": hbm(timed(lambda: ops.to_tensor_mask(b, sz, meta, None))[0], 4 * (nv + npad) + npad),
-          "from_padded_tensor": hbm(timed(lambda: ops.from_padded_tensor(padded, sz, meta))[0], 8 * nv),
-          "sizes_from_padded": hbm(timed(lambda: ops.sizes_from_padded(padded, 0.0))[0], 4 * npad)}
+          "to_padded_tensor": hbm(timed(f_pad)[0], 4 * (nv + npad), f_pad),
+          "to_tensor_mask": hbm(timed(f_mask)[0], 4 * (nv + npad) + npad, f_mask),
+          "from_padded_tensor": hbm(timed(f_unpad)[0], 8 * nv, f_unpad),
+          "sizes_from_padded": hbm(timed(f_scan)[0], 4 * npad, f_scan)}
     ref = reference_kernel_times(w, device, n)
     if ref is not None:
         c3["reference_kernels_sm100a"] = ref
@@ -938,11 +981,15 @@ def run_kernels(args, local):
 
     only = args.only
 
-    def add(name, config, ms, nbytes=None, flops=None):
+    def add(name, config, ms, nbytes=None, flops=None, graph_fn=None):
         r = {"op": name, "config": config, "ms": ms}
         if nbytes is not None:
             r["GB/s"] = nbytes / ms / 1e6
             r["frac_hbm_measured"] = r["GB/s"] / peaks["hbm_gbs"]
+            gm = graph_ms(graph_fn, n, device) if graph_fn is not None else None
+            if gm is not None:
+                r["graph_ms"] = gm
+                r["graph_frac_hbm_measured"] = nbytes / gm / 1e6 / peaks["hbm_gbs"]
         if flops is not None:
             r["TFLOP/s"] = flops / ms / 1e9
             r["frac_bf16_burst"] = r["TFLOP/s"] / peaks["bf16_tflops"]
@@ -974,11 +1021,15 @@ def run_kernels(args, local):
         nv = w.buffer.numel()
         padded = ops.to_padded_tensor(b, sz, meta, 0.0)
         npad = padded.numel()
-        add("to_padded_tensor (4-D)", "c3", timed(lambda: ops.to_padded_tensor(b, sz, meta, 0.0), n), es * (nv + npad))
-        add("to_tensor_mask (4-D uint8 mask)", "c3", timed(lambda: ops.to_tensor_mask(b, sz, meta, None), n), es * (nv + npad) + npad)
+        f_pad = lambda: ops.to_padded_tensor(b, sz, meta, 0.0)
+        f_mask = lambda: ops.to_tensor_mask(b, sz, meta, None)
+        f_unpad = lambda: ops.from_padded_tensor(padded, sz, meta)
+        f_scan = lambda: ops.sizes_from_padded(padded, 0.0)
+        add("to_padded_tensor (4-D)", "c3", timed(f_pad, n), es * (nv + npad), graph_fn=f_pad)
+        add("to_tensor_mask (4-D uint8 mask)", "c3", timed(f_mask, n), es * (nv + npad) + npad, graph_fn=f_mask)
         add("to_mask(mask_dim=3)", "c3", timed(lambda: ops.to_mask(sz, meta, 3), n), None)
-        add("from_padded_tensor (4-D)", "c3", timed(lambda: ops.from_padded_tensor(padded, sz, meta), n), 2 * es * nv)
-        add("sizes_from_padded (scan)", "c3", timed(lambda: ops.sizes_from_padded(padded, 0.0), n), es * npad)
+        add("from_padded_tensor (4-D)", "c3", timed(f_unpad, n), 2 * es * nv, graph_fn=f_unpad)
+        add("sizes_from_padded (scan)", "c3", timed(f_scan, n), es * npad, graph_fn=f_scan)
         del padded
 
     if only in ("transpose", "c3"):

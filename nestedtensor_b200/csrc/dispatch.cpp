@@ -413,8 +413,9 @@ std::tuple<Tensor, Tensor> sizes_from_padded(const Tensor& tensor_, const at::Sc
   TORCH_CHECK(es == 1 || es == 2 || es == 4 || es == 8, "Input datatype ", tensor.dtype(), " is not supported.");
   std::vector<int64_t> dims(tensor.sizes().begin() + 1, tensor.sizes().end());
   auto opt = at::TensorOptions().dtype(at::kLong).device(tensor.device());
-  Tensor out_sizes = at::empty({B, nd}, opt);
-  Tensor out_counts = at::empty({B}, opt);
+  Tensor scan_out = at::empty({B * (nd + 1)}, opt);  // sizes, then counts: the library clears both with one launch
+  Tensor out_sizes = scan_out.narrow(0, 0, B * nd).view({B, nd});
+  Tensor out_counts = scan_out.narrow(0, B * nd, B);
   // A padding value the dtype cannot hold exactly equals no element: everything is valid.
   const int kind = cmp_kind_of(tensor.scalar_type());
   bool representable = true;
@@ -454,8 +455,9 @@ std::tuple<Tensor, Tensor> sizes_from_mask(const Tensor& mask_) {
   const int nd = (int)mask.dim() - 1;
   std::vector<int64_t> dims(mask.sizes().begin() + 1, mask.sizes().end());
   auto opt = at::TensorOptions().dtype(at::kLong).device(mask.device());
-  Tensor out_sizes = at::empty({B, nd}, opt);
-  Tensor out_counts = at::empty({B}, opt);
+  Tensor scan_out = at::empty({B * (nd + 1)}, opt);  // sizes, then counts: the library clears both with one launch
+  Tensor out_sizes = scan_out.narrow(0, 0, B * nd).view({B, nd});
+  Tensor out_counts = scan_out.narrow(0, B * nd, B);
   check_rc(ntb200_sizes_from_mask(static_cast<const uint8_t*>(mask.data_ptr()), out_sizes.data_ptr<int64_t>(),
                                   out_counts.data_ptr<int64_t>(), nd, B, dims.data(), cur_stream()),
            "ntb200_sizes_from_mask");

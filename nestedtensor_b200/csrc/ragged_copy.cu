@@ -693,6 +693,7 @@ struct RowParams {
   uint64_t blocks_per_entry;  // unpad: CTAs of kRowWarps rows per entry
 };
 constexpr int kRowWarps = 8;
+constexpr int kRowUnroll = 8;  // vectors per lane in flight: one trip covers a row of 4 KB
 
 template <int ES, int ND, bool FUSE>
 __global__ void __launch_bounds__(kRowWarps * 32) pad_rows_kernel(const RowParams p) {
@@ -741,7 +742,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) pad_rows_kernel(const RowParam
   Vec padvec;
 #pragma unroll
   for (int k = 0; k < VE; ++k) padvec.e[k] = padv;
-  constexpr int U = 4;  // vectors per lane in flight
+  constexpr int U = kRowUnroll;
   for (int64_t j0 = lane; j0 < nvec; j0 += 32 * U) {
     Vec val[U];
     int n[U];
@@ -814,7 +815,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) unpad_rows_kernel(const RowPar
     uint4 v;
     E e[VE];
   };
-  constexpr int U = 4;
+  constexpr int U = kRowUnroll;
   for (int64_t j0 = lane; j0 < nvec; j0 += 32 * U) {
     Vec val[U];
 #pragma unroll
@@ -903,7 +904,7 @@ template <int ES, int CMP>
 struct VecAllPad {
   uint32_t pl, ph, ml, mh;
   bool never;
-  __device__ explicit VecAllPad(uint64_t bits) {
+  __host__ __device__ explicit VecAllPad(uint64_t bits) {
     const uint64_t emask = ES == 8 ? ~0ull : ((1ull << (8 * (ES & 7))) - 1);
     uint64_t rep = bits & emask, srep = 1ull << (8 * ES - 1), mask = ~0ull;
 #pragma unroll
@@ -1311,29 +1312,50 @@ int launch_unpad_es(const UnpadParams& p, int nd, cudaStream_t st) {
   return NTB200_INVALID_ARG;
 }
 
-// Row walk of the same scan (2-3 dims, rows of at least 32 vectors): a warp reads one innermost row, keeps the count
-// of non-padding elements and the end of the last one, and the CTA's eight rows are merged per entry before the
-// atomics.  No division per vector; the row's coordinates are computed once.
-template <int ES, int ND, int CMP>
+// Row walk of the same scan (2-3 dims, rows of at least 32 vectors): a warp reads one innermost row and keeps the
+// count of non-padding elements and the end of the last one; thread 0 folds the CTA's eight consecutive rows per
+// entry (coordinates by increments, one division per CTA) before the atomics, which are the expensive part: with
+// one set of atomics per row instead of per CTA the kernel took 2.5 times as long.
+// The vector test (for a padding value that is not NaN) is integer and branch-free on the common classes: inside a constituent nearly every vector holds no
+// padding element, outside it only padding; the per-element compare runs on the mixed vectors alone.
+template <int ES, int CMP>
+__device__ __forceinline__ void vec_class(const VecAllPad<ES, CMP>& t, const uint4& v, bool& any_valid, bool& all_valid) {
+  const uint32_t y0 = (v.x ^ t.pl) & t.ml, y1 = (v.y ^ t.ph) & t.mh, y2 = (v.z ^ t.pl) & t.ml, y3 = (v.w ^ t.ph) & t.mh;
+  any_valid = (y0 | y1 | y2 | y3) != 0;
+  if (ES == 8) {
+    all_valid = ((y0 | y1) != 0) & ((y2 | y3) != 0);
+  } else if (ES == 4) {
+    all_valid = (y0 != 0) & (y1 != 0) & (y2 != 0) & (y3 != 0);
+  } else {  // a zero byte / half-word inside a word: (y - 0x01..) & ~y & 0x80..
+    constexpr uint32_t lo = ES == 2 ? 0x00010001u : 0x01010101u, hi = ES == 2 ? 0x80008000u : 0x80808080u;
+    const uint32_t z = ((y0 - lo) & ~y0) | ((y1 - lo) & ~y1) | ((y2 - lo) & ~y2) | ((y3 - lo) & ~y3);
+    all_valid = (z & hi) == 0;
+  }
+}
+
+// ALIGNED: every row is a whole number of 16-byte vectors (no element-wise head or tail).
+template <int ES, int ND, int CMP, bool ALIGNED>
 __global__ void __launch_bounds__(kRowWarps * 32) scan_rows_kernel(const ScanParams p) {
   using E = typename ElemBits<ES>::T;
   constexpr int VE = 16 / ES;
+  constexpr int U = kRowUnroll;
   const NotPad<ES, CMP> notpad(p.pad_bits);
-  const VecAllPad<ES, CMP> all_pad(p.pad_bits);
+  const VecAllPad<ES, CMP> t(p.pad_bits);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t rows_per_entry = ND == 2 ? p.m[0] : p.m[0] * p.m[1];
   const uint64_t n_rows = (uint64_t)p.batch * rows_per_entry;
-  const uint64_t row = (uint64_t)blockIdx.x * kRowWarps + warp;
-  const int64_t m_last = (int64_t)p.m[ND - 1];
-  __shared__ unsigned long long s_row[kRowWarps][3];  // entry, count, end of the last non-padding element
+  const uint64_t cta_row0 = (uint64_t)blockIdx.x * kRowWarps;
+  const uint64_t row = cta_row0 + warp;
+  const uint32_t m_last = (uint32_t)p.m[ND - 1];
+  __shared__ uint32_t s_cnt[kRowWarps], s_last[kRowWarps];
   uint32_t cnt = 0, last = 0;
   if (row < n_rows) {
     const E* __restrict__ srow = reinterpret_cast<const E*>(p.src) + row * (uint64_t)m_last;
-    int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(srow) & 15)) & 15) / ES);
+    uint32_t head = ALIGNED ? 0 : (uint32_t)(((16 - (reinterpret_cast<uintptr_t>(srow) & 15)) & 15) / ES);
     head = head < m_last ? head : m_last;
-    const int64_t nvec = (m_last - head) / VE;
-    const int64_t tail0 = head + nvec * VE;
-    if (lane < head && notpad(srow[lane])) {
+    const uint32_t nvec = (m_last - head) / VE;
+    const uint32_t tail0 = head + nvec * VE;
+    if (!ALIGNED && lane < head && notpad(srow[lane])) {
       cnt = 1;
       last = (uint32_t)lane + 1;
     }
@@ -1341,71 +1363,78 @@ __global__ void __launch_bounds__(kRowWarps * 32) scan_rows_kernel(const ScanPar
       uint4 v;
       E e[VE];
     };
-    constexpr int U = 4;
-    for (int64_t j0 = lane; j0 < nvec; j0 += 32 * U) {
+    const uint4* __restrict__ vrow = reinterpret_cast<const uint4*>(srow + head);
+    for (uint32_t j0 = lane; j0 < nvec; j0 += 32 * U) {
       Vec val[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (j0 + 32 * u < nvec) val[u].v = ld_global_16_stream(srow + head + (j0 + 32 * u) * VE);
+      for (int u = 0; u < U; ++u) {
+        val[u].v = make_uint4(t.pl, t.ph, t.pl, t.ph);  // past the row: padding
+        if (j0 + 32 * u < nvec) val[u].v = ld_global_16_stream(vrow + j0 + 32 * u);
+      }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        if (j0 + 32 * u >= nvec || all_pad(val[u].v)) continue;
-        uint32_t bits = 0;
+        bool any_valid, all_valid;
+        vec_class(t, val[u].v, any_valid, all_valid);
+        const uint32_t end = head + (j0 + 32 * u + 1) * VE;
+        cnt += all_valid ? VE : 0;
+        last = all_valid ? end : last;  // j0 and u only grow
+        if (any_valid && !all_valid) {
+          uint32_t bits = 0;
 #pragma unroll
-        for (int k = 0; k < VE; ++k)
-          if (notpad(val[u].e[k])) bits |= 1u << k;
-        if (bits == 0) continue;
-        cnt += (uint32_t)__popc(bits);
-        last = (uint32_t)(head + (j0 + 32 * u) * VE) + (uint32_t)(32 - __clz(bits));  // j0 only grows
+          for (int k = 0; k < VE; ++k)
+            if (notpad(val[u].e[k])) bits |= 1u << k;
+          cnt += (uint32_t)__popc(bits);
+          if (bits != 0) last = end - VE + (uint32_t)(32 - __clz(bits));
+        }
       }
     }
-    if (tail0 + lane < m_last && notpad(srow[tail0 + lane])) {
+    if (!ALIGNED && tail0 + lane < m_last && notpad(srow[tail0 + lane])) {
       cnt += 1;
-      last = (uint32_t)(tail0 + lane) + 1;
+      last = tail0 + (uint32_t)lane + 1;
     }
   }
-  const unsigned full = 0xffffffffu;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    cnt += __shfl_xor_sync(full, cnt, o);
-    const uint32_t other = __shfl_xor_sync(full, last, o);
-    last = last > other ? last : other;
-  }
+  cnt = __reduce_add_sync(0xffffffffu, cnt);
+  last = __reduce_max_sync(0xffffffffu, last);
   if (lane == 0) {
-    s_row[warp][0] = row < n_rows ? row : ~0ull;
-    s_row[warp][1] = cnt;
-    s_row[warp][2] = last;
+    s_cnt[warp] = cnt;
+    s_last[warp] = last;
   }
   __syncthreads();
-  if (threadIdx.x != 0) return;
-  // rows of one CTA are consecutive: merge runs of the same entry
-  long long cur_b = -1;
+  if (threadIdx.x != 0 || cta_row0 >= n_rows) return;
+  uint64_t b, rr, i0 = 0, i1 = 0;
+  divmod_u64(cta_row0, rows_per_entry, b, rr);
+  if (ND == 2) i0 = rr;
+  else divmod_u64(rr, p.m[1], i0, i1);
   unsigned long long c = 0, mx[3] = {0, 0, 0};
-  for (int w = 0; w < kRowWarps; ++w) {
-    if (s_row[w][0] == ~0ull || s_row[w][1] == 0) continue;
-    uint64_t b, rr;
-    divmod_u64(s_row[w][0], rows_per_entry, b, rr);
-    if ((long long)b != cur_b) {
-      if (cur_b >= 0) scan_flush<ND>(p, cur_b, c, mx);
-      cur_b = (long long)b;
+  const int n_here = (int)(n_rows - cta_row0 < (uint64_t)kRowWarps ? n_rows - cta_row0 : (uint64_t)kRowWarps);
+  for (int w = 0; w < n_here; ++w) {
+    const uint32_t cw = s_cnt[w];
+    if (cw != 0) {
+      c += cw;
+      const unsigned long long l = s_last[w];
+      mx[ND - 1] = mx[ND - 1] > l ? mx[ND - 1] : l;
+      mx[0] = mx[0] > i0 + 1 ? mx[0] : i0 + 1;
+      if (ND == 3) mx[1] = mx[1] > i1 + 1 ? mx[1] : i1 + 1;
+    }
+    bool next_entry;
+    if (ND == 2) {
+      next_entry = ++i0 == p.m[0];
+    } else {
+      next_entry = false;
+      if (++i1 == p.m[1]) {
+        i1 = 0;
+        next_entry = ++i0 == p.m[0];
+      }
+    }
+    if (next_entry) {
+      scan_flush<ND>(p, (int64_t)b, c, mx);
       c = 0;
       mx[0] = mx[1] = mx[2] = 0;
+      i0 = 0;
+      ++b;
     }
-    c += s_row[w][1];
-    unsigned long long e[3];
-    if (ND == 2) {
-      e[0] = rr + 1;
-    } else {
-      uint64_t i0, i1;
-      divmod_u64(rr, p.m[1], i0, i1);
-      e[0] = i0 + 1;
-      e[1] = i1 + 1;
-    }
-    e[ND - 1] = s_row[w][2];
-#pragma unroll
-    for (int j = 0; j < ND; ++j) mx[j] = mx[j] > e[j] ? mx[j] : e[j];
   }
-  if (cur_b >= 0) scan_flush<ND>(p, cur_b, c, mx);
+  scan_flush<ND>(p, (int64_t)b, c, mx);
 }
 
 template <int ES, int ND, int CMP>
@@ -1414,11 +1443,15 @@ int launch_scan_es_nd(const ScanParams& p, bool big, cudaStream_t st) {
   const int64_t tile = (int64_t)kThreads * kVecPerThread * VE;
   const int64_t blocks = ceil_div(p.total, tile);
   if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
-  if (ND >= 2 && p.m[ND - 1] * (uint64_t)ES >= 512 && p.m[ND - 1] < (1ull << 31)) {
+  // (a NaN padding value equals no element: the row kernel's vector classes assume a value that can match)
+  if (ND >= 2 && p.m[ND - 1] * (uint64_t)ES >= 512 && p.m[ND - 1] < (1ull << 31) && !VecAllPad<ES, CMP>(p.pad_bits).never) {
     const uint64_t rows = (uint64_t)p.batch * (ND == 2 ? p.m[0] : p.m[0] * p.m[1]);
     const uint64_t row_blocks = (rows + kRowWarps - 1) / kRowWarps;
     if (row_blocks > 0x7fffffffull) return NTB200_UNSUPPORTED_SHAPE;
-    scan_rows_kernel<ES, (ND >= 2 ? ND : 2), CMP><<<(unsigned)row_blocks, kRowWarps * 32, 0, st>>>(p);
+    if ((p.m[ND - 1] * (uint64_t)ES) % 16 == 0)  // (the base is 16-byte aligned)
+      scan_rows_kernel<ES, (ND >= 2 ? ND : 2), CMP, true><<<(unsigned)row_blocks, kRowWarps * 32, 0, st>>>(p);
+    else
+      scan_rows_kernel<ES, (ND >= 2 ? ND : 2), CMP, false><<<(unsigned)row_blocks, kRowWarps * 32, 0, st>>>(p);
     return status_from_cuda(cudaGetLastError());
   }
   if (big) sizes_scan_kernel<ES, ND, CMP, true><<<(unsigned)blocks, kThreads, 0, st>>>(p);
@@ -1668,9 +1701,11 @@ static int sizes_scan_common(const void* src, int64_t* out_sizes, int64_t* out_c
   if (batch == 0) return NTB200_OK;
   if (out_sizes == nullptr || out_counts == nullptr) return NTB200_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t ce = cudaMemsetAsync(out_sizes, 0, sizeof(int64_t) * (size_t)batch * nd, st);
+  // one clearing launch when the counts follow the sizes in memory (as the operator layer allocates them)
+  const bool adjacent = out_counts == out_sizes + batch * nd;
+  cudaError_t ce = cudaMemsetAsync(out_sizes, 0, sizeof(int64_t) * (size_t)batch * (adjacent ? nd + 1 : nd), st);
   if (ce != cudaSuccess) return NTB200_LAUNCH_FAILED;
-  ce = cudaMemsetAsync(out_counts, 0, sizeof(int64_t) * (size_t)batch, st);
+  if (!adjacent) ce = cudaMemsetAsync(out_counts, 0, sizeof(int64_t) * (size_t)batch, st);
   if (ce != cudaSuccess) return NTB200_LAUNCH_FAILED;
   if (g.P == 0) return NTB200_OK;
   if (g.P > (uint64_t)INT64_MAX / (uint64_t)batch) return NTB200_INVALID_ARG;

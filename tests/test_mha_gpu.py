@@ -464,3 +464,33 @@ def test_sizes_from_padded_semantics(native_libs, cuda_device, dtype):
         t2[2, 0, 1] = float("nan")   # NaN != 0 -> valid
         b = nt.nested_tensor_from_padded_tensor(t2.to(cuda_device), padding=0)
         assert b.nested_size()[2] == torch.Size([1, 2])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.uint8],
+                         ids=str)
+@pytest.mark.parametrize("width", [640, 637])
+def test_sizes_from_padded_semantics_long_rows(native_libs, cuda_device, dtype, width):
+    """The same comparison rules in the warp-per-row scan (rows of at least 512 bytes; 637 wide: rows that start at
+    every phase of a 16-byte vector): -0.0 is padding 0.0, NaN is never padding, a NaN padding value matches nothing,
+    and a box that holds the padding value inside is refused."""
+    t = torch.zeros(3, 4, width, dtype=dtype)
+    t[0, :2, :333] = 1
+    t[1, :4, :width] = 2
+    t[2, :1, :17] = 3
+    if dtype.is_floating_point:
+        t[0, 3, width - 1] = -0.0    # still padding
+    a = nt.nested_tensor_from_padded_tensor(t.to(cuda_device), padding=0)
+    assert a.nested_size() == (torch.Size([2, 333]), torch.Size([4, width]), torch.Size([1, 17]))
+    assert_close_bits = torch.equal(a.unbind()[0].cpu(), t[0, :2, :333])
+    assert assert_close_bits
+    if dtype.is_floating_point:
+        t2 = t.clone()
+        t2[2, 0, 17] = float("nan")  # NaN != 0 -> valid
+        b = nt.nested_tensor_from_padded_tensor(t2.to(cuda_device), padding=0)
+        assert b.nested_size()[2] == torch.Size([1, 18])
+        c = nt.nested_tensor_from_padded_tensor(t.to(cuda_device), padding=float("nan"))
+        assert c.nested_size() == (torch.Size([4, width]),) * 3
+    t3 = t.clone()
+    t3[1, 2, 100] = 0                # a padding value inside the box
+    with pytest.raises(RuntimeError, match="not a padding mask"):
+        nt.nested_tensor_from_padded_tensor(t3.to(cuda_device), padding=0)
