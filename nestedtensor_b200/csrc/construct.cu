@@ -308,6 +308,145 @@ transpose_ragged_vec_kernel(const T* __restrict__ in, T* __restrict__ out, const
   }
 }
 
+// 2-byte elements (fp16 / bf16 feature maps): the ragged side moves aligned PAIRS of pixels, 4 bytes per thread and
+// access, which halves its load/store instructions and doubles the bytes a thread keeps in flight.  The tile lives
+// in shared memory as [regular][pixel pair] 32-bit words (one word = two neighbouring pixels of one channel) with
+// an odd word stride: the pair side touches consecutive words, the vector side reads, per pixel pair and group of
+// eight channels, eight words and regroups them into the two 16-byte vectors of the two pixels with byte permutes;
+// both are free of bank conflicts.  A pair is 4-byte aligned in global memory unless the constituent has an odd
+// number of pixels AND the channel index is odd; the channel parity is fixed per thread, so that case (and a last
+// single pixel) falls back to two 2-byte accesses without divergence inside a warp.
+constexpr int kPairPx = 128;                // pixels per tile
+constexpr int kPairWords = kPairPx / 2 + 1;  // words per channel row of the tile (odd)
+
+template <bool REG_IS_ROWS>
+__global__ void __launch_bounds__(256)
+transpose_ragged_pair_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, const int64_t* __restrict__ offsets,
+                             int64_t regular) {
+  __shared__ uint32_t tile[kTrTile][kPairWords];  // [channel][pixel pair]
+  const int64_t b = blockIdx.y;
+  const int64_t off = offsets[b];
+  const int64_t n = (offsets[b + 1] - off) / regular;
+  const int64_t tiles_reg = (regular + kTrTile - 1) / kTrTile;
+  const int64_t t_rag = blockIdx.x / tiles_reg, t_reg = blockIdx.x % tiles_reg;
+  if (t_rag * kPairPx >= n) return;
+  const int64_t p0 = t_rag * kPairPx, c0 = t_reg * kTrTile;
+  const uint16_t* src = in + off;
+  uint16_t* dst = out + off;
+  // pair side: thread (pp, cy) owns pixel pair pp of channels c0 + cy, c0 + cy + 4, ...
+  constexpr int kChStep = 4, kPerThread = kTrTile / kChStep;
+  const int pp = threadIdx.x & 63, cy = threadIdx.x >> 6;
+  const int64_t px = p0 + 2 * pp;
+  const int n_here = px + 1 < n ? 2 : (px < n ? 1 : 0);
+  const bool aligned = !((n & 1) && (cy & 1));  // (off, p0 and c0 are even)
+  const int64_t ch_left = regular - c0 - cy;
+  const int lim = n_here > 0 && ch_left > 0 ? (int)(ch_left < kTrTile ? ch_left : kTrTile) : 0;  // valid while i * 4 < lim
+  const int64_t step = (int64_t)kChStep * n;
+  // vector side: item (pixel pair q, channel group v): a pixel's eight channel groups on eight neighbouring lanes
+  // (128-byte rows of the channel-contiguous matrix), four pixel pairs per warp
+  auto item = [&](int k, int& q, int& v) {
+    const int idx = k * 256 + threadIdx.x;
+    v = idx & 7;
+    q = idx >> 3;
+  };
+  // word column of pixel pair q in channel row c: pairs of the upper 32 channel rows sit four words off, which keeps
+  // the eight channel groups of the vector side (rows 8 v + m, a stride of 8 * 65 words = 8 banks) on distinct banks
+  auto col = [](int c, int q) { return q ^ ((c >> 5) << 2); };
+  if (REG_IS_ROWS) {  // in [regular][n] -> out [n][regular]
+    // (the choice between word and half-word accesses is made once, outside the unrolled loops, so that every
+    // load of the thread is issued before the first shared-memory store)
+    const uint16_t* p = src + (c0 + cy) * n + px;
+    if (aligned && n_here == 2) {
+      uint32_t w[kPerThread];
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) {
+        w[i] = (i * kChStep < lim) ? *reinterpret_cast<const uint32_t*>(p) : 0u;
+        p += step;
+      }
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) tile[cy + i * kChStep][col(cy + i * kChStep, pp)] = w[i];
+    } else {
+      constexpr int kBatch = kPerThread / 2;  // the same number of registers as the word path
+#pragma unroll
+      for (int h = 0; h < kPerThread; h += kBatch) {
+        uint16_t lo[kBatch], hi[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+          lo[i] = ((h + i) * kChStep < lim) ? p[0] : (uint16_t)0;
+          hi[i] = ((h + i) * kChStep < lim && n_here == 2) ? p[1] : (uint16_t)0;
+          p += step;
+        }
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) tile[cy + (h + i) * kChStep][col(cy + (h + i) * kChStep, pp)] = (uint32_t)lo[i] | ((uint32_t)hi[i] << 16);
+      }
+    }
+  } else {  // in [n][regular] -> out [regular][n]
+    uint4 x0[2], x1[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      int q, v;
+      item(k, q, v);
+      const int64_t q0 = p0 + 2 * q, c = c0 + v * 8;
+      x0[k] = (q0 < n && c < regular) ? *reinterpret_cast<const uint4*>(src + q0 * regular + c) : make_uint4(0, 0, 0, 0);
+      x1[k] = (q0 + 1 < n && c < regular) ? *reinterpret_cast<const uint4*>(src + (q0 + 1) * regular + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      int q, v;
+      item(k, q, v);
+      const uint32_t a[4] = {x0[k].x, x0[k].y, x0[k].z, x0[k].w}, c[4] = {x1[k].x, x1[k].y, x1[k].z, x1[k].w};
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        tile[v * 8 + 2 * m][col(v * 8, q)] = __byte_perm(a[m], c[m], 0x5410);      // channel 2m: low halves of both pixels
+        tile[v * 8 + 2 * m + 1][col(v * 8, q)] = __byte_perm(a[m], c[m], 0x7632);  // channel 2m + 1: high halves
+      }
+    }
+  }
+  __syncthreads();
+  if (REG_IS_ROWS) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      int q, v;
+      item(k, q, v);
+      uint32_t w[8];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) w[m] = tile[v * 8 + m][col(v * 8, q)];
+      const int64_t q0 = p0 + 2 * q, c = c0 + v * 8;
+      if (c < regular) {
+        if (q0 < n)
+          *reinterpret_cast<uint4*>(dst + q0 * regular + c) =
+              make_uint4(__byte_perm(w[0], w[1], 0x5410), __byte_perm(w[2], w[3], 0x5410), __byte_perm(w[4], w[5], 0x5410),
+                         __byte_perm(w[6], w[7], 0x5410));
+        if (q0 + 1 < n)
+          *reinterpret_cast<uint4*>(dst + (q0 + 1) * regular + c) =
+              make_uint4(__byte_perm(w[0], w[1], 0x7632), __byte_perm(w[2], w[3], 0x7632), __byte_perm(w[4], w[5], 0x7632),
+                         __byte_perm(w[6], w[7], 0x7632));
+      }
+    }
+  } else {
+    uint16_t* q = dst + (c0 + cy) * n + px;
+    uint32_t w[kPerThread];
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) w[i] = tile[cy + i * kChStep][col(cy + i * kChStep, pp)];
+    if (aligned && n_here == 2) {
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) {
+        if (i * kChStep < lim) *reinterpret_cast<uint32_t*>(q) = w[i];
+        q += step;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) {
+        if (i * kChStep < lim) {
+          q[0] = (uint16_t)w[i];
+          if (n_here == 2) q[1] = (uint16_t)(w[i] >> 16);
+        }
+        q += step;
+      }
+    }
+  }
+}
+
 template <typename T>
 int launch_transpose_ragged(const void* in, void* out, const int64_t* offsets, int64_t batch, int64_t regular,
                             int regular_is_rows, int64_t max_ragged, cudaStream_t st) {
@@ -319,6 +458,15 @@ int launch_transpose_ragged(const void* in, void* out, const int64_t* offsets, i
   for (int64_t b0 = 0; b0 < batch; b0 += 65535) {  // gridDim.y limit
     const int64_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
     dim3 grid((unsigned)tiles, (unsigned)nb);
+    if constexpr (sizeof(T) == 2) {
+      if (vec) {  // (kPairPx == kTrRag: the same grid)
+        if (regular_is_rows)
+          transpose_ragged_pair_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out), offsets + b0, regular);
+        else
+          transpose_ragged_pair_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out), offsets + b0, regular);
+        continue;
+      }
+    }
     if constexpr (sizeof(T) < 8) {
       if (vec && regular_is_rows) {
         transpose_ragged_vec_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets + b0, regular);

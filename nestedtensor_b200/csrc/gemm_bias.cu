@@ -362,20 +362,44 @@ struct Ctrl2 {
   uint64_t tfull[2];          // one per CTA
   uint64_t tempty[2];         // used in CTA 0: the epilogue warps of both CTAs arrive
   uint64_t done;
+  uint64_t rfull[4];          // RES: residual box landed (bytes), one per 64-column box of this CTA's 128 x 256 tile
+  uint64_t rempty[4];         // RES: the four warps that read a box are done with it
   uint32_t tmem_base;
   volatile int abort;
 };
 static_assert(sizeof(Ctrl2) <= 256, "control block");
+// RES (a residual matrix is added in the epilogue): the residual tile of each CTA, 128 rows x 256 columns, is staged
+// in shared memory by TMA as four 128 x 64 boxes (16 KB each, 128-byte swizzle) instead of per-thread 64-byte row
+// reads; it takes the place of one main-loop stage and a bit.  Each group of four epilogue warps (128 columns) owns
+// two boxes; the first warp's lane 0 reloads a box for the CTA's next tile as soon as the four warps have released
+// it, so the load of box h for tile i + 1 runs under the epilogue of the other box and the next main loop.
+constexpr int k2ResBoxBytes = 128 * 64 * 2;
+constexpr int k2ResBytes = 4 * k2ResBoxBytes;
+constexpr int k2StagesRes = k2Stages - 1;
+constexpr int k2SmemRes = 1024 + k2StagesRes * k2StageBytes + k2ResBytes + kCtrlBytes;
+static_assert(k2SmemRes <= 232448, "shared memory of the residual variant");
 
-template <int FMT>
+// The thread's 64 bytes (32 columns) of row r of a swizzled 128 x 64 residual box: 16-byte units u0 .. u0 + 3.
+__device__ __forceinline__ void load_res_smem(uint32_t box, int r, int u0, uint4 (&q)[4]) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint32_t addr = box + (uint32_t)r * 128u + ((uint32_t)((u0 + g) ^ (r & 7)) << 4);
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[g].x), "=r"(q[g].y), "=r"(q[g].z), "=r"(q[g].w) : "r"(addr));
+  }
+}
+
+template <int FMT, bool RES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                              const void* __restrict__ bias, const void* __restrict__ residual, int act, void* __restrict__ C,
-                         int M, int N, int K) {
+                              const __grid_constant__ CUtensorMap map_r, const void* __restrict__ bias,
+                              const void* __restrict__ residual, int act, void* __restrict__ C, int M, int N, int K) {
+  constexpr int k2Stages = RES ? k2StagesRes : ntb200::k2Stages;  // (shadows the namespace constant below)
+  constexpr int kResOff = k2Stages * k2StageBytes;                // residual boxes (RES), then the control block
+  constexpr int kCtrlOff = kResOff + (RES ? k2ResBytes : 0);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Ctrl2* ctrl = reinterpret_cast<Ctrl2*>(smem + k2Stages * k2StageBytes);
-  float* s_bias = reinterpret_cast<float*>(smem + k2Stages * k2StageBytes + 256);
+  Ctrl2* ctrl = reinterpret_cast<Ctrl2*>(smem + kCtrlOff);
+  float* s_bias = reinterpret_cast<float*>(smem + kCtrlOff + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -393,6 +417,13 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
       ptx::mbar_init(ptx::smem_u32(&ctrl->tempty[a]), 2 * kEpiWarps);
     }
     ptx::mbar_init(ptx::smem_u32(&ctrl->done), 1);
+    if (RES) {
+      for (int j = 0; j < 4; ++j) {
+        ptx::mbar_init(ptx::smem_u32(&ctrl->rfull[j]), 1);
+        ptx::mbar_init(ptx::smem_u32(&ctrl->rempty[j]), 4);
+      }
+      ptx::prefetch_tensormap(&map_r);
+    }
     ctrl->abort = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_a);
@@ -489,6 +520,7 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     const bool wide = (N % 16 == 0) && (reinterpret_cast<uintptr_t>(C) % 32 == 0);
     uint32_t tile_iter = 0;
     bool ok = true;
+    uint32_t res_issued[2] = {0, 0}, res_landed[2] = {0, 0};  // RES, loader thread: loads issued / seen landed per box
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tile_iter) {
       const int m0 = (tile / num_n) * 256 + (int)rank * 128, n0 = (tile % num_n) * 256;
       const uint32_t acc = tile_iter & 1;
@@ -500,6 +532,75 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       const int row = m0 + q * 32 + lane;
       uint16_t* crow = reinterpret_cast<uint16_t*>(C) + (size_t)row * N + n0;
+      if constexpr (RES) {
+        const int g = (warp - 2) >> 2;                          // column group: boxes 2g and 2g + 1
+        const bool loader = ((warp - 2) & 3) == 0 && lane == 0;  // reloads the group's boxes
+        const int c_begin = g * (kBN / 2);
+        const uint32_t box0 = smem_base + kResOff + (uint32_t)(2 * g) * k2ResBoxBytes;
+        const int next_tile = tile + num_pairs;
+        if (tile_iter == 0 && loader) {  // the first tile's boxes (later ones are loaded a tile ahead, below)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t bar = ptx::smem_u32(&ctrl->rfull[2 * g + h]);
+            ptx::mbar_arrive_expect_tx(bar, k2ResBoxBytes);
+            ptx::tma_load_2d(box0 + h * k2ResBoxBytes, &map_r, bar, n0 + c_begin + 64 * h, m0);
+            res_issued[h] = 1;
+          }
+        }
+        __syncwarp();
+        if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
+        if (!ok) continue;  // (aborted: nobody issues or awaits anything further; the loads in flight are drained below)
+        ptx::tc_fence_after_sync();
+        const uint32_t tacc = tmem_base + acc * kAccCols + ((uint32_t)(q * 32) << 16);
+        const int r_loc = q * 32 + lane;
+        uint32_t ra[32], rb[32];
+        uint4 qa[4], qb[4];
+        if (n0 + c_begin < N) ptx::tmem_ld_32x32b_x32(tacc + c_begin, ra);
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          const int c = c_begin + 64 * h;
+          const uint32_t box = box0 + h * k2ResBoxBytes;
+          if (!wait_or_abort(ptx::smem_u32(&ctrl->rfull[2 * g + h]), tile_iter & 1, &ctrl->abort)) ok = false;
+          else res_landed[h] = tile_iter + 1;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            ptx::tmem_ld_wait();  // (a tensor-memory load may be in flight)
+            break;
+          }
+          if (n0 + c < N) {  // (uniform over the group)
+            ptx::tmem_ld_wait();
+            const bool second = n0 + c + 32 < N;
+            if (second) ptx::tmem_ld_32x32b_x32(tacc + c + 32, rb);
+            load_res_smem(box, r_loc, 0, qa);
+            if (row < M) store_chunk32<FMT>(crow + c, ra, s_bias + c, N - (n0 + c), wide, act, qa, true);
+            if (second) {
+              ptx::tmem_ld_wait();
+              if (h == 0 && n0 + c + 64 < N) ptx::tmem_ld_32x32b_x32(tacc + c + 64, ra);
+              load_res_smem(box, r_loc, 4, qb);
+              if (row < M) store_chunk32<FMT>(crow + c + 32, rb, s_bias + c + 32, N - (n0 + c + 32), wide, act, qb, true);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->rempty[2 * g + h]));
+          if (loader && next_tile < num_tiles) {  // the same box of the CTA's next tile, once all four warps left it
+            if (wait_or_abort(ptx::smem_u32(&ctrl->rempty[2 * g + h]), tile_iter & 1, &ctrl->abort)) {
+              const int nm0 = (next_tile / num_n) * 256 + (int)rank * 128, nn0 = (next_tile % num_n) * 256;
+              const uint32_t bar = ptx::smem_u32(&ctrl->rfull[2 * g + h]);
+              ptx::mbar_arrive_expect_tx(bar, k2ResBoxBytes);
+              ptx::tma_load_2d(box, &map_r, bar, nn0 + c, nm0);
+              res_issued[h] = tile_iter + 2;
+            } else {
+              ctrl->abort = 1;
+            }
+          }
+          __syncwarp();
+        }
+        if (!ok) continue;
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(&ctrl->tempty[acc]), 0));
+        continue;
+      }
       const uint16_t* rrow = residual != nullptr ? reinterpret_cast<const uint16_t*>(residual) + (size_t)row * N + n0 : nullptr;
       prefetch_res_l2(rrow, row < M, ((warp - 2) >> 2) * (kBN / 2), N - n0);  // while the main loop of this tile still runs
       if (ok && !wait_or_abort(ptx::smem_u32(&ctrl->tfull[acc]), (tile_iter >> 1) & 1, &ctrl->abort)) ok = false;
@@ -542,6 +643,12 @@ gemm_bias_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     if (!ok && lane == 0) {
       ctrl->abort = 1;
       atomicOr(&g_gemm_error, 4);
+    }
+    if (RES) {  // after an abort: a residual box still in flight must land before the shared memory is released
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        if (res_issued[h] > res_landed[h])
+          ptx::mbar_wait(ptx::smem_u32(&ctrl->rfull[2 * ((warp - 2) >> 2) + h]), (res_issued[h] - 1) & 1);
     }
   }
 
@@ -605,16 +712,22 @@ int launch_tcgen05(const void* A, const void* W, const void* bias, const void* r
   return status_from_cuda(cudaGetLastError());
 }
 
-template <int FMT>
+template <int FMT, bool RES>
 int launch_tcgen05_pair(const void* A, const void* W, const void* bias, const void* residual, int act, void* C, int M, int N,
                         int K, int dtype, cudaStream_t st) {
-  CUtensorMap map_a, map_w;
+  constexpr int smem_bytes = RES ? k2SmemRes : k2Smem;
+  CUtensorMap map_a, map_w, map_r;
   if (!make_map_2d(&map_a, A, dtype, (uint64_t)M, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
   if (!make_map_2d(&map_w, W, dtype, (uint64_t)N, (uint64_t)K, 128)) return NTB200_LAUNCH_FAILED;
+  if (RES) {
+    if (!make_map_2d(&map_r, residual, dtype, (uint64_t)M, (uint64_t)N, 128)) return NTB200_LAUNCH_FAILED;
+  } else {
+    map_r = map_a;  // (not read)
+  }
   static std::atomic<int> attr_set[kMaxDevices];
   if (!once_per_device(attr_set, [] {
-        return cudaFuncSetAttribute(gemm_bias_tcgen05_pair_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, k2Smem) ==
-               cudaSuccess;
+        return cudaFuncSetAttribute(gemm_bias_tcgen05_pair_kernel<FMT, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    smem_bytes) == cudaSuccess;
       }))
     return NTB200_LAUNCH_FAILED;
   const int num_tiles = ((M + 255) / 256) * ((N + 255) / 256);
@@ -627,7 +740,7 @@ int launch_tcgen05_pair(const void* A, const void* W, const void* bias, const vo
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = k2Smem;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -638,14 +751,15 @@ int launch_tcgen05_pair(const void* A, const void* W, const void* bias, const vo
   if (max_pairs == 0) {
     cfg.gridDim = dim3(2 * (sms / 2));
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bias_tcgen05_pair_kernel<FMT>, &cfg) == cudaSuccess && n > 0) max_pairs = n;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bias_tcgen05_pair_kernel<FMT, RES>, &cfg) == cudaSuccess && n > 0) max_pairs = n;
     else max_pairs = sms / 2;
     (void)cudaGetLastError();
     max_pairs_of[dev].store(max_pairs, std::memory_order_relaxed);
   }
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
   cfg.gridDim = dim3(2 * pairs);
-  if (cudaLaunchKernelEx(&cfg, gemm_bias_tcgen05_pair_kernel<FMT>, map_a, map_w, bias, residual, act, C, M, N, K) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemm_bias_tcgen05_pair_kernel<FMT, RES>, map_a, map_w, map_r, bias, residual, act, C, M, N, K) !=
+      cudaSuccess) {
     (void)cudaGetLastError();
     return NTB200_LAUNCH_FAILED;
   }
@@ -770,9 +884,15 @@ int ntb200_gemm_bias_act(const void* A, const void* W, const void* bias, const v
   if ((force_simt == 2 || force_simt == 3) && !tc) return NTB200_UNSUPPORTED_SHAPE;
   if (tc) {
     const bool pair = force_simt == 3 || (force_simt == 0 && M > 128);
+    // The residual tile comes through shared memory (at the price of one main-loop stage) while the main loop of a
+    // tile is short; from K = 2048 on the per-thread row reads of the other variant hide under it (K = 4096: 2 % faster).
+    if (pair && residual != nullptr && K < 2048) {
+      if (dtype == NTB200_F16) return launch_tcgen05_pair<0, true>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
+      return launch_tcgen05_pair<1, true>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
+    }
     if (pair) {
-      if (dtype == NTB200_F16) return launch_tcgen05_pair<0>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
-      return launch_tcgen05_pair<1>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
+      if (dtype == NTB200_F16) return launch_tcgen05_pair<0, false>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
+      return launch_tcgen05_pair<1, false>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
     }
     if (dtype == NTB200_F16) return launch_tcgen05<0>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
     return launch_tcgen05<1>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);

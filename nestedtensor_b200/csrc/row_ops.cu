@@ -128,13 +128,17 @@ constexpr int kLnThreads = 256;
 // One row per GROUP threads, the row held in registers between the passes (one global read, one global
 // write per element).  VPL = 16-byte vectors per thread; vector v of the row belongs to thread v % GROUP.
 // Mean and variance are the two-pass forms of the reference kernel (sum, then sum of squared deviations).
-template <int DT, int VPL, int GROUP, bool FUSED>
-__global__ void __launch_bounds__(kLnThreads)
+// A 16-bit row without the fused additions stays in its packed form (4 registers per vector instead of 8) and is
+// widened again in each pass, which is exact: half the registers, twice the rows in flight per SM.
+// FULL: the row is exactly VPL * GROUP vectors (no per-vector bound test).
+template <int DT, int VPL, int GROUP, bool FUSED, bool FULL>
+__global__ void __launch_bounds__(kLnThreads, (!FUSED && FULL && DT != NTB200_F32 && VPL <= 4) ? 6 : 1)
 layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* __restrict__ bias,
                   const void* __restrict__ gamma, const void* __restrict__ beta, float eps, void* out, int64_t rows,
                   int cols) {  // out may alias x: a thread has read all it needs of the row before it writes
   constexpr int EPV = Vec16<DT>::kElems;
   constexpr int kRowsPerBlock = kLnThreads / GROUP;
+  constexpr bool RAW = !FUSED && DT != NTB200_F32;
   __shared__ float scratch[kLnThreads / 32];
   const int t = threadIdx.x % GROUP;
   const int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + threadIdx.x / GROUP;
@@ -144,12 +148,26 @@ layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* 
   const uint4* xr = reinterpret_cast<const uint4*>(x) + row * nv;
   const uint4* rr = reinterpret_cast<const uint4*>(residual) + row * nv;
   constexpr int PPV = EPV / 2;  // packed pairs per vector
-  uint64_t v[VPL][PPV];
+  uint4 raw[RAW ? VPL : 1];
+  uint64_t v[RAW ? 1 : VPL][PPV];
+  if (RAW) {  // all loads of the row first
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int vec = t + j * GROUP;
+      raw[j] = make_uint4(0u, 0u, 0u, 0u);
+      if ((FULL || vec < nv) && live) raw[j] = xr[vec];
+    }
+  }
   uint64_t sum2 = 0;
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     const int vec = t + j * GROUP;
-    if (vec < nv) {
+    if (RAW) {
+      uint64_t a[PPV];
+      unpack_pairs<DT>(raw[j], a);  // (vectors past the row are zero)
+#pragma unroll
+      for (int k = 0; k < PPV; ++k) sum2 = ptx::f32x2_add(sum2, a[k]);
+    } else if ((FULL || vec < nv) && live) {
       unpack_pairs<DT>(xr[vec], v[j]);
       if (FUSED) {
         uint64_t a[PPV];
@@ -171,6 +189,13 @@ layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* 
       for (int k = 0; k < PPV; ++k) v[j][k] = 0;
     }
   }
+  // (an empty asm that "rewrites" the packed row: keeps the compiler from carrying the widened copy across the pass)
+#define NTB200_LN_LAUNDER()                                                                                     \
+  if (RAW) {                                                                                                    \
+    _Pragma("unroll") for (int j = 0; j < VPL; ++j)                                                             \
+        asm volatile("" : "+r"(raw[j].x), "+r"(raw[j].y), "+r"(raw[j].z), "+r"(raw[j].w));                      \
+  }
+  NTB200_LN_LAUNDER();
   float s_lo, s_hi;
   ptx::f32x2_unpack(sum2, s_lo, s_hi);
   const float mean = group_sum<GROUP>(s_lo + s_hi, scratch) / (float)cols;
@@ -178,32 +203,53 @@ layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* 
   uint64_t sq2 = 0;
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
-    if (t + j * GROUP < nv) {
+    if (FULL || t + j * GROUP < nv) {
+      if (RAW) {
+        uint64_t a[PPV];
+        unpack_pairs<DT>(raw[j], a);
 #pragma unroll
-      for (int k = 0; k < PPV; ++k) {
-        v[j][k] = ptx::f32x2_sub(v[j][k], mean2);  // deviations replace the values
-        sq2 = ptx::f32x2_fma(v[j][k], v[j][k], sq2);
+        for (int k = 0; k < PPV; ++k) {
+          const uint64_t d = ptx::f32x2_sub(a[k], mean2);
+          sq2 = ptx::f32x2_fma(d, d, sq2);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < PPV; ++k) {
+          v[j][k] = ptx::f32x2_sub(v[j][k], mean2);  // deviations replace the values
+          sq2 = ptx::f32x2_fma(v[j][k], v[j][k], sq2);
+        }
       }
     }
   }
+  NTB200_LN_LAUNDER();
+#undef NTB200_LN_LAUNDER
   ptx::f32x2_unpack(sq2, s_lo, s_hi);
   const float rstd = rsqrtf(group_sum<GROUP>(s_lo + s_hi, scratch) / (float)cols + eps);
+  if (!live) return;
   const uint64_t rstd2 = ptx::f32x2_pack(rstd, rstd);
   uint4* orow = reinterpret_cast<uint4*>(out) + row * nv;
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     const int vec = t + j * GROUP;
-    if (vec < nv) {
-      uint64_t o[PPV];
+    if (FULL || vec < nv) {
+      uint64_t o[PPV], d[PPV];
+      if (RAW) {
+        unpack_pairs<DT>(raw[j], d);
+#pragma unroll
+        for (int k = 0; k < PPV; ++k) d[k] = ptx::f32x2_sub(d[k], mean2);
+      } else {
+#pragma unroll
+        for (int k = 0; k < PPV; ++k) d[k] = v[j][k];
+      }
       if (gamma != nullptr) {
         uint64_t g[PPV], b[PPV];
         unpack_pairs<DT>(reinterpret_cast<const uint4*>(gamma)[vec], g);
         unpack_pairs<DT>(reinterpret_cast<const uint4*>(beta)[vec], b);
 #pragma unroll
-        for (int k = 0; k < PPV; ++k) o[k] = ptx::f32x2_fma(ptx::f32x2_fma(v[j][k], rstd2, 0ull), g[k], b[k]);
+        for (int k = 0; k < PPV; ++k) o[k] = ptx::f32x2_fma(ptx::f32x2_fma(d[k], rstd2, 0ull), g[k], b[k]);
       } else {
 #pragma unroll
-        for (int k = 0; k < PPV; ++k) o[k] = ptx::f32x2_fma(v[j][k], rstd2, 0ull);
+        for (int k = 0; k < PPV; ++k) o[k] = ptx::f32x2_fma(d[k], rstd2, 0ull);
       }
       orow[vec] = pack_pairs<DT>(o);
     }
@@ -291,8 +337,12 @@ int launch_layer_norm(const void* x, const void* residual, const void* bias, con
     const int64_t rpb = kLnThreads / GROUP;                                                                       \
     const int64_t grid = (rows + rpb - 1) / rpb;                                                                  \
     if (grid > 0x7fffffff) return NTB200_INVALID_ARG;                                                             \
-    layer_norm_kernel<DT, VPL, GROUP, FUSED><<<(unsigned)grid, kLnThreads, 0, st>>>(x, residual, bias, gamma, beta, \
-                                                                                   eps, out, rows, (int)cols);     \
+    if (nv == (int64_t)(VPL) * (GROUP))                                                                           \
+      layer_norm_kernel<DT, VPL, GROUP, FUSED, true><<<(unsigned)grid, kLnThreads, 0, st>>>(x, residual, bias, gamma, beta, \
+                                                                                           eps, out, rows, (int)cols); \
+    else                                                                                                          \
+      layer_norm_kernel<DT, VPL, GROUP, FUSED, false><<<(unsigned)grid, kLnThreads, 0, st>>>(x, residual, bias, gamma, beta, \
+                                                                                            eps, out, rows, (int)cols); \
   } while (0)
   if (vec_ok && nv <= 32) NTB200_LN_LAUNCH(1, 32);
   else if (vec_ok && nv <= 64) NTB200_LN_LAUNCH(2, 32);

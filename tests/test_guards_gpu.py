@@ -173,6 +173,28 @@ def test_guards_gemm(native_libs, cuda_device, M, N, K, force):
     assert lib.ntb200_device_error_flags() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 264, 64), (1000, 1024 + 8, 1024), (257, 72, 128), (2100, 1024, 256)])
+@pytest.mark.parametrize("force", [0, 2, 3])
+def test_guards_gemm_residual(native_libs, cuda_device, M, N, K, force):
+    """The residual epilogue (CTA pairs: the residual tile staged in shared memory by TMA, several tiles per CTA pair at
+    M = 2100 so that boxes are reloaded; single CTA: per-thread row reads): guard bytes around the output, result
+    against fp32, error flags clear."""
+    lib = _lib()
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_device)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(cuda_device)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(cuda_device)
+    r = Guarded([M, N], torch.bfloat16, cuda_device)
+    r.t.copy_((torch.randn(M, N, generator=g) * 3).to(torch.bfloat16))
+    c = Guarded([M, N], torch.bfloat16, cuda_device)
+    _cabi.check("gemm", lib.ntb200_gemm_bias_act(a.data_ptr(), w.data_ptr(), b.data_ptr(), r.t.data_ptr(), c.t.data_ptr(), M, N, K, 2,
+                                                 0, force, stream_ptr()))
+    c.check("ntb200_gemm_bias_act + residual, force=%d" % force)
+    want = a.float() @ w.float().t() + b.float() + r.t.float()
+    assert float((c.t.float() - want).abs().max()) <= 2e-2 * (1 + float(want.abs().max()))
+    assert lib.ntb200_device_error_flags() == 0
+
+
 @pytest.mark.parametrize("path", [1, 2, 3])
 def test_guards_attention(native_libs, cuda_device, path):
     lib = _lib()

@@ -23,7 +23,7 @@ def _images(g, n, C, lo, hi, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.int64, torch.uint8], ids=str)
-@pytest.mark.parametrize("C,lo,hi", [(1, 1, 9), (3, 1, 70), (64, 5, 40), (100, 1, 33), (256, 60, 70)])
+@pytest.mark.parametrize("C,lo,hi", [(1, 1, 9), (3, 1, 70), (64, 5, 40), (100, 1, 33), (256, 60, 70), (8, 1, 50), (72, 3, 30)])
 def test_transposes_bit_exact_and_round_trip(native_libs, cuda_device, dtype, C, lo, hi):
     g = torch.Generator().manual_seed(C + hi)
     imgs = _images(g, 7, C, lo, hi, dtype)
