@@ -121,7 +121,8 @@ int ntb200_pad_with_mask(const void* ragged, void* padded, uint8_t* mask, const 
  * (IEEE for floating point: -0.0 == 0.0, NaN != anything).
  *   cmp_kind  0 = compare bit patterns (integers, bool), 1 = IEEE float of that width
  *             (elem_size 2: f16), 2 = bfloat16 (elem_size 2)
- * out_sizes (B*nd int64) and out_counts (B int64) are cleared by this call.
+ * out_sizes (B*nd int64) and out_counts (B int64) are cleared by this call (with one launch
+ * instead of two when out_counts == out_sizes + B*nd, i.e. one allocation holds both).
  * Replaces `tensor != padding` (nestedtensor/nested/masking.py:12-14) plus the per-element
  * host recursion of nt_from_tensor_mask (nestedtensor/csrc/masking.cpp:181-249).
  */
