@@ -868,7 +868,61 @@ def run_small_configs(args, local):
           "ms_per_step": ms, "best_ms": best, "tokens": int(Ls.sum()), "tokens_per_s": float(Ls.sum()) / (ms * 1e-3),
           "step_tflops": fl / ms / 1e9, "step_frac_of_bf16_peak": fl / ms / 1e9 / peaks["bf16_tflops"],
           "note": "0.198 TFLOP per step: a step lasts about 0.3 ms, short of filling the GPU for long"}
-    return {"config3": c3, "config4": c4}
+    return {"config3": c3, "config4": c4, "next_rows": run_next_rows(args, local, peaks, n)}
+
+
+def run_next_rows(args, local, peaks, n):
+    """The rows beside the path (packed LayerNorm, projection with residual, feed-forward up-projection with GELU, ragged
+    image transposes) at the configuration-5 token count / a stride-8 feature-map batch, device-timed on one GPU:
+    a sub-record of the default line."""
+    import nestedtensor_b200 as nt
+    from nestedtensor_b200 import _ops
+    device = torch.device("cuda", local)
+    ops = _ops.ops()
+    T, E = 151792, 1024
+    g = torch.Generator().manual_seed(20250)
+    x = torch.randn(T, E, generator=g).to(torch.bfloat16).to(device)
+    res = torch.randn(T, E, generator=g).to(torch.bfloat16).to(device)
+    w = (torch.randn(E, E, generator=g) * E ** -0.5).to(torch.bfloat16).to(device)
+    w_up = (torch.randn(4 * E, E, generator=g) * E ** -0.5).to(torch.bfloat16).to(device)
+    b = torch.randn(E, generator=g).to(torch.bfloat16).to(device)
+    b_up = torch.randn(4 * E, generator=g).to(torch.bfloat16).to(device)
+    gamma, beta = torch.ones(E, dtype=torch.bfloat16, device=device), torch.zeros(E, dtype=torch.bfloat16, device=device)
+
+    def timed(fn, settle=False):
+        """(median ms per call, median SM MHz during the regions).  `settle`: idle for a quarter of a second first, so
+        that a row bound by instruction issue or latency is not measured at the clock the power governor still holds
+        from the tensor-core work before it (the clock is reported either way)."""
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(device)
+        if settle:
+            time.sleep(0.25)
+        with ClockSampler(local, period_s=0.005) as cs:
+            ms = timed_regions(fn, n, 1, device)[0]
+        return ms, cs.summary().get("sm_mhz")
+
+    def hbm_row(ms, mhz, nbytes):
+        return {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / peaks["hbm_gbs"], "sm_mhz": mhz}
+
+    out = {"workload": "T = 151 792 packed tokens (configuration 5), E = 1024, bf16; transposes: 32 fp16 maps (256, 100-168, 100-168)",
+           "note": "memory-bound rows first, each after 0.25 s of idle; the SM clock seen during each row is beside it"}
+    gi = torch.Generator().manual_seed(20248)
+    hw = torch.randint(100, 169, (32, 2), generator=gi)
+    isz = torch.cat([torch.full((32, 1), 256), hw], 1).contiguous()
+    nimg = int((isz[:, 0] * isz[:, 1] * isz[:, 2]).sum())
+    img = nt.NestedTensor(torch.randn(nimg, device=device).to(torch.float16), isz)
+    nhwc = nt.nn.transpose_nchw_nhwc(img)
+    out["transpose_nchw_nhwc"] = hbm_row(*timed(lambda: nt.nn.transpose_nchw_nhwc(img), True), 4.0 * nimg)
+    out["transpose_nhwc_nchw"] = hbm_row(*timed(lambda: nt.nn.transpose_nhwc_nchw(nhwc), True), 4.0 * nimg)
+    del img, nhwc
+    out["layer_norm"] = hbm_row(*timed(lambda: ops.add_bias_residual_layer_norm(x, None, None, gamma, beta, 1e-5), True), 4.0 * T * E)
+    for name, fn, fl in (("out_proj_bias_residual", lambda: ops.packed_linear(x, w, b, 0, res), 2.0 * T * E * E),
+                         ("out_proj_bias", lambda: ops.packed_linear(x, w, b, 0, None), 2.0 * T * E * E),
+                         ("ffn_up_bias_gelu", lambda: ops.packed_linear(x, w_up, b_up, 1, None), 8.0 * T * E * E)):
+        ms, mhz = timed(fn)
+        out[name] = {"ms": ms, "TFLOP/s": fl / ms / 1e9, "frac_bf16_burst": fl / ms / 1e9 / peaks["bf16_tflops"], "sm_mhz": mhz}
+    return out
 
 
 def run_strong(args, rank, world, local):
