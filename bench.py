@@ -760,52 +760,107 @@ def run_mha(args, rank, world, local, brief=False):
     return line
 
 
-def reference_kernel_times(w, device, n):
-    """The reference's own CUDA padding kernels (nestedtensor/csrc/cuda/padding.cu compiled unmodified for sm_100a into
-    oracle/_ref/ by oracle/build_ref.py) on a workload whose padded tensor has fewer than 2^31 elements (the
-    reference indexes with `int`): a secondary comparator beside the CPU baseline.  None when the library is absent."""
+def _ref_cuda_lib():
+    """oracle/_ref/libntref_cuda.so (the reference's own CUDA files compiled for sm_100a by oracle/build_ref.py), or None."""
     import ctypes
     path = os.path.join(ROOT, "oracle", "_ref", "libntref_cuda.so")
     if not os.path.exists(path):
         return None
-    sizes = w.sizes
+    lib = ctypes.CDLL(path)
+    P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    lib.ntref_add_padding.restype = I
+    lib.ntref_add_padding.argtypes = [P, P, F, P, P, I, P, I, I, P]
+    lib.ntref_remove_padding.restype = I
+    lib.ntref_remove_padding.argtypes = [P, P, P, P, P, I, I, I, P]
+    if hasattr(lib, "ntref_softmax"):
+        lib.ntref_softmax.restype = I
+        lib.ntref_softmax.argtypes = [P, P, I, I, I, F, I, P]
+    if hasattr(lib, "ntref_add_padding_mask"):
+        lib.ntref_add_padding_mask.restype = I
+        lib.ntref_add_padding_mask.argtypes = [P, P, P, P, I, I, I, I, P]
+    return lib
+
+
+def reference_kernel_times(sizes, buf, device, n, note=""):
+    """The reference's own CUDA padding kernels on `buf` / `sizes` (a batch whose padded tensor has fewer than 2^31
+    elements: the reference indexes with `int`), driven as its operators drive them: (L_i, E) batches are collapsed to
+    one ragged dimension for the pad (masking.cpp:569-575, add_padding_1) and un-padded in two (remove_padding_2);
+    (C, H_i, W_i) batches use add_padding_3 / remove_padding.  16-bit data goes through its half instantiation (a bit
+    copy).  A secondary comparator beside the CPU baseline; None when the library is absent."""
+    import ctypes
+    lib = _ref_cuda_lib()
     B, dim = sizes.shape
     mx = sizes.max(0).values.tolist()
     npad = B
     for v in mx:
         npad *= v
-    if npad >= 2 ** 31 or w.dtype not in (torch.float32, torch.float16) or dim < 2 or dim > 3:
+    if lib is None or npad >= 2 ** 31 or buf.element_size() not in (2, 4) or dim < 2 or dim > 3:
         return None
-    lib = ctypes.CDLL(path)
-    lib.ntref_add_padding.restype = ctypes.c_int
-    lib.ntref_add_padding.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
-                                      ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
-    lib.ntref_remove_padding.restype = ctypes.c_int
-    lib.ntref_remove_padding.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
-                                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     numel = sizes.prod(1)
     offsets = torch.zeros(B, dtype=torch.int64)
     offsets[1:] = numel.cumsum(0)[:-1]
-    buf = w.buffer.to(device)
     d_off = offsets.to(torch.int32).to(device)
+    collapse = dim == 2 and bool((sizes[:, 1] == sizes[0, 1]).all())
+    pad_sizes = numel[:, None] if collapse else sizes
+    pad_dim = pad_sizes.shape[1]
+    pad_mx = pad_sizes.max(0).values.tolist()
+    d_pad_sizes = pad_sizes.to(torch.int32).contiguous().to(device)
     d_sizes = sizes.to(torch.int32).contiguous().to(device)
     out = torch.empty([B] + mx, dtype=buf.dtype, device=device)
     back = torch.empty_like(buf)
-    out_sizes = (ctypes.c_int64 * (dim + 1))(*([B] + mx))
+    out_sizes = (ctypes.c_int64 * (pad_dim + 1))(*([B] + pad_mx))
     d_padded_sizes = torch.tensor([B] + mx, dtype=torch.int32, device=device)
-    code = 0 if buf.dtype == torch.float32 else 1
+    code = 0 if buf.element_size() == 4 else 1
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    pad = lambda: lib.ntref_add_padding(buf.data_ptr(), out.data_ptr(), 0.0, d_off.data_ptr(), d_sizes.data_ptr(), dim, out_sizes, B, code, stream)
+    pad = lambda: lib.ntref_add_padding(buf.data_ptr(), out.data_ptr(), 0.0, d_off.data_ptr(), d_pad_sizes.data_ptr(), pad_dim, out_sizes, B,
+                                        code, stream)
     unpad = lambda: lib.ntref_remove_padding(out.data_ptr(), back.data_ptr(), d_off.data_ptr(), d_padded_sizes.data_ptr(), d_sizes.data_ptr(),
                                              dim, B, code, stream)
     es, nv = buf.element_size(), buf.numel()
-    res = {"what": "add_padding_3 / remove_padding of the reference, grid (B,16) x 256 threads, same inputs, CUDA events"}
+    res = {"what": "%s / %s of the reference, grid (B,16) x 256 threads, same inputs, CUDA events%s" %
+                   ("add_padding_%d" % pad_dim, "remove_padding_2" if dim == 2 else "remove_padding", note)}
     for name, fn, nbytes in (("to_padded_tensor", pad, es * (nv + npad)), ("from_padded_tensor", unpad, 2 * es * nv)):
         for _ in range(3):
             assert fn() == 0
         ms, _ = timed_regions(fn, n, 1, device)
         res[name] = {"ms": ms, "GB/s": nbytes / ms / 1e6}
-    res["round_trip_bit_exact"] = bool(torch.equal(back.view(torch.int32 if es == 4 else torch.int16), buf.view(torch.int32 if es == 4 else torch.int16)))
+    iv = torch.int32 if es == 4 else torch.int16
+    res["round_trip_bit_exact"] = bool(torch.equal(back.view(iv), buf.view(iv)))
+    return res
+
+
+def reference_attention_helper_times(lengths, E, H, dtype, device, n):
+    """The reference's fused data + mask kernel (add_padding_mask: one thread per sequence) and its masked softmax on
+    padded scores [B, H, maxL, maxL], at the lengths of a configuration: what bt_min_mha runs around its batched GEMMs
+    (cuda/mha.cpp:57-93).  This library has no counterpart on its MHA path (nothing is padded and no score matrix is
+    stored); the times show what that path avoids."""
+    import ctypes
+    lib = _ref_cuda_lib()
+    if lib is None or not hasattr(lib, "ntref_softmax") or not hasattr(lib, "ntref_add_padding_mask"):
+        return None
+    B, maxL, T = len(lengths), int(max(lengths)), int(sum(lengths))
+    if B * H * maxL * maxL >= 2 ** 31 or maxL > 1024:
+        return None
+    code = 0 if dtype == torch.float32 else 1
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    x = torch.randn(T, E, device=device).to(dtype)
+    off = torch.zeros(B + 1, dtype=torch.int32)
+    off[1:] = torch.tensor(lengths, dtype=torch.int64).cumsum(0).to(torch.int32)
+    d_off = off.to(device)
+    padded = torch.zeros(B, maxL, E, dtype=dtype, device=device)
+    mask = torch.zeros(B, maxL, dtype=torch.int32, device=device)
+    f_mask = lambda: lib.ntref_add_padding_mask(x.data_ptr(), padded.data_ptr(), mask.data_ptr(), d_off.data_ptr(), B, maxL, E, code, stream)
+    scores = torch.randn(B, H, maxL, maxL, device=device).to(dtype)
+    valid = torch.arange(maxL, device=device)[None, :] < torch.tensor(lengths, device=device)[:, None]
+    amask = (valid[:, :, None] & valid[:, None, :]).to(dtype).contiguous()
+    f_soft = lambda: lib.ntref_softmax(scores.data_ptr(), amask.data_ptr(), B, H, maxL, 0.125, code, stream)
+    res = {"what": "add_padding_mask (grid B x 1 thread) and softmax_kernel_kernelLauncher of the reference at these lengths"}
+    for name, fn, reps in (("add_padding_mask", f_mask, min(n, 5)), ("masked_softmax", f_soft, n)):
+        for _ in range(2):
+            assert fn() == 0
+        ms, _ = timed_regions(fn, reps, 1, device, regions=3)
+        res[name] = {"ms": ms}
+    res["masked_softmax"]["score_bytes"] = scores.numel() * scores.element_size()
     return res
 
 
@@ -849,7 +904,7 @@ def run_small_configs(args, local):
           "to_tensor_mask": hbm(timed(f_mask)[0], 4 * (nv + npad) + npad, f_mask),
           "from_padded_tensor": hbm(timed(f_unpad)[0], 8 * nv, f_unpad),
           "sizes_from_padded": hbm(timed(f_scan)[0], 4 * npad, f_scan)}
-    ref = reference_kernel_times(w, device, n)
+    ref = reference_kernel_times(w.sizes, b, device, n)
     if ref is not None:
         c3["reference_kernels_sm100a"] = ref
     del padded, a, b
@@ -868,7 +923,39 @@ def run_small_configs(args, local):
           "ms_per_step": ms, "best_ms": best, "tokens": int(Ls.sum()), "tokens_per_s": float(Ls.sum()) / (ms * 1e-3),
           "step_tflops": fl / ms / 1e9, "step_frac_of_bf16_peak": fl / ms / 1e9 / peaks["bf16_tflops"],
           "note": "0.198 TFLOP per step: a step lasts about 0.3 ms, short of filling the GPU for long"}
-    return {"config3": c3, "config4": c4, "next_rows": run_next_rows(args, local, peaks, n)}
+    ref = reference_kernel_times(w.sizes, b, device, n)
+    if ref is not None:  # the same (L_i, 768) fp16 batch through the reference's padding kernels and this library's
+        ours = {}
+        padded4 = ops.to_padded_tensor(b, sz, meta, 0.0)
+        for name, fn in (("to_padded_tensor", lambda: ops.to_padded_tensor(b, sz, meta, 0.0)),
+                         ("from_padded_tensor", lambda: ops.from_padded_tensor(padded4, sz, meta))):
+            ours[name] = {"ms": timed(fn)[0]}
+        ref["this_library_same_batch"] = ours
+        helpers = reference_attention_helper_times([int(v) for v in Ls], E, H, torch.float16, device, n)
+        if helpers is not None:
+            ref["attention_helpers"] = helpers
+        c4["reference_kernels_sm100a"] = ref
+        del padded4
+    del a, b
+    torch.cuda.empty_cache()
+    # configuration 2 is beyond the reference's int indexing; its first 2047 sequences are not (2047 * 1024 * 1024 < 2^31)
+    w2 = workloads.config2(with_values=False)
+    sz2 = w2.sizes[:2047].contiguous()
+    buf2 = torch.randn(int(sz2.prod(1).sum()), device=device).to(torch.bfloat16)
+    c2 = reference_kernel_times(sz2, buf2, device, min(n, 10), note="; first 2047 sequences of configuration 2 (bf16 as a 16-bit copy)")
+    out = {"config3": c3, "config4": c4}
+    if c2 is not None:
+        a2 = nt.NestedTensor(buf2, sz2)
+        b2, s2, m2 = a2._record()
+        p2 = ops.to_padded_tensor(b2, s2, m2, 0.0)
+        c2["this_library_same_batch"] = {"to_padded_tensor": {"ms": timed(lambda: ops.to_padded_tensor(b2, s2, m2, 0.0))[0]},
+                                         "from_padded_tensor": {"ms": timed(lambda: ops.from_padded_tensor(p2, s2, m2))[0]}}
+        out["config2_subbatch_reference_kernels_sm100a"] = c2
+        del a2, b2, p2
+    del buf2
+    torch.cuda.empty_cache()
+    out["next_rows"] = run_next_rows(args, local, peaks, n)
+    return out
 
 
 def run_next_rows(args, local, peaks, n):

@@ -6,7 +6,10 @@
 //     derived per vector with launch-constant multiply-shift division (no per-element / or %);
 //   * 64-bit element indices everywhere (a (4096,1024,1024) bf16 output has 2^32 elements);
 //   * loads fall back to element-wise only where source and destination differ in
-//     16-byte phase (ragged rows of odd length) or at row / entry edges.
+//     16-byte phase (ragged rows of odd length) or at row / entry edges;
+//   * with two or three ragged dimensions and long innermost rows (images) a warp takes one innermost
+//     row instead: the row is located once and its vectors need no division (pad_rows_kernel,
+//     unpad_rows_kernel, scan_rows_kernel).
 // The reference's counterparts are add_padding_{1,2,3}, remove_padding_2 / remove_padding and
 // add_padding_mask in nestedtensor/csrc/cuda/padding.cu:10-414 (scalar strided copies with int
 // indices, one thread per sequence for the mask variant).

@@ -54,6 +54,25 @@ int ntref_remove_padding(const void* input, void* output, const int* offsets, co
   return (int)cudaGetLastError();
 }
 
+// The reference's fused data + mask kernel for (L_i, inner) sequences (padding.cu:217-284: one THREAD per sequence):
+// output [batch, max_len * inner] (left untouched past each sequence, the caller zero-fills), mask int32 [batch, max_len].
+// offsets: batch + 1 int32 row offsets.  dtype: 0 = float, 1 = half.
+int ntref_add_padding_mask(const void* input, void* output, int* mask, const int* offsets, int batch, int max_len, int inner, int dtype,
+                           void* stream) {
+  if (batch < 1 || max_len < 1 || inner < 1) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    nested_tensor::cuda::add_padding_mask_kernelLauncher<float>(static_cast<float*>(const_cast<void*>(input)), static_cast<float*>(output),
+                                                                mask, offsets, batch, max_len, max_len * inner, inner, st);
+  else if (dtype == 1)
+    nested_tensor::cuda::add_padding_mask_kernelLauncher<c10::Half>(static_cast<c10::Half*>(const_cast<void*>(input)),
+                                                                    static_cast<c10::Half*>(output), mask, offsets, batch, max_len,
+                                                                    max_len * inner, inner, st);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}
+
 // In-place softmax of scores [batch, heads, seq_len, seq_len] under a mask [batch, seq_len, seq_len] of the same dtype
 // (1 = attend), the reference's arithmetic: scores * scaling + (1 - mask) * -10000, row sum + 1e-6
 // (attention.cu:182-482; seq_len <= 1024).  dtype: 0 = float, 1 = half.
