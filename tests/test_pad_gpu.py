@@ -8,7 +8,8 @@ import torch
 import nestedtensor_b200 as nt
 from nestedtensor_b200 import workloads
 from oracle import ntref
-from _helpers import (assert_bit_equal, cabi_mask, cabi_pad, cabi_unpad, random_list, sizes_of)
+from nestedtensor_b200 import _cabi
+from _helpers import (assert_bit_equal, bits_of, cabi_mask, cabi_pad, cabi_unpad, random_list, sizes_of, stream_ptr)
 
 pytestmark = pytest.mark.gpu
 
@@ -177,6 +178,53 @@ def test_long_rows(native_libs, cuda_device, dtype, tdim, regular_last):
     for got_t, want_t in zip(back.unbind(), oback):
         assert got_t.numel() == want_t.numel() and (want_t.numel() == 0 or tuple(got_t.shape) == tuple(want_t.shape))
     assert_bit_equal(back._buffer, torch.cat([t.reshape(-1) for t in oback]), "nested_tensor_from_padded_tensor")
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_row_and_vector_walks_random_shapes(native_libs, cuda_device, seed):
+    """Random batches around the switch between the vector walk and the warp-per-row kernels (innermost padded row of
+    512 bytes): 2 and 3 ragged dims, four element sizes, optional regular trailing dim, extents of zero in any position,
+    one to six constituents; pad, unpad and the size scan through the C ABI against plain torch on the CPU."""
+    g = torch.Generator().manual_seed(9000 + seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+    dtype = [torch.uint8, torch.bfloat16, torch.float32, torch.float64][r(0, 3)]
+    es = torch.empty(0, dtype=dtype).element_size()
+    tdim, B = r(2, 3), r(1, 6)
+    regular_last = r(2, 6) if r(0, 2) == 0 else None
+    width_hi = max(2, (r(300, 1400) // es) // (regular_last or 1))
+    tensors = []
+    for _ in range(B):
+        shape = [r(0, 5) if r(0, 5) == 0 else r(1, 6) for _ in range(tdim - 1)] + [r(0, width_hi) if r(0, 4) == 0 else r(max(1, width_hi - 40), width_hi)]
+        if regular_last is not None:
+            shape[-1], shape[-2] = regular_last, shape[-1]
+        x = torch.randn(shape, generator=g)
+        tensors.append(((x * 40).abs() + 1).to(dtype) if dtype == torch.uint8 else x.to(dtype))
+    sizes = sizes_of(tensors)
+    mx = sizes.max(0).values.tolist()
+    pad_value = 0 if dtype == torch.uint8 else 777.0
+    want = torch.full([B] + mx, pad_value, dtype=dtype)
+    for b, t in enumerate(tensors):
+        want[(b,) + tuple(slice(0, n) for n in t.shape)] = t
+    if min(mx) == 0:
+        return  # nothing to pad: the entry points return at once (covered by the edge-case tests)
+    got = cabi_pad(tensors, pad_value, cuda_device)
+    assert_bit_equal(got, want, "ntb200_pad_nd %s %s" % (dtype, sizes.tolist()))
+    flat = torch.cat([t.reshape(-1) for t in tensors])
+    if flat.numel():
+        assert_bit_equal(cabi_unpad(got, sizes), flat, "ntb200_unpad_nd %s %s" % (dtype, sizes.tolist()))
+    # size scan of the padded tensor: extents of each entry's bounding box of non-padding elements, and their count
+    lib = _cabi.load()
+    nd = len(mx)
+    out = torch.empty(B * (nd + 1), dtype=torch.int64, device=cuda_device)
+    kind = 0 if dtype == torch.uint8 else (2 if dtype == torch.bfloat16 else 1)
+    rc = lib.ntb200_sizes_from_padded(got.data_ptr(), out.data_ptr(), out.data_ptr() + 8 * B * nd, nd, B, _cabi.host_i64(mx), es, kind,
+                                      bits_of(pad_value, dtype), stream_ptr())
+    _cabi.check("ntb200_sizes_from_padded", rc)
+    torch.cuda.synchronize()
+    got_sizes, got_counts = out[:B * nd].view(B, nd).cpu(), out[B * nd:].cpu()
+    for b, t in enumerate(tensors):
+        assert int(got_counts[b]) == t.numel(), (b, sizes.tolist())
+        assert got_sizes[b].tolist() == (list(t.shape) if t.numel() else [0] * nd), (b, sizes.tolist())
 
 
 def test_config3_images(native_libs, cuda_device):
