@@ -2,7 +2,7 @@
 (masked softmax, bias add + pad, transpose + remove padding), compiled for sm_100a from the reference's source files
 where they lie (never copied), behind the C names of oracle/ref_cuda_shim.cu.
 
-    python oracle/build_ref.py [path of the reference checkout, default /root/reference]
+    python oracle/build_ref.py [path of the reference checkout]
 
 Test infrastructure only.  The output directory is git-ignored; the built library travels with the tree to a GPU
 machine, where the reference checkout itself is absent.  Needs nvcc and the c10 headers of the installed torch
