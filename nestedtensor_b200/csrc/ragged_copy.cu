@@ -796,47 +796,57 @@ __global__ void __launch_bounds__(kRowWarps * 32) unpad_rows_kernel(const RowPar
   const int64_t rows_b = ND == 2 ? s[0] : s[0] * s[1];
   const int64_t rr = (int64_t)c * kRowWarps + warp;
   if (rr >= rows_b) return;
-  const int64_t s_last = s[ND - 1] * p.inner;
-  if (s_last <= 0) return;
-  int64_t src_row;  // row index in the padded tensor
+  const int64_t s_last64 = s[ND - 1] * p.inner;
+  if (s_last64 <= 0) return;
+  const uint32_t s_last = (uint32_t)s_last64;  // (a row of the padded tensor has fewer than 2^31 elements)
+  int64_t src_row;                             // row index in the padded tensor
   if (ND == 2) {
     src_row = (int64_t)b * (int64_t)p.m0 + rr;
   } else {
-    const int64_t i0 = rr / s[1], i1 = rr - i0 * s[1];
-    src_row = ((int64_t)b * (int64_t)p.m0 + i0) * (int64_t)p.m1 + i1;
+    uint64_t i0, i1;
+    divmod_u64((uint64_t)rr, (uint64_t)s[1], i0, i1);
+    src_row = ((int64_t)b * (int64_t)p.m0 + (int64_t)i0) * (int64_t)p.m1 + (int64_t)i1;
   }
   const E* __restrict__ srow = reinterpret_cast<const E*>(p.src) + src_row * (int64_t)p.m_last;
-  E* __restrict__ drow = reinterpret_cast<E*>(p.dst) + p.offsets[b] + rr * s_last;
-  int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(drow) & 15)) & 15) / ES);
+  E* __restrict__ drow = reinterpret_cast<E*>(p.dst) + p.offsets[b] + rr * s_last64;
+  uint32_t head = (uint32_t)(((16 - (reinterpret_cast<uintptr_t>(drow) & 15)) & 15) / ES);
   head = head < s_last ? head : s_last;
-  const int64_t nvec = (s_last - head) / VE;
-  const int64_t tail0 = head + nvec * VE;
-  if (lane < head) drow[lane] = srow[lane];
+  const uint32_t nvec = (s_last - head) / VE;
+  const uint32_t tail0 = head + nvec * VE;
+  if ((uint32_t)lane < head) drow[lane] = srow[lane];
   if (tail0 + lane < s_last) drow[tail0 + lane] = srow[tail0 + lane];
-  const bool src_aligned = (reinterpret_cast<uintptr_t>(srow + head) & 15) == 0;
+  const E* __restrict__ sb = srow + head;  // the vector body of the row: source and destination
+  uint4* __restrict__ db = reinterpret_cast<uint4*>(drow + head);
   union Vec {
     uint4 v;
     E e[VE];
   };
   constexpr int U = kRowUnroll;
-  for (int64_t j0 = lane; j0 < nvec; j0 += 32 * U) {
-    Vec val[U];
+  if ((reinterpret_cast<uintptr_t>(sb) & 15) == 0) {
+    const uint4* __restrict__ sv = reinterpret_cast<const uint4*>(sb);
+    for (uint32_t j0 = lane; j0 < nvec; j0 += 32 * U) {
+      uint4 val[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t j = j0 + 32 * u;
-      if (j >= nvec) continue;
-      const int64_t e0 = head + j * VE;
-      if (src_aligned) {
-        val[u].v = ld_global_16_stream(srow + e0);
-      } else {
+      for (int u = 0; u < U; ++u)
+        if (j0 + 32 * u < nvec) val[u] = ld_global_16_stream(sv + j0 + 32 * u);
 #pragma unroll
-        for (int k = 0; k < VE; ++k) val[u].e[k] = srow[e0 + k];
-      }
+      for (int u = 0; u < U; ++u)
+        if (j0 + 32 * u < nvec) st_global_16_stream(db + j0 + 32 * u, val[u]);
     }
+  } else {
+    for (uint32_t j0 = lane; j0 < nvec; j0 += 32 * U) {
+      Vec val[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t j = j0 + 32 * u;
-      if (j < nvec) st_global_16_stream(drow + head + j * VE, val[u].v);
+      for (int u = 0; u < U; ++u) {
+        const uint32_t j = j0 + 32 * u;
+        if (j < nvec) {
+#pragma unroll
+          for (int k = 0; k < VE; ++k) val[u].e[k] = sb[j * VE + k];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (j0 + 32 * u < nvec) st_global_16_stream(db + j0 + 32 * u, val[u].v);
     }
   }
 }
@@ -1255,7 +1265,9 @@ int launch_pad_es(const PadParams& p, int nd, bool big, cudaStream_t st) {
 }
 
 // Rows long enough for the warp-per-row kernels: at least 32 sixteen-byte vectors.
-inline bool long_rows(int nd, const Geometry& g, int elem_size) { return nd >= 2 && g.m[nd - 1] * (uint64_t)elem_size >= 512; }
+inline bool long_rows(int nd, const Geometry& g, int elem_size) {
+  return nd >= 2 && g.m[nd - 1] * (uint64_t)elem_size >= 512 && g.m[nd - 1] < (1ull << 31);
+}
 
 template <int ES>
 int launch_pad_rows(const RowParams& p, int nd, bool fuse, cudaStream_t st) {
