@@ -679,7 +679,7 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
 // the row is located once (entry, plane, row index, valid length, source row) and its vectors then cost a compare, an
 // address step, a load and a store each.  The destination row is walked in 16-byte-aligned vectors with an
 // element-wise head and tail; the source row has one phase for the whole row, so its loads are either all aligned
-// 16-byte loads or all element-wise.  Used when a padded row holds at least 32 vectors.
+// 16-byte loads or all element-wise.  Used for rows of a few KB and more (row_kernel_min_bytes below).
 struct RowParams {
   const void* src;
   void* dst;
@@ -1264,9 +1264,17 @@ int launch_pad_es(const PadParams& p, int nd, bool big, cudaStream_t st) {
   return NTB200_INVALID_ARG;
 }
 
-// Rows long enough for the warp-per-row kernels: at least 32 sixteen-byte vectors.
-inline bool long_rows(int nd, const Geometry& g, int elem_size) {
-  return nd >= 2 && g.m[nd - 1] * (uint64_t)elem_size >= 512 && g.m[nd - 1] < (1ull << 31);
+// Where the warp-per-row kernels take over from the vector walks (2-3 ragged dims), by the bytes of an innermost
+// padded row.  Measured on B200 with batches of about 400 MB (fp32 and bf16, 2 and 3 ragged dims, rows of 0.5-8 KB):
+// at 512-byte rows the row kernels run at 0.25-0.45 of the vector walks' rate (a warp's trip is mostly empty and the
+// per-row set-up dominates), they draw level between 2 and 3 KB and win by 10-40 % from there on.
+enum RowOp { kRowPad = 0, kRowUnpad = 1, kRowScan = 2 };
+inline uint64_t row_kernel_min_bytes(RowOp op, int elem_size) {
+  if (op == kRowScan) return 3072;
+  return elem_size <= 2 ? 2048 : 2560;
+}
+inline bool long_rows(int nd, const Geometry& g, int elem_size, RowOp op) {
+  return nd >= 2 && g.m[nd - 1] * (uint64_t)elem_size >= row_kernel_min_bytes(op, elem_size) && g.m[nd - 1] < (1ull << 31);
 }
 
 template <int ES>
@@ -1327,7 +1335,7 @@ int launch_unpad_es(const UnpadParams& p, int nd, cudaStream_t st) {
   return NTB200_INVALID_ARG;
 }
 
-// Row walk of the same scan (2-3 dims, rows of at least 32 vectors): a warp reads one innermost row and keeps the
+// Row walk of the same scan (2-3 dims, rows of 3 KB and more): a warp reads one innermost row and keeps the
 // count of non-padding elements and the end of the last one; thread 0 folds the CTA's eight consecutive rows per
 // entry (coordinates by increments, one division per CTA) before the atomics, which are the expensive part: with
 // one set of atomics per row instead of per CTA the kernel took 2.5 times as long.
@@ -1459,7 +1467,8 @@ int launch_scan_es_nd(const ScanParams& p, bool big, cudaStream_t st) {
   const int64_t blocks = ceil_div(p.total, tile);
   if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
   // (a NaN padding value equals no element: the row kernel's vector classes assume a value that can match)
-  if (ND >= 2 && p.m[ND - 1] * (uint64_t)ES >= 512 && p.m[ND - 1] < (1ull << 31) && !VecAllPad<ES, CMP>(p.pad_bits).never) {
+  if (ND >= 2 && p.m[ND - 1] * (uint64_t)ES >= row_kernel_min_bytes(kRowScan, ES) && p.m[ND - 1] < (1ull << 31) &&
+      !VecAllPad<ES, CMP>(p.pad_bits).never) {
     const uint64_t rows = (uint64_t)p.batch * (ND == 2 ? p.m[0] : p.m[0] * p.m[1]);
     const uint64_t row_blocks = (rows + kRowWarps - 1) / kRowWarps;
     if (row_blocks > 0x7fffffffull) return NTB200_UNSUPPORTED_SHAPE;
@@ -1541,7 +1550,7 @@ static int pad_common(const void* ragged, void* padded, uint8_t* fused_mask, con
   p.mask = fused_mask;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (fused_mask != nullptr && !aligned_to(fused_mask, 16)) return NTB200_MISALIGNED;
-  if (long_rows(nd, g, elem_size) && ragged != nullptr) {
+  if (long_rows(nd, g, elem_size, kRowPad) && ragged != nullptr) {
     RowParams rp;
     rp.src = ragged;
     rp.dst = padded;
@@ -1670,7 +1679,7 @@ int ntb200_unpad_nd(const void* padded, void* ragged, const int64_t* offsets, co
   for (int j = 0; j < 3; ++j) p.m[j] = g.m[j];
   p.inner = inner;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (long_rows(nd, g, elem_size)) {
+  if (long_rows(nd, g, elem_size, kRowUnpad)) {
     RowParams rp;
     rp.src = padded;
     rp.dst = ragged;

@@ -468,11 +468,12 @@ def test_sizes_from_padded_semantics(native_libs, cuda_device, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.uint8],
                          ids=str)
-@pytest.mark.parametrize("width", [640, 637])
-def test_sizes_from_padded_semantics_long_rows(native_libs, cuda_device, dtype, width):
-    """The same comparison rules in the warp-per-row scan (rows of at least 512 bytes; 637 wide: rows that start at
+@pytest.mark.parametrize("odd", [0, 3])
+def test_sizes_from_padded_semantics_long_rows(native_libs, cuda_device, dtype, odd):
+    """The same comparison rules in the warp-per-row scan (rows of 3.3 KB; three elements less: rows that start at
     every phase of a 16-byte vector): -0.0 is padding 0.0, NaN is never padding, a NaN padding value matches nothing,
     and a box that holds the padding value inside is refused."""
+    width = 3328 // torch.empty(0, dtype=dtype).element_size() - odd
     t = torch.zeros(3, 4, width, dtype=dtype)
     t[0, :2, :333] = 1
     t[1, :4, :width] = 2

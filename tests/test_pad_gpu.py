@@ -136,13 +136,12 @@ def test_unpad_many_entries_per_tile(native_libs, cuda_device, dtype, tdim):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.uint8, torch.float64], ids=str)
 @pytest.mark.parametrize("tdim,regular_last", [(2, None), (3, None), (3, 3), (2, 5)])
 def test_long_rows(native_libs, cuda_device, dtype, tdim, regular_last):
-    """2 and 3 ragged dims whose innermost padded rows hold at least 32 sixteen-byte vectors (images): the
-    warp-per-row kernels.  Odd widths (every source row starts at another phase of a 16-byte vector), widths below
+    """2 and 3 ragged dims whose innermost padded rows are a few KB long (images): the warp-per-row kernels.  Odd widths (every source row starts at another phase of a 16-byte vector), widths below
     one vector, an empty constituent, one of a single element, a regular folded trailing dim; pad, data + mask in one
     pass, unpad, and the size scan of the padded result."""
     g = torch.Generator().manual_seed(977 + tdim)
     es = torch.empty(0, dtype=dtype).element_size()
-    hi = 1100 // es + 37
+    hi = 3300 // es + 37  # rows of 3.3 KB and more: beyond every threshold of the row kernels
     tensors = random_list(g, 9, tdim, 3, 11, dtype, regular_last)
     for i, t in enumerate(tensors):  # widen the innermost ragged dim
         shape = list(t.shape)
@@ -182,8 +181,8 @@ def test_long_rows(native_libs, cuda_device, dtype, tdim, regular_last):
 
 @pytest.mark.parametrize("seed", range(24))
 def test_row_and_vector_walks_random_shapes(native_libs, cuda_device, seed):
-    """Random batches around the switch between the vector walk and the warp-per-row kernels (innermost padded row of
-    512 bytes): 2 and 3 ragged dims, four element sizes, optional regular trailing dim, extents of zero in any position,
+    """Random batches around the switch between the vector walk and the warp-per-row kernels (innermost padded rows of
+    2 to 3 KB): 2 and 3 ragged dims, four element sizes, optional regular trailing dim, extents of zero in any position,
     one to six constituents; pad, unpad and the size scan through the C ABI against plain torch on the CPU."""
     g = torch.Generator().manual_seed(9000 + seed)
     r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
@@ -191,7 +190,7 @@ def test_row_and_vector_walks_random_shapes(native_libs, cuda_device, seed):
     es = torch.empty(0, dtype=dtype).element_size()
     tdim, B = r(2, 3), r(1, 6)
     regular_last = r(2, 6) if r(0, 2) == 0 else None
-    width_hi = max(2, (r(300, 1400) // es) // (regular_last or 1))
+    width_hi = max(2, (r(1200, 4200) // es) // (regular_last or 1))  # the switch lies between 2 and 3 KB
     tensors = []
     for _ in range(B):
         shape = [r(0, 5) if r(0, 5) == 0 else r(1, 6) for _ in range(tdim - 1)] + [r(0, width_hi) if r(0, 4) == 0 else r(max(1, width_hi - 40), width_hi)]
