@@ -203,6 +203,9 @@ int ntb200_gemm_bias(const void* A, const void* W, const void* bias, void* C, in
  * separate pass over their [sum(L_i), N] outputs.  Replaces add_bias_act_kernelLauncher
  * (nestedtensor/csrc/cuda/cuda_kernels.cu:73-104) and add_bias_input_kernelLauncher
  * (nestedtensor/csrc/cuda/transformer_kernels.cu:235-258) run after a cuBLAS GEMM.
+ * With a residual, K < 2048 and the CTA-pair kernel, the residual tile is staged in shared memory by TMA;
+ *   force_simt  as above, and 4 = CTA-pair kernel that reads the residual rows per thread whatever K is
+ *               (the form used from K = 2048 on; for comparisons).
  */
 int ntb200_gemm_bias_act(const void* A, const void* W, const void* bias, const void* residual, void* C,
                          int64_t M, int64_t N, int64_t K, int dtype, int act, int force_simt, void* stream);

@@ -878,15 +878,17 @@ int ntb200_gemm_bias_act(const void* A, const void* W, const void* bias, const v
   if (M == 0 || N == 0) return NTB200_OK;
   if (A == nullptr || W == nullptr || C == nullptr) return NTB200_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // force_simt: 0 = best available, 1 = SIMT, 2 = single-CTA tcgen05 kernel, 3 = CTA-pair tcgen05 kernel
+  // force_simt: 0 = best available, 1 = SIMT, 2 = single-CTA tcgen05 kernel, 3 = CTA-pair tcgen05 kernel,
+  // 4 = CTA-pair kernel that reads the residual rows per thread whatever K is (for comparisons)
   const bool tc = force_simt != 1 && dtype != NTB200_F32 && K >= 8 && (K % 8) == 0 && (N % 8) == 0 && aligned16(A) && aligned16(W) &&
                   aligned16(C) && (residual == nullptr || aligned16(residual)) && M < (1ll << 31) - 256 && N < (1ll << 31) - 256 && K < (1ll << 31) - kBK;
-  if ((force_simt == 2 || force_simt == 3) && !tc) return NTB200_UNSUPPORTED_SHAPE;
+  if ((force_simt == 2 || force_simt == 3 || force_simt == 4) && !tc) return NTB200_UNSUPPORTED_SHAPE;
+  if (force_simt < 0 || force_simt > 4) return NTB200_INVALID_ARG;
   if (tc) {
-    const bool pair = force_simt == 3 || (force_simt == 0 && M > 128);
+    const bool pair = force_simt == 3 || force_simt == 4 || (force_simt == 0 && M > 128);
     // The residual tile comes through shared memory (at the price of one main-loop stage) while the main loop of a
     // tile is short; from K = 2048 on the per-thread row reads of the other variant hide under it (K = 4096: 2 % faster).
-    if (pair && residual != nullptr && K < 2048) {
+    if (pair && residual != nullptr && K < 2048 && force_simt != 4) {
       if (dtype == NTB200_F16) return launch_tcgen05_pair<0, true>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
       return launch_tcgen05_pair<1, true>(A, W, bias, residual, act, C, (int)M, (int)N, (int)K, dtype, st);
     }
