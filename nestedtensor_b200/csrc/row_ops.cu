@@ -110,9 +110,15 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// Sum over the GROUP threads that share a row: a warp (GROUP == 32) or the whole block.
+// Sum over the GROUP threads that share a row: part of a warp (GROUP == 8, 16: neighbouring lanes), a warp
+// (GROUP == 32) or the whole block.
 template <int GROUP>
 __device__ __forceinline__ float group_sum(float v, float* scratch) {
+  if (GROUP < 32) {
+#pragma unroll
+    for (int o = GROUP / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+  }
   v = warp_sum(v);
   if (GROUP == 32) return v;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,7 +148,7 @@ layer_norm_kernel(const void* x, const void* __restrict__ residual, const void* 
   __shared__ float scratch[kLnThreads / 32];
   const int t = threadIdx.x % GROUP;
   const int64_t row = (int64_t)blockIdx.x * kRowsPerBlock + threadIdx.x / GROUP;
-  const bool live = row < rows;  // whole groups are live or not (a group is a warp or the block)
+  const bool live = row < rows;  // whole groups are live or not; a warp of several short rows may hold both kinds
   if (GROUP == 32 && !live) return;
   const int nv = cols / EPV;
   const uint4* xr = reinterpret_cast<const uint4*>(x) + row * nv;
@@ -344,12 +350,29 @@ int launch_layer_norm(const void* x, const void* residual, const void* bias, con
       layer_norm_kernel<DT, VPL, GROUP, FUSED, false><<<(unsigned)grid, kLnThreads, 0, st>>>(x, residual, bias, gamma, beta, \
                                                                                             eps, out, rows, (int)cols); \
   } while (0)
-  if (vec_ok && nv <= 32) NTB200_LN_LAUNCH(1, 32);
+  // Vectors per thread = ceil(nv / GROUP): widths such as 768, 1280 or 1536 get an exact fit (3, 5 or 6 vectors per
+  // lane, no idle slots, the variant without bound tests) instead of the next power of two.  A packed 16-bit row
+  // (no fused additions) stays on one warp up to 512 vectors: 16 loads in flight per lane, no block-wide reduction.
+  constexpr bool kPacked = !FUSED && DT != NTB200_F32;
+  if (vec_ok && nv <= 8) NTB200_LN_LAUNCH(1, 8);  // short rows: several rows per warp, every lane busy
+  else if (vec_ok && nv <= 16) NTB200_LN_LAUNCH(1, 16);
+  else if (vec_ok && nv <= 32) NTB200_LN_LAUNCH(1, 32);
   else if (vec_ok && nv <= 64) NTB200_LN_LAUNCH(2, 32);
+  else if (vec_ok && nv <= 96) NTB200_LN_LAUNCH(3, 32);
   else if (vec_ok && nv <= 128) NTB200_LN_LAUNCH(4, 32);
+  else if (vec_ok && nv <= 160) NTB200_LN_LAUNCH(5, 32);
+  else if (vec_ok && nv <= 192) NTB200_LN_LAUNCH(6, 32);
   else if (vec_ok && nv <= 256) NTB200_LN_LAUNCH(8, 32);
-  else if (vec_ok && nv <= 512) NTB200_LN_LAUNCH(2, kLnThreads);
+  else if (vec_ok && kPacked && nv <= 512) {
+    if constexpr (kPacked) {
+      if (nv <= 384) NTB200_LN_LAUNCH(12, 32);
+      else NTB200_LN_LAUNCH(16, 32);
+    }
+  } else if (vec_ok && nv <= 512) NTB200_LN_LAUNCH(2, kLnThreads);
+  else if (vec_ok && nv <= 768) NTB200_LN_LAUNCH(3, kLnThreads);
   else if (vec_ok && nv <= 1024) NTB200_LN_LAUNCH(4, kLnThreads);
+  else if (vec_ok && nv <= 1280) NTB200_LN_LAUNCH(5, kLnThreads);
+  else if (vec_ok && nv <= 1536) NTB200_LN_LAUNCH(6, kLnThreads);
   else if (vec_ok && nv <= 2048) NTB200_LN_LAUNCH(8, kLnThreads);
   else {
     const int64_t grid = rows < 148 * 32 ? rows : 148 * 32;

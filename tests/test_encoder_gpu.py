@@ -39,7 +39,8 @@ def _layer_norm(x, res, bias, gamma, beta, eps, inplace=False):
 
 # the reference's test sizes (test/test_nested_tensor_functional.py:953) plus rows handled by a whole block
 # (cols * element size > 4 KB), rows that are not a multiple of 16 bytes and a row longer than 32 KB
-@pytest.mark.parametrize("cols", [1024, 512, 256, 128, 2, 4, 32, 8, 40, 3000, 4096, 8192, 1023, 20000])
+@pytest.mark.parametrize("cols", [1024, 512, 256, 128, 2, 4, 32, 8, 40, 3000, 4096, 8192, 1023, 20000, 64, 96, 768, 1280, 1536, 2560, 3072,
+                                  6144, 10240, 12288])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=str)
 def test_cabi_layer_norm(native_libs, cuda_device, dtype, cols):
     g = torch.Generator().manual_seed(cols)
@@ -56,7 +57,7 @@ def test_cabi_layer_norm(native_libs, cuda_device, dtype, cols):
     assert (got.float().cpu() - want).abs().max().item() <= TOL[dtype] * (4 if dtype == torch.float32 else 1)
 
 
-@pytest.mark.parametrize("cols", [1024, 768, 64, 6, 4104])
+@pytest.mark.parametrize("cols", [1024, 768, 64, 6, 4104, 96, 1280, 1536, 3072, 6144])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16], ids=str)
 def test_cabi_add_bias_residual_layer_norm(native_libs, cuda_device, dtype, cols):
     g = torch.Generator().manual_seed(cols + 1)
