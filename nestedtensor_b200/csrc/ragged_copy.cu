@@ -461,6 +461,30 @@ __device__ __forceinline__ int64_t find_entry(const int64_t* __restrict__ offset
   return lo;
 }
 
+// The same search by a whole warp: 32 probes per step instead of one, so a batch of 4096 entries takes three
+// dependent loads instead of twelve (every lane returns the result; requires offsets[lo] <= e).
+__device__ __forceinline__ int64_t find_entry_warp(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
+  const int lane = threadIdx.x & 31;
+  while (hi > lo) {
+    const int64_t span = hi - lo;                 // candidates lo + 1 .. hi
+    const int64_t step = (span + 31) / 32;        // probe lo + step, lo + 2 step, ... (clamped to hi)
+    int64_t probe = lo + step * (lane + 1);
+    probe = probe > hi ? hi : probe;
+    const unsigned le = __ballot_sync(0xffffffffu, offsets[probe] <= e);
+    if (le == 0) {                                // the answer lies below the first probe
+      hi = lo + step - 1;
+    } else {
+      const int top = 31 - __clz(le);             // last probe that is still <= e
+      int64_t nlo = lo + step * (top + 1);
+      nlo = nlo > hi ? hi : nlo;
+      const int64_t nhi = nlo + step - 1;
+      lo = nlo;
+      hi = nhi > hi ? hi : nhi;
+    }
+  }
+  return lo;
+}
+
 // source index (in the padded tensor) of element r of entry b, and the number of
 // elements left in that innermost row starting at r
 template <int ND>
@@ -493,6 +517,7 @@ __device__ __forceinline__ void unpad_locate(const UnpadParams& p, int64_t b, ui
 // builds the pairs for the first kUnpadEnt of them in shared memory once, and a vector whose entry is in the
 // table (and small enough for 32-bit arithmetic) locates itself without a division.
 constexpr int kUnpadEnt = 8;
+constexpr int kUnpadOff = 128;  // entries per tile whose offsets are kept in shared memory
 struct UnpadEnt {
   FastDiv f_plane, f_row;  // divide by s12 (3 ragged dims only) and by s2
   uint32_t s12, s2;        // elements of one valid plane / of one valid innermost row
@@ -563,20 +588,38 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
   __shared__ int64_t s_range[2];
   __shared__ UnpadEnt s_ent[ND >= 2 ? kUnpadEnt : 1];
 
+  __shared__ int64_t s_off[kUnpadOff + 1];  // offsets of the tile's entries (when there are at most kUnpadOff)
   const int64_t tile_e0 = (int64_t)blockIdx.x * kTileElems;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 64) {  // warp 0 finds the tile's first entry, warp 1 its last one
     int64_t tile_last = tile_e0 + kTileElems - 1;
     if (tile_last > p.total - 1) tile_last = p.total - 1;
-    const int64_t lo = find_entry(p.offsets, 0, p.batch - 1, tile_e0);
-    s_range[0] = lo;
-    s_range[1] = find_entry(p.offsets, lo, p.batch - 1, tile_last);
+    const int64_t found = find_entry_warp(p.offsets, 0, p.batch - 1, threadIdx.x < 32 ? tile_e0 : tile_last);
+    if ((threadIdx.x & 31) == 0) s_range[threadIdx.x >> 5] = found;
   }
   __syncthreads();
   const int64_t blo = s_range[0], bhi = s_range[1];
+  const bool off_cached = bhi - blo < kUnpadOff;
+  if (off_cached && threadIdx.x <= bhi - blo + 1) s_off[threadIdx.x] = p.offsets[blo + threadIdx.x];
   if (ND >= 2) {
     if (threadIdx.x < kUnpadEnt && blo + threadIdx.x <= bhi) s_ent[threadIdx.x] = unpad_entry_divisors<ND>(p, blo + threadIdx.x);
-    __syncthreads();
   }
+  __syncthreads();
+  // entry of output element e (inside this tile) and its first element
+  auto entry_of = [&](int64_t e, int64_t& first) {
+    if (off_cached) {
+      int lo = 0, hi = (int)(bhi - blo);
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (s_off[mid] <= e) lo = mid;
+        else hi = mid - 1;
+      }
+      first = s_off[lo];
+      return blo + lo;
+    }
+    const int64_t b = find_entry(p.offsets, blo, bhi, e);
+    first = p.offsets[b];
+    return b;
+  };
   E* __restrict__ dst = reinterpret_cast<E*>(p.dst);
   const E* __restrict__ src = reinterpret_cast<const E*>(p.src);
   union Vec {
@@ -591,14 +634,15 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
   for (int u = 0; u < kVecPerThread; ++u) {
     const int64_t e = tile_e0 + (int64_t)(u * kThreads + threadIdx.x) * VE;
     if (e >= p.total) break;
-    const int64_t b = find_entry(p.offsets, blo, bhi, e);
+    int64_t first;
+    const int64_t b = entry_of(e, first);
     int64_t src_idx, run;
     uint64_t w0, w1;
     const int64_t ei = b - blo;
     if (ND >= 2 && ei < kUnpadEnt && s_ent[ei].ok) {
-      unpad_locate_fast<ND>(p, s_ent[ei], b, (uint32_t)(e - p.offsets[b]), src_idx, run, w0, w1);
+      unpad_locate_fast<ND>(p, s_ent[ei], b, (uint32_t)(e - first), src_idx, run, w0, w1);
     } else {
-      unpad_locate<ND>(p, b, (uint64_t)(e - p.offsets[b]), src_idx, run, w0, w1);
+      unpad_locate<ND>(p, b, (uint64_t)(e - first), src_idx, run, w0, w1);
     }
     if (run < VE) {  // also covers the ragged tail: run >= VE implies e + VE <= total
       boundary |= 1u << u;
@@ -624,10 +668,11 @@ __global__ void __launch_bounds__(kThreads) unpad_kernel(const UnpadParams p) {
     const int u = __ffs(boundary) - 1;
     boundary &= boundary - 1;
     const int64_t e = tile_e0 + (int64_t)(u * kThreads + threadIdx.x) * VE;
-    int64_t b = find_entry(p.offsets, blo, bhi, e);
+    int64_t first;
+    int64_t b = entry_of(e, first);
     int64_t si, left;
     uint64_t w0, w1;
-    unpad_locate<ND>(p, b, (uint64_t)(e - p.offsets[b]), si, left, w0, w1);
+    unpad_locate<ND>(p, b, (uint64_t)(e - first), si, left, w0, w1);
     Vec out;
 #pragma unroll
     for (int k = 0; k < VE; ++k) {
