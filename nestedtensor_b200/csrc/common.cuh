@@ -83,6 +83,40 @@ struct ElemBits<4> { using T = uint32_t; };
 template <>
 struct ElemBits<8> { using T = uint64_t; };
 
+// largest b in [lo, hi] with offsets[b] <= e (requires offsets[lo] <= e)
+__device__ __forceinline__ int64_t find_entry(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
+  while (lo < hi) {
+    const int64_t mid = (lo + hi + 1) >> 1;
+    if (offsets[mid] <= e) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+// The same search by a whole warp: 32 probes per step instead of one, so a batch of 4096 entries takes three
+// dependent loads instead of twelve (every lane returns the result; requires offsets[lo] <= e).
+__device__ __forceinline__ int64_t find_entry_warp(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
+  const int lane = threadIdx.x & 31;
+  while (hi > lo) {
+    const int64_t span = hi - lo;                 // candidates lo + 1 .. hi
+    const int64_t step = (span + 31) / 32;        // probe lo + step, lo + 2 step, ... (clamped to hi)
+    int64_t probe = lo + step * (lane + 1);
+    probe = probe > hi ? hi : probe;
+    const unsigned le = __ballot_sync(0xffffffffu, offsets[probe] <= e);
+    if (le == 0) {                                // the answer lies below the first probe
+      hi = lo + step - 1;
+    } else {
+      const int top = 31 - __clz(le);             // last probe that is still <= e
+      int64_t nlo = lo + step * (top + 1);
+      nlo = nlo > hi ? hi : nlo;
+      const int64_t nhi = nlo + step - 1;
+      lo = nlo;
+      hi = nhi > hi ? hi : nhi;
+    }
+  }
+  return lo;
+}
+
 // 16-byte global accesses of the copy kernels.  Measured on B200 at the 4096 x (L_i, 1024) bf16 workload: default-cached
 // loads and stores beat the streaming (.cs) forms (pad 6.62 vs 6.22 TB/s, unpad 6.31 vs 5.72 TB/s).
 __device__ __forceinline__ uint4 ld_global_16_stream(const void* p) { return *reinterpret_cast<const uint4*>(p); }

@@ -16,16 +16,7 @@ namespace {
 __device__ int g_construct_error = 0;  // bit 0: an embedding index was out of range (its row was zero-filled)
 
 constexpr int kPackThreads = 256, kPackVecs = 8;  // 32 KB of output per tile, as in the pad / unpad kernels
-
-// last b in [lo, hi] with offsets[b] <= e
-__device__ __forceinline__ int64_t find_entry(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
-  while (lo < hi) {
-    const int64_t mid = (lo + hi + 1) >> 1;
-    if (offsets[mid] <= e) lo = mid;
-    else hi = mid - 1;
-  }
-  return lo;
-}
+constexpr int kPackEnt = 128;                      // entries per tile kept in shared memory
 
 // Flat walk over 16-byte vectors of the OUTPUT.  A vector that lies inside one constituent whose source is
 // 16-byte aligned at that point is one 16-byte load; any other vector is assembled element by element
@@ -38,23 +29,47 @@ pack_pointers_kernel(const void* const* __restrict__ srcs, const int64_t* __rest
   using T = typename ElemBits<ES>::T;
   constexpr int EPV = 16 / ES;
   __shared__ int64_t s_range[2];
+  __shared__ int64_t s_off[kPackEnt + 1];     // offsets and sources of the tile's entries (when at most kPackEnt)
+  __shared__ const void* s_src[kPackEnt];
   const int64_t n_vec = (total_elems + EPV - 1) / EPV;
   const int64_t tile0 = (int64_t)blockIdx.x * (kPackThreads * kPackVecs);
-  if (threadIdx.x < 2) {
-    int64_t e = (threadIdx.x == 0 ? tile0 : tile0 + kPackThreads * kPackVecs - 1) * EPV;
+  if (threadIdx.x < 64) {  // warp 0: the tile's first entry, warp 1: its last one (32 probes per search step)
+    int64_t e = (threadIdx.x < 32 ? tile0 : tile0 + kPackThreads * kPackVecs - 1) * EPV;
     e = e < total_elems ? e : total_elems - 1;
-    s_range[threadIdx.x] = find_entry(offsets, 0, batch - 1, e);
+    const int64_t found = find_entry_warp(offsets, 0, batch - 1, e);
+    if ((threadIdx.x & 31) == 0) s_range[threadIdx.x >> 5] = found;
   }
   __syncthreads();
   const int64_t lo = s_range[0], hi = s_range[1];
+  const bool cached = hi - lo < kPackEnt;
+  if (cached && threadIdx.x <= hi - lo + 1) s_off[threadIdx.x] = offsets[lo + threadIdx.x];
+  if (cached && threadIdx.x <= hi - lo) s_src[threadIdx.x] = srcs[lo + threadIdx.x];
+  __syncthreads();
 #pragma unroll
   for (int j = 0; j < kPackVecs; ++j) {
     const int64_t v = tile0 + (int64_t)j * kPackThreads + threadIdx.x;
     if (v >= n_vec) break;
     const int64_t e0 = v * EPV;
-    int64_t b = find_entry(offsets, lo, hi, e0);
-    const int64_t end_b = offsets[b + 1];
-    const T* src = static_cast<const T*>(srcs[b]) + (e0 - offsets[b]);
+    int64_t b, first, end_b;
+    const void* base;
+    if (cached) {
+      int l = 0, h = (int)(hi - lo);
+      while (l < h) {
+        const int mid = (l + h + 1) >> 1;
+        if (s_off[mid] <= e0) l = mid;
+        else h = mid - 1;
+      }
+      b = lo + l;
+      first = s_off[l];
+      end_b = s_off[l + 1];
+      base = s_src[l];
+    } else {
+      b = find_entry(offsets, lo, hi, e0);
+      first = offsets[b];
+      end_b = offsets[b + 1];
+      base = srcs[b];
+    }
+    const T* src = static_cast<const T*>(base) + (e0 - first);
     if (e0 + EPV <= end_b && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
       st_global_16_stream(static_cast<T*>(out) + e0, ld_global_16_stream(src));
     } else {

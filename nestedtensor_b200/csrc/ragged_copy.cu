@@ -451,40 +451,6 @@ struct UnpadParams {
   int64_t inner;
 };
 
-// largest b in [lo, hi] with offsets[b] <= e (requires offsets[lo] <= e)
-__device__ __forceinline__ int64_t find_entry(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
-  while (lo < hi) {
-    const int64_t mid = (lo + hi + 1) >> 1;
-    if (offsets[mid] <= e) lo = mid;
-    else hi = mid - 1;
-  }
-  return lo;
-}
-
-// The same search by a whole warp: 32 probes per step instead of one, so a batch of 4096 entries takes three
-// dependent loads instead of twelve (every lane returns the result; requires offsets[lo] <= e).
-__device__ __forceinline__ int64_t find_entry_warp(const int64_t* __restrict__ offsets, int64_t lo, int64_t hi, int64_t e) {
-  const int lane = threadIdx.x & 31;
-  while (hi > lo) {
-    const int64_t span = hi - lo;                 // candidates lo + 1 .. hi
-    const int64_t step = (span + 31) / 32;        // probe lo + step, lo + 2 step, ... (clamped to hi)
-    int64_t probe = lo + step * (lane + 1);
-    probe = probe > hi ? hi : probe;
-    const unsigned le = __ballot_sync(0xffffffffu, offsets[probe] <= e);
-    if (le == 0) {                                // the answer lies below the first probe
-      hi = lo + step - 1;
-    } else {
-      const int top = 31 - __clz(le);             // last probe that is still <= e
-      int64_t nlo = lo + step * (top + 1);
-      nlo = nlo > hi ? hi : nlo;
-      const int64_t nhi = nlo + step - 1;
-      lo = nlo;
-      hi = nhi > hi ? hi : nhi;
-    }
-  }
-  return lo;
-}
-
 // source index (in the padded tensor) of element r of entry b, and the number of
 // elements left in that innermost row starting at r
 template <int ND>
