@@ -71,22 +71,31 @@ Record make_record(const Tensor& sizes, const Tensor& meta) {
               "nestedtensor_b200: meta must be a CUDA int64 tensor of (B+1) + B*tensor_dim entries");
   r.d_offsets = meta.data_ptr<int64_t>();
   r.d_sizes = r.d_offsets + (r.B + 1);
-  r.max_sizes.assign(r.tdim, 0);
-  r.regular.assign(r.tdim, true);
-  r.any_empty = false;
-  r.numel = 0;
+  // One pass over the host sizes per operator call: kept branch-light (batches of 10^5 short sequences make this
+  // loop, not the kernel, the cost of a call).
+  constexpr int kMaxDims = 8;
+  TORCH_CHECK(r.tdim <= kMaxDims, "nestedtensor_b200: at most ", kMaxDims, " tensor dimensions");
+  int64_t mx[kMaxDims] = {0}, differs[kMaxDims] = {0}, min_seen = 0, numel = 0, empties = 0;
+  const int64_t td = r.tdim;
+  const int64_t* __restrict__ sz = r.sz;
   for (int64_t b = 0; b < r.B; ++b) {
     int64_t n = 1;
-    for (int64_t j = 0; j < r.tdim; ++j) {
-      const int64_t v = r.sz[b * r.tdim + j];
-      TORCH_CHECK(v >= 0, "nestedtensor_b200: negative size");
+    for (int64_t j = 0; j < td; ++j) {
+      const int64_t v = sz[b * td + j];
+      min_seen = v < min_seen ? v : min_seen;
       n *= v;
-      if (v > r.max_sizes[j]) r.max_sizes[j] = v;
-      if (v != r.sz[j]) r.regular[j] = false;
+      mx[j] = v > mx[j] ? v : mx[j];
+      differs[j] |= v ^ sz[j];
     }
-    if (n == 0) r.any_empty = true;
-    r.numel += n;
+    empties += n == 0;
+    numel += n;
   }
+  TORCH_CHECK(min_seen >= 0, "nestedtensor_b200: negative size");
+  r.max_sizes.assign(mx, mx + td);
+  r.regular.resize(td);
+  for (int64_t j = 0; j < td; ++j) r.regular[j] = differs[j] == 0;
+  r.any_empty = empties != 0;
+  r.numel = numel;
   return r;
 }
 
