@@ -122,6 +122,38 @@ __device__ __forceinline__ int64_t find_entry_warp(const int64_t* __restrict__ o
 __device__ __forceinline__ uint4 ld_global_16_stream(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ void st_global_16_stream(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
 
+// The 16 bytes at `sp` for 1- and 2-byte elements whose address is not 16-byte aligned: five aligned 4-byte words
+// realigned with funnel shifts instead of sixteen or eight element loads.  Reads up to 3 bytes before `sp` (inside the
+// aligned word that holds its first byte) and up to 3 bytes after sp + 16 (inside the word that holds its last byte);
+// `limit` is the end of the source buffer, and a vector whose last word would pass it takes the element loads.
+// Used by the pad kernels only: in the unpad kernels the same form measured slower (it keeps fewer loads in flight).
+template <int ES>
+__device__ __forceinline__ uint4 load16_realign(const void* sp, const void* limit) {
+  static_assert(ES <= 2, "1- and 2-byte elements");
+  const uintptr_t a = reinterpret_cast<uintptr_t>(sp);
+  const uintptr_t w0 = a & ~uintptr_t(3);
+  if (w0 + 20 <= reinterpret_cast<uintptr_t>(limit)) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(w0);
+    const uint32_t c0 = w[0], c1 = w[1], c2 = w[2], c3 = w[3], c4 = w[4];
+    const uint32_t shift = (uint32_t)(a & 3) * 8;  // (a funnel shift by 0 returns the low word)
+    return make_uint4(__funnelshift_r(c0, c1, shift), __funnelshift_r(c1, c2, shift), __funnelshift_r(c2, c3, shift),
+                      __funnelshift_r(c3, c4, shift));
+  }
+  union {
+    uint4 v;
+    uint8_t b1[16];
+    uint16_t b2[8];
+  } out;
+  if (ES == 1) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) out.b1[k] = reinterpret_cast<const uint8_t*>(sp)[k];
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out.b2[k] = reinterpret_cast<const uint16_t*>(sp)[k];
+  }
+  return out.v;
+}
+
 // One-time, per-device host set-up (cudaFuncSetAttribute and occupancy queries apply to the current device only, so
 // a process that drives several GPUs must repeat them on each).  `done` is an array of kMaxDevices flags; `setup`
 // runs with the calling thread's current device and returns false on failure.  Two threads racing on the same
