@@ -44,6 +44,14 @@ constexpr int kTmemCols = 256;        // S: columns [0,128), P: [128,192), O: [1
 constexpr int kPCol = 128;
 constexpr int kOCol = 192;
 constexpr int kAttnThreads = 256;     // warps 0-3 softmax, warp 4 TMA, warp 5 MMA, warps 6-7 idle
+// Register exchange of setmaxnreg.  A request for more registers than the other warps of the CTA give back blocks for
+// ever (it is not one of the bounded waits), so the two counts must add up to twice the count the kernel is launched
+// with: 128 at two 256-thread CTAs per SM.  With eight warps every SM sub-partition hosts one softmax warp and one
+// control / idle warp of the CTA, so the exchange also balances per sub-partition.
+constexpr int kRegLaunch = 65536 / (2 * kAttnThreads);
+constexpr int kRegSoftmax = 208;
+constexpr int kRegControl = 48;
+static_assert(kRegSoftmax + kRegControl == 2 * kRegLaunch && kRegLaunch % 8 == 0, "setmaxnreg exchange must balance");
 constexpr int kAttnSmem = 1024 + kTile * (2 + 2 * kStages) + 256;  // 2 Q buffers + 2 stages of (K, V)
 
 struct Ctrl {
@@ -249,7 +257,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   };
 
   if (warp >= 4) {
-    ptx::setmaxnreg_dec<48>();
+    ptx::setmaxnreg_dec<kRegControl>();
     if (warp == 4 && ptx::elect_one()) {
       // ------------------------------------------------------------ TMA producer
       bool ok = true;
@@ -383,7 +391,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------ softmax, one thread per query row
-    ptx::setmaxnreg_inc<208>();
+    ptx::setmaxnreg_inc<kRegSoftmax>();
     const int q = warp;                              // TMEM lane quarter of this warp
     const int row = q * 32 + lane;                   // row inside the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
