@@ -17,6 +17,7 @@
 #include <cuda_fp16.h>
 
 #include "attention_internal.cuh"
+#include "attention_tiny.cuh"
 #include "common.cuh"
 
 namespace ntb200 {
@@ -127,57 +128,6 @@ attn_simt_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k, 
 
 // ------------------------------------------------------- tensor-core flash kernel, head_dim 32 / 64 / 128
 constexpr int kBQ = 64, kBKV = 64, kFaThreads = 128;
-
-template <typename T>
-struct MmaOp;
-template <>
-struct MmaOp<__half> {
-  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-  static __device__ __forceinline__ uint32_t pack(float x, float y) {
-    __half2 h = __floats2half2_rn(x, y);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-};
-template <>
-struct MmaOp<__nv_bfloat16> {
-  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-  static __device__ __forceinline__ uint32_t pack(float x, float y) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-};
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// byte offset of 16-byte chunk `c` of row `r` in a [rows][D] two-byte tile; the chunk index is XOR-swizzled with
-// the row so that the eight rows one ldmatrix phase reads fall into eight different 16-byte bank groups
-template <int D>
-__device__ __forceinline__ uint32_t tile_off(int r, int c) {
-  if (D == 32) return (uint32_t)(r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
-  if (D == 64) return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
-  return (uint32_t)(r * 256 + ((((c & 7) ^ (r & 7)) | (c & 8)) << 4));
-}
 
 // copy rows [row0, row0+64) (clamped to last_row) x D columns of one head from global into a swizzled tile
 template <typename T, int D>
@@ -561,6 +511,26 @@ int launch_attn_fa_any(const QkvSrc& s, void* out, int64_t batch, int H, int d, 
   return launch_attn_fa<T, 128>(s, out, batch, H, max_len_q, scale, st);
 }
 
+template <typename T, int D, int R>
+int launch_attn_tiny_dr(const QkvSrc& s, void* out, int64_t batch, int H, float scale, cudaStream_t st) {
+  constexpr int kPerWarp = 3 * R * D * 2;  // 3 ... 24 KB
+  constexpr int kWarps = 48 * 1024 / kPerWarp > 8 ? 8 : 48 * 1024 / kPerWarp;
+  const int64_t blocks = ceil_div(batch * H, kWarps);
+  if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+  attn_tiny_kernel<T, D, R, kWarps><<<(unsigned)blocks, kWarps * 32, kWarps * kPerWarp, st>>>(
+      static_cast<const T*>(s.q), s.ldq, static_cast<const T*>(s.k), s.ldk, static_cast<const T*>(s.v), s.ldv, static_cast<T*>(out),
+      s.offsets_q, s.offsets_k, batch, H, scale * 1.4426950408889634f);
+  return status_from_cuda(cudaGetLastError());
+}
+
+template <typename T>
+int launch_attn_tiny(const QkvSrc& s, void* out, int64_t batch, int H, int d, int64_t max_len, float scale, cudaStream_t st) {
+  const bool r16 = max_len <= 16;
+  if (d == 32) return r16 ? launch_attn_tiny_dr<T, 32, 16>(s, out, batch, H, scale, st) : launch_attn_tiny_dr<T, 32, 32>(s, out, batch, H, scale, st);
+  if (d == 64) return r16 ? launch_attn_tiny_dr<T, 64, 16>(s, out, batch, H, scale, st) : launch_attn_tiny_dr<T, 64, 32>(s, out, batch, H, scale, st);
+  return r16 ? launch_attn_tiny_dr<T, 128, 16>(s, out, batch, H, scale, st) : launch_attn_tiny_dr<T, 128, 32>(s, out, batch, H, scale, st);
+}
+
 // The non-tcgen05 kernels behind both entry points: mma.sync flash kernel for head_dim 32 / 64 / 128 in fp16 / bf16 with
 // 16-byte aligned rows, SIMT otherwise.  path: 0 best of the two, 1 SIMT, 2 flash (error if unsupported).
 int launch_attn_generic(const QkvSrc& s, void* out, int64_t batch, int64_t q_tokens, int H, int d, int64_t max_len_q,
@@ -605,8 +575,21 @@ int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, 
   if (batch == 0 || total_tokens == 0) return NTB200_OK;
   if (qkv == nullptr || out == nullptr || offsets == nullptr) return NTB200_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // path 0: best available (tcgen05 when a workspace is given and the shape is supported, else mma.sync,
-  // else SIMT); 1: SIMT; 2: mma.sync flash kernel; 3: tcgen05 (error if unsupported)
+  // path 0: best available (the warp-per-(sequence, head) kernel when no sequence is longer than 32 tokens, else tcgen05
+  // when a workspace is given and the shape is supported, else mma.sync, else SIMT); 1: SIMT; 2: mma.sync flash kernel;
+  // 3: tcgen05 (error if unsupported); 4: warp-per-(sequence, head) kernel (error if unsupported)
+  {
+    const int64_t E = (int64_t)num_heads * head_dim;
+    const bool tiny_ok = dtype != NTB200_F32 && (head_dim == 32 || head_dim == 64 || head_dim == 128) && aligned16(qkv) &&
+                         aligned16(out) && max_len >= 1 && max_len <= kTinyMaxLen;
+    if (path == 4 || (path == 0 && tiny_ok)) {
+      if (!tiny_ok) return NTB200_UNSUPPORTED_SHAPE;
+      const char* base = static_cast<const char*>(qkv);
+      const QkvSrc src = {base, base + E * 2, base + 2 * E * 2, 3 * E, 3 * E, 3 * E, offsets, offsets};
+      if (dtype == NTB200_F16) return launch_attn_tiny<__half>(src, out, batch, num_heads, head_dim, max_len, scaling, st);
+      return launch_attn_tiny<__nv_bfloat16>(src, out, batch, num_heads, head_dim, max_len, scaling, st);
+    }
+  }
   const bool tc_ok = dtype != NTB200_F32 && (num_heads * (int64_t)head_dim) % 8 == 0 && aligned16(qkv) && aligned16(out) &&
                      attn_tcgen05_supported(batch, total_tokens, num_heads, head_dim, dtype);
   if (path == 3 || (path == 0 && tc_ok && workspace != nullptr)) {
@@ -614,7 +597,12 @@ int ntb200_varlen_attention(const void* qkv, void* out, const int64_t* offsets, 
     const size_t need = attn_tcgen05_workspace_bytes(batch, total_tokens);
     if (workspace == nullptr || workspace_bytes < need) return NTB200_WORKSPACE_TOO_SMALL;
     if (!aligned16(workspace)) return NTB200_MISALIGNED;
-    return attn_tcgen05_launch(qkv, out, offsets, batch, total_tokens, num_heads, scaling, dtype, workspace, st);
+    // On the default path the sequences of at most 32 tokens are computed by single warps beside the block that builds
+    // the work list (same launch), and get no work item: each of them would cost the tensor-memory kernel a whole
+    // 128-row item.  Which kernel computes a sequence thus depends on the sequence alone, never on the batch around it,
+    // so a batch cut into shards or ranges reproduces the one-call result bit for bit.
+    const int skip_short = path == 0 ? (int)kTinyMaxLen : 0;
+    return attn_tcgen05_launch(qkv, out, offsets, batch, total_tokens, num_heads, scaling, dtype, workspace, st, skip_short);
   }
   const int64_t E = (int64_t)num_heads * head_dim;
   const size_t es = dtype == NTB200_F32 ? 4 : 2;

@@ -19,7 +19,10 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "attention_internal.cuh"
+#include "attention_tiny.cuh"
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -97,22 +100,23 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // items[i] = (first query token of the tile, valid query rows in the tile, first key token of the sequence, number
 // of keys) for every 128-query tile, ordered by decreasing number of key blocks so that the longest items start
 // first; *count = number of items.  Sequences without queries or without keys produce no item; the output rows of a
-// sequence without keys are zeroed here (an empty softmax).  One block.
+// sequence without keys are zeroed here (an empty softmax).  Sequences of at most skip_short queries and keys produce
+// no item either: the caller has given them to the warp-per-(sequence, head) kernel.  One block.
 constexpr int kListThreads = 1024;
 constexpr int kBuckets = 9;  // key blocks 1..8+, (0 unused)
 
-__global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t* __restrict__ offsets_q,
-                                                                   const int64_t* __restrict__ offsets_k, int64_t batch,
-                                                                   int64_t row_elems, int4* __restrict__ items,
-                                                                   int* __restrict__ count, int64_t capacity,
-                                                                   uint16_t* __restrict__ out) {
+__device__ __forceinline__ void build_items_block(const int64_t* __restrict__ offsets_q, const int64_t* __restrict__ offsets_k,
+                                                  int64_t batch, int64_t row_elems, int4* __restrict__ items,
+                                                  int* __restrict__ count, int64_t capacity, uint16_t* __restrict__ out,
+                                                  int skip_short) {
+  const int nthreads = (int)blockDim.x;  // 1024 alone, 256 beside the short-sequence warps
   __shared__ int s_cnt[kBuckets];
   __shared__ int s_base[kBuckets];
   if (threadIdx.x < kBuckets) s_cnt[threadIdx.x] = 0;
   __syncthreads();
-  for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
+  for (int64_t b = threadIdx.x; b < batch; b += nthreads) {
     const int64_t Lq = (offsets_q[b + 1] - offsets_q[b]) / row_elems, Lk = (offsets_k[b + 1] - offsets_k[b]) / row_elems;
-    if (Lq <= 0 || Lk <= 0) continue;
+    if (Lq <= 0 || Lk <= 0 || (Lq <= skip_short && Lk <= skip_short)) continue;
     const int nq = (int)((Lq + kQT - 1) / kQT);
     int nb = (int)((Lk + kKV - 1) / kKV);
     nb = nb >= kBuckets ? kBuckets - 1 : nb;
@@ -128,9 +132,9 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
     *count = acc < capacity ? acc : (int)capacity;
   }
   __syncthreads();
-  for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
+  for (int64_t b = threadIdx.x; b < batch; b += nthreads) {
     const int64_t Lq = (offsets_q[b + 1] - offsets_q[b]) / row_elems, Lk = (offsets_k[b + 1] - offsets_k[b]) / row_elems;
-    if (Lq <= 0 || Lk <= 0) continue;
+    if (Lq <= 0 || Lk <= 0 || (Lq <= skip_short && Lk <= skip_short)) continue;
     const int nq = (int)((Lq + kQT - 1) / kQT);
     int nb = (int)((Lk + kKV - 1) / kKV);
     nb = nb >= kBuckets ? kBuckets - 1 : nb;
@@ -147,7 +151,7 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
   __shared__ int s_empty[kListThreads];
   if (threadIdx.x == 0) s_nempty = 0;
   __syncthreads();
-  for (int64_t b = threadIdx.x; b < batch; b += kListThreads) {
+  for (int64_t b = threadIdx.x; b < batch; b += nthreads) {
     if (offsets_k[b + 1] > offsets_k[b] || offsets_q[b + 1] == offsets_q[b]) continue;
     const int pos = atomicAdd(&s_nempty, 1);
     if (pos < kListThreads) {
@@ -160,8 +164,39 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
   const int n_listed = s_nempty < kListThreads ? s_nempty : kListThreads;
   for (int i = 0; i < n_listed; ++i) {
     const int64_t e0 = offsets_q[s_empty[i]], e1 = offsets_q[s_empty[i] + 1];
-    for (int64_t e = e0 + threadIdx.x; e < e1; e += kListThreads) out[e] = 0;
+    for (int64_t e = e0 + threadIdx.x; e < e1; e += nthreads) out[e] = 0;
   }
+}
+
+__global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t* __restrict__ offsets_q,
+                                                                   const int64_t* __restrict__ offsets_k, int64_t batch,
+                                                                   int64_t row_elems, int4* __restrict__ items,
+                                                                   int* __restrict__ count, int64_t capacity,
+                                                                   uint16_t* __restrict__ out) {
+  build_items_block(offsets_q, offsets_k, batch, row_elems, items, count, capacity, out, 0);
+}
+
+// The same list for self-attention on the default path, in one launch with the short sequences: block 0 builds the list
+// without the sequences of at most kTinyMaxLen tokens, and every warp of the other blocks computes one (sequence, head)
+// of those sequences by itself (attn_tiny_warp; it returns at once for a longer sequence).  The short sequences thus
+// cost no launch of their own, and which kernel computes a sequence depends on its own length only.
+constexpr int kPrepWarps = 8;
+constexpr int kPrepSmem = kPrepWarps * 3 * (int)kTinyMaxLen * kHD * 2;  // 96 KB: Q, K, V tiles of 32 x 64 per warp
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+prepare_self_attention_kernel(const int64_t* __restrict__ offsets, int64_t batch, int64_t row_elems, int4* __restrict__ items,
+                              int* __restrict__ count, int64_t capacity, const T* __restrict__ qkv, T* __restrict__ out, int H,
+                              float scale_log2e) {
+  extern __shared__ __align__(128) uint8_t prep_smem[];
+  if (blockIdx.x == 0) {
+    build_items_block(offsets, offsets, batch, row_elems, items, count, capacity, reinterpret_cast<uint16_t*>(out), (int)kTinyMaxLen);
+    return;
+  }
+  const int warp = threadIdx.x >> 5;
+  attn_tiny_warp<T, kHD, (int)kTinyMaxLen>(qkv, 3 * row_elems, qkv + row_elems, 3 * row_elems, qkv + 2 * row_elems, 3 * row_elems, out,
+                                           offsets, offsets, batch, H, scale_log2e, ((int64_t)blockIdx.x - 1) * kPrepWarps + warp,
+                                           (uint32_t)__cvta_generic_to_shared(prep_smem) + (uint32_t)warp * (uint32_t)(kPrepSmem / kPrepWarps));
 }
 
 // ------------------------------------------------------------------ attention
@@ -641,7 +676,7 @@ bool make_tile_map(CUtensorMap* map, const TileSource& src, int dtype) {
 template <int FMT>
 int launch(const TileSource& q, int col_q, const TileSource& k, int col_k, const TileSource& v, int col_v, void* out,
            const int64_t* offsets_q, const int64_t* offsets_k, int64_t batch, int64_t q_tokens, int H, float scaling, int dtype,
-           void* workspace, cudaStream_t st) {
+           void* workspace, cudaStream_t st, int skip_short) {  // skip_short > 0: self-attention only
   const int64_t E = (int64_t)H * kHD;
   CUtensorMap map_q, map_k, map_v;
   if (!make_tile_map(&map_q, q, dtype) || !make_tile_map(&map_k, k, dtype) || !make_tile_map(&map_v, v, dtype))
@@ -654,7 +689,21 @@ int launch(const TileSource& q, int col_q, const TileSource& k, int col_k, const
   const int64_t capacity = attn_tcgen05_item_capacity(batch, q_tokens);
   int* count = static_cast<int*>(workspace);
   int4* items = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + 16);
-  build_items_kernel<<<1, kListThreads, 0, st>>>(offsets_q, offsets_k, batch, E, items, count, capacity, static_cast<uint16_t*>(out));
+  if (skip_short > 0) {
+    // self-attention on the default path (q, k and v are column blocks of one [T, 3E] matrix, offsets_q == offsets_k)
+    using T16 = typename std::conditional<FMT == 0, __half, __nv_bfloat16>::type;
+    static std::atomic<int> prep_set[kMaxDevices];
+    if (!once_per_device(prep_set, [] {
+          return cudaFuncSetAttribute(prepare_self_attention_kernel<T16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem) == cudaSuccess;
+        }))
+      return NTB200_LAUNCH_FAILED;
+    const int64_t blocks = 1 + (batch * H + kPrepWarps - 1) / kPrepWarps;
+    if (blocks > 0x7fffffffll) return NTB200_UNSUPPORTED_SHAPE;
+    prepare_self_attention_kernel<T16><<<(unsigned)blocks, kPrepWarps * 32, kPrepSmem, st>>>(
+        offsets_q, batch, E, items, count, capacity, static_cast<const T16*>(q.base), static_cast<T16*>(out), H, scaling * 1.4426950408889634f);
+  } else {
+    build_items_kernel<<<1, kListThreads, 0, st>>>(offsets_q, offsets_k, batch, E, items, count, capacity, static_cast<uint16_t*>(out));
+  }
   int dev = 0, sms = kNumSMs;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int64_t grid = 2ll * sms;  // two resident CTAs per SM, each loops over its share of the items
@@ -679,12 +728,14 @@ bool attn_tcgen05_supported(int64_t batch, int64_t total_tokens, int num_heads, 
 }
 
 int attn_tcgen05_launch(const void* qkv, void* out, const int64_t* offsets, int64_t batch, int64_t total_tokens, int H,
-                        float scaling, int dtype, void* workspace, cudaStream_t st) {
+                        float scaling, int dtype, void* workspace, cudaStream_t st, int skip_short) {
   const int64_t E = (int64_t)H * kHD;
   const TileSource src = {qkv, total_tokens, 3 * E, 3 * E};  // one map, three column offsets
   if (dtype == NTB200_F16)
-    return launch<0>(src, 0, src, (int)E, src, (int)(2 * E), out, offsets, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
-  return launch<1>(src, 0, src, (int)E, src, (int)(2 * E), out, offsets, offsets, batch, total_tokens, H, scaling, dtype, workspace, st);
+    return launch<0>(src, 0, src, (int)E, src, (int)(2 * E), out, offsets, offsets, batch, total_tokens, H, scaling, dtype, workspace, st,
+                     skip_short);
+  return launch<1>(src, 0, src, (int)E, src, (int)(2 * E), out, offsets, offsets, batch, total_tokens, H, scaling, dtype, workspace, st,
+                   skip_short);
 }
 
 int attn_tcgen05_cross_launch(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, void* out,
@@ -693,8 +744,8 @@ int attn_tcgen05_cross_launch(const void* q, int64_t ldq, const void* k, int64_t
   const int64_t E = (int64_t)H * kHD;
   const TileSource sq = {q, q_tokens, E, ldq}, sk = {k, k_tokens, E, ldk}, sv = {v, k_tokens, E, ldv};
   if (dtype == NTB200_F16)
-    return launch<0>(sq, 0, sk, 0, sv, 0, out, offsets_q, offsets_k, batch, q_tokens, H, scaling, dtype, workspace, st);
-  return launch<1>(sq, 0, sk, 0, sv, 0, out, offsets_q, offsets_k, batch, q_tokens, H, scaling, dtype, workspace, st);
+    return launch<0>(sq, 0, sk, 0, sv, 0, out, offsets_q, offsets_k, batch, q_tokens, H, scaling, dtype, workspace, st, 0);
+  return launch<1>(sq, 0, sk, 0, sv, 0, out, offsets_q, offsets_k, batch, q_tokens, H, scaling, dtype, workspace, st, 0);
 }
 
 int attn_tcgen05_error_flags_read_and_clear() {

@@ -134,6 +134,102 @@ def test_varlen_attention_tcgen05_lengths(native_libs, cuda_device, lengths):
     assert err <= 2e-2, "tcgen05 attention max-abs %g" % err
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+@pytest.mark.parametrize("H,d", [(4, 64), (8, 32), (3, 128), (1, 64)])
+@pytest.mark.parametrize("max_len", [16, 32, 9, 17])
+def test_varlen_attention_short_sequences(native_libs, cuda_device, dtype, H, d, max_len):
+    """Batches whose longest sequence has at most 32 tokens run on the warp-per-(sequence, head) kernel (path 4; the
+    default picks it from max_len): every length from 1 to max_len, against the oracle and the SIMT kernel."""
+    g = torch.Generator().manual_seed(100 * max_len + d)
+    lengths = list(range(1, max_len + 1)) + [max_len, 1, 7, max_len, 2]
+    lengths = [lengths[i] for i in torch.randperm(len(lengths), generator=g).tolist()]
+    qkv = (torch.randn(sum(lengths), 3 * H * d, generator=g) * 1.5).to(dtype).to(cuda_device)
+    want = _attention_oracle(qkv, lengths, H, d)
+    got = {}
+    for path, name in ((4, "warp per (sequence, head)"), (0, "default"), (1, "SIMT")):
+        got[path] = _attention(qkv, lengths, H, d, path=path)
+        err = (got[path].float().cpu() - want).abs().max().item()
+        assert err <= 2e-2, "%s attention max-abs %g" % (name, err)
+    assert torch.equal(got[0].view(torch.int16), got[4].view(torch.int16)), "the default did not take the short-sequence kernel"
+
+
+def test_varlen_attention_short_sequences_large_batch(native_libs, cuda_device):
+    """30 000 sequences of 1..8 tokens, 16 heads x 64: more (sequence, head) pairs than one grid dimension of the
+    other kernels holds; compared on the GPU with the SIMT kernel."""
+    H, d = 16, 64
+    g = torch.Generator().manual_seed(8)
+    lengths = torch.randint(1, 9, (30000,), generator=g).tolist()
+    qkv = torch.randn(sum(lengths), 3 * H * d, generator=g).to(torch.bfloat16).to(cuda_device)
+    got = _attention(qkv, lengths, H, d, path=0)
+    ref = _attention(qkv, lengths, H, d, path=1)
+    assert bool(torch.isfinite(got.float()).all())
+    assert (got.float() - ref.float()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=str)
+def test_varlen_attention_mostly_short_sequences(native_libs, cuda_device, dtype):
+    """Mostly short sequences with a few longer ones: the default splits the batch between the warp-per-(sequence,
+    head) kernel (at most 32 tokens) and the tcgen05 work list (the rest); every row must be written exactly once
+    and agree with the SIMT kernel and, for a sample, with the oracle."""
+    H, d = 4, 64
+    g = torch.Generator().manual_seed(77)
+    lengths = torch.randint(1, 33, (1500,), generator=g).tolist()
+    for pos, l in ((3, 100), (700, 300), (701, 64), (1200, 33), (1499, 40), (0, 32)):
+        lengths[pos] = l
+    qkv = (torch.randn(sum(lengths), 3 * H * d, generator=g) * 1.5).to(dtype).to(cuda_device)
+    got = _attention(qkv, lengths, H, d, path=0)
+    ref = _attention(qkv, lengths, H, d, path=1)
+    assert bool(torch.isfinite(got.float()).all()), "rows left unwritten"
+    # two 16-bit roundings of one value may lie an ulp apart (0.031 for values of 4..8): the 2e-2 bar is the one against
+    # the fp32 oracle, checked below on the first 300 sequences (among them the long ones at 3 and 0)
+    assert (got.float() - ref.float()).abs().max().item() <= 4e-2
+    only_tc = _attention(qkv, lengths, H, d, path=3)
+    assert (got.float() - only_tc.float()).abs().max().item() <= 4e-2
+    head = sum(lengths[:300])
+    want = _attention_oracle(qkv[:head], lengths[:300], H, d)
+    assert (got[:head].float().cpu() - want).abs().max().item() <= 2e-2
+    tail = sum(lengths[:-300])
+    want = _attention_oracle(qkv[tail:], lengths[-300:], H, d)
+    assert (got[tail:].float().cpu() - want).abs().max().item() <= 2e-2
+
+
+UNSUPPORTED_SHAPE = -7  # NTB200_UNSUPPORTED_SHAPE
+
+
+def test_varlen_attention_short_sequence_kernel_limits(native_libs, cuda_device):
+    """Path 4 refuses a batch whose longest sequence exceeds 32 tokens, fp32 data and other head sizes; a non-finite
+    value stays inside its sequence."""
+    lib = _cabi.load()
+    H, d = 2, 64
+    E = H * d
+
+    def call(qkv, lengths, max_len, code, path, head_dim=d, heads=H):
+        meta = build_meta(torch.tensor([[l, heads * head_dim] for l in lengths], dtype=torch.int64), cuda_device)
+        out = torch.full((sum(lengths), heads * head_dim), float("nan"), dtype=qkv.dtype, device=cuda_device)
+        rc = lib.ntb200_varlen_attention(qkv.data_ptr(), out.data_ptr(), meta.data_ptr(), len(lengths), sum(lengths), heads, head_dim,
+                                         max_len, head_dim ** -0.5, code, path, None, 0, stream_ptr())
+        torch.cuda.synchronize()
+        return rc, out
+
+    lengths = [5, 33, 2]
+    qkv = torch.randn(sum(lengths), 3 * E).to(torch.bfloat16).to(cuda_device)
+    assert call(qkv, lengths, 33, 2, 4)[0] == UNSUPPORTED_SHAPE
+    assert call(qkv.float(), [5, 7, 2], 7, 0, 4)[0] == UNSUPPORTED_SHAPE
+    q40 = torch.randn(14, 3 * 2 * 40).to(torch.bfloat16).to(cuda_device)
+    assert call(q40, [5, 7, 2], 7, 2, 4, head_dim=40)[0] == UNSUPPORTED_SHAPE
+    for bad in (float("nan"), float("inf")):
+        lengths = [7, 16, 3, 32, 1, 20]
+        x = torch.randn(sum(lengths), 3 * E)
+        x[7:23] = bad  # every token of sequence 1
+        rc, out = call(x.to(torch.bfloat16).to(cuda_device), lengths, 32, 2, 4)
+        assert rc == 0
+        off = 0
+        for b, l in enumerate(lengths):
+            if b != 1:
+                assert bool(torch.isfinite(out[off:off + l].float()).all()), "sequence %d picked up a non-finite value" % b
+            off += l
+
+
 @pytest.mark.parametrize("H", [1, 3, 7, 40, 300])
 def test_varlen_attention_tcgen05_head_counts(native_libs, cuda_device, H):
     """The persistent kernel steps through the flattened (item, head) list by its grid size: head counts that do not
