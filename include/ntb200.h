@@ -225,8 +225,11 @@ int ntb200_device_error_flags(void);
  *   path       0 = best available: when max_len <= 32 (fp16/bf16, head_dim 32 / 64 / 128) one warp per
  *              (sequence, head) on mma.sync, so that batches of very short sequences cost by the token
  *              and not by the sequence; else head_dim 64 in fp16/bf16 runs on tcgen05/TMEM fed by TMA when a
- *              workspace is supplied, on an mma.sync flash kernel when it is not (as do head_dim 32
- *              and 128), everything else on a SIMT kernel;  1 = SIMT;  2 = mma.sync kernel;  3 = tcgen05 kernel;
+ *              workspace is supplied (its sequences of at most 32 tokens still on single warps, inside the
+ *              launch that builds the work list: which kernel computes a sequence depends on its own
+ *              length only, so shards of a batch reproduce the one-call result bit for bit), on an mma.sync
+ *              flash kernel when it is not (as do head_dim 32 and 128), everything else on a SIMT kernel;
+ *              1 = SIMT;  2 = mma.sync kernel;  3 = tcgen05 kernel for every sequence;
  *              4 = the warp-per-(sequence, head) kernel (1-4: for cross-checks, NTB200_UNSUPPORTED_SHAPE when
  *              the shape does not fit).  Sequences longer than max_len are not computed by paths 0, 2 and 4.
  *   workspace  device scratch of ntb200_varlen_attention_workspace_bytes(...) bytes, 16-byte aligned
