@@ -193,6 +193,45 @@ def test_varlen_attention_mostly_short_sequences(native_libs, cuda_device, dtype
     assert (got[tail:].float().cpu() - want).abs().max().item() <= 2e-2
 
 
+def test_varlen_attention_default_path_random_sweep(native_libs, cuda_device):
+    """100 random batches (1 to 3000 sequences of 1 to 600 tokens, head sizes 32 / 64 / 128, 1 to 20 heads, fp16 / bf16,
+    with and without a workspace) through the default path, whatever kernels it picks, against the SIMT kernel's
+    fp32 arithmetic on the GPU: every row written, within the 16-bit bar relative to the largest output."""
+    lib = _cabi.load()
+    for seed in range(100):
+        g = torch.Generator().manual_seed(55000 + seed)
+        r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+        dtype, code = [(torch.bfloat16, 2), (torch.float16, 1)][r(0, 1)]
+        d = [64, 64, 64, 32, 128][r(0, 4)]
+        H = [1, 2, 3, 8, 16, 20][r(0, 5)]
+        B = [1, 2, 5, r(6, 40), r(41, 300), r(500, 3000)][r(0, 5)]
+        hi = [4, 16, 32, 33, 64, 130, 300, 600][r(0, 7)]
+        if B > 300:
+            hi = min(hi, 64)
+        L = torch.randint(1, hi + 1, (B,), generator=g).tolist()
+        if r(0, 3) == 0:
+            L[r(0, B - 1)] = hi
+        E, T = H * d, sum(L)
+        qkv = (torch.randn(T, 3 * E, generator=g) * [0.5, 1.0, 2.0][r(0, 2)]).to(dtype).to(cuda_device)
+        meta = build_meta(torch.tensor([[l, E] for l in L]), cuda_device)
+        nb = lib.ntb200_varlen_attention_workspace_bytes(B, T, H, d, code)
+        use_ws = nb > 0 and r(0, 4) != 0
+        ws = torch.empty(max(nb, 16), dtype=torch.uint8, device=cuda_device)
+        outs = {}
+        for path in (0, 1):
+            out = torch.full((T, E), float("nan"), dtype=dtype, device=cuda_device)
+            _cabi.check("ntb200_varlen_attention",
+                        lib.ntb200_varlen_attention(qkv.data_ptr(), out.data_ptr(), meta.data_ptr(), B, T, H, d, max(L), d ** -0.5, code,
+                                                    path, ws.data_ptr() if use_ws else None, nb if use_ws else 0, stream_ptr()))
+            torch.cuda.synchronize()
+            outs[path] = out.float()
+        tag = "seed %d %s d=%d H=%d B=%d longest %d workspace %s" % (seed, dtype, d, H, B, max(L), use_ws)
+        assert bool(torch.isfinite(outs[0]).all()), "rows left unwritten: " + tag
+        bar = 2e-2 * max(1.0, float(outs[1].abs().max()))
+        assert float((outs[0] - outs[1]).abs().max()) <= bar, tag
+    assert lib.ntb200_device_error_flags() == 0
+
+
 UNSUPPORTED_SHAPE = -7  # NTB200_UNSUPPORTED_SHAPE
 
 

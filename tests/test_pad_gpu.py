@@ -226,6 +226,70 @@ def test_row_and_vector_walks_random_shapes(native_libs, cuda_device, seed):
         assert got_sizes[b].tolist() == (list(t.shape) if t.numel() else [0] * nd), (b, sizes.tolist())
 
 
+def test_copy_kernels_wide_random_sweep(native_libs, cuda_device):
+    """300 random batches over everything the dispatch of the copy kernels looks at: six dtypes, 1 to 4 tensor dims
+    (at most three ragged after folding), 1 to 400 constituents, innermost rows from a few bytes to 9 KB, extents of
+    zero, regular trailing dims, padding values 777, NaN, +0 and -0; pad, unpad and the size scan through the C ABI
+    against plain torch on the CPU, bit for bit."""
+    lib = _cabi.load()
+    for seed in range(300):
+        g = torch.Generator().manual_seed(777000 + seed)
+        r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+        dtype = [torch.uint8, torch.bfloat16, torch.float16, torch.float32, torch.float64, torch.int32][r(0, 5)]
+        es = torch.empty(0, dtype=dtype).element_size()
+        tdim = r(1, 4)
+        B = [1, 2, 3, r(4, 12), r(13, 60), r(100, 400)][r(0, 5)]
+        regular_last = r(1, 9) if (tdim >= 2 and (r(0, 2) == 0 or tdim == 4)) else None
+        width_bytes = [r(1, 64), r(64, 1024), r(1024, 4200), r(4200, 9000)][r(0, 3)]
+        width_hi = max(1, (width_bytes // es) // (regular_last or 1))
+        outer_hi = [1, 2, 6, 20][r(0, 3)] if B < 100 else r(1, 3)
+        n_outer = max(0, tdim - 1 - (1 if regular_last is not None else 0))
+        while B * outer_hi ** n_outer * width_hi * (regular_last or 1) * es > 64e6 and outer_hi > 1:
+            outer_hi -= 1
+        tensors = []
+        for _ in range(B):
+            shape = [(0 if r(0, 9) == 0 else r(1, outer_hi)) for _ in range(n_outer)]
+            w = r(0, width_hi) if r(0, 3) == 0 else r(max(1, width_hi - 9), width_hi)
+            if r(0, 12) == 0:
+                w = 0
+            shape = [w] if tdim == 1 else shape + [w] + ([regular_last] if regular_last is not None else [])
+            x = torch.randn(shape, generator=g)
+            tensors.append(((x * 40).abs() + 1).to(dtype) if dtype in (torch.uint8, torch.int32) else x.to(dtype))
+        sizes = sizes_of(tensors)
+        mx = sizes.max(0).values.tolist()
+        if min(mx) == 0:
+            continue
+        pad_value = 0 if dtype in (torch.uint8, torch.int32) else [777.0, float("nan"), -0.0, 0.0][r(0, 3)]
+        want = torch.full([B] + mx, pad_value, dtype=dtype)
+        for b, t in enumerate(tensors):
+            want[(b,) + tuple(slice(0, n) for n in t.shape)] = t
+        tag = "seed %d %s B=%d max %s padding %s" % (seed, dtype, B, mx, pad_value)
+        got = cabi_pad(tensors, pad_value, cuda_device)
+        assert_bit_equal(got, want, "ntb200_pad_nd " + tag)
+        flat = torch.cat([t.reshape(-1) for t in tensors])
+        if flat.numel():
+            assert_bit_equal(cabi_unpad(got, sizes), flat, "ntb200_unpad_nd " + tag)
+        nd = len(mx)
+        if nd > 3:
+            continue  # the scan takes at most three dims
+        out = torch.empty(B * (nd + 1), dtype=torch.int64, device=cuda_device)
+        kind = 0 if dtype in (torch.uint8, torch.int32) else (2 if dtype == torch.bfloat16 else 1)
+        rc = lib.ntb200_sizes_from_padded(got.data_ptr(), out.data_ptr(), out.data_ptr() + 8 * B * nd, nd, B, _cabi.host_i64(mx), es, kind,
+                                          bits_of(pad_value, dtype), stream_ptr())
+        _cabi.check("ntb200_sizes_from_padded", rc)
+        torch.cuda.synchronize()
+        got_sizes, got_counts = out[:B * nd].view(B, nd).cpu(), out[B * nd:].cpu()
+        for b, t in enumerate(tensors):
+            if pad_value != pad_value:  # NaN differs from everything: every element of the padded box counts
+                assert int(got_counts[b]) == math.prod(mx) and got_sizes[b].tolist() == mx, (tag, b)
+                continue
+            n_valid = int((t != pad_value).sum()) if t.numel() else 0  # (a value equal to the padding is not counted)
+            assert int(got_counts[b]) == n_valid, (tag, b)
+            if n_valid == t.numel():
+                assert got_sizes[b].tolist() == (list(t.shape) if n_valid else [0] * nd), (tag, b)
+    assert lib.ntb200_device_error_flags() == 0
+
+
 def test_config3_images(native_libs, cuda_device):
     """Configuration 3: 32 fp32 images (3, H_i, W_i): 4-D pad, the un-collapsible 4-D mask, and the
     DETR (B, maxH, maxW) mask = channel 0 of it."""
