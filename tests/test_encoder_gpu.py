@@ -168,6 +168,58 @@ def test_gemm_fused_epilogue_fp32(native_libs, cuda_device, act):
     assert lib.ntb200_gemm_bias_act(A.data_ptr(), W.data_ptr(), None, None, A.data_ptr(), M, N, K, 0, 3, 0, None) == -1  # bad act
 
 
+def test_row_operators_and_gemm_random_sweep(native_libs, cuda_device):
+    """120 random shapes: LayerNorm (1 to 9000 columns, 1 to 6000 rows, with / without affine, plain and with bias and
+    residual fused) and the projection with every epilogue (bias, activation, residual) on every kernel that takes the
+    shape (default, SIMT, single-CTA and CTA-pair tcgen05, per-thread residual), against fp32 torch."""
+    lib = _cabi.load()
+    for seed in range(120):
+        g = torch.Generator().manual_seed(31000 + seed)
+        r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+        dtype = [torch.float32, torch.float16, torch.bfloat16][r(0, 2)]
+        tol = {torch.float32: 8e-5, torch.float16: 1.6e-2, torch.bfloat16: 0.12}[dtype]  # outputs reach |y| ~ 8
+        cols = [r(1, 64), r(1, 64) * 8, r(64, 1100), r(16, 1600) * 8, r(1100, 9000), 128 * r(1, 96)][r(0, 5)]
+        rows = [1, r(2, 40), r(41, 700), r(1000, 6000)][r(0, 3)]
+        if rows * cols > 8e6:
+            rows = max(1, int(8e6 // cols))
+        x = (torch.randn(rows, cols, generator=g) * 2 + 0.5).to(dtype).to(cuda_device)
+        affine = r(0, 3) != 0
+        gamma = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).to(cuda_device) if affine else None
+        beta = (0.1 * torch.randn(cols, generator=g)).to(dtype).to(cuda_device) if affine else None
+        fused = r(0, 1)
+        res = torch.randn(rows, cols, generator=g).to(dtype).to(cuda_device) if fused and r(0, 3) != 0 else None
+        bias = (0.3 * torch.randn(cols, generator=g)).to(dtype).to(cuda_device) if fused and (res is None or r(0, 1)) else None
+        got = _layer_norm(x, res, bias, gamma, beta, 1e-5)
+        pre = x.float() + (res.float() if res is not None else 0) + (bias.float() if bias is not None else 0)
+        want = torch.nn.functional.layer_norm(pre, (cols,), gamma.float() if affine else None, beta.float() if affine else None, 1e-5)
+        tag = "seed %d %s rows %d cols %d residual %s bias %s affine %s" % (seed, dtype, rows, cols, res is not None, bias is not None, affine)
+        assert float((got.float() - want).abs().max()) <= tol, "layer norm " + tag
+        if dtype == torch.float32 and r(0, 3) != 0:
+            continue
+        M = [r(1, 130), r(130, 1200), r(1200, 9000)][r(0, 2)]
+        N = [8 * r(1, 40), 64 * r(1, 48), r(1, 300), 256 * r(1, 12)][r(0, 3)]
+        K = [8 * r(1, 40), 64 * r(1, 48), r(1, 300), 1024, 2048, 4096][r(0, 5)]
+        if dtype == torch.float32:
+            M, N, K = min(M, 1500), min(N, 600), min(K, 600)
+        act = r(0, 2)
+        A = torch.randn(M, K, generator=g).to(dtype).to(cuda_device)
+        W = (torch.randn(N, K, generator=g) * K ** -0.5).to(dtype).to(cuda_device)
+        b = (torch.randn(N, generator=g) * 0.1).to(dtype).to(cuda_device) if r(0, 4) else None
+        rs = torch.randn(M, N, generator=g).to(dtype).to(cuda_device) if r(0, 1) else None
+        base = _act_ref(A.float() @ W.float().t() + (b.float() if b is not None else 0), act) + (rs.float() if rs is not None else 0)
+        for path in (0, 1, 2, 3, 4):
+            C = torch.full((M, N), float("nan"), dtype=dtype, device=cuda_device)
+            rc = lib.ntb200_gemm_bias_act(A.data_ptr(), W.data_ptr(), _ptr(b), _ptr(rs), C.data_ptr(), M, N, K, CODE[dtype], act, path,
+                                          stream_ptr())
+            torch.cuda.synchronize()
+            if rc == -7 and path >= 2:
+                continue  # NTB200_UNSUPPORTED_SHAPE: that kernel does not take the shape
+            _cabi.check("ntb200_gemm_bias_act", rc)
+            err = float((C.float() - base).abs().max())
+            assert err <= (1e-4 if dtype == torch.float32 else 4e-2), "gemm seed %d %s M %d N %d K %d act %d path %d: %g" % (seed, dtype, M, N, K, act, path, err)
+    assert lib.ntb200_device_error_flags() == 0
+
+
 @pytest.mark.parametrize("size", [1024, 512, 256, 128, 2, 4, 32])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32], ids=str)
 def test_layer_norm_module_on_nested_tensor(native_libs, cuda_device, dtype, size):

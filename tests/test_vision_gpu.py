@@ -37,6 +37,24 @@ def test_transposes_bit_exact_and_round_trip(native_libs, cuda_device, dtype, C,
     assert_bit_equal(z._buffer, x._buffer.cpu(), "transpose round trip")
 
 
+def test_transposes_random_sweep(native_libs, cuda_device):
+    """150 random batches (five element types, 1 to 320 channels, 1 to 9 images of 1 to 80 pixels a side): both
+    transposes bit for bit against torch.permute, and the round trip."""
+    for seed in range(150):
+        g = torch.Generator().manual_seed(41000 + seed)
+        r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+        dtype = [torch.float16, torch.bfloat16, torch.float32, torch.uint8, torch.int64][r(0, 4)]
+        C = [1, 3, r(2, 40), 8 * r(1, 40), 64, 256][r(0, 5)]
+        lo = r(1, 20)
+        imgs = _images(g, r(1, 9), C, lo, lo + r(0, 60), dtype)
+        x = nt.nested_tensor(imgs, device=cuda_device, dtype=dtype)
+        y = torch.ops.nestedtensor.transpose_nchw_nhwc(x)
+        for a, b in zip(y.unbind(), imgs):
+            assert_bit_equal(a, b.permute(1, 2, 0).contiguous(), "transpose_nchw_nhwc seed %d %s C %d" % (seed, dtype, C))
+        z = torch.ops.nestedtensor.transpose_nhwc_nchw(y)
+        assert_bit_equal(z._buffer, x._buffer.cpu(), "transpose round trip seed %d %s C %d" % (seed, dtype, C))
+
+
 def test_transpose_errors(native_libs, cuda_device):
     x = nt.nested_tensor([torch.randn(3, 4), torch.randn(2, 4)], device=cuda_device)
     with pytest.raises(RuntimeError, match="transpose_nchw_nhwc needs 4d input."):
