@@ -158,3 +158,53 @@ def test_full_size_construction_embedding_and_transposes(native_libs, cuda_devic
     assert torch.equal(back._buffer.view(torch.int16), img._buffer.view(torch.int16))
     first = img.unbind()[0]
     assert torch.equal(nhwc.unbind()[0], first.permute(1, 2, 0))
+
+
+def test_operator_layer_random_sweep(native_libs, cuda_device):
+    """150 random batches through the operator layer against the oracle, bit for bit: construction from separately
+    allocated device tensors (pointer-table gather), to_tensor_mask with every mask_dim (or the same error as the
+    oracle), to_padded_tensor, and both constructors that take a padded tensor back (by padding value, by mask)."""
+    for seed in range(150):
+        g = torch.Generator().manual_seed(91000 + seed)
+        r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+        dtype = [torch.uint8, torch.bfloat16, torch.float16, torch.float32, torch.float64, torch.int64][r(0, 5)]
+        tdim = r(1, 3)
+        B = [1, 2, r(3, 12), r(13, 80), r(100, 600)][r(0, 4)]
+        wide = [r(1, 9), r(1, 70), r(60, 700), r(600, 2400)][r(0, 3)]
+        reg = r(1, 9) if tdim >= 2 and r(0, 2) == 0 else None
+        outer = [1, 3, 12][r(0, 2)] if B < 100 else r(1, 2)
+        tensors = []
+        for _ in range(B):
+            n_outer = max(0, tdim - 1 - (1 if reg is not None else 0))
+            shape = [r(1, outer) for _ in range(n_outer)] + [r(max(1, wide - 7), wide)] + ([reg] if reg is not None else [])
+            if tdim == 1:
+                shape = [r(max(1, wide - 7), wide)]
+            x = torch.randn(shape, generator=g)
+            if dtype.is_floating_point:  # no element equals a padding value used below
+                tensors.append((x.abs() + 0.01).to(dtype) * torch.where(x < 0, -1, 1).to(dtype))
+            else:
+                tensors.append(((x * 40).abs() + 1).to(dtype))
+        tag = "seed %d %s tdim %d B %d first %s" % (seed, dtype, tdim, B, [tuple(t.shape) for t in tensors[:3]])
+        a = nt.nested_tensor([t.to(cuda_device) for t in tensors], device=cuda_device, dtype=dtype)
+        assert_bit_equal(a._buffer, torch.cat([t.reshape(-1) for t in tensors]), "construction " + tag)
+        for mask_dim in [None] + list(range(1, tdim + 2)):
+            try:
+                want = ntref.to_tensor_mask(tensors, mask_dim)
+            except RuntimeError:
+                with pytest.raises(RuntimeError):
+                    a.to_tensor_mask(mask_dim=mask_dim)
+                continue
+            data, mask = a.to_tensor_mask(mask_dim=mask_dim)
+            assert mask.dtype == want[1].dtype, (tag, mask_dim)
+            assert_bit_equal(data, want[0], "to_tensor_mask data, mask_dim %s, %s" % (mask_dim, tag))
+            assert_bit_equal(mask, want[1], "to_tensor_mask mask, mask_dim %s, %s" % (mask_dim, tag))
+        padding = -7 if dtype != torch.uint8 else 0
+        dense = a.to_padded_tensor(padding=padding)
+        assert_bit_equal(dense, ntref.to_padded_tensor(tensors, padding), "to_padded_tensor " + tag)
+        back = nt.nested_tensor_from_padded_tensor(dense, padding=padding)
+        assert [tuple(t.shape) for t in back.unbind()] == [tuple(t.shape) for t in tensors], tag
+        assert_bit_equal(back._buffer, a._buffer.cpu(), "nested_tensor_from_padded_tensor " + tag)
+        data, mask = a.to_tensor_mask()
+        back = nt.nested_tensor_from_tensor_mask(data, mask)
+        assert_bit_equal(back._buffer, a._buffer.cpu(), "nested_tensor_from_tensor_mask " + tag)
+    assert _cabi.load().ntb200_device_error_flags() == 0
