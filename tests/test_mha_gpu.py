@@ -490,6 +490,60 @@ def test_cabi_cross_attention_tcgen05_against_simt(native_libs, cuda_device, dty
                                                 H, d, max(lq), d ** -0.5, code, 3, ws.data_ptr(), 16, stream_ptr()) == -6
 
 
+def test_cabi_cross_attention_random_sweep(native_libs, cuda_device):
+    """100 random cross-attention batches (1 to 400 sequences, up to 300 queries over up to 900 keys, sequences without
+    keys or without queries, head sizes 32 / 64 / 128, k / v packed in one matrix or apart): every kernel that takes the
+    shape (default, mma.sync, tcgen05) against the SIMT kernel; rows of a sequence without keys are zeros."""
+    lib = _cabi.load()
+    for seed in range(100):
+        g = torch.Generator().manual_seed(66000 + seed)
+        r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+        dtype, code = [(torch.bfloat16, 2), (torch.float16, 1)][r(0, 1)]
+        d, H = [64, 64, 32, 128][r(0, 3)], [1, 2, 4, 8, 11][r(0, 4)]
+        E = H * d
+        B = [1, 2, r(3, 10), r(11, 60), r(100, 400)][r(0, 4)]
+        hq, hk = [3, 40, 130, 300][r(0, 3)], [3, 40, 130, 300, 900][r(0, 4)]
+        if B >= 100:
+            hq, hk = min(hq, 130), min(hk, 130)
+        lq = [0 if r(0, 14) == 0 else r(1, hq) for _ in range(B)]
+        lk = [0 if r(0, 14) == 0 else r(1, hk) for _ in range(B)]
+        lq[0], lk[0] = max(lq[0], 1), max(lk[0], 1)
+        Tq, Tk = sum(lq), sum(lk)
+        q = torch.randn(Tq, E, generator=g).to(dtype).to(cuda_device)
+        if r(0, 1):
+            kv = torch.randn(Tk, 2 * E, generator=g).to(dtype).to(cuda_device)
+            kp, vp, ld = kv.data_ptr(), kv.data_ptr() + E * 2, 2 * E
+        else:
+            k = torch.randn(Tk, E, generator=g).to(dtype).to(cuda_device)
+            v = torch.randn(Tk, E, generator=g).to(dtype).to(cuda_device)
+            kp, vp, ld = k.data_ptr(), v.data_ptr(), E
+        mq = build_meta(torch.tensor([[l, E] for l in lq]), cuda_device)
+        mk = build_meta(torch.tensor([[l, E] for l in lk]), cuda_device)
+        nb = lib.ntb200_varlen_cross_attention_workspace_bytes(B, Tq, H, d, code)
+        ws = torch.empty(max(nb, 16), dtype=torch.uint8, device=cuda_device)
+        outs = {}
+        for path in (1, 0, 2, 3):
+            o = torch.full((Tq, E), float("nan"), dtype=dtype, device=cuda_device)
+            rc = lib.ntb200_varlen_cross_attention_ws(q.data_ptr(), E, kp, ld, vp, ld, o.data_ptr(), mq.data_ptr(), mk.data_ptr(), B, Tq,
+                                                      Tk, H, d, max(lq), d ** -0.5, code, path, ws.data_ptr() if nb else None, nb,
+                                                      stream_ptr())
+            torch.cuda.synchronize()
+            if rc == UNSUPPORTED_SHAPE and path >= 2:
+                continue
+            _cabi.check("ntb200_varlen_cross_attention_ws", rc)
+            outs[path] = o.float()
+        tag = "seed %d %s d %d H %d B %d" % (seed, dtype, d, H, B)
+        for path, o in outs.items():
+            assert bool(torch.isfinite(o).all()), "rows left unwritten, path %d, %s" % (path, tag)
+            assert float((o - outs[1]).abs().max()) <= 2e-2 * max(1.0, float(outs[1].abs().max())), "path %d, %s" % (path, tag)
+        off = 0
+        for b in range(B):
+            if lk[b] == 0 and lq[b] > 0:
+                assert int(outs[0][off:off + lq[b]].count_nonzero()) == 0, tag
+            off += lq[b]
+    assert lib.ntb200_device_error_flags() == 0
+
+
 def test_cabi_cross_attention_paths_and_empty_key_sequence(native_libs, cuda_device):
     """SIMT and mma.sync kernels agree with plain torch; a query whose key sequence is empty gets zeros."""
     lib = _cabi.load()
