@@ -462,11 +462,125 @@ transpose_ragged_pair_kernel(const uint16_t* __restrict__ in, uint16_t* __restri
   }
 }
 
+// The same transpose for a SMALL regular extent (RGB / RGBA images, a few channels): the 64-channel tiles of the kernels
+// above would be all but empty.  A block takes kSmallThreads * PPT consecutive pixels of one constituent; on the
+// pixel-major side these are one contiguous run of pixels * C elements, moved by the whole block in element order, and
+// on the channel-major side C runs of pixels, PPT elements per thread and channel (PPT loads in flight per thread and
+// channel: with one, the kernel is bound by latency); the two meet in shared memory.  There a pixel's C elements are
+// consecutive, which for an even C puts the threads of a warp up to 16 ways onto the same banks on the channel-major
+// side; an even C of 4 or more therefore gets one element of padding per pixel, and the element-order side steps its
+// (pixel, channel) position along with the linear index instead of dividing.
+constexpr int kSmallThreads = 256;
+constexpr int64_t kSmallRegularMax = 24;    // ... and at most kSmallPixelBytes per pixel (measured: from 32 channels on the tile kernels are level or ahead)
+constexpr int64_t kSmallPixelBytes = 192;  // (padding included: 256 pixels of a block then fill 48 KB)
+
+// MODE 0: C odd or below 4, no padding, linear slots; 1: C a power of two (pixel and channel of a linear index are a
+// shift and a mask); 2: any other even C (pixel and channel stepped along with the index)
+template <typename T, bool REG_IS_ROWS, int PPT, int MODE>
+__global__ void __launch_bounds__(kSmallThreads)
+transpose_small_regular_kernel(const T* __restrict__ in, T* __restrict__ out, const int64_t* __restrict__ offsets, int regular) {
+  extern __shared__ __align__(16) uint8_t small_smem[];
+  T* sm = reinterpret_cast<T*>(small_smem);
+  constexpr int kPx = kSmallThreads * PPT;
+  const int64_t off = offsets[blockIdx.y];
+  const int64_t n = (offsets[blockIdx.y + 1] - off) / regular;  // pixels
+  const int64_t p0 = (int64_t)blockIdx.x * kPx;
+  if (p0 >= n) return;
+  const int np = n - p0 < kPx ? (int)(n - p0) : kPx;
+  const int C = regular, t = threadIdx.x;
+  const int S = MODE == 0 ? C : C + 1;  // shared-memory pixel stride
+  // element-order side: linear index i = t, t + 256, ... as (pixel q, channel r)
+  const int sh = 31 - __clz(C);  // MODE 1
+  int q = 0, r = 0, dq = 0, dr = 0;  // MODE 2: advanced by (256 / C, 256 % C)
+  if (MODE == 2) {
+    q = t / C, r = t - q * C;
+    dq = kSmallThreads / C, dr = kSmallThreads - dq * C;
+  }
+  auto slot = [&](int i) { return MODE == 0 ? i : (MODE == 1 ? (i >> sh) * S + (i & (C - 1)) : q * S + r); };
+  auto advance = [&]() {
+    if (MODE == 2) {
+      q += dq;
+      r += dr;
+      if (r >= C) {
+        r -= C;
+        ++q;
+      }
+    }
+  };
+  const T* src = in + off;
+  T* dst = out + off;
+  if (REG_IS_ROWS) {  // [C x n] -> [n x C]
+    const T* s = src + p0 + t;
+#pragma unroll 2
+    for (int c = 0; c < C; ++c) {
+      T v[PPT];
+#pragma unroll
+      for (int k = 0; k < PPT; ++k) v[k] = t + k * kSmallThreads < np ? s[(int64_t)c * n + k * kSmallThreads] : T(0);
+#pragma unroll
+      for (int k = 0; k < PPT; ++k)
+        if (t + k * kSmallThreads < np) sm[(t + k * kSmallThreads) * S + c] = v[k];
+    }
+    __syncthreads();
+    T* d = dst + p0 * C;
+    for (int i = t; i < np * C; i += kSmallThreads, advance()) d[i] = sm[slot(i)];
+  } else {  // [n x C] -> [C x n]
+    const T* s = src + p0 * C;
+    for (int i = t; i < np * C; i += kSmallThreads, advance()) sm[slot(i)] = s[i];
+    __syncthreads();
+    T* d = dst + p0 + t;
+#pragma unroll 2
+    for (int c = 0; c < C; ++c) {
+#pragma unroll
+      for (int k = 0; k < PPT; ++k)
+        if (t + k * kSmallThreads < np) d[(int64_t)c * n + k * kSmallThreads] = sm[(t + k * kSmallThreads) * S + c];
+    }
+  }
+}
+
+constexpr int small_mode(int64_t regular) { return (regular < 4 || (regular & 1)) ? 0 : ((regular & (regular - 1)) == 0 ? 1 : 2); }
+constexpr int64_t small_stride(int64_t regular) { return small_mode(regular) == 0 ? regular : regular + 1; }
+
+template <typename T, int PPT, int MODE>
+void launch_transpose_small_m(const void* in, void* out, const int64_t* offsets, int64_t nb, int64_t regular, int regular_is_rows,
+                              int64_t max_ragged, cudaStream_t st) {
+  constexpr int kPx = kSmallThreads * PPT;
+  dim3 grid((unsigned)((max_ragged + kPx - 1) / kPx), (unsigned)nb);
+  const size_t smem = (size_t)kPx * (size_t)small_stride(regular) * sizeof(T);  // at most 48 KB
+  if (regular_is_rows)
+    transpose_small_regular_kernel<T, true, PPT, MODE><<<grid, kSmallThreads, smem, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets, (int)regular);
+  else
+    transpose_small_regular_kernel<T, false, PPT, MODE><<<grid, kSmallThreads, smem, st>>>(static_cast<const T*>(in), static_cast<T*>(out), offsets, (int)regular);
+}
+
+template <typename T, int PPT>
+void launch_transpose_small(const void* in, void* out, const int64_t* offsets, int64_t nb, int64_t regular, int regular_is_rows,
+                            int64_t max_ragged, cudaStream_t st) {
+  switch (small_mode(regular)) {
+    case 0: return launch_transpose_small_m<T, PPT, 0>(in, out, offsets, nb, regular, regular_is_rows, max_ragged, st);
+    case 1: return launch_transpose_small_m<T, PPT, 1>(in, out, offsets, nb, regular, regular_is_rows, max_ragged, st);
+    default: return launch_transpose_small_m<T, PPT, 2>(in, out, offsets, nb, regular, regular_is_rows, max_ragged, st);
+  }
+}
+
 template <typename T>
 int launch_transpose_ragged(const void* in, void* out, const int64_t* offsets, int64_t batch, int64_t regular,
                             int regular_is_rows, int64_t max_ragged, cudaStream_t st) {
   const bool vec = sizeof(T) < 8 && (regular * (int64_t)sizeof(T)) % 16 == 0 &&
                    ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (regular <= kSmallRegularMax && small_stride(regular) * (int64_t)sizeof(T) <= kSmallPixelBytes) {
+    if ((max_ragged + kSmallThreads - 1) / kSmallThreads > 0x7fffffff) return NTB200_UNSUPPORTED_SHAPE;
+    const int64_t pixel_bytes = small_stride(regular) * (int64_t)sizeof(T);  // 1024 / 512 / 256 pixels per block: what fits 48 KB of shared memory
+    for (int64_t b0 = 0; b0 < batch; b0 += 65535) {  // gridDim.y limit
+      const int64_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
+      if (pixel_bytes <= 48)
+        launch_transpose_small<T, 4>(in, out, offsets + b0, nb, regular, regular_is_rows, max_ragged, st);
+      else if (pixel_bytes <= 96)
+        launch_transpose_small<T, 2>(in, out, offsets + b0, nb, regular, regular_is_rows, max_ragged, st);
+      else
+        launch_transpose_small<T, 1>(in, out, offsets + b0, nb, regular, regular_is_rows, max_ragged, st);
+    }
+    return status_from_cuda(cudaGetLastError());
+  }
   const int64_t rag_tile = vec ? kTrRag : kTrTile;
   const int64_t tiles = ((regular + kTrTile - 1) / kTrTile) * ((max_ragged + rag_tile - 1) / rag_tile);
   if (tiles > 0x7fffffff) return NTB200_UNSUPPORTED_SHAPE;
