@@ -992,7 +992,7 @@ def run_next_rows(args, local, peaks, n):
     def hbm_row(ms, mhz, nbytes):
         return {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_hbm_measured": nbytes / ms / 1e6 / peaks["hbm_gbs"], "sm_mhz": mhz}
 
-    out = {"workload": "T = 151 792 packed tokens (configuration 5), E = 1024, bf16; transposes: 32 fp16 maps (256, 100-168, 100-168)",
+    out = {"workload": "T = 151 792 packed tokens (configuration 5), E = 1024, bf16; transposes: 32 fp16 maps (256, 100-168, 100-168), and the 32 fp32 RGB images of configuration 3",
            "note": "memory-bound rows first, each after 0.25 s of idle; the SM clock seen during each row is beside it"}
     gi = torch.Generator().manual_seed(20248)
     hw = torch.randint(100, 169, (32, 2), generator=gi)
@@ -1003,6 +1003,15 @@ def run_next_rows(args, local, peaks, n):
     out["transpose_nchw_nhwc"] = hbm_row(*timed(lambda: nt.nn.transpose_nchw_nhwc(img), True), 4.0 * nimg)
     out["transpose_nhwc_nchw"] = hbm_row(*timed(lambda: nt.nn.transpose_nhwc_nchw(nhwc), True), 4.0 * nimg)
     del img, nhwc
+    # the images of configuration 3 themselves (32 fp32 RGB images, 400..1024 pixels a side): the small-channel kernel
+    from nestedtensor_b200 import workloads as _workloads
+    rgb = _workloads.config3()
+    rimg = nt.NestedTensor(rgb.buffer.to(device), rgb.sizes)
+    rnhwc = nt.nn.transpose_nchw_nhwc(rimg)
+    nrgb = int(rimg._buffer.numel())
+    out["transpose_rgb_nchw_nhwc"] = hbm_row(*timed(lambda: nt.nn.transpose_nchw_nhwc(rimg), True), 8.0 * nrgb)
+    out["transpose_rgb_nhwc_nchw"] = hbm_row(*timed(lambda: nt.nn.transpose_nhwc_nchw(rnhwc), True), 8.0 * nrgb)
+    del rimg, rnhwc, rgb
     out["layer_norm"] = hbm_row(*timed(lambda: ops.add_bias_residual_layer_norm(x, None, None, gamma, beta, 1e-5), True), 4.0 * T * E)
     for name, fn, fl in (("out_proj_bias_residual", lambda: ops.packed_linear(x, w, b, 0, res), 2.0 * T * E * E),
                          ("out_proj_bias", lambda: ops.packed_linear(x, w, b, 0, None), 2.0 * T * E * E),
@@ -1172,6 +1181,10 @@ def run_kernels(args, local):
         add("from_padded_tensor (4-D)", "c3", timed(f_unpad, n), 2 * es * nv, graph_fn=f_unpad)
         add("sizes_from_padded (scan)", "c3", timed(f_scan, n), es * npad, graph_fn=f_scan)
         del padded
+        add("transpose_nchw_nhwc (3 channels)", "c3", timed(lambda: nt.nn.transpose_nchw_nhwc(a), n), 2 * es * nv)
+        a_nhwc = nt.nn.transpose_nchw_nhwc(a)
+        add("transpose_nhwc_nchw (3 channels)", "c3", timed(lambda: nt.nn.transpose_nhwc_nchw(a_nhwc), n), 2 * es * nv)
+        del a_nhwc
 
     if only in ("transpose", "c3"):
         image_path() if only == "transpose" else config3_group()
