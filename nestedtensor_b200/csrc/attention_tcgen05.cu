@@ -105,6 +105,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 constexpr int kListThreads = 1024;
 constexpr int kBuckets = 9;  // key blocks 1..8+, (0 unused)
 
+template <bool SELF>  // SELF: queries and keys are the same sequences, so none has queries without keys
 __device__ __forceinline__ void build_items_block(const int64_t* __restrict__ offsets_q, const int64_t* __restrict__ offsets_k,
                                                   int64_t batch, int64_t row_elems, int4* __restrict__ items,
                                                   int* __restrict__ count, int64_t capacity, uint16_t* __restrict__ out,
@@ -145,6 +146,7 @@ __device__ __forceinline__ void build_items_block(const int64_t* __restrict__ of
       if (pos + t < capacity) items[pos + t] = make_int4(tq0 + t * kQT, (int)rows, tk0, (int)Lk);
     }
   }
+  if (SELF) return;
   // Queries whose key sequence is empty get zeros (self-attention never has any: Lq == Lk).  The sequences are found in
   // parallel and listed in shared memory; the block then clears their rows together.
   __shared__ int s_nempty;
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(kListThreads) build_items_kernel(const int64_t
                                                                    int64_t row_elems, int4* __restrict__ items,
                                                                    int* __restrict__ count, int64_t capacity,
                                                                    uint16_t* __restrict__ out) {
-  build_items_block(offsets_q, offsets_k, batch, row_elems, items, count, capacity, out, 0);
+  build_items_block<false>(offsets_q, offsets_k, batch, row_elems, items, count, capacity, out, 0);
 }
 
 // The same list for self-attention on the default path, in one launch with the short sequences: block 0 builds the list
@@ -190,7 +192,7 @@ prepare_self_attention_kernel(const int64_t* __restrict__ offsets, int64_t batch
                               float scale_log2e) {
   extern __shared__ __align__(128) uint8_t prep_smem[];
   if (blockIdx.x == 0) {
-    build_items_block(offsets, offsets, batch, row_elems, items, count, capacity, reinterpret_cast<uint16_t*>(out), (int)kTinyMaxLen);
+    build_items_block<true>(offsets, offsets, batch, row_elems, items, count, capacity, reinterpret_cast<uint16_t*>(out), (int)kTinyMaxLen);
     return;
   }
   const int warp = threadIdx.x >> 5;
